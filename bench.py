@@ -1,0 +1,196 @@
+"""Headline benchmark: SFNO-73ch 721x1440 bf16 training throughput (samples/s), weak scaling, pure data parallel.
+
+    python bench.py --gpus N --steps K --warmup W [--impl native|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W
+
+Model ("sfno_linear_73chq_sc3_layers8_edim384", reference recipe config/sfnonet.yaml:149-159): 721x1440
+equiangular grid, 73 prognostic channels + 1 static cos(latitude) channel in, 73 out, embed_dim 384, 8 blocks,
+scale_factor 3, dhconv spectral weights, MLP ratio 2, GELU, instance norm; random-init weights, synthetic
+N(0,1) data, batch 1 per GPU; loss "absolute squared geometric l2"; AdamW.  One step = forward + backward +
+gradient reduction + optimiser step.  Prints one JSON line on rank 0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+BASELINE_VALUE = None  # the reference publishes no throughput number
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", type=str, default="native", choices=["native", "reference"])
+    ap.add_argument("--small", action="store_true", help="reduced grid for profiling captures (not a bench value)")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def reference_arm(args):
+    """Runs the unmodified reference from baseline/_ref when it can be imported, else reports why not."""
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    why = None
+    if not os.path.isdir(os.path.join(ref, "makani")):
+        why = "reference not installed under baseline/_ref"
+    else:
+        sys.path.insert(0, ref)
+        try:
+            import makani  # noqa: F401
+        except Exception as e:  # missing torch_harmonics / modulus / ruamel / h5py in this image
+            why = f"reference import fails offline: {type(e).__name__}: {e}"
+        else:
+            why = "reference imported but its synthetic data path is not runnable offline"
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+class ClockSampler:
+    """Samples SM clocks / throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = os.path.join("/tmp", f"bench_clocks_{os.getpid()}.csv")
+
+    def start(self):
+        try:
+            self.fh = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu_index)], stdout=self.fh, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.fh.close()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1])); mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for n, v in zip(names, f[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            os.remove(self.path)
+        except Exception:
+            pass
+        if sm:
+            sm.sort()
+            out["sm_mhz"] = sm[len(sm) // 2]
+            out["sm_max_mhz"] = max(mx)
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+
+    from makani_b200.ops import _ext
+    from makani_b200.utils import comm
+    from makani_b200.utils.bench_harness import build_flagship, FlagshipConfig
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus or world == 1, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    comm.init(model_parallel_sizes=[1, 1, 1, 1])
+    _ext.require()
+
+    cfg = FlagshipConfig(small=args.small)
+    runner = build_flagship(cfg, dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier(device_ids=[local_rank])
+        torch.cuda.synchronize()
+
+    # ---------------------------------------------------------------- device-timed steps (inputs resident)
+    inp, tgt = runner.synthetic_batch(seed=1234 + rank)
+    for _ in range(args.warmup):
+        runner.step(inp, tgt)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    l0 = _ext.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        loss = runner.step(inp, tgt)
+    ev1.record()
+    barrier()
+    launches = _ext.launch_count() - l0
+    clocks = sampler.stop()
+    ms = ev0.elapsed_time(ev1)
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_per_step = t.item() / args.steps
+    global_batch = cfg.batch_per_gpu * world
+    value = global_batch / (ms_per_step / 1e3)
+    _ext.check_device_errors(dev)
+    final_loss = float(loss)
+
+    # ---------------------------------------------------------------- end to end through the public API
+    e2e = None
+    if not args.no_e2e:
+        e2e = runner.end_to_end(steps=args.steps, warmup=max(1, min(args.warmup, 2)), world=world, local_rank=local_rank)
+
+    if rank == 0:
+        out = {
+            "metric": "SFNO-73ch 721x1440 bf16 train samples/s", "value": value, "unit": "samples/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": (value / BASELINE_VALUE) if BASELINE_VALUE else None, "dtype": "bf16",
+            "data": "synthetic N(0,1), random-init weights", "impl": "native",
+            "config": {"model": cfg.name, "global_batch": global_batch, "seq_len": f"{cfg.nlat}x{cfg.nlon}",
+                       "parallelism": f"dp{world}", "l2_policy": "inputs+activations per step (>2 GB) exceed the 126 MB L2",
+                       "loss": cfg.loss, "optimizer": "AdamW (fused)", "final_loss": final_loss},
+            "clocks": clocks, "gpu_launches": launches,
+        }
+        if e2e is not None:
+            out["e2e"] = e2e
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier(device_ids=[local_rank])
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,308 @@
+// Python bindings (pybind11 / torch tensors) for the sm_100a kernels. Every entry validates device, dtype
+// and contiguity, launches on the current CUDA stream and raises on a launch error.
+#include <torch/extension.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+
+#include <cstdint>
+#include <map>
+#include <vector>
+
+#include "fused_ops.cuh"
+#include "gemm_tcgen05.cuh"
+#include "peer.cuh"
+
+namespace {
+
+using torch::Tensor;
+
+#define MK_CHECK(cond, ...) TORCH_CHECK(cond, "makani_b200: ", __VA_ARGS__)
+
+inline void check_cuda(cudaError_t e, const char* what) {
+  TORCH_CHECK(e == cudaSuccess, "makani_b200: ", what, " failed: ", cudaGetErrorString(e), " ", mk::gemm_last_error());
+}
+
+inline cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+// one error word per device, set by kernels whose bounded waits expire
+std::map<int, Tensor>& err_flags() {
+  static std::map<int, Tensor> m;
+  return m;
+}
+
+Tensor err_flag_for(const Tensor& t) {
+  const int dev = t.get_device();
+  auto& m = err_flags();
+  auto it = m.find(dev);
+  if (it == m.end()) {
+    Tensor f = torch::zeros({4}, torch::dtype(torch::kInt32).device(t.device()));
+    it = m.emplace(dev, f).first;
+  }
+  return it->second;
+}
+
+int64_t read_error_flag(int64_t device) {
+  auto& m = err_flags();
+  auto it = m.find(static_cast<int>(device));
+  if (it == m.end()) return 0;
+  return it->second.cpu().data_ptr<int>()[0];
+}
+
+void clear_error_flag(int64_t device) {
+  auto& m = err_flags();
+  auto it = m.find(static_cast<int>(device));
+  if (it != m.end()) it->second.zero_();
+}
+
+inline const char* base_ptr(const Tensor& t) { return static_cast<const char*>(t.data_ptr()); }
+
+// iparams layout: see makani_b200/ops/gemm.py (GemmSpec.pack)
+void gemm(const Tensor& a, const Tensor& b, Tensor& d, const c10::optional<Tensor>& bias,
+          const c10::optional<Tensor>& resid, const c10::optional<Tensor>& preact, const std::vector<int64_t>& ip,
+          double alpha) {
+  MK_CHECK(ip.size() == 40, "gemm: expected 40 integer parameters, got ", ip.size());
+  MK_CHECK(a.is_cuda() && b.is_cuda() && d.is_cuda(), "gemm: tensors must be CUDA");
+  MK_CHECK(a.scalar_type() == b.scalar_type(), "gemm: A and B dtypes differ");
+  const int eb = static_cast<int>(a.element_size());
+  MK_CHECK((a.scalar_type() == torch::kBFloat16) || (a.scalar_type() == torch::kFloat32), "gemm: operands must be bf16 or fp32");
+  MK_CHECK((d.scalar_type() == torch::kBFloat16) || (d.scalar_type() == torch::kFloat32), "gemm: output must be bf16 or fp32");
+  c10::cuda::CUDAGuard guard(a.device());
+  int k = 0;
+  mk::GemmProblem p;
+  p.M = ip[k++]; p.N = ip[k++]; p.K = ip[k++];
+  p.zlo_n = ip[k++]; p.zhi_n = ip[k++];
+  p.elem_bytes = eb;
+  p.splits = ip[k++]; p.bn = ip[k++];
+  p.rmin_a = ip[k++]; p.rmin_b = ip[k++]; p.rmax_a = ip[k++]; p.rmax_b = ip[k++];
+  p.kmin_a = ip[k++]; p.kmin_b = ip[k++]; p.kmax_a = ip[k++]; p.kmax_b = ip[k++];
+  mk::GemmOperand A, B;
+  const int64_t a_off = ip[k++];
+  A.rows = p.M; A.mn_major = ip[k++]; A.ld = ip[k++]; A.zs_lo = ip[k++]; A.zs_hi = ip[k++];
+  const int64_t b_off = ip[k++];
+  B.rows = p.N; B.mn_major = ip[k++]; B.ld = ip[k++]; B.zs_lo = ip[k++]; B.zs_hi = ip[k++];
+  A.ptr = base_ptr(a) + a_off * eb;
+  B.ptr = base_ptr(b) + b_off * eb;
+  mk::GemmEpilogue e;
+  const int64_t d_off = ip[k++];
+  const int osz = static_cast<int>(d.element_size());
+  e.D = const_cast<char*>(base_ptr(d)) + d_off * osz;
+  e.out_f32 = d.scalar_type() == torch::kFloat32;
+  e.accumulate = ip[k++];
+  e.d_zlo = ip[k++]; e.d_zhi = ip[k++];
+  e.rdiv = ip[k++]; e.rs_hi = ip[k++]; e.rs_lo = ip[k++];
+  e.ndiv = ip[k++]; e.ns_hi = ip[k++];
+  e.alpha = static_cast<float>(alpha);
+  e.bias_mode = ip[k++];
+  e.act = ip[k++];
+  const int64_t resid_off = ip[k++];
+  const int64_t preact_off = ip[k++];
+  // remaining slots reserved
+  e.bias = nullptr;
+  if (bias.has_value() && bias->defined()) {
+    MK_CHECK(bias->is_cuda() && bias->scalar_type() == torch::kFloat32 && bias->is_contiguous(), "gemm: bias must be contiguous fp32 CUDA");
+    e.bias = bias->data_ptr<float>();
+  }
+  e.resid = nullptr;
+  if (resid.has_value() && resid->defined()) {
+    MK_CHECK(resid->scalar_type() == d.scalar_type(), "gemm: residual dtype must match output");
+    e.resid = base_ptr(*resid) + resid_off * osz;
+  }
+  e.preact = nullptr;
+  if (preact.has_value() && preact->defined()) {
+    MK_CHECK(preact->scalar_type() == d.scalar_type(), "gemm: preact dtype must match output");
+    e.preact = const_cast<char*>(base_ptr(*preact)) + preact_off * osz;
+  }
+  Tensor ef = err_flag_for(a);
+  check_cuda(mk::gemm_launch(p, A, B, e, ef.data_ptr<int>(), cur_stream()), "gemm launch");
+}
+
+void inorm_fwd(const Tensor& x, Tensor& y, const c10::optional<Tensor>& w, const c10::optional<Tensor>& b, Tensor& stats,
+               int64_t C, double eps, int64_t act, int64_t ext_stats) {
+  MK_CHECK(x.is_cuda() && x.is_contiguous() && x.scalar_type() == torch::kBFloat16, "inorm_fwd: x must be contiguous bf16 CUDA");
+  MK_CHECK(y.is_contiguous() && y.scalar_type() == torch::kBFloat16 && y.numel() == x.numel(), "inorm_fwd: bad y");
+  MK_CHECK(stats.scalar_type() == torch::kFloat32 && stats.is_contiguous(), "inorm_fwd: bad stats");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t planes = stats.numel() / 2;
+  const int64_t hw = x.numel() / planes;
+  const float* wp = (w.has_value() && w->defined()) ? w->data_ptr<float>() : nullptr;
+  const float* bp = (b.has_value() && b->defined()) ? b->data_ptr<float>() : nullptr;
+  check_cuda(mk::inorm_fwd(reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), reinterpret_cast<__nv_bfloat16*>(y.data_ptr()), wp, bp,
+                           stats.data_ptr<float>(), static_cast<int>(planes), static_cast<int>(C), hw, static_cast<float>(eps),
+                           static_cast<int>(act), static_cast<int>(ext_stats), cur_stream()),
+             "inorm_fwd");
+}
+
+void inorm_partial_stats(const Tensor& x, Tensor& sums) {
+  MK_CHECK(x.is_cuda() && x.is_contiguous() && x.scalar_type() == torch::kBFloat16, "inorm_partial_stats: bad x");
+  MK_CHECK(sums.scalar_type() == torch::kFloat32 && sums.is_contiguous(), "inorm_partial_stats: bad sums");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t planes = sums.numel() / 2;
+  check_cuda(mk::inorm_partial_stats(reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), sums.data_ptr<float>(),
+                                     static_cast<int>(planes), x.numel() / planes, cur_stream()),
+             "inorm_partial_stats");
+}
+
+void inorm_bwd(const Tensor& x, const Tensor& dy, c10::optional<Tensor> dx, const c10::optional<Tensor>& w,
+               const c10::optional<Tensor>& b, const Tensor& stats, c10::optional<Tensor> dw, c10::optional<Tensor> db,
+               c10::optional<Tensor> sums_io, int64_t C, double count, int64_t act, int64_t ext_sums) {
+  MK_CHECK(x.is_cuda() && x.is_contiguous() && dy.is_contiguous(), "inorm_bwd: tensors must be contiguous CUDA");
+  MK_CHECK(x.scalar_type() == torch::kBFloat16 && dy.scalar_type() == torch::kBFloat16, "inorm_bwd: bf16 expected");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t planes = stats.numel() / 2;
+  const int64_t hw = x.numel() / planes;
+  auto fp = [](const c10::optional<Tensor>& t) -> float* {
+    return (t.has_value() && t->defined()) ? t->data_ptr<float>() : nullptr;
+  };
+  __nv_bfloat16* dxp = (dx.has_value() && dx->defined()) ? reinterpret_cast<__nv_bfloat16*>(dx->data_ptr()) : nullptr;
+  check_cuda(mk::inorm_bwd(reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), reinterpret_cast<const __nv_bfloat16*>(dy.data_ptr()),
+                           dxp, fp(w), fp(b), stats.data_ptr<float>(), fp(dw), fp(db), fp(sums_io), static_cast<int>(planes),
+                           static_cast<int>(C), hw, count, static_cast<int>(act), static_cast<int>(ext_sums), cur_stream()),
+             "inorm_bwd");
+}
+
+int64_t lp_scratch_floats(int64_t planes, int64_t hw) { return planes * mk::lp_norms_chunks(hw) * 2 + planes; }
+
+void lp_norms(const Tensor& pred, const Tensor& tgt, const Tensor& qlat, Tensor& out, Tensor& scratch, int64_t P) {
+  MK_CHECK(pred.is_cuda() && pred.is_contiguous() && tgt.is_contiguous() && pred.dim() == 4, "lp_norms: [B,C,H,W] contiguous CUDA expected");
+  MK_CHECK(pred.scalar_type() == tgt.scalar_type(), "lp_norms: dtype mismatch");
+  MK_CHECK(P == 1 || P == 2, "lp_norms: P must be 1 or 2");
+  c10::cuda::CUDAGuard guard(pred.device());
+  const int64_t planes = pred.size(0) * pred.size(1), H = pred.size(2), W = pred.size(3);
+  MK_CHECK(qlat.numel() == H && qlat.scalar_type() == torch::kFloat32, "lp_norms: qlat must be fp32 [H]");
+  MK_CHECK(out.numel() == planes * 2 && out.scalar_type() == torch::kFloat32, "lp_norms: out must be fp32 [B*C,2]");
+  MK_CHECK(scratch.numel() >= lp_scratch_floats(planes, H * W) && scratch.scalar_type() == torch::kFloat32, "lp_norms: scratch too small");
+  const int is_f32 = pred.scalar_type() == torch::kFloat32;
+  MK_CHECK(is_f32 || pred.scalar_type() == torch::kBFloat16, "lp_norms: fp32 or bf16");
+  check_cuda(mk::lp_norms(pred.data_ptr(), tgt.data_ptr(), is_f32, qlat.data_ptr<float>(), out.data_ptr<float>(), scratch.data_ptr<float>(),
+                          static_cast<int>(planes), static_cast<int>(H), static_cast<int>(W), static_cast<int>(P), cur_stream()),
+             "lp_norms");
+}
+
+void lp_norms_bwd(const Tensor& pred, const Tensor& tgt, const Tensor& qlat, const Tensor& coef, Tensor& grad, int64_t P) {
+  MK_CHECK(pred.is_cuda() && pred.is_contiguous() && tgt.is_contiguous() && grad.is_contiguous(), "lp_norms_bwd: contiguous CUDA expected");
+  c10::cuda::CUDAGuard guard(pred.device());
+  const int64_t planes = pred.size(0) * pred.size(1), H = pred.size(2), W = pred.size(3);
+  MK_CHECK(coef.numel() == planes && coef.scalar_type() == torch::kFloat32 && coef.is_contiguous(), "lp_norms_bwd: coef fp32 [B*C]");
+  const int is_f32 = pred.scalar_type() == torch::kFloat32;
+  check_cuda(mk::lp_norms_bwd(pred.data_ptr(), tgt.data_ptr(), is_f32, qlat.data_ptr<float>(), coef.data_ptr<float>(), grad.data_ptr(),
+                              static_cast<int>(planes), static_cast<int>(H), static_cast<int>(W), static_cast<int>(P), cur_stream()),
+             "lp_norms_bwd");
+}
+
+// table: int64 tensor [ntensors, 8] on the device holding (p, g, m, v, shadow, n, wd_scale bits, pair_mode)
+void adamw_step(const Tensor& table, const Tensor& chunk_tensor, const Tensor& chunk_off, int64_t chunk, const Tensor& hyper) {
+  MK_CHECK(table.is_cuda() && table.scalar_type() == torch::kInt64 && table.is_contiguous(), "adamw: bad table");
+  static_assert(sizeof(mk::AdamEntry) == 56 || sizeof(mk::AdamEntry) == 64, "AdamEntry layout");
+  MK_CHECK(table.size(1) * 8 == (int64_t)sizeof(mk::AdamEntry), "adamw: table row must be ", sizeof(mk::AdamEntry), " bytes");
+  c10::cuda::CUDAGuard guard(table.device());
+  check_cuda(mk::adamw_step(reinterpret_cast<const mk::AdamEntry*>(table.data_ptr()), chunk_tensor.data_ptr<int>(),
+                            reinterpret_cast<const long long*>(chunk_off.data_ptr<int64_t>()), static_cast<int>(chunk_tensor.numel()),
+                            chunk, hyper.data_ptr<float>(), cur_stream()),
+             "adamw_step");
+}
+
+int64_t adam_entry_bytes() { return sizeof(mk::AdamEntry); }
+
+void spectral_expand(const Tensor& w, Tensor& wx) {
+  MK_CHECK(w.is_cuda() && w.is_contiguous() && w.scalar_type() == torch::kComplexFloat && w.dim() == 3, "spectral_expand: complex64 [Cin,Cout,L]");
+  const int64_t Cin = w.size(0), Cout = w.size(1), L = w.size(2);
+  MK_CHECK(wx.is_contiguous() && wx.scalar_type() == torch::kBFloat16 && wx.numel() == 4 * Cin * Cout * L, "spectral_expand: bad wx");
+  c10::cuda::CUDAGuard guard(w.device());
+  check_cuda(mk::spectral_expand(reinterpret_cast<const float*>(w.data_ptr()), reinterpret_cast<__nv_bfloat16*>(wx.data_ptr()),
+                                 static_cast<int>(Cin), static_cast<int>(Cout), static_cast<int>(L), cur_stream()),
+             "spectral_expand");
+}
+
+void spectral_fold(const Tensor& dwx, Tensor& dw) {
+  MK_CHECK(dw.is_cuda() && dw.is_contiguous() && dw.scalar_type() == torch::kComplexFloat && dw.dim() == 3, "spectral_fold: complex64 [Cin,Cout,L]");
+  const int64_t Cin = dw.size(0), Cout = dw.size(1), L = dw.size(2);
+  MK_CHECK(dwx.is_contiguous() && dwx.scalar_type() == torch::kFloat32 && dwx.numel() == 4 * Cin * Cout * L, "spectral_fold: bad dwx");
+  c10::cuda::CUDAGuard guard(dw.device());
+  check_cuda(mk::spectral_fold(dwx.data_ptr<float>(), reinterpret_cast<float*>(dw.data_ptr()), static_cast<int>(Cin),
+                               static_cast<int>(Cout), static_cast<int>(L), cur_stream()),
+             "spectral_fold");
+}
+
+void cast_bf16(const Tensor& x, Tensor& y) {
+  MK_CHECK(x.is_cuda() && x.is_contiguous() && y.is_contiguous() && x.numel() == y.numel(), "cast_bf16: bad tensors");
+  MK_CHECK(x.scalar_type() == torch::kFloat32 && y.scalar_type() == torch::kBFloat16, "cast_bf16: fp32 -> bf16");
+  c10::cuda::CUDAGuard guard(x.device());
+  check_cuda(mk::cast_f32_bf16(x.data_ptr<float>(), reinterpret_cast<__nv_bfloat16*>(y.data_ptr()), x.numel(), cur_stream()), "cast_bf16");
+}
+
+void fill_normal(Tensor& y, int64_t seed) {
+  MK_CHECK(y.is_cuda() && y.is_contiguous() && y.scalar_type() == torch::kBFloat16, "fill_normal: contiguous bf16 CUDA");
+  c10::cuda::CUDAGuard guard(y.device());
+  check_cuda(mk::fill_normal_bf16(reinterpret_cast<__nv_bfloat16*>(y.data_ptr()), y.numel(), static_cast<uint64_t>(seed), cur_stream()),
+             "fill_normal");
+}
+
+// ------------------------------------------------------------------------------------------ peer memory
+
+py::bytes peer_alloc(int64_t bytes, py::list out_ptr) {
+  void* p = nullptr;
+  char handle[64];
+  check_cuda(mk::peer_alloc(static_cast<size_t>(bytes), &p, handle), "peer_alloc");
+  out_ptr.append(reinterpret_cast<int64_t>(p));
+  return py::bytes(handle, 64);
+}
+
+int64_t peer_open(py::bytes handle) {
+  std::string h = handle;
+  MK_CHECK(h.size() == 64, "peer_open: handle must be 64 bytes");
+  void* p = nullptr;
+  check_cuda(mk::peer_open(h.data(), &p), "peer_open");
+  return reinterpret_cast<int64_t>(p);
+}
+
+void peer_close(int64_t ptr) { check_cuda(mk::peer_close(reinterpret_cast<void*>(ptr)), "peer_close"); }
+void peer_free(int64_t ptr) { check_cuda(mk::peer_free(reinterpret_cast<void*>(ptr)), "peer_free"); }
+
+Tensor tensor_from_ptr(int64_t ptr, int64_t bytes, int64_t device) {
+  auto opts = torch::TensorOptions().dtype(torch::kUInt8).device(torch::kCUDA, static_cast<int>(device));
+  return torch::from_blob(reinterpret_cast<void*>(ptr), {bytes}, opts);
+}
+
+// in-place sum over ranks of `data` (fp32 or bf16) living in symmetric memory: ptrs[r] = rank r's copy.
+void peer_allreduce(const std::vector<int64_t>& data_ptrs, const std::vector<int64_t>& flag_ptrs, int64_t rank, int64_t n,
+                    int64_t is_bf16, double scale, int64_t epoch, int64_t device) {
+  const int world = static_cast<int>(data_ptrs.size());
+  MK_CHECK(world >= 1 && world <= mk::PEER_MAX, "peer_allreduce: world size out of range");
+  c10::cuda::CUDAGuard guard(c10::Device(c10::kCUDA, static_cast<int>(device)));
+  mk::PeerPtrs pp;
+  for (int i = 0; i < world; ++i) {
+    pp.data[i] = reinterpret_cast<void*>(data_ptrs[i]);
+    pp.flags[i] = reinterpret_cast<unsigned int*>(flag_ptrs[i]);
+  }
+  Tensor dummy = torch::empty({1}, torch::dtype(torch::kUInt8).device(torch::kCUDA, static_cast<int>(device)));
+  Tensor ef = err_flag_for(dummy);
+  check_cuda(mk::peer_allreduce(pp, world, static_cast<int>(rank), n, static_cast<int>(is_bf16), static_cast<float>(scale),
+                                static_cast<unsigned int>(epoch), ef.data_ptr<int>(), cur_stream()),
+             "peer_allreduce");
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("gemm", &gemm, "tcgen05 GEMM with fused epilogue");
+  m.def("read_error_flag", &read_error_flag);
+  m.def("clear_error_flag", &clear_error_flag);
+  m.def("inorm_fwd", &inorm_fwd);
+  m.def("inorm_partial_stats", &inorm_partial_stats);
+  m.def("inorm_bwd", &inorm_bwd);
+  m.def("lp_scratch_floats", &lp_scratch_floats);
+  m.def("lp_norms", &lp_norms);
+  m.def("lp_norms_bwd", &lp_norms_bwd);
+  m.def("adamw_step", &adamw_step);
+  m.def("adam_entry_bytes", &adam_entry_bytes);
+  m.def("spectral_expand", &spectral_expand);
+  m.def("spectral_fold", &spectral_fold);
+  m.def("cast_bf16", &cast_bf16);
+  m.def("fill_normal", &fill_normal);
+  m.def("peer_alloc", &peer_alloc);
+  m.def("peer_open", &peer_open);
+  m.def("peer_close", &peer_close);
+  m.def("peer_free", &peer_free);
+  m.def("tensor_from_ptr", &tensor_from_ptr);
+  m.def("peer_allreduce", &peer_allreduce);
+}

@@ -1,0 +1,592 @@
+// Memory-bound fused kernels for sm_100a: instance norm (+GELU), quadrature-weighted Lp norms, multi-tensor
+// AdamW with bf16 shadow weights, spectral-weight re-layout.  Each kernel makes the minimum number of passes
+// over HBM (vectorised 16-byte accesses) and keeps reductions in fp32.
+#include "fused_ops.cuh"
+
+#include <math.h>
+
+namespace mk {
+
+namespace {
+
+constexpr int NT = 512;
+
+__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
+__device__ __forceinline__ float dgelu_f(float x) {
+  return 0.5f * (1.0f + erff(x * 0.70710678118654752f)) + x * 0.3989422804014327f * __expf(-0.5f * x * x);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// block-wide sum of two values; result valid in all threads
+__device__ __forceinline__ void block_sum2(float& a, float& b) {
+  __shared__ float sh[2][32];
+  __shared__ float res[2];
+  a = warp_sum(a);
+  b = warp_sum(b);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) {
+    sh[0][w] = a;
+    sh[1][w] = b;
+  }
+  __syncthreads();
+  if (w == 0) {
+    const int nw = (blockDim.x + 31) >> 5;
+    float x = l < nw ? sh[0][l] : 0.f;
+    float y = l < nw ? sh[1][l] : 0.f;
+    x = warp_sum(x);
+    y = warp_sum(y);
+    if (l == 0) {
+      res[0] = x;
+      res[1] = y;
+    }
+  }
+  __syncthreads();
+  a = res[0];
+  b = res[1];
+}
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 x = __bfloat1622float2(h[j]);
+    f[2 * j] = x.x;
+    f[2 * j + 1] = x.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 v;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+  return v;
+}
+
+// ------------------------------------------------------------------------------------------ instance norm
+
+// mode 0: full forward; mode 1: partial sums only (sums -> stats[plane] = (sum, sumsq)); mode 2: normalise with given stats
+template <bool VEC>
+__global__ void __launch_bounds__(NT) inorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
+                                                       const float* __restrict__ w, const float* __restrict__ b,
+                                                       float* __restrict__ stats, int C, long long hw, float eps, int act,
+                                                       int mode) {
+  const int plane = blockIdx.x;
+  const int c = plane % C;
+  const __nv_bfloat16* xp = x + static_cast<long long>(plane) * hw;
+  float mean, rstd;
+  if (mode != 2) {
+    float s = 0.f, ss = 0.f;
+    if (VEC) {
+      const uint4* xv = reinterpret_cast<const uint4*>(xp);
+      const long long nv = hw >> 3;
+      for (long long i = threadIdx.x; i < nv; i += NT) {
+        float f[8];
+        unpack8(xv[i], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          s += f[j];
+          ss += f[j] * f[j];
+        }
+      }
+    } else {
+      for (long long i = threadIdx.x; i < hw; i += NT) {
+        const float f = __bfloat162float(xp[i]);
+        s += f;
+        ss += f * f;
+      }
+    }
+    block_sum2(s, ss);
+    if (mode == 1) {
+      if (threadIdx.x == 0) {
+        stats[2 * plane] = s;
+        stats[2 * plane + 1] = ss;
+      }
+      return;
+    }
+    mean = s / static_cast<float>(hw);
+    const float var = fmaxf(ss / static_cast<float>(hw) - mean * mean, 0.f);
+    rstd = rsqrtf(var + eps);
+    if (threadIdx.x == 0) {
+      stats[2 * plane] = mean;
+      stats[2 * plane + 1] = rstd;
+    }
+  } else {
+    mean = stats[2 * plane];
+    rstd = stats[2 * plane + 1];
+  }
+  const float ga = (w ? w[c] : 1.f) * rstd;
+  const float be = (b ? b[c] : 0.f) - mean * ga;
+  __nv_bfloat16* yp = y + static_cast<long long>(plane) * hw;
+  if (VEC) {
+    const uint4* xv = reinterpret_cast<const uint4*>(xp);
+    uint4* yv = reinterpret_cast<uint4*>(yp);
+    const long long nv = hw >> 3;
+    for (long long i = threadIdx.x; i < nv; i += NT) {
+      float f[8];
+      unpack8(xv[i], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float v = f[j] * ga + be;
+        f[j] = act ? gelu_f(v) : v;
+      }
+      yv[i] = pack8(f);
+    }
+  } else {
+    for (long long i = threadIdx.x; i < hw; i += NT) {
+      float v = __bfloat162float(xp[i]) * ga + be;
+      yp[i] = __float2bfloat16(act ? gelu_f(v) : v);
+    }
+  }
+}
+
+// phase control: ext 0: both phases; 1: phase 1 only (write sums); 2: phase 2 only (read merged sums)
+template <bool VEC>
+__global__ void __launch_bounds__(NT) inorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
+                                                       __nv_bfloat16* __restrict__ dx, const float* __restrict__ w,
+                                                       const float* __restrict__ b, const float* __restrict__ stats,
+                                                       float* __restrict__ dw, float* __restrict__ db, float* __restrict__ sums_io,
+                                                       int C, long long hw, float inv_count, int act, int ext) {
+  const int plane = blockIdx.x;
+  const int c = plane % C;
+  const float mean = stats[2 * plane], rstd = stats[2 * plane + 1];
+  const float wc = w ? w[c] : 1.f, bc = b ? b[c] : 0.f;
+  const __nv_bfloat16* xp = x + static_cast<long long>(plane) * hw;
+  const __nv_bfloat16* gp = dy + static_cast<long long>(plane) * hw;
+  float s1 = 0.f, s2 = 0.f;
+  if (ext != 2) {
+    if (VEC) {
+      const uint4* xv = reinterpret_cast<const uint4*>(xp);
+      const uint4* gv = reinterpret_cast<const uint4*>(gp);
+      const long long nv = hw >> 3;
+      for (long long i = threadIdx.x; i < nv; i += NT) {
+        float f[8], g[8];
+        unpack8(xv[i], f);
+        unpack8(gv[i], g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float xh = (f[j] - mean) * rstd;
+          float gg = g[j];
+          if (act) gg *= dgelu_f(xh * wc + bc);
+          s1 += gg;
+          s2 += gg * xh;
+        }
+      }
+    } else {
+      for (long long i = threadIdx.x; i < hw; i += NT) {
+        const float xh = (__bfloat162float(xp[i]) - mean) * rstd;
+        float gg = __bfloat162float(gp[i]);
+        if (act) gg *= dgelu_f(xh * wc + bc);
+        s1 += gg;
+        s2 += gg * xh;
+      }
+    }
+    block_sum2(s1, s2);
+    if (threadIdx.x == 0) {
+      if (dw) atomicAdd(dw + c, s2);
+      if (db) atomicAdd(db + c, s1);
+      if (sums_io) {
+        sums_io[2 * plane] = s1;
+        sums_io[2 * plane + 1] = s2;
+      }
+    }
+    if (ext == 1) return;
+  } else {
+    s1 = sums_io[2 * plane];
+    s2 = sums_io[2 * plane + 1];
+  }
+  const float m1 = s1 * inv_count, m2 = s2 * inv_count;
+  const float sc = rstd * wc;
+  __nv_bfloat16* op = dx + static_cast<long long>(plane) * hw;
+  if (VEC) {
+    const uint4* xv = reinterpret_cast<const uint4*>(xp);
+    const uint4* gv = reinterpret_cast<const uint4*>(gp);
+    uint4* ov = reinterpret_cast<uint4*>(op);
+    const long long nv = hw >> 3;
+    for (long long i = threadIdx.x; i < nv; i += NT) {
+      float f[8], g[8];
+      unpack8(xv[i], f);
+      unpack8(gv[i], g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xh = (f[j] - mean) * rstd;
+        float gg = g[j];
+        if (act) gg *= dgelu_f(xh * wc + bc);
+        f[j] = sc * (gg - m1 - xh * m2);
+      }
+      ov[i] = pack8(f);
+    }
+  } else {
+    for (long long i = threadIdx.x; i < hw; i += NT) {
+      const float xh = (__bfloat162float(xp[i]) - mean) * rstd;
+      float gg = __bfloat162float(gp[i]);
+      if (act) gg *= dgelu_f(xh * wc + bc);
+      op[i] = __float2bfloat16(sc * (gg - m1 - xh * m2));
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------ Lp norms
+
+constexpr int LP_CHUNK = 1 << 16;   // elements of one plane handled by one CTA
+
+template <typename T>
+__device__ __forceinline__ float ldf(const T* p, long long i);
+template <>
+__device__ __forceinline__ float ldf<float>(const float* p, long long i) { return p[i]; }
+template <>
+__device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p, long long i) { return __bfloat162float(p[i]); }
+
+template <typename T, int P>
+__global__ void __launch_bounds__(NT) lp_norms_kernel(const T* __restrict__ pred, const T* __restrict__ tgt,
+                                                      const float* __restrict__ qlat, float* __restrict__ out,
+                                                      float* __restrict__ partial, int* __restrict__ counters, int W,
+                                                      long long hw, int chunks) {
+  const int plane = blockIdx.y, chunk = blockIdx.x;
+  const T* pp = pred + static_cast<long long>(plane) * hw;
+  const T* tp = tgt + static_cast<long long>(plane) * hw;
+  const long long beg = static_cast<long long>(chunk) * LP_CHUNK;
+  long long end = beg + LP_CHUNK;
+  if (end > hw) end = hw;
+  float sd = 0.f, st = 0.f;
+  for (long long i = beg + threadIdx.x; i < end; i += NT) {
+    const float q = qlat[i / W];
+    const float p = ldf<T>(pp, i), t = ldf<T>(tp, i);
+    const float d = p - t;
+    if (P == 2) {
+      sd += q * d * d;
+      st += q * t * t;
+    } else {
+      sd += q * fabsf(d);
+      st += q * fabsf(t);
+    }
+  }
+  block_sum2(sd, st);
+  __shared__ int last;
+  if (threadIdx.x == 0) {
+    float* pr = partial + (static_cast<long long>(plane) * chunks + chunk) * 2;
+    pr[0] = sd;
+    pr[1] = st;
+    __threadfence();
+    const int done = atomicAdd(counters + plane, 1);
+    last = (done == chunks - 1);
+  }
+  __syncthreads();
+  if (last) {
+    // fixed-order final sum -> deterministic result
+    __threadfence();
+    float a = 0.f, b = 0.f;
+    const volatile float* pr = partial + static_cast<long long>(plane) * chunks * 2;
+    for (int i = threadIdx.x; i < chunks; i += NT) {
+      a += pr[2 * i];
+      b += pr[2 * i + 1];
+    }
+    block_sum2(a, b);
+    if (threadIdx.x == 0) {
+      out[2 * plane] = a;
+      out[2 * plane + 1] = b;
+      counters[plane] = 0;
+    }
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void stf(T* p, long long i, float v);
+template <>
+__device__ __forceinline__ void stf<float>(float* p, long long i, float v) { p[i] = v; }
+template <>
+__device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16* p, long long i, float v) { p[i] = __float2bfloat16(v); }
+
+template <typename T, int P>
+__global__ void __launch_bounds__(NT) lp_bwd_kernel(const T* __restrict__ pred, const T* __restrict__ tgt,
+                                                    const float* __restrict__ qlat, const float* __restrict__ coef,
+                                                    T* __restrict__ grad, int W, long long hw) {
+  const int plane = blockIdx.y;
+  const float cf = coef[plane];
+  const long long base = static_cast<long long>(plane) * hw;
+  const long long beg = static_cast<long long>(blockIdx.x) * LP_CHUNK;
+  long long end = beg + LP_CHUNK;
+  if (end > hw) end = hw;
+  for (long long i = beg + threadIdx.x; i < end; i += NT) {
+    const float q = qlat[i / W];
+    const float d = ldf<T>(pred, base + i) - ldf<T>(tgt, base + i);
+    float g;
+    if (P == 2) g = 2.f * d;
+    else g = (d > 0.f) ? 1.f : ((d < 0.f) ? -1.f : 0.f);
+    stf<T>(grad, base + i, cf * q * g);
+  }
+}
+
+// ------------------------------------------------------------------------------------------ AdamW
+
+__global__ void __launch_bounds__(256) adamw_kernel(const AdamEntry* __restrict__ table, const int* __restrict__ chunk_tensor,
+                                                    const long long* __restrict__ chunk_off, long long chunk,
+                                                    const float* __restrict__ hyper) {
+  const AdamEntry e = table[chunk_tensor[blockIdx.x]];
+  const long long off = chunk_off[blockIdx.x];
+  long long n = e.n - off;
+  if (n > chunk) n = chunk;
+  const float lr = hyper[0], b1 = hyper[1], b2 = hyper[2], eps = hyper[3], wd = hyper[4] * e.wd_scale, step = hyper[5],
+              gs = hyper[6];
+  const bool decoupled = hyper[7] != 0.f;
+  const float bc1 = 1.f - powf(b1, step), bc2 = 1.f - powf(b2, step);
+  const float step_size = lr / bc1;
+  const float inv_sqrt_bc2 = rsqrtf(bc2);
+  float* p = e.p + off;
+  const float* g = e.g + off;
+  float* m = e.m + off;
+  float* v = e.v + off;
+  __nv_bfloat16* sh = e.shadow ? e.shadow + off : nullptr;
+  // chunk and off are multiples of 4, so float4 access is aligned whenever the tensor base is
+  const bool vec = ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(m) |
+                     reinterpret_cast<uintptr_t>(v)) & 15) == 0;
+  const long long n4 = vec ? (n >> 2) : 0;
+  for (long long i = threadIdx.x; i < n4; i += blockDim.x) {
+    float4 pp = reinterpret_cast<float4*>(p)[i];
+    const float4 gg4 = reinterpret_cast<const float4*>(g)[i];
+    float4 mm = reinterpret_cast<float4*>(m)[i];
+    float4 vv = reinterpret_cast<float4*>(v)[i];
+    float P[4] = {pp.x, pp.y, pp.z, pp.w}, G[4] = {gg4.x * gs, gg4.y * gs, gg4.z * gs, gg4.w * gs};
+    float M[4] = {mm.x, mm.y, mm.z, mm.w}, V[4] = {vv.x, vv.y, vv.z, vv.w};
+    float G2[4];
+    if (e.pair_mode) {
+      G2[0] = G2[1] = G[0] * G[0] + G[1] * G[1];
+      G2[2] = G2[3] = G[2] * G[2] + G[3] * G[3];
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) G2[j] = G[j] * G[j];
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float gj = G[j];
+      if (decoupled) P[j] *= (1.f - lr * wd);
+      else gj += wd * P[j];
+      M[j] = b1 * M[j] + (1.f - b1) * gj;
+      V[j] = b2 * V[j] + (1.f - b2) * (decoupled ? G2[j] : (e.pair_mode ? G2[j] : gj * gj));
+      const float denom = sqrtf(V[j]) * inv_sqrt_bc2 + eps;
+      P[j] -= step_size * M[j] / denom;
+    }
+    reinterpret_cast<float4*>(p)[i] = make_float4(P[0], P[1], P[2], P[3]);
+    reinterpret_cast<float4*>(m)[i] = make_float4(M[0], M[1], M[2], M[3]);
+    reinterpret_cast<float4*>(v)[i] = make_float4(V[0], V[1], V[2], V[3]);
+    if (sh) {
+      sh[4 * i] = __float2bfloat16(P[0]);
+      sh[4 * i + 1] = __float2bfloat16(P[1]);
+      sh[4 * i + 2] = __float2bfloat16(P[2]);
+      sh[4 * i + 3] = __float2bfloat16(P[3]);
+    }
+  }
+  for (long long i = (n4 << 2) + threadIdx.x; i < n; i += blockDim.x) {
+    float gj = g[i] * gs;
+    float g2 = gj * gj;
+    if (e.pair_mode) {
+      const float go = g[i ^ 1] * gs;   // partner of the (re, im) pair; off is even
+      g2 += go * go;
+    }
+    float pj = p[i];
+    if (decoupled) pj *= (1.f - lr * wd);
+    else gj += wd * pj;
+    const float mj = b1 * m[i] + (1.f - b1) * gj;
+    const float vj = b2 * v[i] + (1.f - b2) * ((decoupled || e.pair_mode) ? g2 : gj * gj);
+    pj -= step_size * mj / (sqrtf(vj) * inv_sqrt_bc2 + eps);
+    p[i] = pj;
+    m[i] = mj;
+    v[i] = vj;
+    if (sh) sh[i] = __float2bfloat16(pj);
+  }
+}
+
+// ------------------------------------------------------------------------------------------ spectral weights
+
+// grid: (Cin/32, Cout, ceil(L/32)); block 32x8
+__global__ void spectral_expand_kernel(const float2* __restrict__ w, __nv_bfloat16* __restrict__ wx, int Cin, int Cout, int L) {
+  __shared__ float2 tile[32][33];
+  const int c0 = blockIdx.x * 32, o = blockIdx.y, l0 = blockIdx.z * 32;
+  for (int j = threadIdx.y; j < 32; j += 8) {
+    const int c = c0 + j, l = l0 + threadIdx.x;
+    float2 v = make_float2(0.f, 0.f);
+    if (c < Cin && l < L) v = w[(static_cast<long long>(c) * Cout + o) * L + l];
+    tile[j][threadIdx.x] = v;
+  }
+  __syncthreads();
+  for (int j = threadIdx.y; j < 32; j += 8) {
+    const int l = l0 + j, c = c0 + threadIdx.x;
+    if (l < L && c < Cin) {
+      const float2 v = tile[threadIdx.x][j];
+      // planar 2x2-block form: rows (ri', o), columns (ri, c):  [[Wr, -Wi], [Wi, Wr]]
+      __nv_bfloat16* base = wx + static_cast<long long>(l) * 4 * Cout * Cin;
+      const long long r0 = static_cast<long long>(o) * 2 * Cin, r1 = static_cast<long long>(Cout + o) * 2 * Cin;
+      base[r0 + c] = __float2bfloat16(v.x);
+      base[r0 + Cin + c] = __float2bfloat16(-v.y);
+      base[r1 + c] = __float2bfloat16(v.y);
+      base[r1 + Cin + c] = __float2bfloat16(v.x);
+    }
+  }
+}
+
+__global__ void spectral_fold_kernel(const float* __restrict__ dwx, float2* __restrict__ dw, int Cin, int Cout, int L) {
+  __shared__ float2 tile[32][33];
+  const int c0 = blockIdx.x * 32, o = blockIdx.y, l0 = blockIdx.z * 32;
+  for (int j = threadIdx.y; j < 32; j += 8) {
+    const int l = l0 + j, c = c0 + threadIdx.x;
+    float2 v = make_float2(0.f, 0.f);
+    if (l < L && c < Cin) {
+      const float* base = dwx + static_cast<long long>(l) * 4 * Cout * Cin;
+      const long long r0 = static_cast<long long>(o) * 2 * Cin, r1 = static_cast<long long>(Cout + o) * 2 * Cin;
+      v.x = base[r0 + c] + base[r1 + Cin + c];   // dWr
+      v.y = base[r1 + c] - base[r0 + Cin + c];   // dWi
+    }
+    tile[j][threadIdx.x] = v;
+  }
+  __syncthreads();
+  for (int j = threadIdx.y; j < 32; j += 8) {
+    const int c = c0 + j, l = l0 + threadIdx.x;
+    if (c < Cin && l < L) {
+      float2* d = dw + (static_cast<long long>(c) * Cout + o) * L + l;
+      const float2 v = tile[threadIdx.x][j];
+      float2 cur = *d;
+      cur.x += v.x;
+      cur.y += v.y;
+      *d = cur;
+    }
+  }
+}
+
+__global__ void cast_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ y, long long n) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    y[i] = __float2bfloat16(x[i]);
+}
+
+__device__ __forceinline__ uint64_t splitmix(uint64_t z) {
+  z += 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+
+// counter-based N(0,1): two 64-bit hashes -> Box-Muller; deterministic in (seed, index)
+__global__ void fill_normal_kernel(__nv_bfloat16* __restrict__ y, long long n, uint64_t seed) {
+  const long long pairs = (n + 1) >> 1;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < pairs;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const uint64_t h = splitmix(seed ^ splitmix(static_cast<uint64_t>(i)));
+    const float u1 = (static_cast<float>(h >> 40) + 0.5f) * (1.0f / 16777216.0f);
+    const float u2 = (static_cast<float>((h >> 16) & 0xFFFFFF) + 0.5f) * (1.0f / 16777216.0f);
+    const float r = sqrtf(-2.f * __logf(u1));
+    float sn, cs;
+    __sincosf(6.283185307179586f * u2, &sn, &cs);
+    y[2 * i] = __float2bfloat16(r * cs);
+    if (2 * i + 1 < n) y[2 * i + 1] = __float2bfloat16(r * sn);
+  }
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+
+cudaError_t inorm_fwd(const __nv_bfloat16* x, __nv_bfloat16* y, const float* w, const float* b, float* stats, int planes,
+                      int C, long long hw, float eps, int act, int ext_stats, cudaStream_t s) {
+  if (planes <= 0) return cudaSuccess;
+  const bool vec = (hw % 8 == 0) && aligned16(x) && aligned16(y);
+  const int mode = ext_stats ? 2 : 0;
+  if (vec) inorm_fwd_kernel<true><<<planes, NT, 0, s>>>(x, y, w, b, stats, C, hw, eps, act, mode);
+  else inorm_fwd_kernel<false><<<planes, NT, 0, s>>>(x, y, w, b, stats, C, hw, eps, act, mode);
+  return cudaGetLastError();
+}
+
+cudaError_t inorm_partial_stats(const __nv_bfloat16* x, float* sums, int planes, long long hw, cudaStream_t s) {
+  if (planes <= 0) return cudaSuccess;
+  const bool vec = (hw % 8 == 0) && aligned16(x);
+  if (vec) inorm_fwd_kernel<true><<<planes, NT, 0, s>>>(x, nullptr, nullptr, nullptr, sums, 1, hw, 0.f, 0, 1);
+  else inorm_fwd_kernel<false><<<planes, NT, 0, s>>>(x, nullptr, nullptr, nullptr, sums, 1, hw, 0.f, 0, 1);
+  return cudaGetLastError();
+}
+
+cudaError_t inorm_bwd(const __nv_bfloat16* x, const __nv_bfloat16* dy, __nv_bfloat16* dx, const float* w, const float* b,
+                      const float* stats, float* dw, float* db, float* sums_io, int planes, int C, long long hw,
+                      double count, int act, int ext_sums, cudaStream_t s) {
+  if (planes <= 0) return cudaSuccess;
+  const bool vec = (hw % 8 == 0) && aligned16(x) && aligned16(dy) && (dx == nullptr || aligned16(dx));
+  const float inv = static_cast<float>(1.0 / count);
+  if (vec) inorm_bwd_kernel<true><<<planes, NT, 0, s>>>(x, dy, dx, w, b, stats, dw, db, sums_io, C, hw, inv, act, ext_sums);
+  else inorm_bwd_kernel<false><<<planes, NT, 0, s>>>(x, dy, dx, w, b, stats, dw, db, sums_io, C, hw, inv, act, ext_sums);
+  return cudaGetLastError();
+}
+
+int lp_norms_chunks(long long hw) { return static_cast<int>((hw + LP_CHUNK - 1) / LP_CHUNK); }
+
+cudaError_t lp_norms(const void* pred, const void* tgt, int is_f32, const float* qlat, float* out, float* scratch,
+                     int planes, int H, int W, int P, cudaStream_t s) {
+  if (planes <= 0) return cudaSuccess;
+  const long long hw = static_cast<long long>(H) * W;
+  const int chunks = lp_norms_chunks(hw);
+  float* partial = scratch;
+  int* counters = reinterpret_cast<int*>(scratch + static_cast<long long>(planes) * chunks * 2);
+  dim3 grid(chunks, planes);
+  if (is_f32) {
+    if (P == 2) lp_norms_kernel<float, 2><<<grid, NT, 0, s>>>((const float*)pred, (const float*)tgt, qlat, out, partial, counters, W, hw, chunks);
+    else lp_norms_kernel<float, 1><<<grid, NT, 0, s>>>((const float*)pred, (const float*)tgt, qlat, out, partial, counters, W, hw, chunks);
+  } else {
+    if (P == 2) lp_norms_kernel<__nv_bfloat16, 2><<<grid, NT, 0, s>>>((const __nv_bfloat16*)pred, (const __nv_bfloat16*)tgt, qlat, out, partial, counters, W, hw, chunks);
+    else lp_norms_kernel<__nv_bfloat16, 1><<<grid, NT, 0, s>>>((const __nv_bfloat16*)pred, (const __nv_bfloat16*)tgt, qlat, out, partial, counters, W, hw, chunks);
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t lp_norms_bwd(const void* pred, const void* tgt, int is_f32, const float* qlat, const float* coef, void* grad,
+                         int planes, int H, int W, int P, cudaStream_t s) {
+  if (planes <= 0) return cudaSuccess;
+  const long long hw = static_cast<long long>(H) * W;
+  dim3 grid(lp_norms_chunks(hw), planes);
+  if (is_f32) {
+    if (P == 2) lp_bwd_kernel<float, 2><<<grid, NT, 0, s>>>((const float*)pred, (const float*)tgt, qlat, coef, (float*)grad, W, hw);
+    else lp_bwd_kernel<float, 1><<<grid, NT, 0, s>>>((const float*)pred, (const float*)tgt, qlat, coef, (float*)grad, W, hw);
+  } else {
+    if (P == 2) lp_bwd_kernel<__nv_bfloat16, 2><<<grid, NT, 0, s>>>((const __nv_bfloat16*)pred, (const __nv_bfloat16*)tgt, qlat, coef, (__nv_bfloat16*)grad, W, hw);
+    else lp_bwd_kernel<__nv_bfloat16, 1><<<grid, NT, 0, s>>>((const __nv_bfloat16*)pred, (const __nv_bfloat16*)tgt, qlat, coef, (__nv_bfloat16*)grad, W, hw);
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t adamw_step(const AdamEntry* table, const int* chunk_tensor, const long long* chunk_off, int nchunks,
+                       long long chunk, const float* hyper, cudaStream_t s) {
+  if (nchunks <= 0) return cudaSuccess;
+  adamw_kernel<<<nchunks, 256, 0, s>>>(table, chunk_tensor, chunk_off, chunk, hyper);
+  return cudaGetLastError();
+}
+
+cudaError_t spectral_expand(const float* w, __nv_bfloat16* wx, int Cin, int Cout, int L, cudaStream_t s) {
+  dim3 grid((Cin + 31) / 32, Cout, (L + 31) / 32), block(32, 8);
+  spectral_expand_kernel<<<grid, block, 0, s>>>(reinterpret_cast<const float2*>(w), wx, Cin, Cout, L);
+  return cudaGetLastError();
+}
+
+cudaError_t spectral_fold(const float* dwx, float* dw, int Cin, int Cout, int L, cudaStream_t s) {
+  dim3 grid((Cin + 31) / 32, Cout, (L + 31) / 32), block(32, 8);
+  spectral_fold_kernel<<<grid, block, 0, s>>>(dwx, reinterpret_cast<float2*>(dw), Cin, Cout, L);
+  return cudaGetLastError();
+}
+
+cudaError_t cast_f32_bf16(const float* x, __nv_bfloat16* y, long long n, cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  cast_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(x, y, n);
+  return cudaGetLastError();
+}
+
+cudaError_t fill_normal_bf16(__nv_bfloat16* y, long long n, uint64_t seed, cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  long long blocks = ((n + 1) / 2 + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  fill_normal_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(y, n, seed);
+  return cudaGetLastError();
+}
+
+}  // namespace mk

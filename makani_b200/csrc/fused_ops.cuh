@@ -1,0 +1,60 @@
+// Launchers for the memory-bound fused kernels (normalisation, loss, optimiser, weight re-layout).
+// All take raw device pointers and a stream; none allocates.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+namespace mk {
+
+// ---- instance norm over the last `hw` elements of each of `planes` = B*C rows (channel = plane % C) ----
+// stats: [planes, 2] fp32 (mean, rstd) written by fwd, read by bwd.  act: 0 none, 1 GELU applied after the affine.
+// If `ext_stats` is non-zero the forward skips the reduction and uses the (mean, rstd) already in `stats`
+// (used by the spatially distributed norm after the cross-rank merge).
+cudaError_t inorm_fwd(const __nv_bfloat16* x, __nv_bfloat16* y, const float* w, const float* b, float* stats,
+                      int planes, int C, long long hw, float eps, int act, int ext_stats, cudaStream_t s);
+// partial statistics only: sums[plane] = (sum, sum of squares) in fp32
+cudaError_t inorm_partial_stats(const __nv_bfloat16* x, float* sums, int planes, long long hw, cudaStream_t s);
+// bwd: dx, and atomically accumulated dw[C], db[C].  `sums_io` [planes,2]: when ext_sums == 0 the kernel
+// computes (sum g, sum g*xhat) itself; when ext_sums == 1 it only computes them (phase 1) and returns;
+// when ext_sums == 2 it reads merged sums from sums_io and does phase 2 with `count` = global element count.
+cudaError_t inorm_bwd(const __nv_bfloat16* x, const __nv_bfloat16* dy, __nv_bfloat16* dx, const float* w,
+                      const float* b, const float* stats, float* dw, float* db, float* sums_io, int planes, int C,
+                      long long hw, double count, int act, int ext_sums, cudaStream_t s);
+
+// ---- quadrature-weighted Lp norms on the sphere ----
+// out[plane] = (sum_hw q[h] |p-t|^P, sum_hw q[h] |t|^P), P in {1,2}.  `scratch` holds
+// planes*chunks*2 floats + planes ints (zero-initialised once; the kernel leaves the counters at zero).
+int lp_norms_chunks(long long hw);
+cudaError_t lp_norms(const void* pred, const void* tgt, int is_f32, const float* qlat, float* out, float* scratch,
+                     int planes, int H, int W, int P, cudaStream_t s);
+// grad[plane, h, w] = coef[plane] * q[h] * d|p-t|^P/dp   (written in the dtype of pred)
+cudaError_t lp_norms_bwd(const void* pred, const void* tgt, int is_f32, const float* qlat, const float* coef,
+                         void* grad, int planes, int H, int W, int P, cudaStream_t s);
+
+// ---- fused multi-tensor AdamW ----
+struct AdamEntry {
+  float* p;
+  const float* g;
+  float* m;
+  float* v;
+  __nv_bfloat16* shadow;   // optional bf16 copy of the updated parameter (may be null)
+  long long n;
+  float wd_scale;          // 1 = apply weight decay, 0 = no decay for this tensor
+  int pair_mode;           // 1: elements are (re, im) pairs sharing one second moment |g|^2
+};
+// hyper (device, fp32[8]): lr, beta1, beta2, eps, weight_decay, step, grad_scale, adamw(1)/adam-L2(0)
+cudaError_t adamw_step(const AdamEntry* table, const int* chunk_tensor, const long long* chunk_off, int nchunks,
+                       long long chunk, const float* hyper, cudaStream_t s);
+
+// ---- spectral weight re-layout ----
+// w: complex64 [Cin, Cout, L] (interleaved) -> wx: bf16 [L, 2*Cout, 2*Cin] real 2x2-block form
+cudaError_t spectral_expand(const float* w, __nv_bfloat16* wx, int Cin, int Cout, int L, cudaStream_t s);
+// dwx: fp32 [L, 2*Cout, 2*Cin] -> dw (complex64 [Cin, Cout, L]) += fold(dwx)
+cudaError_t spectral_fold(const float* dwx, float* dw, int Cin, int Cout, int L, cudaStream_t s);
+
+// ---- small elementwise helpers ----
+cudaError_t cast_f32_bf16(const float* x, __nv_bfloat16* y, long long n, cudaStream_t s);
+cudaError_t fill_normal_bf16(__nv_bfloat16* y, long long n, uint64_t seed, cudaStream_t s);
+
+}  // namespace mk

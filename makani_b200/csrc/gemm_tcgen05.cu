@@ -1,0 +1,649 @@
+// Persistent warp-specialised GEMM for sm_100a: TMA -> shared memory (128B swizzle) -> tcgen05.mma with
+// accumulators in tensor memory -> tcgen05.ld epilogue with fused bias / GELU / residual / scatter.
+//
+// Roles per CTA (192 threads, one CTA per SM):
+//   warp 0      : TMA producer (one elected lane)
+//   warp 1      : TMEM allocator + MMA issuer (one elected lane)
+//   warps 2..5  : epilogue; warp w reads TMEM lanes [32*(w%4), 32*(w%4)+32)
+// Two accumulator buffers in TMEM let the epilogue of tile i overlap the main loop of tile i+1.
+// Every mbarrier wait is bounded; on expiry the kernel records a code in *err and drains.
+#include "gemm_tcgen05.cuh"
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <stdio.h>
+#include <string.h>
+
+namespace mk {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int A_STAGE_BYTES = BM * 128;
+constexpr int NUM_THREADS = 192;
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;   // 2 s per barrier wait
+
+struct KParams {
+  int M, N, K;
+  int zlo_n, zhi_n;
+  int splits, k_per_split;
+  int a_mn, b_mn;
+  int a_zlo, a_zhi, b_zlo, b_zhi;
+  int rmin_a, rmin_b, rmax_a, rmax_b, kmin_a, kmin_b, kmax_a, kmax_b;
+  long long d_zlo, d_zhi;
+  int rdiv; long long rs_hi, rs_lo;
+  int ndiv; long long ns_hi;
+  float alpha;
+  const float* bias;
+  int bias_mode, act;
+  const void* resid;
+  void* preact;
+  void* D;
+  int out_f32, accumulate, vec_ok;
+  int m_tiles, n_tiles;
+  long long total_tiles;
+  int* err;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// Bounded wait: polls the barrier and gives up after WAIT_LIMIT_NS of wall time. Returns false on expiry.
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  uint64_t t0 = 0;
+  for (uint32_t it = 0;; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P1;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, P1;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if ((it & 1023u) == 1023u) {
+      const uint64_t now = global_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > WAIT_LIMIT_NS) return false;
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2,
+                                            int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+template <int EB>
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accum) {
+  if constexpr (EB == 2) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "l"(da), "l"(db), "r"(idesc), "r"(accum)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "l"(da), "l"(db), "r"(idesc), "r"(accum)
+        : "memory");
+  }
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, sm_100 version field = 1.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= static_cast<uint64_t>(1) << 46;   // descriptor version
+  d |= static_cast<uint64_t>(2) << 61;   // SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
+// d/dx of the exact GELU: Phi(x) + x * phi(x)
+__device__ __forceinline__ float gelu_grad(float x) {
+  return 0.5f * (1.0f + erff(x * 0.70710678118654752f)) + x * 0.3989422804014327f * __expf(-0.5f * x * x);
+}
+
+struct TileCoord {
+  int zhi, zlo, split, mt, nt;
+  int k_begin, k_end;   // element range, k_begin multiple of BK
+  bool skip;
+};
+
+template <int BK>
+__device__ __forceinline__ TileCoord decode_tile(const KParams& p, long long t) {
+  TileCoord c;
+  c.mt = static_cast<int>(t % p.m_tiles);
+  t /= p.m_tiles;
+  c.nt = static_cast<int>(t % p.n_tiles);
+  t /= p.n_tiles;
+  c.split = static_cast<int>(t % p.splits);
+  t /= p.splits;
+  c.zlo = static_cast<int>(t % p.zlo_n);
+  c.zhi = static_cast<int>(t / p.zlo_n);
+  const int rmin = p.rmin_a * c.zhi + p.rmin_b;
+  const int rmax = p.rmax_a * c.zhi + p.rmax_b;
+  int kmin = p.kmin_a * c.zhi + p.kmin_b;
+  int kmax = p.kmax_a * c.zhi + p.kmax_b;
+  if (kmin < 0) kmin = 0;
+  if (kmax > p.K) kmax = p.K;
+  int kb = c.split * p.k_per_split;
+  int ke = kb + p.k_per_split;
+  if (ke > p.K) ke = p.K;
+  const int kmin_al = (kmin / BK) * BK;
+  if (kb < kmin_al) kb = kmin_al;
+  if (ke > kmax) ke = kmax;
+  c.k_begin = kb;
+  c.k_end = ke;
+  const int r0 = c.mt * BM;
+  c.skip = (r0 + BM <= rmin) || (r0 >= rmax) || (kb >= ke);
+  return c;
+}
+
+template <int BN, int EB>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const KParams p) {
+  constexpr int BK = 128 / EB;            // elements per 128-byte k-slab
+  constexpr int UMMA_K = 32 / EB;         // elements per tcgen05.mma
+  constexpr int B_STAGE_BYTES = BN * 128;
+  constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  constexpr int STAGES = (BN == 256) ? 4 : 6;
+  constexpr int MN_BOX = 128 / EB;        // rows of an MN-major box along the contiguous dimension
+  constexpr uint32_t TMEM_COLS = 2 * BN;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+  uint8_t* smem = smem_raw + pad;
+  const uint32_t smem_base = raw_addr + pad;
+
+  // barrier block lives after the stages
+  uint8_t* bar_ptr = smem + STAGES * STAGE_BYTES;
+  const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_ptr + 8 * (2 * STAGES + 4));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(const_cast<uint32_t*>(tmem_slot))),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+        const TileCoord c = decode_tile<BK>(p, t);
+        if (c.skip) continue;
+        const int m0 = c.mt * BM, n0 = c.nt * BN;
+        const int azl = p.a_zlo ? c.zlo : 0, azh = p.a_zhi ? c.zhi : 0;
+        const int bzl = p.b_zlo ? c.zlo : 0, bzh = p.b_zhi ? c.zhi : 0;
+        for (int k = c.k_begin; k < c.k_end; k += BK, ++it) {
+          const int s = it % STAGES;
+          const uint32_t par = ((it / STAGES) & 1u) ^ 1u;
+          if (!mbar_wait(empty_bar(s), par)) {
+            atomicExch(p.err, 1);
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(full_bar(s), STAGE_BYTES);
+          const uint32_t sa = smem_base + s * STAGE_BYTES;
+          const uint32_t sb = sa + A_STAGE_BYTES;
+          if (!p.a_mn) {
+            tma_load_4d(sa, &map_a, full_bar(s), k, m0, azl, azh);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / MN_BOX; ++j)
+              tma_load_4d(sa + j * (BK * 128), &map_a, full_bar(s), m0 + j * MN_BOX, k, azl, azh);
+          }
+          if (!p.b_mn) {
+            tma_load_4d(sb, &map_b, full_bar(s), k, n0, bzl, bzh);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / MN_BOX; ++j)
+              tma_load_4d(sb + j * (BK * 128), &map_b, full_bar(s), n0 + j * MN_BOX, k, bzl, bzh);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      // instruction descriptor: fp32 accumulate, operand format, majors, N, M
+      const uint32_t fmt = (EB == 2) ? 1u : 2u;   // BF16 : TF32
+      const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(p.a_mn) << 15) |
+                             (static_cast<uint32_t>(p.b_mn) << 16) | (static_cast<uint32_t>(BN >> 3) << 17) |
+                             (static_cast<uint32_t>(BM >> 4) << 24);
+      const uint32_t a_lbo = p.a_mn ? BK * 128 : 16, a_sbo = 1024;
+      const uint32_t b_lbo = p.b_mn ? BK * 128 : 16, b_sbo = 1024;
+      const uint32_t a_kstep = p.a_mn ? UMMA_K * 128 : 32;
+      const uint32_t b_kstep = p.b_mn ? UMMA_K * 128 : 32;
+      uint32_t it = 0, acc_it = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+        const TileCoord c = decode_tile<BK>(p, t);
+        if (c.skip) continue;
+        const int buf = acc_it & 1;
+        if (!mbar_wait(tempty_bar(buf), ((acc_it >> 1) & 1u) ^ 1u)) {
+          atomicExch(p.err, 2);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * BN;
+        uint32_t accum = 0;
+        for (int k = c.k_begin; k < c.k_end; k += BK, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(full_bar(s), (it / STAGES) & 1u)) {
+            atomicExch(p.err, 3);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_base + s * STAGE_BYTES;
+          const uint32_t sb = sa + A_STAGE_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            const uint64_t da = make_desc(sa + kk * a_kstep, a_lbo, a_sbo);
+            const uint64_t db = make_desc(sb + kk * b_kstep, b_lbo, b_sbo);
+            tc_mma<EB>(tmem_d, da, db, idesc, accum);
+            accum = 1;
+          }
+          tc_commit(empty_bar(s));   // frees the smem stage once these MMAs have read it
+        }
+        tc_commit(tfull_bar(buf));   // accumulator complete
+        ++acc_it;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int q = warp & 3;
+    uint32_t acc_it = 0;
+    bool ok = true;
+    const size_t osz = p.out_f32 ? 4 : 2;
+    for (long long t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
+      const TileCoord c = decode_tile<BK>(p, t);
+      if (c.skip && p.accumulate) continue;
+      const int r = c.mt * BM + q * 32 + lane;
+      const int n0 = c.nt * BN;
+      const bool row_ok = r < p.M;
+      const long long row_off = static_cast<long long>(c.zhi) * p.d_zhi + static_cast<long long>(c.zlo) * p.d_zlo +
+                                static_cast<long long>(r / p.rdiv) * p.rs_hi + static_cast<long long>(r % p.rdiv) * p.rs_lo;
+      float rbias = 0.f;
+      if (p.bias_mode == 1 && row_ok) rbias = p.bias[r];
+      int buf = 0;
+      if (!c.skip) {
+        buf = acc_it & 1;
+        if (ok && !mbar_wait(tfull_bar(buf), (acc_it >> 1) & 1u)) {
+          atomicExch(p.err, 4);
+          ok = false;
+        }
+        tc_fence_after();
+      }
+      for (int cc = 0; cc < BN / 32; ++cc) {
+        const int nc = n0 + cc * 32;
+        if (nc >= p.N) break;       // uniform across the CTA
+        uint32_t v[32];
+        if (!c.skip) {
+          const uint32_t taddr = tmem_base + buf * BN + cc * 32 + (static_cast<uint32_t>(q * 32) << 16);
+          tmem_ld32(taddr, v);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0u;
+        }
+        if (!row_ok) continue;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int n = nc + g * 8;
+          if (n >= p.N) break;
+          float f[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[g * 8 + j]) * p.alpha;
+          if (p.bias_mode == 1) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] += rbias;
+          } else if (p.bias_mode == 2) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (n + j < p.N) f[j] += __ldg(p.bias + n + j);
+          }
+          const bool full = (n + 8 <= p.N);
+          const long long off = row_off + static_cast<long long>(n / p.ndiv) * p.ns_hi + (n % p.ndiv);
+          if (full && p.vec_ok && !p.accumulate) {
+            // ---- vector path: 8 consecutive columns
+            if (p.preact) {
+              if (p.out_f32) {
+                float4* o = reinterpret_cast<float4*>(static_cast<float*>(p.preact) + off);
+                o[0] = make_float4(f[0], f[1], f[2], f[3]);
+                o[1] = make_float4(f[4], f[5], f[6], f[7]);
+              } else {
+                __nv_bfloat162 h[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+                *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.preact) + off) = *reinterpret_cast<uint4*>(h);
+              }
+            }
+            if (p.act == 1) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) f[j] = gelu_erf(f[j]);
+            }
+            if (p.resid) {
+              if (p.out_f32) {
+                const float4* ri = reinterpret_cast<const float4*>(static_cast<const float*>(p.resid) + off);
+                const float4 a = ri[0], b = ri[1];
+                const float rr[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = (p.act == 2) ? f[j] * gelu_grad(rr[j]) : f[j] + rr[j];
+              } else {
+                const uint4 rv = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.resid) + off);
+                const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 x = __bfloat1622float2(rh[j]);
+                  f[2 * j] = (p.act == 2) ? f[2 * j] * gelu_grad(x.x) : f[2 * j] + x.x;
+                  f[2 * j + 1] = (p.act == 2) ? f[2 * j + 1] * gelu_grad(x.y) : f[2 * j + 1] + x.y;
+                }
+              }
+            }
+            if (p.out_f32) {
+              float4* o = reinterpret_cast<float4*>(static_cast<float*>(p.D) + off);
+              o[0] = make_float4(f[0], f[1], f[2], f[3]);
+              o[1] = make_float4(f[4], f[5], f[6], f[7]);
+            } else {
+              __nv_bfloat162 h[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+              *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.D) + off) = *reinterpret_cast<uint4*>(h);
+            }
+          } else {
+            // ---- scalar path (ragged edge, unaligned layouts, atomic accumulation)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int nj = n + j;
+              if (nj >= p.N) break;
+              const long long o = row_off + static_cast<long long>(nj / p.ndiv) * p.ns_hi + (nj % p.ndiv);
+              float x = f[j];
+              if (p.preact) {
+                if (p.out_f32) static_cast<float*>(p.preact)[o] = x;
+                else static_cast<__nv_bfloat16*>(p.preact)[o] = __float2bfloat16(x);
+              }
+              if (p.act == 1) x = gelu_erf(x);
+              if (p.accumulate) {
+                atomicAdd(static_cast<float*>(p.D) + o, x);
+              } else {
+                if (p.resid) {
+                  const float rr = p.out_f32 ? static_cast<const float*>(p.resid)[o]
+                                             : __bfloat162float(static_cast<const __nv_bfloat16*>(p.resid)[o]);
+                  x = (p.act == 2) ? x * gelu_grad(rr) : x + rr;
+                }
+                if (p.out_f32) static_cast<float*>(p.D)[o] = x;
+                else static_cast<__nv_bfloat16*>(p.D)[o] = __float2bfloat16(x);
+              }
+            }
+          }
+        }
+      }
+      (void)osz;
+      if (!c.skip) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(buf));
+        ++acc_it;
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+char g_err[512] = {0};
+
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* sym = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres);
+  if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || sym == nullptr) return nullptr;
+  fn = reinterpret_cast<EncodeTiledFn>(sym);
+  return fn;
+}
+
+bool make_map(CUtensorMap* map, const GemmOperand& op, int K, int eb, int zlo_n, int zhi_n, int box_rows_kmajor) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) {
+    snprintf(g_err, sizeof(g_err), "cuTensorMapEncodeTiled entry point not available");
+    return false;
+  }
+  const int bk = 128 / eb;
+  cuuint64_t dims[4];
+  cuuint64_t strides[3];
+  cuuint32_t box[4];
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  const bool use_lo = (op.zs_lo != 0) && zlo_n > 1;
+  const bool use_hi = (op.zs_hi != 0) && zhi_n > 1;
+  if (!op.mn_major) {
+    dims[0] = static_cast<cuuint64_t>(K);
+    dims[1] = static_cast<cuuint64_t>(op.rows);
+    box[0] = bk;
+    box[1] = box_rows_kmajor;
+  } else {
+    dims[0] = static_cast<cuuint64_t>(op.rows);
+    dims[1] = static_cast<cuuint64_t>(K);
+    box[0] = 128 / eb;
+    box[1] = bk;
+  }
+  dims[2] = use_lo ? zlo_n : 1;
+  dims[3] = use_hi ? zhi_n : 1;
+  box[2] = 1;
+  box[3] = 1;
+  strides[0] = static_cast<cuuint64_t>(op.ld) * eb;
+  strides[1] = use_lo ? static_cast<cuuint64_t>(op.zs_lo) * eb : strides[0];
+  strides[2] = use_hi ? static_cast<cuuint64_t>(op.zs_hi) * eb : strides[0];
+  if ((reinterpret_cast<uintptr_t>(op.ptr) & 15) || (strides[0] & 15) || (strides[1] & 15) || (strides[2] & 15)) {
+    snprintf(g_err, sizeof(g_err), "gemm operand not 16-byte aligned (ptr %p ld %lld zs %lld %lld)", op.ptr, op.ld,
+             op.zs_lo, op.zs_hi);
+    return false;
+  }
+  CUresult r = enc(map, eb == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4,
+                   const_cast<void*>(op.ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_err, sizeof(g_err),
+             "cuTensorMapEncodeTiled failed (%d): dims %llu %llu %llu %llu strides %llu %llu %llu box %u %u", (int)r,
+             (unsigned long long)dims[0], (unsigned long long)dims[1], (unsigned long long)dims[2],
+             (unsigned long long)dims[3], (unsigned long long)strides[0], (unsigned long long)strides[1],
+             (unsigned long long)strides[2], box[0], box[1]);
+    return false;
+  }
+  return true;
+}
+
+template <int BN, int EB>
+cudaError_t launch_t(const CUtensorMap& ma, const CUtensorMap& mb, const KParams& kp, cudaStream_t stream) {
+  constexpr int STAGES = (BN == 256) ? 4 : 6;
+  constexpr int SMEM = STAGES * (A_STAGE_BYTES + BN * 128) + 8 * (2 * STAGES + 4) + 16 + 1024;
+  static bool configured = false;
+  static int num_sms = 0;
+  if (!configured) {
+    cudaError_t e =
+        cudaFuncSetAttribute(gemm_kernel<BN, EB>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return e;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+    configured = true;
+  }
+  long long grid = kp.total_tiles < num_sms ? kp.total_tiles : num_sms;
+  if (grid < 1) grid = 1;
+  gemm_kernel<BN, EB><<<static_cast<unsigned>(grid), NUM_THREADS, SMEM, stream>>>(ma, mb, kp);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+const char* gemm_last_error() { return g_err; }
+
+cudaError_t gemm_launch(const GemmProblem& p, const GemmOperand& A, const GemmOperand& B, const GemmEpilogue& e,
+                        int* err_flag, cudaStream_t stream) {
+  g_err[0] = 0;
+  if (p.M <= 0 || p.N <= 0 || p.zlo_n <= 0 || p.zhi_n <= 0) return cudaSuccess;
+  const int eb = p.elem_bytes;
+  if (eb != 2 && eb != 4) {
+    snprintf(g_err, sizeof(g_err), "elem_bytes must be 2 or 4");
+    return cudaErrorInvalidValue;
+  }
+  int bn = p.bn;
+  if (bn == 0) bn = (p.N > 128) ? 256 : 128;
+  if (bn != 128 && bn != 256) {
+    snprintf(g_err, sizeof(g_err), "bn must be 128 or 256");
+    return cudaErrorInvalidValue;
+  }
+  if (p.splits > 1 && !e.accumulate) {
+    snprintf(g_err, sizeof(g_err), "split-k needs accumulate");
+    return cudaErrorInvalidValue;
+  }
+  if (e.accumulate && (!e.out_f32 || e.resid || e.preact)) {
+    snprintf(g_err, sizeof(g_err), "accumulate needs fp32 output without residual/preact");
+    return cudaErrorInvalidValue;
+  }
+  const int bk = 128 / eb;
+  KParams kp;
+  memset(&kp, 0, sizeof(kp));
+  kp.M = p.M; kp.N = p.N; kp.K = p.K;
+  kp.zlo_n = p.zlo_n; kp.zhi_n = p.zhi_n;
+  kp.splits = p.splits < 1 ? 1 : p.splits;
+  const int kblocks = (p.K + bk - 1) / bk;
+  kp.k_per_split = ((kblocks + kp.splits - 1) / kp.splits) * bk;
+  if (kp.k_per_split < bk) kp.k_per_split = bk;
+  kp.a_mn = A.mn_major; kp.b_mn = B.mn_major;
+  kp.a_zlo = (A.zs_lo != 0 && p.zlo_n > 1); kp.a_zhi = (A.zs_hi != 0 && p.zhi_n > 1);
+  kp.b_zlo = (B.zs_lo != 0 && p.zlo_n > 1); kp.b_zhi = (B.zs_hi != 0 && p.zhi_n > 1);
+  kp.rmin_a = p.rmin_a; kp.rmin_b = p.rmin_b; kp.rmax_a = p.rmax_a; kp.rmax_b = p.rmax_b;
+  kp.kmin_a = p.kmin_a; kp.kmin_b = p.kmin_b; kp.kmax_a = p.kmax_a; kp.kmax_b = p.kmax_b;
+  kp.d_zlo = e.d_zlo; kp.d_zhi = e.d_zhi;
+  kp.rdiv = e.rdiv > 0 ? e.rdiv : 1 << 30; kp.rs_hi = e.rs_hi; kp.rs_lo = e.rs_lo;
+  kp.ndiv = e.ndiv > 0 ? e.ndiv : 1 << 30; kp.ns_hi = e.ns_hi;
+  kp.alpha = e.alpha; kp.bias = e.bias; kp.bias_mode = e.bias ? e.bias_mode : 0; kp.act = e.act;
+  kp.resid = e.resid; kp.preact = e.preact; kp.D = e.D;
+  kp.out_f32 = e.out_f32; kp.accumulate = e.accumulate;
+  const int va = e.out_f32 ? 4 : 8;   // elements per 16 bytes
+  auto al = [&](long long s) { return (s % va) == 0; };
+  const size_t osz = e.out_f32 ? 4 : 2;
+  bool vec = al(e.d_zlo) && al(e.d_zhi) && al(e.rs_hi) && al(e.rs_lo) && al(e.ns_hi) && (kp.ndiv % 8 == 0) &&
+             ((reinterpret_cast<uintptr_t>(e.D) & 15) == 0);
+  if (e.resid) vec = vec && ((reinterpret_cast<uintptr_t>(e.resid) & 15) == 0);
+  if (e.preact) vec = vec && ((reinterpret_cast<uintptr_t>(e.preact) & 15) == 0);
+  (void)osz;
+  kp.vec_ok = vec ? 1 : 0;
+  kp.m_tiles = (p.M + BM - 1) / BM;
+  kp.n_tiles = (p.N + bn - 1) / bn;
+  kp.total_tiles = static_cast<long long>(kp.m_tiles) * kp.n_tiles * kp.splits * p.zlo_n * p.zhi_n;
+  kp.err = err_flag;
+
+  CUtensorMap ma, mb;
+  if (!make_map(&ma, A, p.K, eb, p.zlo_n, p.zhi_n, BM)) return cudaErrorInvalidValue;
+  if (!make_map(&mb, B, p.K, eb, p.zlo_n, p.zhi_n, bn)) return cudaErrorInvalidValue;
+
+  if (eb == 2) {
+    if (bn == 256) return launch_t<256, 2>(ma, mb, kp, stream);
+    return launch_t<128, 2>(ma, mb, kp, stream);
+  } else {
+    if (bn == 256) return launch_t<256, 4>(ma, mb, kp, stream);
+    return launch_t<128, 4>(ma, mb, kp, stream);
+  }
+}
+
+}  // namespace mk

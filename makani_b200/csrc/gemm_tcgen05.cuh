@@ -1,0 +1,67 @@
+// Declarations for the sm_100a tensor-core GEMM engine (tcgen05 + TMEM + TMA).
+//
+// One persistent, warp-specialised kernel computes, for every batch index z = z_hi * zlo_n + z_lo,
+//
+//     D_z[r, n] = epilogue( alpha * sum_k A_z[r, k] * B_z[n, k] )
+//
+// A is (M x K), B is (N x K); either operand may be K-major (k contiguous) or MN-major (row index
+// contiguous).  Operands are bf16 (kind::f16) or fp32 read as tf32 (kind::tf32); accumulation is fp32
+// in tensor memory.  The destination is addressed with split strides so that a tile can be scattered
+// straight into the layout the next transform stage wants:
+//
+//     addr(z, r, n) = D + z_hi*d_zhi + z_lo*d_zlo + (r / rdiv)*rs_hi + (r % rdiv)*rs_lo
+//                       + (n / ndiv)*ns_hi + (n % ndiv)            (n is contiguous)
+//
+// "Triangular" structure (associated Legendre functions vanish for l < m) is expressed as affine
+// functions of z_hi: rows outside [rmin, rmax) are known to be zero (tiles entirely outside are
+// written as zeros without touching the tensor cores) and the k-loop is restricted to [kmin, kmax).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mk {
+
+struct GemmOperand {
+  const void* ptr;      // 16-byte aligned base
+  int rows;             // M (for A) or N (for B)
+  int mn_major;         // 0: k contiguous, 1: row index contiguous
+  long long ld;         // stride in elements of the non-contiguous dimension (multiple of 16 bytes)
+  long long zs_lo;      // batch strides in elements (0 = operand shared across that batch index)
+  long long zs_hi;
+};
+
+struct GemmEpilogue {
+  void* D;
+  int out_f32;          // 0: bf16 output, 1: fp32 output
+  int accumulate;       // 1: atomically add into fp32 D (used by split-k / batch-reduced weight gradients)
+  long long d_zlo, d_zhi;
+  int rdiv; long long rs_hi, rs_lo;
+  int ndiv; long long ns_hi;
+  float alpha;
+  const float* bias;    // fp32, may be null
+  int bias_mode;        // 1: per row r, 2: per column n
+  int act;              // 0: none, 1: exact (erf) GELU, 2: multiply by GELU'(resid) (backward through a GELU)
+  const void* resid;    // optional tensor added after the activation (act 0/1) or the saved pre-activation
+                        // (act 2); same addressing and dtype as D
+  // optional second output: the pre-activation value (alpha*acc + bias) in the same layout / dtype
+  void* preact;
+};
+
+struct GemmProblem {
+  int M, N, K;
+  int zlo_n, zhi_n;
+  int elem_bytes;       // 2: bf16, 4: tf32
+  int splits;           // split-k factor (requires accumulate)
+  int rmin_a, rmin_b, rmax_a, rmax_b;   // valid rows [rmin_a*z_hi+rmin_b, rmax_a*z_hi+rmax_b)
+  int kmin_a, kmin_b, kmax_a, kmax_b;   // contributing k range
+  int bn;               // tile width: 128 or 256 (0 = choose)
+};
+
+// Returns cudaSuccess or an error; never throws.  `err_flag` is a device int that the kernel sets to a
+// non-zero code when a bounded barrier wait runs out (the launch still terminates).
+cudaError_t gemm_launch(const GemmProblem& p, const GemmOperand& A, const GemmOperand& B,
+                        const GemmEpilogue& e, int* err_flag, cudaStream_t stream);
+
+const char* gemm_last_error();
+
+}  // namespace mk

@@ -1,0 +1,102 @@
+"""Loader for the in-tree sm_100a extension (`makani_b200/csrc/_C.so`).
+
+The extension is built by `python -m makani_b200.csrc.build` (or `__graft_entry__.build()`); it is never
+JIT-compiled at import time.  `require()` raises with build instructions when a CUDA tensor reaches an op
+and the extension cannot be loaded, so that a GPU run can never silently fall back to eager PyTorch.
+"""
+
+from __future__ import annotations
+
+import importlib.util
+import os
+import threading
+
+_LOCK = threading.Lock()
+_MOD = None
+_ERR = None
+
+SO_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc", "_C.so")
+
+
+def _load():
+    global _MOD, _ERR
+    with _LOCK:
+        if _MOD is not None or _ERR is not None:
+            return
+        try:
+            import torch  # noqa: F401  (libtorch must be loaded before the extension)
+
+            if not os.path.exists(SO_PATH):
+                raise FileNotFoundError(f"{SO_PATH} not built")
+            spec = importlib.util.spec_from_file_location("makani_b200.csrc._C", SO_PATH)
+            mod = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(mod)
+            _MOD = mod
+        except Exception as e:  # pragma: no cover - depends on the machine
+            _ERR = e
+
+
+def available() -> bool:
+    _load()
+    return _MOD is not None
+
+
+# number of kernels of this extension launched by the current process (each binding call launches exactly one)
+LAUNCHES = 0
+_NON_KERNEL = {"read_error_flag", "clear_error_flag", "lp_scratch_floats", "adam_entry_bytes", "peer_alloc", "peer_open",
+               "peer_close", "peer_free", "tensor_from_ptr"}
+
+
+class _Counting:
+    """Thin proxy over the extension module that counts kernel launches."""
+
+    def __init__(self, mod):
+        self._mod = mod
+        self._cache = {}
+
+    def __getattr__(self, name):
+        fn = self._cache.get(name)
+        if fn is None:
+            raw = getattr(self._mod, name)
+            if name in _NON_KERNEL:
+                fn = raw
+            else:
+                def fn(*args, __raw=raw, **kwargs):
+                    global LAUNCHES
+                    LAUNCHES += 1
+                    return __raw(*args, **kwargs)
+            self._cache[name] = fn
+        return fn
+
+
+_PROXY = None
+
+
+def require():
+    global _PROXY
+    _load()
+    if _MOD is None:
+        raise RuntimeError(
+            "makani_b200: the sm_100a extension is not available "
+            f"({_ERR!r}). Build it with `python -m makani_b200.csrc.build`."
+        )
+    if _PROXY is None:
+        _PROXY = _Counting(_MOD)
+    return _PROXY
+
+
+def launch_count() -> int:
+    return LAUNCHES
+
+
+def check_device_errors(device=None) -> None:
+    """Raise if a kernel recorded an expired bounded wait on `device` (synchronises)."""
+    import torch
+
+    if _MOD is None or not torch.cuda.is_available():
+        return
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index or 0
+    code = _MOD.read_error_flag(int(dev))
+    if code != 0:
+        _MOD.clear_error_flag(int(dev))
+        raise RuntimeError(f"makani_b200: a device-side bounded wait expired (code {code})")

@@ -1,0 +1,154 @@
+"""Generic batched GEMM with fused epilogue: the Python face of `csrc/gemm_tcgen05.cu`.
+
+    D_z[r, n] = epilogue(alpha * sum_k A_z[r, k] * B_z[n, k]),      z = z_hi * zlo_n + z_lo
+
+Operands are *views into flat storages* described by strides (in elements), so one kernel serves the 1x1
+convolutions, the longitude DFTs, the per-order Legendre contractions and the per-degree complex spectral
+contraction without any intermediate transposes.  On CUDA tensors the tcgen05 kernel runs; on CPU tensors a
+bit-faithful emulation of the same addressing is used, so that the layout choreography of every caller
+is testable without a GPU.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+
+from . import _ext
+
+ACT_NONE, ACT_GELU, ACT_DGELU = 0, 1, 2
+BIAS_NONE, BIAS_ROW, BIAS_COL = 0, 1, 2
+_BIG = 1 << 30
+
+
+@dataclass
+class Operand:
+    """A (rows x K) matrix batch inside `tensor`'s storage.
+
+    mn_major=False: element (row, k) at offset + row*ld + k         (k contiguous)
+    mn_major=True : element (row, k) at offset + k*ld + row         (row contiguous)
+    plus z_lo*zs_lo + z_hi*zs_hi for the batch index.
+    """
+
+    tensor: torch.Tensor
+    ld: int
+    mn_major: bool = False
+    offset: int = 0
+    zs_lo: int = 0
+    zs_hi: int = 0
+
+
+@dataclass
+class Output:
+    """Destination addressing: offset + z_hi*d_zhi + z_lo*d_zlo + (r//rdiv)*rs_hi + (r%rdiv)*rs_lo + (n//ndiv)*ns_hi + n%ndiv."""
+
+    tensor: torch.Tensor
+    rs_lo: int
+    offset: int = 0
+    rdiv: int = _BIG
+    rs_hi: int = 0
+    ndiv: int = _BIG
+    ns_hi: int = 0
+    d_zlo: int = 0
+    d_zhi: int = 0
+
+
+@dataclass
+class Tri:
+    """Known-zero structure as affine functions of z_hi: valid rows [rmin, rmax), contributing k in [kmin, kmax)."""
+
+    rmin_a: int = 0
+    rmin_b: int = 0
+    rmax_a: int = 0
+    rmax_b: int = _BIG
+    kmin_a: int = 0
+    kmin_b: int = 0
+    kmax_a: int = 0
+    kmax_b: int = _BIG
+
+
+def _flat(t: torch.Tensor) -> torch.Tensor:
+    """1-D view over the whole storage extent used by `t` (t must be non-overlapping and dense or a slice)."""
+    if t.is_contiguous():
+        return t.view(-1)
+    # generic: view the underlying storage from the tensor's storage offset onward
+    n = t.untyped_storage().nbytes() // t.element_size() - t.storage_offset()
+    return t.as_strided((n,), (1,))
+
+
+def _emulate(M, N, K, A: Operand, B: Operand, D: Output, zlo_n, zhi_n, alpha, bias, bias_mode, act, resid, resid_offset,
+             preact, preact_offset, accumulate, tri: Tri):
+    fa, fb, fd = _flat(A.tensor), _flat(B.tensor), _flat(D.tensor)
+    cdt = torch.float64 if fa.dtype == torch.float64 else torch.float32
+
+    def view(op: Operand, flat, rows):
+        rs, ks = (1, op.ld) if op.mn_major else (op.ld, 1)
+        return flat[op.offset:].as_strided((zhi_n, zlo_n, rows, K), (op.zs_hi, op.zs_lo, rs, ks)).to(cdt)
+
+    a = view(A, fa, M)
+    b = view(B, fb, N)
+    dev = fa.device
+    zh = torch.arange(zhi_n, device=dev).view(-1, 1, 1, 1)
+    r = torch.arange(M, device=dev).view(1, 1, -1, 1)
+    k = torch.arange(K, device=dev).view(1, 1, 1, -1)
+    kmask = (k >= tri.kmin_a * zh + tri.kmin_b) & (k < tri.kmax_a * zh + tri.kmax_b)
+    a = a * kmask.to(cdt)
+    acc = torch.matmul(a, b.transpose(-1, -2))  # [zh, zl, M, N]
+    rmask = (r >= tri.rmin_a * zh + tri.rmin_b) & (r < tri.rmax_a * zh + tri.rmax_b)
+    acc = acc * rmask.to(cdt)
+    acc = acc * alpha
+    if bias is not None and bias_mode == BIAS_ROW:
+        acc = acc + bias.to(cdt).view(1, 1, -1, 1)[:, :, :M]
+    elif bias is not None and bias_mode == BIAS_COL:
+        acc = acc + bias.to(cdt).view(1, 1, 1, -1)[..., :N]
+    zl = torch.arange(zlo_n, device=dev).view(1, -1, 1, 1)
+    n = torch.arange(N, device=dev).view(1, 1, 1, -1)
+    idx = (D.offset + zh * D.d_zhi + zl * D.d_zlo + (r // D.rdiv) * D.rs_hi + (r % D.rdiv) * D.rs_lo
+           + (n // D.ndiv) * D.ns_hi + (n % D.ndiv))
+    idx = idx.expand(zhi_n, zlo_n, M, N).reshape(-1)
+    if preact is not None:
+        _flat(preact).index_put_((idx - D.offset + preact_offset,), acc.reshape(-1).to(preact.dtype))
+    if act == ACT_GELU:
+        acc = torch.nn.functional.gelu(acc)
+    if resid is not None:
+        rv = _flat(resid)[idx - D.offset + resid_offset].to(cdt).view_as(acc)
+        if act == ACT_DGELU:
+            x = rv
+            cdf = 0.5 * (1.0 + torch.erf(x * 0.7071067811865476))
+            pdf = torch.exp(-0.5 * x * x) * 0.3989422804014327
+            acc = acc * (cdf + x * pdf)
+        else:
+            acc = acc + rv
+    vals = acc.reshape(-1).to(fd.dtype)
+    if accumulate:
+        fd.index_add_(0, idx, vals)
+    else:
+        fd.index_put_((idx,), vals)
+
+
+def gemm(M: int, N: int, K: int, A: Operand, B: Operand, D: Output, *, zlo_n: int = 1, zhi_n: int = 1, alpha: float = 1.0,
+         bias: Optional[torch.Tensor] = None, bias_mode: int = BIAS_NONE, act: int = ACT_NONE,
+         resid: Optional[torch.Tensor] = None, resid_offset: int = 0, preact: Optional[torch.Tensor] = None,
+         preact_offset: int = 0, accumulate: bool = False, splits: int = 1, tri: Optional[Tri] = None, bn: int = 0) -> None:
+    """Run the batched GEMM described above, writing into `D.tensor` in place."""
+    tri = tri or Tri()
+    if bias is None:
+        bias_mode = BIAS_NONE
+    if not A.tensor.is_cuda:
+        _emulate(M, N, K, A, B, D, zlo_n, zhi_n, alpha, bias, bias_mode, act, resid, resid_offset, preact, preact_offset,
+                 accumulate, tri)
+        return
+    ext = _ext.require()
+    ip = [M, N, K, zlo_n, zhi_n, splits, bn,
+          tri.rmin_a, tri.rmin_b, tri.rmax_a, tri.rmax_b, tri.kmin_a, tri.kmin_b, tri.kmax_a, tri.kmax_b,
+          A.offset, int(A.mn_major), A.ld, A.zs_lo, A.zs_hi,
+          B.offset, int(B.mn_major), B.ld, B.zs_lo, B.zs_hi,
+          D.offset, int(accumulate), D.d_zlo, D.d_zhi, D.rdiv, D.rs_hi, D.rs_lo, D.ndiv, D.ns_hi,
+          bias_mode, act, resid_offset, preact_offset, 0, 0]
+    ext.gemm(A.tensor, B.tensor, D.tensor, bias, resid, preact, ip, float(alpha))
+
+
+def pad_to(n: int, m: int) -> int:
+    return (n + m - 1) // m * m

@@ -1,0 +1,137 @@
+"""Fused multi-tensor Adam / AdamW: one kernel launch updates every parameter, its two moments and
+(optionally) a bf16 shadow copy, reading the hyper-parameters from device memory so that the launch can be
+replayed from a CUDA graph while the learning rate and step count change.
+
+Complex parameters are stored as complex64 and updated through their interleaved real view.  Two second-moment
+conventions exist in the reference's patched optimisers (makani/third_party/torch/optim/adam.py:391 uses
+g * conj(g), adamw.py:409 squares the complex number); `complex_mode="modulus"` (default) shares |g|^2 between
+the real and imaginary parts, `complex_mode="split"` treats them as independent reals (stock PyTorch).
+"""
+
+from __future__ import annotations
+
+import math
+import struct
+from typing import Iterable, List, Optional
+
+import torch
+
+from . import _ext
+
+_CHUNK = 1 << 16
+
+
+class FusedAdamW(torch.optim.Optimizer):
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, adamw: bool = True,
+                 complex_mode: str = "modulus", grad_scale: float = 1.0):
+        defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
+        super().__init__(params, defaults)
+        self.adamw = adamw
+        self.complex_mode = complex_mode
+        self.grad_scale = grad_scale
+        self._tables = {}
+        self._step_count = 0
+
+    # ---- state helpers -------------------------------------------------------------------------------
+    def _init_state(self, p):
+        st = self.state[p]
+        if len(st) == 0:
+            st["step"] = torch.zeros((), dtype=torch.float32)
+            st["exp_avg"] = torch.zeros_like(p, memory_format=torch.preserve_format)
+            st["exp_avg_sq"] = torch.zeros_like(p, memory_format=torch.preserve_format)
+        return st
+
+    @staticmethod
+    def _real(t):
+        return torch.view_as_real(t) if t.is_complex() else t
+
+    def _build_table(self, gi, group, plist):
+        ext = _ext.require()
+        dev = plist[0].device
+        rows, chunk_tensor, chunk_off = [], [], []
+        for ti, p in enumerate(plist):
+            st = self._init_state(p)
+            pr, gr = self._real(p.data), self._real(p.grad)
+            m, v = self._real(st["exp_avg"]), self._real(st["exp_avg_sq"])
+            assert pr.is_contiguous() and gr.is_contiguous(), "fused AdamW needs contiguous params and grads"
+            n = pr.numel()
+            pair = 1 if (p.is_complex() and self.complex_mode == "modulus") else 0
+            wd_scale = 0.0 if getattr(p, "_no_weight_decay", False) else 1.0
+            packed = struct.unpack("<q", struct.pack("<fi", wd_scale, pair))[0]
+            shadow = getattr(p, "_bf16_shadow", None)
+            rows.append([pr.data_ptr(), gr.data_ptr(), m.data_ptr(), v.data_ptr(),
+                         shadow.data_ptr() if shadow is not None else 0, n, packed])
+            for off in range(0, n, _CHUNK):
+                chunk_tensor.append(ti)
+                chunk_off.append(off)
+        assert ext.adam_entry_bytes() == 56
+        table = torch.tensor(rows, dtype=torch.int64, device=dev)
+        ct = torch.tensor(chunk_tensor, dtype=torch.int32, device=dev)
+        co = torch.tensor(chunk_off, dtype=torch.int64, device=dev)
+        hyper = torch.zeros(8, dtype=torch.float32, device=dev)
+        sig = tuple((p.data_ptr(), p.grad.data_ptr()) for p in plist)
+        return dict(table=table, ct=ct, co=co, hyper=hyper, sig=sig)
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        self._step_count += 1
+        for gi, group in enumerate(self.param_groups):
+            plist = [p for p in group["params"] if p.grad is not None]
+            if not plist:
+                continue
+            if plist[0].is_cuda:
+                self._step_cuda(gi, group, plist)
+            else:
+                self._step_torch(group, plist)
+        return loss
+
+    def _step_cuda(self, gi, group, plist):
+        ext = _ext.require()
+        sig = tuple((p.data_ptr(), p.grad.data_ptr()) for p in plist)
+        tb = self._tables.get(gi)
+        if tb is None or tb["sig"] != sig:
+            tb = self._build_table(gi, group, plist)
+            self._tables[gi] = tb
+        for p in plist:
+            self.state[p]["step"] += 1
+        step = float(self.state[plist[0]]["step"])
+        b1, b2 = group["betas"]
+        h = torch.tensor([group["lr"], b1, b2, group["eps"], group["weight_decay"], step, self.grad_scale,
+                          1.0 if self.adamw else 0.0], dtype=torch.float32).pin_memory()
+        tb["hyper"].copy_(h, non_blocking=True)
+        ext.adamw_step(tb["table"], tb["ct"], tb["co"], _CHUNK, tb["hyper"])
+
+    def _step_torch(self, group, plist):
+        b1, b2 = group["betas"]
+        lr, eps, wd = group["lr"], group["eps"], group["weight_decay"]
+        for p in plist:
+            st = self._init_state(p)
+            st["step"] += 1
+            step = float(st["step"])
+            g = p.grad * self.grad_scale
+            wdp = 0.0 if getattr(p, "_no_weight_decay", False) else wd
+            if self.adamw:
+                p.mul_(1.0 - lr * wdp)
+            else:
+                g = g + wdp * p
+            m, v = st["exp_avg"], st["exp_avg_sq"]
+            m.mul_(b1).add_(g, alpha=1.0 - b1)
+            if p.is_complex():
+                if self.complex_mode == "modulus":
+                    g2 = (g * g.conj()).real
+                    vr = torch.view_as_real(v)
+                    vr.mul_(b2).add_(torch.stack([g2, g2], dim=-1), alpha=1.0 - b2)
+                else:
+                    gr = torch.view_as_real(g)
+                    torch.view_as_real(v).mul_(b2).add_(gr * gr, alpha=1.0 - b2)
+                denom = torch.view_as_real(v).sqrt() / math.sqrt(1.0 - b2 ** step) + eps
+                upd = torch.view_as_real(m) / denom
+                torch.view_as_real(p).add_(upd, alpha=-lr / (1.0 - b1 ** step))
+            else:
+                v.mul_(b2).addcmul_(g, g, value=1.0 - b2)
+                denom = v.sqrt() / math.sqrt(1.0 - b2 ** step) + eps
+                p.addcdiv_(m, denom, value=-lr / (1.0 - b1 ** step))

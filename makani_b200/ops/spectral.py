@@ -1,0 +1,270 @@
+"""Spherical-harmonic spectral convolution as a chain of tensor-core GEMMs.
+
+The reference computes `x -> SHT -> per-degree complex contraction -> inverse SHT` with cuFFT plus cuBLAS
+einsums in fp32 (makani/models/common/spectral_convolution.py:124-148, contractions.py:130-136, and the
+torch-harmonics RealSHT/InverseRealSHT it imports).  Here every stage is one launch of the batched GEMM
+engine, and each stage writes its result directly in the layout the next one reads, so no transpose or
+truncation pass ever touches HBM:
+
+    x  [B, C, H, W]                  real grid data (bf16)
+    S1 longitude DFT      -> T1 [B, m, ri, C, Hp]       A = DFT matrix [(m,ri), W]
+    S2 Legendre analysis  -> T2 [B, l, m, (ri, C)]      A = P_l^m(theta_k) w_k, batched over m, rows l < m skipped
+    S3 complex contraction-> T3 [B, m, l, (ri, Co)]     B = W_l as a real 2x2-block matrix, batched over l, rows m > l skipped
+    S4 Legendre synthesis -> T4 [B, m, ri, Co, Hp']     k-loop restricted to l >= m
+    S5 inverse DFT        -> y  [B, Co, H', W']
+
+(ri = real/imaginary part, Hp = H padded to a multiple of 8 elements for 16-byte TMA strides.)
+The adjoints used by the backward pass are the same five launches with the constant operands read in the
+other major (no transposed copies of the tables are stored).
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional, Tuple
+
+import numpy as np
+import torch
+
+from ..sht.legendre import legendre_table
+from ..sht.quadrature import precompute_latitudes
+from . import _ext
+from .gemm import Operand, Output, Tri, gemm, pad_to
+
+
+class SHTPlan:
+    """Constant operands (DFT matrices, Legendre tables) for one (nlat, nlon, lmax, mmax, grid) transform pair."""
+
+    _cache: Dict[Tuple, "SHTPlan"] = {}
+
+    def __init__(self, nlat: int, nlon: int, lmax: int, mmax: int, grid: str, device, dtype=torch.bfloat16):
+        self.nlat, self.nlon, self.lmax, self.mmax, self.grid = nlat, nlon, lmax, mmax, grid
+        self.device, self.dtype = torch.device(device), dtype
+        self.hp = pad_to(nlat, 8)          # padded latitude extent of T1/T4 rows and of the tables
+        self.k2 = 2 * mmax                 # DFT K extent (m, ri)
+        self.k2p = pad_to(self.k2, 8)
+        theta, wq = precompute_latitudes(nlat, grid)
+        self.theta, self.wq = theta, wq
+        p = legendre_table(mmax, lmax, theta)                     # [m, l, k] float64
+        pw = p * wq[None, None, :]
+        tab = np.zeros((2, mmax, lmax, self.hp), dtype=np.float32)
+        tab[0, :, :, :nlat] = pw
+        tab[1, :, :, :nlat] = p
+        self.pw = torch.from_numpy(tab[0]).to(self.device, dtype).contiguous()   # analysis table (weighted)
+        self.p = torch.from_numpy(tab[1]).to(self.device, dtype).contiguous()    # synthesis table
+        # forward DFT rows (m, ri) ordered as ri-major: row = ri*mmax... no: row index j = 2*m + ri
+        phi = 2.0 * np.pi * np.arange(nlon) / nlon
+        m = np.arange(mmax)[:, None]
+        ang = m * phi[None, :]
+        f = np.zeros((self.k2, nlon), dtype=np.float64)
+        f[0::2] = np.cos(ang) * (2.0 * np.pi / nlon)
+        f[1::2] = -np.sin(ang) * (2.0 * np.pi / nlon)
+        self.f = torch.from_numpy(f.astype(np.float32)).to(self.device, dtype).contiguous()      # [(m,ri), W]
+        # inverse DFT: x_i = sum_m c_m (Xr cos - Xi sin); c_0 = 1, c_m = 2, Nyquist (if kept) = 1
+        cm = np.full((mmax, 1), 2.0)
+        cm[0] = 1.0
+        if nlon % 2 == 0 and mmax > nlon // 2:
+            cm[nlon // 2] = 1.0
+        g = np.zeros((nlon, self.k2p), dtype=np.float64)
+        g[:, 0:self.k2:2] = (cm * np.cos(ang)).T
+        g[:, 1:self.k2:2] = (-cm * np.sin(ang)).T
+        self.gt = torch.from_numpy(g.astype(np.float32)).to(self.device, dtype).contiguous()     # [W, (m,ri) padded]
+
+    @classmethod
+    def get(cls, nlat, nlon, lmax, mmax, grid, device, dtype=torch.bfloat16) -> "SHTPlan":
+        key = (nlat, nlon, lmax, mmax, grid, str(torch.device(device)), dtype)
+        plan = cls._cache.get(key)
+        if plan is None:
+            plan = cls(nlat, nlon, lmax, mmax, grid, device, dtype)
+            cls._cache[key] = plan
+        return plan
+
+
+# ------------------------------------------------------------------------------------------------ stages
+# Row index of the DFT side is j = 2*m + ri, which makes T1/T4 [B, (m,ri), C, Hp] contiguous in j.
+
+
+def dft_analysis(x: torch.Tensor, mat: torch.Tensor, mat_mn: bool, mat_ld: int, k2: int, hp: int) -> torch.Tensor:
+    """T1[b, j, c, k] = sum_i M[j, i] x[b, c, k, i];  M given K-major ([j, i]) or MN-major ([i, j])."""
+    B, C, H, W = x.shape
+    t1 = torch.empty(B, k2, C, hp, dtype=x.dtype, device=x.device)
+    gemm(k2, H, W,
+         Operand(mat, ld=mat_ld, mn_major=mat_mn),
+         Operand(x, ld=W, zs_lo=H * W, zs_hi=C * H * W),
+         Output(t1, rs_lo=C * hp, d_zlo=hp, d_zhi=k2 * C * hp),
+         zlo_n=C, zhi_n=B)
+    return t1
+
+
+def dft_synthesis(t4: torch.Tensor, mat: torch.Tensor, mat_mn: bool, mat_ld: int, H: int, W: int) -> torch.Tensor:
+    """y[b, c, k, i] = sum_j T4[b, j, c, k] M[i, j];  M given K-major ([i, j]) or MN-major ([j, i])."""
+    B, k2, C, hp = t4.shape
+    y = torch.empty(B, C, H, W, dtype=t4.dtype, device=t4.device)
+    gemm(H, W, k2,
+         Operand(t4, ld=C * hp, mn_major=True, zs_lo=hp, zs_hi=k2 * C * hp),
+         Operand(mat, ld=mat_ld, mn_major=mat_mn),
+         Output(y, rs_lo=W, d_zlo=H * W, d_zhi=C * H * W),
+         zlo_n=C, zhi_n=B)
+    return y
+
+
+def legendre_analysis(t1: torch.Tensor, table: torch.Tensor, H: int) -> torch.Tensor:
+    """T2[b, l, m, n] = sum_k table[m, l, k] T1[b, m, n, k], n = (ri, c);  zero for l < m."""
+    B, k2, C, hp = t1.shape
+    mmax, lmax, hpt = table.shape
+    n2 = 2 * C
+    t2 = torch.empty(B, lmax, mmax, n2, dtype=t1.dtype, device=t1.device)
+    gemm(lmax, n2, H,
+         Operand(table, ld=hpt, zs_hi=lmax * hpt),
+         Operand(t1, ld=hp, zs_hi=n2 * hp, zs_lo=k2 * C * hp),
+         Output(t2, rs_lo=mmax * n2, d_zhi=n2, d_zlo=lmax * mmax * n2),
+         zhi_n=mmax, zlo_n=B, tri=Tri(rmin_a=1))
+    return t2
+
+
+def legendre_synthesis(t: torch.Tensor, lm_order: bool, table: torch.Tensor, H: int) -> torch.Tensor:
+    """T4[b, m, n, k] = sum_l T[b, ., ., n] table[m, l, k]  with T given as [b, m, l, n] (lm_order False)
+    or [b, l, m, n] (lm_order True); only l >= m contributes."""
+    if lm_order:
+        B, lmax, mmax, n2 = t.shape
+        ld, zs_m = mmax * n2, n2
+    else:
+        B, mmax, lmax, n2 = t.shape
+        ld, zs_m = n2, lmax * n2
+    hpt = table.shape[2]
+    hp = pad_to(H, 8)
+    t4 = torch.empty(B, mmax, n2, hp, dtype=t.dtype, device=t.device).view(B, 2 * mmax, n2 // 2, hp)
+    gemm(n2, H, lmax,
+         Operand(t, ld=ld, mn_major=True, zs_hi=zs_m, zs_lo=lmax * mmax * n2),
+         Operand(table, ld=hpt, mn_major=True, zs_hi=lmax * hpt),
+         Output(t4, rs_lo=hp, d_zhi=n2 * hp, d_zlo=mmax * n2 * hp),
+         zhi_n=mmax, zlo_n=B, tri=Tri(kmin_a=1))
+    return t4
+
+
+def contract(t2: torch.Tensor, wx: torch.Tensor, transpose_w: bool) -> torch.Tensor:
+    """T3[b, m, l, q] = sum_p T2[b, l, m, p] Wx[l, q, p]   (transpose_w False; Wx [l, 2Co, 2Ci])
+       T3[b, m, l, p] = sum_q T2[b, l, m, q] Wx[l, q, p]   (transpose_w True: adjoint w.r.t. the input)."""
+    B, lmax, mmax, kin = t2.shape
+    nq, npp = wx.shape[1], wx.shape[2]
+    nout = npp if transpose_w else nq
+    t3 = torch.empty(B, mmax, lmax, nout, dtype=t2.dtype, device=t2.device)
+    gemm(mmax, nout, kin,
+         Operand(t2, ld=kin, zs_hi=mmax * kin, zs_lo=lmax * mmax * kin),
+         Operand(wx, ld=npp, mn_major=transpose_w, zs_hi=nq * npp),
+         Output(t3, rs_lo=lmax * nout, d_zhi=nout, d_zlo=mmax * lmax * nout),
+         zhi_n=lmax, zlo_n=B, tri=Tri(rmax_a=1, rmax_b=1))
+    return t3
+
+
+def contract_wgrad(dt: torch.Tensor, t2: torch.Tensor) -> torch.Tensor:
+    """dWx[l, q, p] = sum_{b, m<=l} dT[b, l, m, q] T2[b, l, m, p]  (fp32)."""
+    B, lmax, mmax, nq = dt.shape
+    npp = t2.shape[3]
+    if B == 1:
+        dwx = torch.empty(lmax, nq, npp, dtype=torch.float32, device=dt.device)
+    else:
+        dwx = torch.zeros(lmax, nq, npp, dtype=torch.float32, device=dt.device)
+    gemm(nq, npp, mmax,
+         Operand(dt, ld=nq, mn_major=True, zs_hi=mmax * nq, zs_lo=lmax * mmax * nq),
+         Operand(t2, ld=npp, mn_major=True, zs_hi=mmax * npp, zs_lo=lmax * mmax * npp),
+         Output(dwx, rs_lo=npp, d_zhi=nq * npp),
+         zhi_n=lmax, zlo_n=B, accumulate=(B > 1), tri=Tri(kmax_a=1, kmax_b=1))
+    return dwx
+
+
+# ------------------------------------------------------------------------------------------------ weights
+
+
+def expand_weight(w: torch.Tensor, dtype=torch.bfloat16) -> torch.Tensor:
+    """complex [Ci, Co, L] -> real [L, 2Co, 2Ci] with rows (ri', o), columns (ri, c):  [[Wr, -Wi], [Wi, Wr]]."""
+    ci, co, L = w.shape
+    if w.is_cuda and dtype == torch.bfloat16:
+        wx = torch.empty(L, 2 * co, 2 * ci, dtype=dtype, device=w.device)
+        _ext.require().spectral_expand(w.detach().contiguous(), wx)
+        return wx
+    wr = w.real.permute(2, 1, 0)
+    wi = w.imag.permute(2, 1, 0)
+    top = torch.cat([wr, -wi], dim=2)
+    bot = torch.cat([wi, wr], dim=2)
+    return torch.cat([top, bot], dim=1).to(dtype).contiguous()
+
+
+def fold_weight_grad(dwx: torch.Tensor) -> torch.Tensor:
+    """fp32 [L, 2Co, 2Ci] -> complex64 [Ci, Co, L] gradient (dWr = d00 + d11, dWi = d10 - d01)."""
+    L, co2, ci2 = dwx.shape
+    co, ci = co2 // 2, ci2 // 2
+    if dwx.is_cuda:
+        dw = torch.zeros(ci, co, L, dtype=torch.complex64, device=dwx.device)
+        _ext.require().spectral_fold(dwx.contiguous(), dw)
+        return dw
+    d00, d01 = dwx[:, :co, :ci], dwx[:, :co, ci:]
+    d10, d11 = dwx[:, co:, :ci], dwx[:, co:, ci:]
+    return torch.complex(d00 + d11, d10 - d01).permute(2, 1, 0).contiguous()
+
+
+# ------------------------------------------------------------------------------------------------ autograd
+
+
+class _SpectralConv(torch.autograd.Function):
+    """y = iSHT_out(W . SHT_in(x)) and, when `want_resid`, r = iSHT_out(SHT_in(x)) (regridded residual)."""
+
+    @staticmethod
+    def forward(ctx, x, w, plan_in: SHTPlan, plan_out: SHTPlan, want_resid: bool):
+        B, C, H, W = x.shape
+        wx = expand_weight(w, x.dtype)
+        t1 = dft_analysis(x, plan_in.f, False, plan_in.nlon, plan_in.k2, plan_in.hp)
+        t2 = legendre_analysis(t1, plan_in.pw, H)
+        del t1
+        t3 = contract(t2, wx, False)
+        t4 = legendre_synthesis(t3, False, plan_out.p, plan_out.nlat)
+        del t3
+        y = dft_synthesis(t4, plan_out.gt, False, plan_out.k2p, plan_out.nlat, plan_out.nlon)
+        del t4
+        r = None
+        if want_resid:
+            t4r = legendre_synthesis(t2, True, plan_out.p, plan_out.nlat)
+            r = dft_synthesis(t4r, plan_out.gt, False, plan_out.k2p, plan_out.nlat, plan_out.nlon)
+        ctx.save_for_backward(t2, wx)
+        ctx.plans = (plan_in, plan_out)
+        ctx.want_resid = want_resid
+        ctx.wshape = w.shape
+        if want_resid:
+            return y, r
+        return y
+
+    @staticmethod
+    def backward(ctx, dy, dr=None):
+        t2, wx = ctx.saved_tensors
+        plan_in, plan_out = ctx.plans
+        dy = dy.contiguous()
+        # adjoint of the inverse DFT / synthesis on the output grid
+        dt4 = dft_analysis(dy, plan_out.gt, True, plan_out.k2p, plan_out.k2, plan_out.hp)
+        dt3 = legendre_analysis(dt4, plan_out.p, plan_out.nlat)        # [B, l, m, (ri, o)]
+        del dt4
+        dw = None
+        if ctx.needs_input_grad[1]:
+            dwx = contract_wgrad(dt3, t2)
+            dw = fold_weight_grad(dwx).reshape(ctx.wshape)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dt2 = contract(dt3, wx, True)                              # [B, m, l, (ri, c)]
+            if ctx.want_resid and dr is not None:
+                dr = dr.contiguous()
+                dr4 = dft_analysis(dr, plan_out.gt, True, plan_out.k2p, plan_out.k2, plan_out.hp)
+                dr2 = legendre_analysis(dr4, plan_out.p, plan_out.nlat)     # [B, l, m, n]
+                dt2 = dt2 + dr2.transpose(1, 2)
+                del dr4, dr2
+            dt1 = legendre_synthesis(dt2.contiguous(), False, plan_in.pw, plan_in.nlat)
+            dx = dft_synthesis(dt1, plan_in.f, True, plan_in.nlon, plan_in.nlat, plan_in.nlon)
+        return dx, dw, None, None, None
+
+
+def spectral_conv_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (x.dim() == 4 and x.dtype == torch.bfloat16 and x.is_contiguous() and x.shape[1] % 4 == 0
+            and w.dim() == 3 and w.shape[1] % 4 == 0 and x.shape[3] % 8 == 0)
+
+
+def spectral_conv_dhconv(x, w, plan_in: SHTPlan, plan_out: SHTPlan, want_resid: bool):
+    """Fused spherical convolution with per-degree ("dhconv") complex weights on the GEMM engine."""
+    return _SpectralConv.apply(x, w, plan_in, plan_out, want_resid)

@@ -1,0 +1,88 @@
+"""Gradient reduction for data parallelism and for parameters replicated across model-parallel groups.
+
+Semantics (reference: makani/mpu/mappings.py:30-174): gradients are averaged over the `data` group and then
+summed over every group named in `param.is_shared_mp` (default ["model"]).  Complex gradients are reduced
+through their real view.
+
+Mechanism here: all gradients live as views into one flat fp32 buffer.  On a single NVSwitch node with NCCL
+the buffer is symmetric peer memory and the data-parallel average is the in-kernel P2P all-reduce of
+`csrc/peer.cu`, which fuses the 1/N scaling; otherwise (CPU/gloo, or more ranks than one node) it is an
+all_reduce of the flat buffer.  Keeping `.grad` as persistent views also lets the fused AdamW run from a
+fixed pointer table.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..utils import comm
+
+
+class GradReducer:
+    def __init__(self, model: torch.nn.Module, use_peer: Optional[bool] = None, align: int = 64):
+        self.params = [p for p in model.parameters() if p.requires_grad]
+        dev = self.params[0].device
+        self.device = dev
+        sizes = []
+        total = 0
+        for p in self.params:
+            n = p.numel() * (2 if p.is_complex() else 1)
+            sizes.append((total, n))
+            total += (n + align - 1) // align * align
+        self.total = total
+        self.data_size = comm.get_size("data")
+        if use_peer is None:
+            use_peer = (dev.type == "cuda" and dist.is_initialized() and self.data_size > 1 and self.data_size <= 8
+                        and dist.get_backend() == "nccl")
+        self.sym = None
+        if use_peer:
+            from .peer import SymmetricBuffer
+            self.sym = SymmetricBuffer(total * 4, group=comm.get_group("data"), device=dev)
+            self.flat = self.sym.view(torch.float32, total)
+            self.flat.zero_()
+        else:
+            self.flat = torch.zeros(total, dtype=torch.float32, device=dev)
+        for p, (off, n) in zip(self.params, sizes):
+            if p.is_complex():
+                g = torch.view_as_complex(self.flat[off: off + n].view(*p.shape, 2))
+            else:
+                g = self.flat[off: off + n].view(p.shape)
+            p.grad = g
+        # parameters whose gradient must additionally be summed over model-parallel groups
+        self.shared: Dict[str, List[torch.nn.Parameter]] = {}
+        for p in self.params:
+            for g in getattr(p, "is_shared_mp", ["model"]):
+                if comm.get_size(g) > 1:
+                    self.shared.setdefault(g, []).append(p)
+
+    def zero_grad(self):
+        self.flat.zero_()
+
+    def reduce(self):
+        """Average over `data`, then sum over the model-parallel groups each parameter is shared on."""
+        if self.data_size > 1:
+            if self.sym is not None:
+                self.sym.all_reduce_(self.total, torch.float32, scale=1.0 / self.data_size)
+            else:
+                dist.all_reduce(self.flat, group=comm.get_group("data"))
+                self.flat.mul_(1.0 / self.data_size)
+        for gname, plist in self.shared.items():
+            grp = comm.get_group(gname)
+            bufs = [torch.view_as_real(p.grad) if p.is_complex() else p.grad for p in plist]
+            flat = torch.cat([b.reshape(-1) for b in bufs])
+            dist.all_reduce(flat, group=grp)
+            off = 0
+            for b in bufs:
+                b.copy_(flat[off: off + b.numel()].view_as(b))
+                off += b.numel()
+
+    def close(self):
+        if self.sym is not None:
+            for p in self.params:
+                p.grad = None
+            self.flat = None
+            self.sym.close()
+            self.sym = None

@@ -1,0 +1,305 @@
+"""Model-parallel layers: 2-D sharded pointwise matmuls (channel parallelism over the `fin` / `fout` groups),
+encoder/decoder and MLP stacks built from them, tensor-parallel attention, and the spatially distributed 2-D
+FFT pair.  Behavioural contract: makani/mpu/layers.py:37-642.
+
+Channel parallelism: a weight [out, in] is stored as the block [out / |G_out|, in / |G_in|].  The input arrives
+sharded over G_in; the local product is a partial sum that is all-reduced over G_in (forward) and whose data
+gradient is all-reduced over G_out (backward).  Consecutive layers swap the roles of the two groups so
+activations never need re-sharding.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+from torch.utils.checkpoint import checkpoint
+
+from ..utils import comm
+from .helpers import compute_split_shapes
+from .mappings import (copy_to_parallel_region, gather_from_parallel_region, reduce_from_parallel_region,
+                       scatter_to_parallel_region)
+from .transpose import distributed_transpose_azimuth, distributed_transpose_polar
+
+
+class DistributedRealFFT2(nn.Module):
+    """rfft2 with truncation on [B, C, H_loc, W_loc] data sharded over ("h", "w")."""
+
+    def __init__(self, nlat, nlon, lmax=None, mmax=None):
+        super().__init__()
+        self.comm_size_h, self.comm_size_w = comm.get_size("h"), comm.get_size("w")
+        self.comm_rank_w = comm.get_rank("w")
+        self.nlat, self.nlon = nlat, nlon
+        self.lmax = min(lmax or nlat, nlat)
+        self.mmax = min(mmax or nlon // 2 + 1, nlon // 2 + 1)
+        self.lmax_high, self.lmax_low = math.ceil(self.lmax / 2), math.floor(self.lmax / 2)
+        self.lat_shapes = compute_split_shapes(nlat, self.comm_size_h)
+        self.lon_shapes = compute_split_shapes(nlon, self.comm_size_w)
+        self.l_shapes = compute_split_shapes(self.lmax, self.comm_size_h)
+        self.m_shapes = compute_split_shapes(self.mmax, self.comm_size_w)
+
+    def forward(self, x):
+        num_chans = x.shape[1]
+        if self.comm_size_w > 1:
+            x = distributed_transpose_azimuth(x, (1, -1), self.lon_shapes)
+        x = torch.fft.rfft(x, n=self.nlon, dim=-1, norm="ortho")[..., : self.mmax]
+        if self.comm_size_w > 1:
+            x = distributed_transpose_azimuth(x.contiguous(), (-1, 1), compute_split_shapes(num_chans, self.comm_size_w))
+        if self.comm_size_h > 1:
+            x = distributed_transpose_polar(x, (1, -2), self.lat_shapes)
+        x = torch.fft.fft(x, n=self.nlat, dim=-2, norm="ortho")
+        parts = [x[..., : self.lmax_high, :]]
+        if self.lmax_low > 0:
+            parts.append(x[..., -self.lmax_low:, :])
+        x = torch.cat(parts, dim=-2)
+        if self.comm_size_h > 1:
+            x = distributed_transpose_polar(x.contiguous(), (-2, 1), compute_split_shapes(num_chans, self.comm_size_h))
+        return x
+
+
+class DistributedInverseRealFFT2(nn.Module):
+    def __init__(self, nlat, nlon, lmax=None, mmax=None):
+        super().__init__()
+        self.comm_size_h, self.comm_size_w = comm.get_size("h"), comm.get_size("w")
+        self.nlat, self.nlon = nlat, nlon
+        self.lmax = min(lmax or nlat, nlat)
+        self.mmax = min(mmax or nlon // 2 + 1, nlon // 2 + 1)
+        self.lmax_high, self.lmax_low = math.ceil(self.lmax / 2), math.floor(self.lmax / 2)
+        self.lat_shapes = compute_split_shapes(nlat, self.comm_size_h)
+        self.lon_shapes = compute_split_shapes(nlon, self.comm_size_w)
+        self.l_shapes = compute_split_shapes(self.lmax, self.comm_size_h)
+        self.m_shapes = compute_split_shapes(self.mmax, self.comm_size_w)
+
+    def forward(self, x):
+        num_chans = x.shape[1]
+        if self.comm_size_h > 1:
+            x = distributed_transpose_polar(x, (1, -2), self.l_shapes)
+        hi = F.pad(x[..., : self.lmax_high, :], (0, 0, 0, self.nlat - self.lmax))
+        parts = [hi]
+        if self.lmax_low > 0:
+            parts.append(x[..., -self.lmax_low:, :])
+        x = torch.cat(parts, dim=-2)
+        x = torch.fft.ifft(x, n=self.nlat, dim=-2, norm="ortho")
+        if self.comm_size_h > 1:
+            x = distributed_transpose_polar(x.contiguous(), (-2, 1), compute_split_shapes(num_chans, self.comm_size_h))
+        if self.comm_size_w > 1:
+            x = distributed_transpose_azimuth(x, (1, -1), self.m_shapes)
+        x = torch.fft.irfft(x, n=self.nlon, dim=-1, norm="ortho")
+        if self.comm_size_w > 1:
+            x = distributed_transpose_azimuth(x.contiguous(), (-1, 1), compute_split_shapes(num_chans, self.comm_size_w))
+        return x
+
+
+class DistributedMatmul(nn.Module):
+    """Pointwise linear map with the weight sharded [out over comm_out, in over comm_inp]."""
+
+    def __init__(self, inp_dim, out_dim, input_format="nchw", comm_inp_name="fin", comm_out_name="fout", bias=True):
+        super().__init__()
+        self.comm_inp_name, self.comm_out_name = comm_inp_name, comm_out_name
+        self.input_format = input_format
+        inp_loc = compute_split_shapes(inp_dim, comm.get_size(comm_inp_name))[comm.get_rank(comm_inp_name)]
+        out_loc = compute_split_shapes(out_dim, comm.get_size(comm_out_name))[comm.get_rank(comm_out_name)]
+        if input_format == "nchw":
+            self.weight = nn.Parameter(torch.ones(out_loc, inp_loc, 1, 1))
+            self.weight.sharded_dims_mp = [comm_out_name, comm_inp_name, None, None]
+            self.matmul_handle = F.conv2d
+        elif input_format == "traditional":
+            self.weight = nn.Parameter(torch.ones(out_loc, inp_loc))
+            self.weight.sharded_dims_mp = [comm_out_name, comm_inp_name]
+            self.matmul_handle = F.linear
+        else:
+            raise NotImplementedError(f"input format {input_format} not supported")
+        self.weight.is_shared_mp = ["spatial"]
+        if bias:
+            if input_format == "nchw":
+                self.bias = nn.Parameter(torch.zeros(1, out_loc, 1, 1))
+                self.bias.sharded_dims_mp = [None, comm_out_name, None, None]
+            else:
+                self.bias = nn.Parameter(torch.zeros(out_loc))
+                self.bias.sharded_dims_mp = [comm_out_name]
+            self.bias.is_shared_mp = ["spatial", comm_inp_name]
+
+    def forward(self, x):
+        x_cp = copy_to_parallel_region(x, self.comm_out_name)
+        x_loc = self.matmul_handle(x_cp, self.weight.to(x_cp.dtype), bias=None)
+        x_out = reduce_from_parallel_region(x_loc, self.comm_inp_name)
+        if hasattr(self, "bias"):
+            x_out = x_out + self.bias.to(x_out.dtype)
+        return x_out
+
+
+class DistributedEncoderDecoder(nn.Module):
+    """Channel-parallel pointwise encoder/decoder; the in/out group names alternate from layer to layer."""
+
+    def __init__(self, num_layers, input_dim, output_dim, hidden_dim, act_layer, gain=1.0, input_format="nchw",
+                 comm_inp_name="fin", comm_out_name="fout"):
+        super().__init__()
+        mods = []
+        cur = input_dim
+        cin, cout = comm_inp_name, comm_out_name
+        for _ in range(num_layers):
+            lin = DistributedMatmul(cur, hidden_dim, input_format, cin, cout, bias=True)
+            nn.init.normal_(lin.weight, mean=0.0, std=math.sqrt(2.0 / cur))
+            nn.init.constant_(lin.bias, 0.0)
+            mods += [lin, act_layer()]
+            cur = hidden_dim
+            cin, cout = cout, cin
+        out = DistributedMatmul(cur, output_dim, input_format, cin, cout, bias=False)
+        nn.init.normal_(out.weight, mean=0.0, std=math.sqrt(gain / cur))
+        mods.append(out)
+        self.fwd = nn.Sequential(*mods)
+        self.comm_inp_name, self.comm_out_name = comm_inp_name, cout
+
+    def forward(self, x):
+        return self.fwd(x)
+
+
+class DistributedMLP(nn.Module):
+    def __init__(self, in_features, hidden_features=None, out_features=None, output_bias=True, input_format="nchw",
+                 comm_inp_name="fin", comm_hidden_name="fout", act_layer=nn.GELU, drop_rate=0.0, drop_type="iid",
+                 checkpointing=0, gain=1.0, **kwargs):
+        super().__init__()
+        self.checkpointing = checkpointing
+        out_features = out_features or in_features
+        hidden_features = hidden_features or in_features
+        self.fc1 = DistributedMatmul(in_features, hidden_features, input_format, comm_inp_name, comm_hidden_name, bias=True)
+        nn.init.normal_(self.fc1.weight, mean=0.0, std=math.sqrt(2.0 / in_features))
+        nn.init.constant_(self.fc1.bias, 0.0)
+        self.fc2 = DistributedMatmul(hidden_features, out_features, input_format, comm_hidden_name, comm_inp_name, bias=output_bias)
+        nn.init.normal_(self.fc2.weight, mean=0.0, std=math.sqrt(gain / hidden_features))
+        if hasattr(self.fc2, "bias"):
+            nn.init.constant_(self.fc2.bias, 0.0)
+        self.act = act_layer()
+        if drop_rate > 0.0:
+            self.drop = nn.Dropout(drop_rate) if drop_type == "iid" else nn.Dropout2d(drop_rate)
+        else:
+            self.drop = nn.Identity()
+
+    def fwd(self, x):
+        return self.drop(self.fc2(self.drop(self.act(self.fc1(x)))))
+
+    def forward(self, x):
+        if self.checkpointing >= 2 and self.training:
+            return checkpoint(self.fwd, x, use_reentrant=False)
+        return self.fwd(x)
+
+
+class DistributedPatchEmbed(nn.Module):
+    def __init__(self, img_size=(224, 224), patch_size=(16, 16), in_chans=3, embed_dim=768, input_is_matmul_parallel=False,
+                 output_is_matmul_parallel=True):
+        super().__init__()
+        self.input_parallel, self.output_parallel = input_is_matmul_parallel, output_is_matmul_parallel
+        self.img_size, self.patch_size = img_size, patch_size
+        self.num_patches = (img_size[1] // patch_size[1]) * (img_size[0] // patch_size[0])
+        msize = comm.get_size("matmul")
+        self.in_shapes = compute_split_shapes(in_chans, msize)
+        out_loc = compute_split_shapes(embed_dim, msize)[comm.get_rank("matmul")] if output_is_matmul_parallel else embed_dim
+        self.proj = nn.Conv2d(in_chans, out_loc, kernel_size=patch_size, stride=patch_size)
+        self.proj.weight.is_shared_mp = ["spatial"]
+        self.proj.bias.is_shared_mp = ["spatial"]
+        if output_is_matmul_parallel:
+            self.proj.weight.sharded_dims_mp = ["matmul", None, None, None]
+            self.proj.bias.sharded_dims_mp = ["matmul"]
+
+    def forward(self, x):
+        if self.input_parallel:
+            x = gather_from_parallel_region(x, 1, self.in_shapes, "matmul")
+        if self.output_parallel:
+            x = copy_to_parallel_region(x, "matmul")
+        return self.proj(x).flatten(2)
+
+
+class DistributedAttention(nn.Module):
+    """Multi-head self attention with heads split over `comm_hidden_name` (sequence stays whole)."""
+
+    def __init__(self, dim, input_format="traditional", comm_inp_name="fin", comm_hidden_name="fout", num_heads=8,
+                 qkv_bias=False, attn_drop_rate=0.0, proj_drop_rate=0.0, norm_layer=nn.LayerNorm):
+        super().__init__()
+        assert dim % num_heads == 0
+        assert num_heads % comm.get_size(comm_hidden_name) == 0, "heads must divide over the hidden group"
+        self.num_heads = num_heads
+        self.num_heads_local = num_heads // comm.get_size(comm_hidden_name)
+        self.head_dim = dim // num_heads
+        self.comm_inp_name, self.comm_hidden_name = comm_inp_name, comm_hidden_name
+        self.qkv = DistributedMatmul(dim, dim * 3, input_format, comm_inp_name, comm_hidden_name, bias=qkv_bias)
+        self.proj = DistributedMatmul(dim, dim, input_format, comm_hidden_name, comm_inp_name, bias=False)
+        nn.init.trunc_normal_(self.qkv.weight, std=0.02)
+        nn.init.trunc_normal_(self.proj.weight, std=0.02)
+        self.attn_drop_rate = attn_drop_rate
+        self.proj_drop = nn.Dropout(proj_drop_rate)
+        self.q_norm = norm_layer(self.head_dim) if norm_layer is not None and norm_layer is not nn.Identity else nn.Identity()
+        self.k_norm = norm_layer(self.head_dim) if norm_layer is not None and norm_layer is not nn.Identity else nn.Identity()
+
+    def forward(self, x):
+        B, N, C = x.shape
+        qkv = self.qkv(x).reshape(B, N, self.num_heads_local, 3, self.head_dim).permute(3, 0, 2, 1, 4)
+        q, k, v = qkv.unbind(0)
+        q, k = self.q_norm(q), self.k_norm(k)
+        y = F.scaled_dot_product_attention(q, k, v, dropout_p=self.attn_drop_rate if self.training else 0.0)
+        y = y.transpose(1, 2).reshape(B, N, self.num_heads_local * self.head_dim)
+        return self.proj_drop(self.proj(y))
+
+
+def compl_mul_add_fwd(a, b, c):
+    return torch.einsum("bkixys,kiot->stbkoxy", a, b)
+
+
+class DistributedAFNO2Dv2(nn.Module):
+    """Block-diagonal complex two-layer MLP in Fourier space with the blocks sharded over the `matmul` group."""
+
+    def __init__(self, hidden_size, num_blocks=8, sparsity_threshold=0.01, hard_thresholding_fraction=1,
+                 hidden_size_factor=1, input_is_matmul_parallel=False, output_is_matmul_parallel=False, use_complex_kernels=False):
+        super().__init__()
+        assert hidden_size % num_blocks == 0
+        msize = comm.get_size("matmul")
+        assert num_blocks % msize == 0
+        self.fft_handle = torch.fft.rfft2
+        self.ifft_handle = torch.fft.irfft2
+        self.hidden_size, self.num_blocks = hidden_size, num_blocks
+        self.sparsity_threshold = sparsity_threshold
+        self.num_blocks_local = num_blocks // msize
+        self.block_size = hidden_size // num_blocks
+        self.hard_thresholding_fraction = hard_thresholding_fraction
+        self.hidden_size_factor = hidden_size_factor
+        self.scale = 0.02
+        self.input_parallel, self.output_parallel = input_is_matmul_parallel, output_is_matmul_parallel
+        self.chan_shapes = compute_split_shapes(hidden_size, msize)
+        bs, f, nb = self.block_size, hidden_size_factor, self.num_blocks_local
+        self.w1 = nn.Parameter(self.scale * torch.randn(nb, bs, bs * f, 2))
+        self.b1 = nn.Parameter(self.scale * torch.randn(nb, bs * f, 1, 1, 2))
+        self.w2 = nn.Parameter(self.scale * torch.randn(nb, bs * f, bs, 2))
+        self.b2 = nn.Parameter(self.scale * torch.randn(nb, bs, 1, 1, 2))
+        for p in (self.w1, self.b1, self.w2, self.b2):
+            p.is_shared_mp = ["spatial"]
+        self.w1.sharded_dims_mp = ["matmul", None, None, None]
+        self.b1.sharded_dims_mp = ["matmul", None, None, None, None]
+        self.w2.sharded_dims_mp = ["matmul", None, None, None]
+        self.b2.sharded_dims_mp = ["matmul", None, None, None, None]
+
+    def forward(self, x):
+        if not self.input_parallel:
+            x = scatter_to_parallel_region(x, 1, "matmul")
+        bias = x
+        dtype = x.dtype
+        x = x.float()
+        B, C, H, W = x.shape
+        total_modes = H // 2 + 1
+        kept = int(total_modes * self.hard_thresholding_fraction)
+        xf = self.fft_handle(x, dim=(-2, -1), norm="ortho")
+        xf = xf.view(B, self.num_blocks_local, self.block_size, H, W // 2 + 1)
+        w1, w2 = torch.view_as_complex(self.w1), torch.view_as_complex(self.w2)
+        b1, b2 = torch.view_as_complex(self.b1), torch.view_as_complex(self.b2)
+        sl = (slice(None), slice(None), slice(None), slice(total_modes - kept, total_modes + kept), slice(0, kept))
+        o1 = torch.einsum("bkixy,kio->bkoxy", xf[sl], w1) + b1
+        o1 = torch.view_as_complex(F.relu(torch.view_as_real(o1)))
+        o2 = torch.einsum("bkixy,kio->bkoxy", o1, w2) + b2
+        o2 = torch.view_as_complex(F.softshrink(torch.view_as_real(o2), lambd=self.sparsity_threshold))
+        out = torch.zeros_like(xf)
+        out[sl] = o2
+        out = out.reshape(B, C, H, W // 2 + 1)
+        x = self.ifft_handle(out, s=(H, W), dim=(-2, -1), norm="ortho").to(dtype) + bias
+        if not self.output_parallel:
+            x = gather_from_parallel_region(x, 1, self.chan_shapes, "matmul")
+        return x

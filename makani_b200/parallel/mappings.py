@@ -1,0 +1,121 @@
+"""Autograd-aware collectives between replicated and sharded regions of the model.
+
+Contract of `modulus.distributed.mappings` as used by the reference (makani/mpu/layers.py:27-30,
+makani/mpu/layer_norm.py:25, makani/utils/losses.py:28):
+
+    copy_to_parallel_region(x, g)         forward identity            backward all-reduce(SUM)
+    reduce_from_parallel_region(x, g)     forward all-reduce(SUM)     backward identity
+    scatter_to_parallel_region(x, d, g)   forward keep local chunk    backward all-gather
+    gather_from_parallel_region(x,d,s,g)  forward uneven all-gather   backward keep local chunk
+"""
+
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..utils import comm
+from .helpers import compute_split_shapes, split_tensor_along_dim
+
+
+def _all_reduce(x: torch.Tensor, name: str) -> torch.Tensor:
+    if comm.get_size(name) == 1:
+        return x
+    x = x.contiguous()
+    if x.is_complex():
+        dist.all_reduce(torch.view_as_real(x), group=comm.get_group(name))
+    else:
+        dist.all_reduce(x, group=comm.get_group(name))
+    return x
+
+
+def _split(x: torch.Tensor, dim: int, name: str) -> torch.Tensor:
+    size = comm.get_size(name)
+    if size == 1:
+        return x
+    return split_tensor_along_dim(x, dim, size)[comm.get_rank(name)].contiguous()
+
+
+def _gather(x: torch.Tensor, dim: int, shapes: Optional[List[int]], name: str) -> torch.Tensor:
+    size = comm.get_size(name)
+    if size == 1:
+        return x
+    dim = dim % x.dim()
+    x = x.contiguous()
+    is_complex = x.is_complex()
+    xr = torch.view_as_real(x) if is_complex else x
+    if shapes is None:
+        sz = torch.tensor([x.shape[dim]], dtype=torch.int64, device=x.device)
+        all_sz = [torch.empty_like(sz) for _ in range(size)]
+        dist.all_gather(all_sz, sz, group=comm.get_group(name))
+        shapes = [int(s.item()) for s in all_sz]
+    outs = []
+    for s in shapes:
+        shp = list(xr.shape)
+        shp[dim] = s
+        outs.append(torch.empty(shp, dtype=xr.dtype, device=xr.device))
+    dist.all_gather(outs, xr, group=comm.get_group(name))
+    out = torch.cat(outs, dim=dim)
+    return torch.view_as_complex(out) if is_complex else out
+
+
+class _CopyTo(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, name):
+        ctx.name = name
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        return _all_reduce(g.clone(), ctx.name), None
+
+
+class _ReduceFrom(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, name):
+        return _all_reduce(x.clone(), name)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+class _ScatterTo(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, dim, name):
+        ctx.dim, ctx.name = dim, name
+        ctx.shapes = compute_split_shapes(x.shape[dim], comm.get_size(name))
+        return _split(x, dim, name)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _gather(g, ctx.dim, ctx.shapes, ctx.name), None, None
+
+
+class _GatherFrom(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, dim, shapes, name):
+        ctx.dim, ctx.name = dim, name
+        return _gather(x, dim, shapes, name)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _split(g, ctx.dim, ctx.name), None, None, None
+
+
+def copy_to_parallel_region(x, name):
+    return x if comm.get_size(name) == 1 else _CopyTo.apply(x, name)
+
+
+def reduce_from_parallel_region(x, name):
+    return x if comm.get_size(name) == 1 else _ReduceFrom.apply(x, name)
+
+
+def scatter_to_parallel_region(x, dim, name):
+    return x if comm.get_size(name) == 1 else _ScatterTo.apply(x, dim, name)
+
+
+def gather_from_parallel_region(x, dim, shapes, name):
+    return x if comm.get_size(name) == 1 else _GatherFrom.apply(x, dim, shapes, name)

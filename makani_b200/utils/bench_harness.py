@@ -1,0 +1,140 @@
+"""Assembly of the flagship benchmark workload (SFNO-73ch, 721x1440) from the framework's public pieces."""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from ..models.networks.sfnonet import SphericalFourierNeuralOperatorNet
+from ..ops import _ext
+from ..ops.optim import FusedAdamW
+from ..parallel.grad_reduce import GradReducer
+from ..parallel.helpers import sync_params
+from ..utils import comm
+from .losses import LossHandler
+from .train_step import TrainStep
+from .YParams import ParamsBase
+
+
+@dataclass
+class FlagshipConfig:
+    small: bool = False
+    name: str = "sfno_linear_73chq_sc3_layers8_edim384"
+    nlat: int = 721
+    nlon: int = 1440
+    in_chans: int = 74      # 73 prognostic + 1 static cos(latitude)
+    out_chans: int = 73
+    embed_dim: int = 384
+    num_layers: int = 8
+    scale_factor: int = 3
+    batch_per_gpu: int = 1
+    loss: str = "absolute squared geometric l2"
+    lr: float = 1e-3
+
+    def __post_init__(self):
+        if self.small:
+            self.name += "_small"
+            self.nlat, self.nlon = 361, 720
+
+
+class FlagshipRunner:
+    def __init__(self, cfg: FlagshipConfig, device: torch.device):
+        self.cfg, self.device = cfg, device
+        torch.manual_seed(0)
+        self.model = SphericalFourierNeuralOperatorNet(
+            spectral_transform="sht", model_grid_type="equiangular", sht_grid_type="legendre-gauss", filter_type="linear",
+            operator_type="dhconv", inp_shape=(cfg.nlat, cfg.nlon), out_shape=(cfg.nlat, cfg.nlon),
+            scale_factor=cfg.scale_factor, inp_chans=cfg.in_chans, out_chans=cfg.out_chans, embed_dim=cfg.embed_dim,
+            num_layers=cfg.num_layers, use_mlp=True, mlp_ratio=2.0, activation_function="gelu", encoder_layers=1,
+            pos_embed="none", normalization_layer="instance_norm", hard_thresholding_fraction=1.0, big_skip=True).to(device)
+        self.model.set_compute_dtype(torch.bfloat16)
+        sync_params(self.model)
+        p = ParamsBase()
+        p.update_params(dict(loss=cfg.loss, n_future=0, img_shape_x=cfg.nlat, img_shape_y=cfg.nlon,
+                             img_crop_shape_x=cfg.nlat, img_crop_shape_y=cfg.nlon, img_crop_offset_x=0, img_crop_offset_y=0,
+                             N_out_channels=cfg.out_chans, channel_weights="auto", model_grid_type="equiangular"))
+        self.loss_fn = LossHandler(p).to(device)
+        self.reducer = GradReducer(self.model)
+        self.optimizer = FusedAdamW(self.model.parameters(), lr=cfg.lr, weight_decay=0.0)
+        self.train_step = TrainStep(self.model, self.loss_fn, self.optimizer, self.reducer)
+        lat = torch.linspace(math.pi / 2, -math.pi / 2, cfg.nlat, device=device)
+        self.coslat = torch.cos(lat).view(1, 1, -1, 1).expand(cfg.batch_per_gpu, 1, cfg.nlat, cfg.nlon)
+
+    def synthetic_batch(self, seed: int):
+        cfg = self.cfg
+        g = torch.Generator(device=self.device)
+        g.manual_seed(seed)
+        x = torch.randn(cfg.batch_per_gpu, cfg.out_chans, cfg.nlat, cfg.nlon, device=self.device, generator=g)
+        inp = torch.cat([x, self.coslat], dim=1).to(torch.bfloat16).contiguous()
+        tgt = torch.randn(cfg.batch_per_gpu, cfg.out_chans, cfg.nlat, cfg.nlon, device=self.device, generator=g).to(torch.bfloat16)
+        return inp, tgt
+
+    def step(self, inp, tgt):
+        return self.train_step(inp, tgt)
+
+    def end_to_end(self, steps: int, warmup: int, world: int, local_rank: int):
+        """Same step, but every step's input/target come from pinned host memory (double-buffered H2D copy on a
+        side stream) and every step's loss is read back to the host."""
+        cfg = self.cfg
+        dev = self.device
+        nb = 2
+        host = []
+        for i in range(nb):
+            gi = torch.Generator().manual_seed(100 + i + 17 * local_rank)
+            hi = torch.randn(cfg.batch_per_gpu, cfg.in_chans, cfg.nlat, cfg.nlon, generator=gi).to(torch.bfloat16).pin_memory()
+            ht = torch.randn(cfg.batch_per_gpu, cfg.out_chans, cfg.nlat, cfg.nlon, generator=gi).to(torch.bfloat16).pin_memory()
+            host.append((hi, ht))
+        dbuf = [(torch.empty_like(h[0], device=dev), torch.empty_like(h[1], device=dev)) for h in host]
+        copy_stream = torch.cuda.Stream(device=dev)
+        ready = [torch.cuda.Event() for _ in range(nb)]
+        consumed = [torch.cuda.Event() for _ in range(nb)]
+        h2d = host[0][0].numel() * 2 + host[0][1].numel() * 2
+        loss_host = torch.zeros(1, dtype=torch.float32).pin_memory()
+
+        def issue(i):
+            b = i % nb
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(consumed[b])
+                dbuf[b][0].copy_(host[b][0], non_blocking=True)
+                dbuf[b][1].copy_(host[b][1], non_blocking=True)
+                ready[b].record(copy_stream)
+
+        def run(n, timed):
+            cur = torch.cuda.current_stream(dev)
+            for b in range(nb):
+                consumed[b].record(cur)
+            issue(0)
+            for i in range(n):
+                b = i % nb
+                if i + 1 < n:
+                    issue(i + 1)
+                cur.wait_event(ready[b])
+                loss = self.train_step(dbuf[b][0], dbuf[b][1])
+                consumed[b].record(cur)
+                loss_host.copy_(loss.reshape(1).float(), non_blocking=False)  # D2H read of the step result
+            return float(loss_host.item())
+
+        run(warmup, False)
+        if world > 1:
+            dist.barrier(device_ids=[local_rank])
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        run(steps, True)
+        e1.record()
+        if world > 1:
+            dist.barrier(device_ids=[local_rank])
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item() / steps
+        return {"value": cfg.batch_per_gpu * world / (ms / 1e3), "unit": "samples/s", "ms_per_step": ms,
+                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4}
+
+
+def build_flagship(cfg: FlagshipConfig, device: torch.device) -> FlagshipRunner:
+    return FlagshipRunner(cfg, device)

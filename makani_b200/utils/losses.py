@@ -1,0 +1,195 @@
+"""Training objective: channel-weighted, quadrature-weighted Lp / H1 losses on the sphere.
+
+Loss-string grammar, channel-weight rules ("auto" by variable name, temp-std re-weighting), multistep weights
+and the absolute / relative / squared variants follow makani/utils/losses.py:34-364.  Two things are done
+differently on purpose:
+
+* The spatial integrals run as one fused reduction kernel over the *local* tile followed by an all-reduce of
+  the per-channel partial integrals over the `spatial` group.  The reference all-gathers prediction and target
+  over `h` then `w` on every rank first (losses.py:137-159), which materialises the full field everywhere.
+* Quadrature selection compares the grid type with "legendre-gauss" (the reference compares with the
+  misspelt "legendre_gauss", so its Gauss rule is never selected).
+"""
+
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import numpy as np
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..ops.loss import weighted_lp_norms
+from ..parallel.mappings import reduce_from_parallel_region
+from ..sht import RealSHT
+from ..utils import comm
+from .grids import GridQuadrature
+
+
+def _auto_channel_weights(channel_names):
+    w = torch.ones(len(channel_names), dtype=torch.float32)
+    for c, chn in enumerate(channel_names):
+        if chn in ["u10m", "v10m", "u100m", "v100m", "tp", "sp", "msl", "tcwv"]:
+            w[c] = 0.1
+        elif chn in ["t2m", "2d"]:
+            w[c] = 1.0
+        elif chn[0] in ["z", "u", "v", "t", "r", "q"]:
+            w[c] = 0.001 * float(chn[1:])
+        else:
+            w[c] = 0.01
+    return w
+
+
+class GeometricLpLoss(nn.Module):
+    """Lp loss with spherical quadrature; per (sample, channel) norms, then channel weights, then a sum."""
+
+    def __init__(self, img_shape, crop_shape, crop_offset, p: float = 2.0, size_average=False, reduction=True,
+                 absolute=False, squared=False, pole_mask=0, jacobian="s2", quadrature_rule="naive",
+                 local_shape=None, local_offset=(0, 0)):
+        super().__init__()
+        self.p, self.reduction, self.size_average = p, reduction, size_average
+        self.absolute, self.squared = absolute, squared
+        self.quadrature = GridQuadrature(quadrature_rule, img_shape=img_shape, crop_shape=crop_shape, crop_offset=crop_offset,
+                                         normalize=True, pole_mask=pole_mask, local_shape=local_shape, local_offset=local_offset)
+
+    def _norms(self, prd, tar):
+        """[B, C, 2]: global integrals of |prd - tar|^p and |tar|^p."""
+        if self.p in (1, 2, 1.0, 2.0) and prd.dim() == 4:
+            n = weighted_lp_norms(prd, tar, self.quadrature.lat_weights, int(self.p))
+        else:
+            d = self.quadrature(torch.abs(prd.float() - tar.float()) ** self.p)
+            t = self.quadrature(torch.abs(tar.float()) ** self.p)
+            n = torch.stack([d, t], dim=-1)
+        return reduce_from_parallel_region(n, "spatial")
+
+    def _finish(self, vals, chw):
+        vals = chw * vals
+        if self.reduction:
+            return torch.mean(vals) if self.size_average else torch.sum(vals)
+        return vals
+
+    def abs(self, prd, tar, chw):
+        n = self._norms(prd, tar)[..., 0]
+        if not self.squared:
+            n = n ** (1.0 / self.p)
+        return self._finish(n, chw)
+
+    def rel(self, prd, tar, chw):
+        n = self._norms(prd, tar)
+        frac = n[..., 0] / n[..., 1]
+        if not self.squared:
+            frac = frac ** (1.0 / self.p)
+        return self._finish(frac, chw)
+
+    def forward(self, prd, tar, chw):
+        return self.abs(prd, tar, chw) if self.absolute else self.rel(prd, tar, chw)
+
+
+class GeometricH1Loss(nn.Module):
+    """Sobolev H1-type loss from spherical harmonic coefficients: alpha ||.||_L2 + (1 - alpha) |.|_H1."""
+
+    def __init__(self, img_shape, p=2.0, size_average=False, reduction=True, absolute=False, squared=False, alpha=0.5):
+        super().__init__()
+        self.reduction, self.size_average = reduction, size_average
+        self.absolute, self.squared, self.alpha = absolute, squared, alpha
+        self.sht = RealSHT(*img_shape, grid="equiangular").float()
+        l = torch.arange(self.sht.lmax).float()
+        self.register_buffer("h1_weights", l * (l + 1), persistent=False)
+
+    def _norms2(self, x):
+        B = x.shape[0]
+        c = self.sht(x.float())
+        c2 = c.real ** 2 + c.imag ** 2
+        n2 = c2[..., :, 0] + 2 * torch.sum(c2[..., :, 1:], dim=-1)
+        return n2.reshape(B, -1).sum(dim=-1), (n2 * self.h1_weights).reshape(B, -1).sum(dim=-1)
+
+    def _combine(self, l2, h1):
+        if self.squared:
+            return self.alpha * l2 + (1 - self.alpha) * h1
+        return self.alpha * torch.sqrt(l2) + (1 - self.alpha) * torch.sqrt(h1)
+
+    def forward(self, prd, tar, chw=None, mask=None):
+        val = self._combine(*self._norms2(prd - tar))
+        if not self.absolute:
+            val = val / self._combine(*self._norms2(tar))
+        if mask is not None:
+            val = val * mask
+        if self.reduction:
+            if self.size_average:
+                return torch.mean(val) if mask is None else torch.sum(val) / torch.sum(mask)
+            return torch.sum(val)
+        return val
+
+
+class LossHandler(nn.Module):
+    """Parses `params.loss` (e.g. "absolute squared geometric l2", "weighted geometric l1", "geometric h1")."""
+
+    def __init__(self, params):
+        super().__init__()
+        self.rank = comm.get_rank("matmul")
+        self.n_future = params.get("n_future", 0)
+        self.img_shape = (params.img_shape_x, params.img_shape_y)
+        self.crop_shape = (params.img_crop_shape_x, params.img_crop_shape_y)
+        self.crop_offset = (params.img_crop_offset_x, params.img_crop_offset_y)
+        local_shape = (params.get("img_local_shape_x", self.crop_shape[0]), params.get("img_local_shape_y", self.crop_shape[1]))
+        local_offset = (params.get("img_local_offset_x", 0), params.get("img_local_offset_y", 0))
+        if comm.get_size("spatial") == 1:
+            local_shape, local_offset = None, (0, 0)
+
+        self.loss_type = params.loss
+        tokens = set(self.loss_type.split())
+        pole_mask = 1 if "pole-masked" in tokens else 0
+        n_out = params.N_out_channels
+
+        if "weighted" in tokens:
+            if params.channel_weights == "auto":
+                cw = _auto_channel_weights(params.channel_names)
+            else:
+                cw = torch.tensor(params.channel_weights, dtype=torch.float32)
+        else:
+            cw = torch.ones(n_out, dtype=torch.float32)
+        cw = cw.reshape(1, -1, 1, 1)
+        cw = cw / torch.sum(cw)
+
+        absolute = "absolute" in tokens
+        squared = "squared" in tokens
+
+        if "temp-std" in tokens:
+            eps = 1e-6
+            gstd = torch.from_numpy(np.load(params.global_stds_path)).reshape(1, -1, 1, 1)[:, params.out_channels]
+            tstd = np.sqrt(params.dt) * torch.from_numpy(np.load(params.time_diff_stds_path)).reshape(1, -1, 1, 1)[:, params.out_channels]
+            tw = gstd / (tstd + eps)
+            if squared:
+                tw = tw ** 2
+            cw = cw * tw.float()
+        self.register_buffer("channel_weights", cw.float(), persistent=False)
+
+        rule = "legendre-gauss" if params.get("model_grid_type", "equiangular") == "legendre-gauss" else "naive"
+        geo = dict(local_shape=local_shape, local_offset=local_offset, pole_mask=pole_mask)
+        if "l2" in tokens:
+            self.loss_obj = GeometricLpLoss(self.img_shape, self.crop_shape, self.crop_offset, p=2, absolute=absolute,
+                                            squared=squared if "geometric" in tokens else False, quadrature_rule=rule, **geo)
+        elif "l1" in tokens:
+            self.loss_obj = GeometricLpLoss(self.img_shape, self.crop_shape, self.crop_offset, p=1, absolute=absolute,
+                                            quadrature_rule=rule, **geo)
+        elif "geometric" in tokens and "h1" in tokens:
+            self.loss_obj = GeometricH1Loss(self.img_shape, absolute=absolute, squared=squared)
+        else:
+            raise ValueError(f"Unknown loss function: {self.loss_type}")
+
+        msw = torch.ones(self.n_future + 1, dtype=torch.float32) / float(self.n_future + 1)
+        self.register_buffer("multistep_weight", msw.reshape(-1, 1, 1, 1), persistent=False)
+
+    def is_distributed(self):
+        return comm.get_size("spatial") > 1
+
+    def forward(self, prd: torch.Tensor, tar: torch.Tensor, inp: Optional[torch.Tensor] = None):
+        chw = self.channel_weights
+        if self.training:
+            chw = (chw * self.multistep_weight).reshape(1, -1)
+        else:
+            chw = chw.reshape(1, -1)
+        if isinstance(self.loss_obj, GeometricH1Loss):
+            return self.loss_obj(prd, tar, chw)
+        return self.loss_obj(prd, tar, chw)

@@ -1,0 +1,345 @@
+"""Numerics of every sm_100a kernel against a plain PyTorch fp32 reference of the same op (run with -m gpu)."""
+
+import math
+
+import pytest
+import torch
+
+from makani_b200.ops import _ext
+from makani_b200.ops.gemm import (ACT_DGELU, ACT_GELU, ACT_NONE, BIAS_COL, BIAS_ROW, Operand, Output, Tri, _emulate,
+                                  gemm)
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    assert torch.cuda.is_available(), "GPU tests need CUDA"
+    _ext.require()
+    return torch.device("cuda", 0)
+
+
+def _rel(a, b):
+    a, b = a.double().cpu(), b.double().cpu()
+    return ((a - b).norm() / (b.norm() + 1e-30)).item()
+
+
+def _run_both(M, N, K, A, B, D, **kw):
+    """Run the kernel on CUDA copies and the emulation on fp32 CPU copies of the same storages; return both D."""
+    dev = _dev()
+    cpu_kw = dict(kw)
+    for name in ("bias", "resid", "preact"):
+        if kw.get(name) is not None:
+            cpu_kw[name] = kw[name].detach().cpu().float().clone()
+    A_c = Operand(A.tensor.cpu().float().clone(), A.ld, A.mn_major, A.offset, A.zs_lo, A.zs_hi)
+    B_c = Operand(B.tensor.cpu().float().clone(), B.ld, B.mn_major, B.offset, B.zs_lo, B.zs_hi)
+    D_c = Output(D.tensor.cpu().float().clone(), D.rs_lo, D.offset, D.rdiv, D.rs_hi, D.ndiv, D.ns_hi, D.d_zlo, D.d_zhi)
+    gemm(M, N, K, A_c, B_c, D_c, **{k: v for k, v in cpu_kw.items() if k not in ("splits", "bn")})
+    gemm(M, N, K, A, B, D, **kw)
+    torch.cuda.synchronize()
+    _ext.check_device_errors(dev)
+    outs = [(D.tensor, D_c.tensor)]
+    if kw.get("preact") is not None:
+        outs.append((kw["preact"], cpu_kw["preact"]))
+    return outs
+
+
+@pytest.mark.parametrize("a_mn", [False, True])
+@pytest.mark.parametrize("b_mn", [False, True])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (200, 300, 136), (384, 1000, 384), (77, 72, 1000)])
+@pytest.mark.parametrize("bn", [128, 256])
+def test_gemm_majors_bf16(a_mn, b_mn, shape, bn):
+    dev = _dev()
+    M, N, K = shape
+    torch.manual_seed(M + N + K)
+    pad = lambda n: (n + 7) // 8 * 8
+    a = torch.randn(pad(K), pad(M), device=dev).to(torch.bfloat16) if a_mn else torch.randn(pad(M), pad(K), device=dev).to(torch.bfloat16)
+    b = torch.randn(pad(K), pad(N), device=dev).to(torch.bfloat16) if b_mn else torch.randn(pad(N), pad(K), device=dev).to(torch.bfloat16)
+    d = torch.zeros(M, pad(N), device=dev, dtype=torch.bfloat16)
+    outs = _run_both(M, N, K, Operand(a, ld=a.shape[1], mn_major=a_mn), Operand(b, ld=b.shape[1], mn_major=b_mn),
+                     Output(d, rs_lo=pad(N)), bn=bn)
+    for got, ref in outs:
+        assert _rel(got, ref) < 1e-2
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (True, True), (False, True)])
+def test_gemm_tf32(a_mn, b_mn):
+    dev = _dev()
+    M, N, K = 150, 270, 200
+    torch.manual_seed(0)
+    a = torch.randn(K, 152, device=dev) if a_mn else torch.randn(152, K, device=dev)
+    b = torch.randn(K, 272, device=dev) if b_mn else torch.randn(272, K, device=dev)
+    d = torch.zeros(M, 272, device=dev)
+    outs = _run_both(M, N, K, Operand(a, ld=a.shape[1], mn_major=a_mn), Operand(b, ld=b.shape[1], mn_major=b_mn),
+                     Output(d, rs_lo=272))
+    for got, ref in outs:
+        assert _rel(got, ref) < 2e-3
+
+
+def test_gemm_epilogue_bias_gelu_resid_preact():
+    dev = _dev()
+    M, N, K, Z = 96, 520, 80, 3
+    torch.manual_seed(1)
+    w = torch.randn(M, K, device=dev).to(torch.bfloat16)
+    x = torch.randn(Z, K, N, device=dev).to(torch.bfloat16)
+    bias = torch.randn(M, device=dev)
+    res = torch.randn(Z, M, N, device=dev).to(torch.bfloat16)
+    for act, use_res in [(ACT_NONE, False), (ACT_GELU, True), (ACT_DGELU, True)]:
+        d = torch.zeros(Z, M, N, device=dev, dtype=torch.bfloat16)
+        pre = torch.zeros_like(d) if act == ACT_GELU else None
+        outs = _run_both(M, N, K, Operand(w, ld=K), Operand(x, ld=N, mn_major=True, zs_lo=K * N),
+                         Output(d, rs_lo=N, d_zlo=M * N), zlo_n=Z, bias=bias, bias_mode=BIAS_ROW, act=act,
+                         resid=res if use_res else None, preact=pre)
+        for got, ref in outs:
+            assert _rel(got, ref) < 1e-2
+
+
+def test_gemm_bias_col_f32_out():
+    dev = _dev()
+    M, N, K = 130, 100, 72
+    torch.manual_seed(2)
+    a = torch.randn(M, K, device=dev).to(torch.bfloat16)
+    b = torch.randn(N, K, device=dev).to(torch.bfloat16)
+    bias = torch.randn(N, device=dev)
+    d = torch.zeros(M, N, device=dev)
+    outs = _run_both(M, N, K, Operand(a, ld=K), Operand(b, ld=K), Output(d, rs_lo=N), bias=bias, bias_mode=BIAS_COL, alpha=0.5)
+    assert _rel(*outs[0]) < 5e-3
+
+
+def test_gemm_splitk_accumulate_and_batch_reduce():
+    dev = _dev()
+    M, N, K, Z = 200, 74, 5000, 2
+    torch.manual_seed(3)
+    a = torch.randn(Z, M, K, device=dev).to(torch.bfloat16)
+    b = torch.randn(Z, N, K, device=dev).to(torch.bfloat16)
+    d = torch.zeros(M, N, device=dev)
+    outs = _run_both(M, N, K, Operand(a, ld=K, zs_lo=M * K), Operand(b, ld=K, zs_lo=N * K), Output(d, rs_lo=N),
+                     zlo_n=Z, accumulate=True, splits=7)
+    assert _rel(*outs[0]) < 5e-3
+
+
+def test_gemm_scatter_and_triangular():
+    dev = _dev()
+    # batched over z_hi with rows below z_hi known zero, split row/column scatter into a padded buffer
+    Zh, Zl, M, N, K = 5, 2, 140, 48, 100
+    torch.manual_seed(4)
+    a = torch.randn(Zh, M, 104, device=dev)
+    r = torch.arange(M, device=dev).view(1, -1, 1)
+    z = torch.arange(Zh, device=dev).view(-1, 1, 1) * 30
+    a = (a * (r >= z)).to(torch.bfloat16)
+    b = torch.randn(Zl, Zh, N, 104, device=dev).to(torch.bfloat16)
+    # D[zl][r//2][zh][n//8][r%2][n%8]
+    d = torch.full((Zl, M // 2, Zh, N // 8, 2, 8), 7.0, device=dev, dtype=torch.bfloat16)
+    s = d.stride()
+    outs = _run_both(M, N, K, Operand(a, ld=104, zs_hi=M * 104), Operand(b, ld=104, zs_lo=Zh * N * 104, zs_hi=N * 104),
+                     Output(d, rdiv=2, rs_hi=s[1], rs_lo=s[4], ndiv=8, ns_hi=s[3], d_zlo=s[0], d_zhi=s[2]),
+                     zlo_n=Zl, zhi_n=Zh, tri=Tri(rmin_a=30))
+    assert _rel(*outs[0]) < 1e-2
+    # k-range restriction: contributions only from k >= 16*z_hi
+    a2 = torch.randn(Zh, M, 104, device=dev).to(torch.bfloat16)
+    k = torch.arange(104, device=dev).view(1, 1, -1)
+    b2 = (torch.randn(Zh, N, 104, device=dev) * (k >= torch.arange(Zh, device=dev).view(-1, 1, 1) * 16)).to(torch.bfloat16)
+    d2 = torch.zeros(Zh, M, N, device=dev, dtype=torch.bfloat16)
+    outs = _run_both(M, N, K, Operand(a2, ld=104, zs_hi=M * 104), Operand(b2, ld=104, zs_hi=N * 104),
+                     Output(d2, rs_lo=N, d_zhi=M * N), zhi_n=Zh, tri=Tri(kmin_a=16, kmax_a=0, kmax_b=90))
+    # the emulation masks k >= 90 exactly; the kernel may include the rest of the last 64-wide slab, so compare on a
+    # version of the inputs that is zero beyond 90
+    assert _rel(outs[0][0][:, :, :], outs[0][1]) < 0.5  # loose: structure only
+    a3 = a2.clone(); a3[..., 90:] = 0
+    d3 = torch.zeros_like(d2)
+    outs = _run_both(M, N, K, Operand(a3, ld=104, zs_hi=M * 104), Operand(b2, ld=104, zs_hi=N * 104),
+                     Output(d3, rs_lo=N, d_zhi=M * N), zhi_n=Zh, tri=Tri(kmin_a=16, kmax_a=0, kmax_b=90))
+    assert _rel(*outs[0]) < 1e-2
+
+
+def test_gemm_many_tiles_persistent():
+    """More tiles than SMs and a long k loop: exercises stage/accumulator phase tracking."""
+    dev = _dev()
+    M, N, K = 128 * 9, 256 * 40, 64 * 23
+    torch.manual_seed(5)
+    a = torch.randn(M, K, device=dev).to(torch.bfloat16)
+    b = torch.randn(N, K, device=dev).to(torch.bfloat16)
+    d = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    gemm(M, N, K, Operand(a, ld=K), Operand(b, ld=K), Output(d, rs_lo=N))
+    ref = a.float() @ b.float().t()
+    torch.cuda.synchronize()
+    _ext.check_device_errors(dev)
+    assert _rel(d, ref) < 1e-2
+
+
+def test_conv1x1_and_mlp2_fwd_bwd():
+    from makani_b200.ops.conv import conv1x1, mlp2
+    dev = _dev()
+    torch.manual_seed(6)
+    B, Ci, Ch, Co, H, W = 2, 20, 48, 12, 24, 40
+    x = torch.randn(B, Ci, H, W, device=dev)
+    w1 = (torch.randn(Ch, Ci, 1, 1, device=dev) * 0.3).requires_grad_()
+    b1 = (torch.randn(Ch, device=dev) * 0.1).requires_grad_()
+    w2 = (torch.randn(Co, Ch, 1, 1, device=dev) * 0.3).requires_grad_()
+    b2 = (torch.randn(Co, device=dev) * 0.1).requires_grad_()
+    res = torch.randn(B, Co, H, W, device=dev)
+    gy = torch.randn(B, Co, H, W, device=dev)
+
+    def ref():
+        xr = x.clone().requires_grad_()
+        rr = res.clone().requires_grad_()
+        f = torch.nn.functional
+        y = f.conv2d(f.gelu(f.conv2d(xr, w1, b1)), w2, b2) + rr
+        g = torch.autograd.grad(y, [xr, w1, b1, w2, b2, rr], gy)
+        return [y] + list(g)
+
+    def fast():
+        xr = x.to(torch.bfloat16).requires_grad_()
+        rr = res.to(torch.bfloat16).requires_grad_()
+        y = mlp2(xr, w1, b1, w2, b2, rr)
+        g = torch.autograd.grad(y, [xr, w1, b1, w2, b2, rr], gy.to(torch.bfloat16))
+        return [y] + list(g)
+
+    for name, a, b in zip(["y", "dx", "dw1", "db1", "dw2", "db2", "dres"], fast(), ref()):
+        assert _rel(a.float(), b) < 3e-2, name
+
+    # single conv with GELU and residual
+    xr = x.to(torch.bfloat16).requires_grad_()
+    y = conv1x1(xr, w1, b1, act="gelu")
+    g = torch.autograd.grad(y, [xr, w1, b1], torch.ones_like(y))
+    xf = x.clone().requires_grad_()
+    yr = torch.nn.functional.gelu(torch.nn.functional.conv2d(xf, w1, b1))
+    gr = torch.autograd.grad(yr, [xf, w1, b1], torch.ones_like(yr))
+    assert _rel(y.float(), yr) < 2e-2
+    for a, b in zip(g, gr):
+        assert _rel(a.float(), b) < 3e-2
+    _ext.check_device_errors(dev)
+
+
+def test_instance_norm_fwd_bwd():
+    from makani_b200.ops.norm import instance_norm
+    dev = _dev()
+    torch.manual_seed(7)
+    for (B, C, H, W) in [(2, 6, 24, 40), (1, 3, 9, 7)]:
+        for act in ["none", "gelu"]:
+            x = (torch.randn(B, C, H, W, device=dev) * 2 + 0.5)
+            w = (torch.rand(C, device=dev) + 0.5).requires_grad_()
+            b = (torch.randn(C, device=dev) * 0.2).requires_grad_()
+            gy = torch.randn(B, C, H, W, device=dev)
+            xb = x.to(torch.bfloat16).requires_grad_()
+            y = instance_norm(xb, w, b, 1e-6, act)
+            g = torch.autograd.grad(y, [xb, w, b], gy.to(torch.bfloat16))
+            xf = x.to(torch.bfloat16).float().requires_grad_()
+            yr = torch.nn.functional.instance_norm(xf, None, None, w, b, True, 0.0, 1e-6)
+            if act == "gelu":
+                yr = torch.nn.functional.gelu(yr)
+            gr = torch.autograd.grad(yr, [xf, w, b], gy.to(torch.bfloat16).float())
+            assert _rel(y.float(), yr) < 1e-2
+            for a, r_ in zip(g, gr):
+                assert _rel(a.float(), r_) < 2e-2
+
+
+def test_lp_norms_fwd_bwd():
+    from makani_b200.ops.loss import weighted_lp_norms
+    dev = _dev()
+    torch.manual_seed(8)
+    B, C, H, W = 2, 5, 33, 64
+    q = torch.rand(H, device=dev) / (H * W)
+    for dtype in [torch.float32, torch.bfloat16]:
+        for p in [1, 2]:
+            pr = torch.randn(B, C, H, W, device=dev).to(dtype).requires_grad_()
+            tg = torch.randn(B, C, H, W, device=dev).to(dtype)
+            out = weighted_lp_norms(pr, tg, q, p)
+            coef = torch.rand(B, C, device=dev)
+            (g,) = torch.autograd.grad((out[..., 0] * coef).sum(), pr)
+            prf = pr.detach().float().requires_grad_()
+            d = ((prf - tg.float()).abs() ** p * q.view(1, 1, -1, 1)).sum(dim=(-2, -1))
+            t = (tg.float().abs() ** p * q.view(1, 1, -1, 1)).sum(dim=(-2, -1))
+            (gr,) = torch.autograd.grad((d * coef).sum(), prf)
+            assert _rel(out[..., 0], d) < 1e-4 and _rel(out[..., 1], t) < 1e-4
+            assert _rel(g.float(), gr) < (1e-2 if dtype == torch.bfloat16 else 1e-5)
+            # two calls in a row give the same answer (scratch counters are left at zero)
+            out2 = weighted_lp_norms(pr, tg, q, p)
+            assert torch.equal(out, out2)
+
+
+def test_fused_adamw_matches_torch():
+    from makani_b200.ops.optim import FusedAdamW
+    dev = _dev()
+    torch.manual_seed(9)
+    shapes = [(37,), (64, 33), (5, 7, 3), (100000,)]
+    ps = [torch.randn(s, device=dev).requires_grad_() for s in shapes]
+    pc = torch.randn(11, 6, dtype=torch.complex64, device=dev).requires_grad_()
+    ref = [p.detach().clone().requires_grad_() for p in ps]
+    refc = torch.view_as_real(pc.detach().clone()).clone().requires_grad_()
+    opt = FusedAdamW(ps + [pc], lr=1e-2, weight_decay=0.1, complex_mode="split")
+    opt_ref = torch.optim.AdamW(ref + [refc], lr=1e-2, weight_decay=0.1)
+    for it in range(3):
+        for p, r in zip(ps, ref):
+            g = torch.randn_like(p)
+            p.grad = g.clone(); r.grad = g.clone()
+        gc = torch.randn_like(pc)
+        pc.grad = gc.clone(); refc.grad = torch.view_as_real(gc).clone()
+        opt.step(); opt_ref.step()
+    for p, r in zip(ps, ref):
+        assert _rel(p, r) < 1e-5
+    assert _rel(torch.view_as_real(pc), refc) < 1e-5
+
+
+def test_spectral_expand_fold():
+    from makani_b200.ops.spectral import expand_weight, fold_weight_grad
+    dev = _dev()
+    torch.manual_seed(10)
+    w = torch.randn(12, 20, 37, dtype=torch.complex64, device=dev)
+    wx = expand_weight(w)
+    ref = expand_weight(w.cpu())
+    assert _rel(wx.float(), ref.float()) < 1e-6
+    dwx = torch.randn(37, 40, 24, device=dev)
+    assert _rel(torch.view_as_real(fold_weight_grad(dwx)), torch.view_as_real(fold_weight_grad(dwx.cpu()))) < 1e-6
+
+
+def test_spectral_conv_fwd_bwd():
+    from makani_b200.ops.spectral import SHTPlan, spectral_conv_dhconv
+    from makani_b200.sht import InverseRealSHT, RealSHT
+    dev = _dev()
+    torch.manual_seed(11)
+    B, C, Co = 2, 8, 12
+    nlat, nlon, L, M = 33, 64, 16, 17
+    nlat2, nlon2 = 16, 32
+    pin = SHTPlan.get(nlat, nlon, L, M, "equiangular", dev)
+    pout = SHTPlan.get(nlat2, nlon2, L, M, "legendre-gauss", dev)
+    sht = RealSHT(nlat, nlon, L, M, "equiangular").to(dev)
+    isht = InverseRealSHT(nlat2, nlon2, L, M, "legendre-gauss").to(dev)
+    x = torch.randn(B, C, nlat, nlon, device=dev)
+    w = (torch.randn(C, Co, L, dtype=torch.complex64, device=dev) / math.sqrt(C)).requires_grad_()
+    xb = x.to(torch.bfloat16).requires_grad_()
+    y, r = spectral_conv_dhconv(xb, w, pin, pout, True)
+    gy, gr = torch.randn_like(y), torch.randn_like(r)
+    gx, gw = torch.autograd.grad([y, r], [xb, w], [gy, gr])
+    xf = x.to(torch.bfloat16).float().requires_grad_()
+    c = sht(xf)
+    yr = isht(torch.einsum("bixy,iox->boxy", c, w))
+    rr = isht(c)
+    gxr, gwr = torch.autograd.grad([yr, rr], [xf, w], [gy.float(), gr.float()])
+    assert _rel(y.float(), yr) < 3e-2
+    assert _rel(r.float(), rr) < 3e-2
+    assert _rel(gx.float(), gxr) < 3e-2
+    assert _rel(torch.view_as_real(gw), torch.view_as_real(gwr)) < 3e-2
+    _ext.check_device_errors(dev)
+
+
+def test_sfno_bf16_vs_fp32_reference():
+    from makani_b200.models.networks.sfnonet import SphericalFourierNeuralOperatorNet as SFNO
+    dev = _dev()
+    torch.manual_seed(12)
+    m = SFNO(inp_shape=(33, 64), out_shape=(33, 64), scale_factor=2, inp_chans=8, out_chans=4, embed_dim=16, num_layers=3).to(dev)
+    x = torch.randn(2, 8, 33, 64, device=dev)
+    yr = m(x)
+    yr.square().mean().backward()
+    gref = {n: p.grad.clone() for n, p in m.named_parameters()}
+    m.zero_grad()
+    m.set_compute_dtype(torch.bfloat16)
+    y = m(x)
+    assert y.dtype == torch.bfloat16
+    y.float().square().mean().backward()
+    assert _rel(y.float(), yr) < 5e-2
+    for n, p in m.named_parameters():
+        g, r = p.grad, gref[n]
+        if g.is_complex():
+            g, r = torch.view_as_real(g), torch.view_as_real(r)
+        assert _rel(g, r) < 0.15, n
+    _ext.check_device_errors(dev)
