@@ -151,8 +151,10 @@ def main():
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     ev0.record()
+    torch.cuda.profiler.start()     # lets `ncu --profile-from-start off` capture exactly the timed steps
     for _ in range(args.steps):
         loss = runner.step(inp, tgt)
+    torch.cuda.profiler.stop()
     ev1.record()
     barrier()
     launches = _ext.launch_count() - l0

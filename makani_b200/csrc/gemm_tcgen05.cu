@@ -20,7 +20,8 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int A_STAGE_BYTES = BM * 128;
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;   // TMA warp + MMA warp + 8 epilogue warps
+constexpr int MAX_STAGES = 6;
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;   // 2 s per barrier wait
 
 struct KParams {
@@ -42,6 +43,7 @@ struct KParams {
   int out_f32, accumulate, vec_ok;
   int m_tiles, n_tiles;
   long long total_tiles;
+  int stages, e_tma;
   int* err;
 };
 
@@ -153,10 +155,31 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes
   return d;
 }
 
-__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
+// Standard normal CDF via the Abramowitz-Stegun 7.1.26 rational form of erf (|error| < 1.5e-7, far below the bf16
+// output rounding): a short chain of FMAs plus one reciprocal and one exponential.
+__device__ __forceinline__ float norm_cdf_and_pdf(float x, float& pdf) {
+  const float ax = fabsf(x) * 0.70710678118654752f;
+  const float t = __frcp_rn(1.0f + 0.3275911f * ax);
+  const float ex = __expf(-ax * ax);            // exp(-x^2/2)
+  float poly = 1.061405429f;
+  poly = poly * t - 1.453152027f;
+  poly = poly * t + 1.421413741f;
+  poly = poly * t - 0.284496736f;
+  poly = poly * t + 0.254829592f;
+  const float erf_abs = 1.0f - poly * t * ex;
+  pdf = 0.3989422804014327f * ex;
+  const float half_erf = 0.5f * erf_abs;
+  return x >= 0.f ? 0.5f + half_erf : 0.5f - half_erf;
+}
+__device__ __forceinline__ float gelu_erf(float x) {
+  float pdf;
+  return x * norm_cdf_and_pdf(x, pdf);
+}
 // d/dx of the exact GELU: Phi(x) + x * phi(x)
 __device__ __forceinline__ float gelu_grad(float x) {
-  return 0.5f * (1.0f + erff(x * 0.70710678118654752f)) + x * 0.3989422804014327f * __expf(-0.5f * x * x);
+  float pdf;
+  const float cdf = norm_cdf_and_pdf(x, pdf);
+  return cdf + x * pdf;
 }
 
 struct TileCoord {
@@ -195,16 +218,20 @@ __device__ __forceinline__ TileCoord decode_tile(const KParams& p, long long t) 
   return c;
 }
 
+constexpr int STG_BYTES = 0;
+
 template <int BN, int EB>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const KParams p) {
+gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+            const __grid_constant__ CUtensorMap map_e, const KParams p) {
   constexpr int BK = 128 / EB;            // elements per 128-byte k-slab
   constexpr int UMMA_K = 32 / EB;         // elements per tcgen05.mma
   constexpr int B_STAGE_BYTES = BN * 128;
   constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-  constexpr int STAGES = (BN == 256) ? 4 : 6;
-  constexpr int MN_BOX = 128 / EB;        // rows of an MN-major box along the contiguous dimension
+  constexpr int MN_BOX = 128 / EB;        // extent of an MN-major box along the contiguous dimension
   constexpr uint32_t TMEM_COLS = 2 * BN;
+  constexpr int E_BYTES = BM * BN * 2;    // bf16 epilogue-operand tile
+  const int STAGES = p.stages;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -212,14 +239,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   uint8_t* smem = smem_raw + pad;
   const uint32_t smem_base = raw_addr + pad;
 
-  // barrier block lives after the stages
-  uint8_t* bar_ptr = smem + STAGES * STAGE_BYTES;
-  const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+  // layout: [stages][E tile x2 (optional)][staging][barriers]
+  const uint32_t e_off = STAGES * STAGE_BYTES;
+  const uint32_t stg_off = e_off + (p.e_tma ? 2 * E_BYTES : 0);
+  const uint32_t bar_off = stg_off + STG_BYTES;
+  uint8_t* bar_ptr = smem + bar_off;
+  const uint32_t bar_base = smem_base + bar_off;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
-  auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
-  auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_ptr + 8 * (2 * STAGES + 4));
+  auto empty_bar = [&](int s) { return bar_base + 8u * (MAX_STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * MAX_STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * MAX_STAGES + 2 + b); };
+  auto efull_bar = [&](int b) { return bar_base + 8u * (2 * MAX_STAGES + 4 + b); };
+  auto eempty_bar = [&](int b) { return bar_base + 8u * (2 * MAX_STAGES + 6 + b); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_ptr + 8 * (2 * MAX_STAGES + 8));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -231,7 +263,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(tfull_bar(b), 1);
-      mbar_init(tempty_bar(b), 4);
+      mbar_init(tempty_bar(b), 8);
+      mbar_init(efull_bar(b), 1);
+      mbar_init(eempty_bar(b), 8);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -251,18 +285,31 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      uint32_t it = 0;
+      int s = 0;
+      uint32_t ph = 0, epi_it = 0;
       bool ok = true;
       for (long long t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
         const TileCoord c = decode_tile<BK>(p, t);
-        if (c.skip) continue;
         const int m0 = c.mt * BM, n0 = c.nt * BN;
+        if (p.e_tma && !(c.skip && p.accumulate)) {
+          // epilogue operand (residual / saved pre-activation) for this tile
+          const int eb = epi_it & 1;
+          if (!mbar_wait(eempty_bar(eb), ((epi_it >> 1) & 1u) ^ 1u)) {
+            atomicExch(p.err, 5);
+            break;
+          }
+          mbar_expect_tx(efull_bar(eb), E_BYTES);
+#pragma unroll
+          for (int j = 0; j < BN / 64; ++j)
+            tma_load_4d(smem_base + e_off + eb * E_BYTES + j * (BM * 128), &map_e, efull_bar(eb), n0 + j * 64, m0, c.zlo,
+                        c.zhi);
+          ++epi_it;
+        }
+        if (c.skip) continue;
         const int azl = p.a_zlo ? c.zlo : 0, azh = p.a_zhi ? c.zhi : 0;
         const int bzl = p.b_zlo ? c.zlo : 0, bzh = p.b_zhi ? c.zhi : 0;
-        for (int k = c.k_begin; k < c.k_end; k += BK, ++it) {
-          const int s = it % STAGES;
-          const uint32_t par = ((it / STAGES) & 1u) ^ 1u;
-          if (!mbar_wait(empty_bar(s), par)) {
+        for (int k = c.k_begin; k < c.k_end; k += BK) {
+          if (!mbar_wait(empty_bar(s), ph ^ 1u)) {
             atomicExch(p.err, 1);
             ok = false;
             break;
@@ -284,6 +331,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             for (int j = 0; j < BN / MN_BOX; ++j)
               tma_load_4d(sb + j * (BK * 128), &map_b, full_bar(s), n0 + j * MN_BOX, k, bzl, bzh);
           }
+          if (++s == STAGES) {
+            s = 0;
+            ph ^= 1u;
+          }
         }
       }
     }
@@ -299,7 +350,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       const uint32_t b_lbo = p.b_mn ? BK * 128 : 16, b_sbo = 1024;
       const uint32_t a_kstep = p.a_mn ? UMMA_K * 128 : 32;
       const uint32_t b_kstep = p.b_mn ? UMMA_K * 128 : 32;
-      uint32_t it = 0, acc_it = 0;
+      int s = 0;
+      uint32_t ph = 0, acc_it = 0;
       bool ok = true;
       for (long long t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
         const TileCoord c = decode_tile<BK>(p, t);
@@ -312,9 +364,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + buf * BN;
         uint32_t accum = 0;
-        for (int k = c.k_begin; k < c.k_end; k += BK, ++it) {
-          const int s = it % STAGES;
-          if (!mbar_wait(full_bar(s), (it / STAGES) & 1u)) {
+        for (int k = c.k_begin; k < c.k_end; k += BK) {
+          if (!mbar_wait(full_bar(s), ph)) {
             atomicExch(p.err, 3);
             ok = false;
             break;
@@ -330,6 +381,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             accum = 1;
           }
           tc_commit(empty_bar(s));   // frees the smem stage once these MMAs have read it
+          if (++s == STAGES) {
+            s = 0;
+            ph ^= 1u;
+          }
         }
         tc_commit(tfull_bar(buf));   // accumulator complete
         ++acc_it;
@@ -337,21 +392,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     }
   } else {
     // ------------------------------------------------------------------ epilogue warps
+    // Eight warps: warp w serves TMEM lanes [32*(w%4), +32) (one accumulator row per thread) and the 32-column
+    // chunks with (chunk % 2) == (w-2)/4, so two warps per scheduler hide each other's latency.
     const int q = warp & 3;
-    uint32_t acc_it = 0;
+    const int half = (warp - 2) >> 2;
+    uint32_t acc_it = 0, epi_it = 0;
     bool ok = true;
-    const size_t osz = p.out_f32 ? 4 : 2;
     for (long long t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
       const TileCoord c = decode_tile<BK>(p, t);
       if (c.skip && p.accumulate) continue;
-      const int r = c.mt * BM + q * 32 + lane;
+      const int rt = q * 32 + lane;                 // row inside the tile
+      const int r = c.mt * BM + rt;
       const int n0 = c.nt * BN;
       const bool row_ok = r < p.M;
       const long long row_off = static_cast<long long>(c.zhi) * p.d_zhi + static_cast<long long>(c.zlo) * p.d_zlo +
                                 static_cast<long long>(r / p.rdiv) * p.rs_hi + static_cast<long long>(r % p.rdiv) * p.rs_lo;
       float rbias = 0.f;
-      if (p.bias_mode == 1 && row_ok) rbias = p.bias[r];
-      int buf = 0;
+      if (p.bias_mode == 1 && row_ok) rbias = __ldg(p.bias + r);
+      int buf = 0, ebuf = 0;
       if (!c.skip) {
         buf = acc_it & 1;
         if (ok && !mbar_wait(tfull_bar(buf), (acc_it >> 1) & 1u)) {
@@ -360,9 +418,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         }
         tc_fence_after();
       }
-      for (int cc = 0; cc < BN / 32; ++cc) {
+      const uint8_t* esm = nullptr;
+      if (p.e_tma) {
+        ebuf = epi_it & 1;
+        if (ok && !mbar_wait(efull_bar(ebuf), (epi_it >> 1) & 1u)) {
+          atomicExch(p.err, 6);
+          ok = false;
+        }
+        esm = smem + e_off + ebuf * E_BYTES;
+      }
+      for (int cc = half; cc < BN / 32; cc += 2) {
         const int nc = n0 + cc * 32;
-        if (nc >= p.N) break;       // uniform across the CTA
+        if (nc >= p.N) break;       // uniform across the warp
         uint32_t v[32];
         if (!c.skip) {
           const uint32_t taddr = tmem_base + buf * BN + cc * 32 + (static_cast<uint32_t>(q * 32) << 16);
@@ -389,6 +456,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           }
           const bool full = (n + 8 <= p.N);
           const long long off = row_off + static_cast<long long>(n / p.ndiv) * p.ns_hi + (n % p.ndiv);
+          // epilogue operand for these 8 columns (bf16 tile prefetched by TMA, 128-byte swizzle: the 16-byte chunk
+          // index inside each 128-byte row segment is XORed with (row % 8))
+          float e8[8];
+          if (p.e_tma) {
+            const int col = cc * 32 + g * 8;                     // column inside the tile
+            const int box = col >> 6, chunk = (col & 63) >> 3;
+            const uint4 ev = *reinterpret_cast<const uint4*>(esm + box * (BM * 128) + rt * 128 + ((chunk ^ (rt & 7)) << 4));
+            const __nv_bfloat162* eh = reinterpret_cast<const __nv_bfloat162*>(&ev);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 x = __bfloat1622float2(eh[j]);
+              e8[2 * j] = x.x;
+              e8[2 * j + 1] = x.y;
+            }
+          }
           if (full && p.vec_ok && !p.accumulate) {
             // ---- vector path: 8 consecutive columns
             if (p.preact) {
@@ -408,22 +490,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
               for (int j = 0; j < 8; ++j) f[j] = gelu_erf(f[j]);
             }
             if (p.resid) {
-              if (p.out_f32) {
-                const float4* ri = reinterpret_cast<const float4*>(static_cast<const float*>(p.resid) + off);
-                const float4 a = ri[0], b = ri[1];
-                const float rr[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+              if (!p.e_tma) {
+                if (p.out_f32) {
+                  const float4* ri = reinterpret_cast<const float4*>(static_cast<const float*>(p.resid) + off);
+                  const float4 a = ri[0], b = ri[1];
+                  e8[0] = a.x; e8[1] = a.y; e8[2] = a.z; e8[3] = a.w;
+                  e8[4] = b.x; e8[5] = b.y; e8[6] = b.z; e8[7] = b.w;
+                } else {
+                  const uint4 rv = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.resid) + off);
+                  const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&rv);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) f[j] = (p.act == 2) ? f[j] * gelu_grad(rr[j]) : f[j] + rr[j];
-              } else {
-                const uint4 rv = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.resid) + off);
-                const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&rv);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const float2 x = __bfloat1622float2(rh[j]);
-                  f[2 * j] = (p.act == 2) ? f[2 * j] * gelu_grad(x.x) : f[2 * j] + x.x;
-                  f[2 * j + 1] = (p.act == 2) ? f[2 * j + 1] * gelu_grad(x.y) : f[2 * j + 1] + x.y;
+                  for (int j = 0; j < 4; ++j) {
+                    const float2 x = __bfloat1622float2(rh[j]);
+                    e8[2 * j] = x.x;
+                    e8[2 * j + 1] = x.y;
+                  }
                 }
               }
+#pragma unroll
+              for (int j = 0; j < 8; ++j) f[j] = (p.act == 2) ? f[j] * gelu_grad(e8[j]) : f[j] + e8[j];
             }
             if (p.out_f32) {
               float4* o = reinterpret_cast<float4*>(static_cast<float*>(p.D) + off);
@@ -452,8 +537,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 atomicAdd(static_cast<float*>(p.D) + o, x);
               } else {
                 if (p.resid) {
-                  const float rr = p.out_f32 ? static_cast<const float*>(p.resid)[o]
-                                             : __bfloat162float(static_cast<const __nv_bfloat16*>(p.resid)[o]);
+                  float rr;
+                  if (p.e_tma) rr = e8[j];
+                  else rr = p.out_f32 ? static_cast<const float*>(p.resid)[o]
+                                      : __bfloat162float(static_cast<const __nv_bfloat16*>(p.resid)[o]);
                   x = (p.act == 2) ? x * gelu_grad(rr) : x + rr;
                 }
                 if (p.out_f32) static_cast<float*>(p.D)[o] = x;
@@ -463,12 +550,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           }
         }
       }
-      (void)osz;
       if (!c.skip) {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty_bar(buf));
         ++acc_it;
+      }
+      if (p.e_tma) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(eempty_bar(ebuf));
+        ++epi_it;
       }
     }
   }
@@ -551,15 +642,25 @@ bool make_map(CUtensorMap* map, const GemmOperand& op, int K, int eb, int zlo_n,
   return true;
 }
 
+constexpr int SMEM_LIMIT = 232448;   // 227 KB per CTA on sm_100
+
 template <int BN, int EB>
-cudaError_t launch_t(const CUtensorMap& ma, const CUtensorMap& mb, const KParams& kp, cudaStream_t stream) {
-  constexpr int STAGES = (BN == 256) ? 4 : 6;
-  constexpr int SMEM = STAGES * (A_STAGE_BYTES + BN * 128) + 8 * (2 * STAGES + 4) + 16 + 1024;
+cudaError_t launch_t(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& me, KParams& kp, cudaStream_t stream) {
+  constexpr int STAGE = A_STAGE_BYTES + BN * 128;
+  constexpr int FIXED = STG_BYTES + 8 * (2 * MAX_STAGES + 8) + 16 + 1024;
+  const int e_bytes = kp.e_tma ? 2 * BM * BN * 2 : 0;
+  int stages = (SMEM_LIMIT - FIXED - e_bytes) / STAGE;
+  if (stages > MAX_STAGES) stages = MAX_STAGES;
+  if (stages < 2) {
+    snprintf(g_err, sizeof(g_err), "not enough shared memory for the requested tile configuration");
+    return cudaErrorInvalidValue;
+  }
+  kp.stages = stages;
+  const int smem = stages * STAGE + e_bytes + FIXED;
   static bool configured = false;
   static int num_sms = 0;
   if (!configured) {
-    cudaError_t e =
-        cudaFuncSetAttribute(gemm_kernel<BN, EB>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN, EB>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
     if (e != cudaSuccess) return e;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -568,8 +669,28 @@ cudaError_t launch_t(const CUtensorMap& ma, const CUtensorMap& mb, const KParams
   }
   long long grid = kp.total_tiles < num_sms ? kp.total_tiles : num_sms;
   if (grid < 1) grid = 1;
-  gemm_kernel<BN, EB><<<static_cast<unsigned>(grid), NUM_THREADS, SMEM, stream>>>(ma, mb, kp);
+  gemm_kernel<BN, EB><<<static_cast<unsigned>(grid), NUM_THREADS, smem, stream>>>(ma, mb, me, kp);
   return cudaGetLastError();
+}
+
+// tensor map for the epilogue operand: plain [M rows][N contiguous] bf16 with two batch dimensions, no swizzle
+bool make_map_e(CUtensorMap* map, const void* ptr, int M, int N, long long row_stride, long long zs_lo, long long zs_hi,
+                int zlo_n, int zhi_n, int bn) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return false;
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(M), static_cast<cuuint64_t>(zlo_n),
+                        static_cast<cuuint64_t>(zhi_n)};
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>(row_stride) * 2,
+                           static_cast<cuuint64_t>(zlo_n > 1 ? zs_lo : row_stride) * 2,
+                           static_cast<cuuint64_t>(zhi_n > 1 ? zs_hi : row_stride) * 2};
+  (void)bn;
+  cuuint32_t box[4] = {64, BM, 1, 1};   // 64 bf16 = one 128-byte swizzle row
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (strides[0] & 15) || (strides[1] & 15) || (strides[2] & 15)) return false;
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
 }
 
 }  // namespace
@@ -580,6 +701,9 @@ cudaError_t gemm_launch(const GemmProblem& p, const GemmOperand& A, const GemmOp
                         int* err_flag, cudaStream_t stream) {
   g_err[0] = 0;
   if (p.M <= 0 || p.N <= 0 || p.zlo_n <= 0 || p.zhi_n <= 0) return cudaSuccess;
+  // cuTensorMapEncodeTiled is a driver call: make sure this host thread has the primary context bound (threads
+  // that only inherited the device index, e.g. autograd workers, do not until their first runtime call)
+  cudaFree(nullptr);
   const int eb = p.elem_bytes;
   if (eb != 2 && eb != 4) {
     snprintf(g_err, sizeof(g_err), "elem_bytes must be 2 or 4");
@@ -589,6 +713,10 @@ cudaError_t gemm_launch(const GemmProblem& p, const GemmOperand& A, const GemmOp
   if (bn == 0) bn = (p.N > 128) ? 256 : 128;
   if (bn != 128 && bn != 256) {
     snprintf(g_err, sizeof(g_err), "bn must be 128 or 256");
+    return cudaErrorInvalidValue;
+  }
+  if (eb == 4 && (A.mn_major || B.mn_major)) {
+    snprintf(g_err, sizeof(g_err), "tf32 operands must be k-major (row-contiguous tf32 operands are not supported)");
     return cudaErrorInvalidValue;
   }
   if (p.splits > 1 && !e.accumulate) {
@@ -619,30 +747,43 @@ cudaError_t gemm_launch(const GemmProblem& p, const GemmOperand& A, const GemmOp
   kp.alpha = e.alpha; kp.bias = e.bias; kp.bias_mode = e.bias ? e.bias_mode : 0; kp.act = e.act;
   kp.resid = e.resid; kp.preact = e.preact; kp.D = e.D;
   kp.out_f32 = e.out_f32; kp.accumulate = e.accumulate;
-  const int va = e.out_f32 ? 4 : 8;   // elements per 16 bytes
+  // 16-byte vector accesses need every stride (and the bases) aligned
+  const int va = e.out_f32 ? 4 : 8;
   auto al = [&](long long s) { return (s % va) == 0; };
-  const size_t osz = e.out_f32 ? 4 : 2;
+  const uintptr_t amask = 15;
   bool vec = al(e.d_zlo) && al(e.d_zhi) && al(e.rs_hi) && al(e.rs_lo) && al(e.ns_hi) && (kp.ndiv % 8 == 0) &&
-             ((reinterpret_cast<uintptr_t>(e.D) & 15) == 0);
-  if (e.resid) vec = vec && ((reinterpret_cast<uintptr_t>(e.resid) & 15) == 0);
-  if (e.preact) vec = vec && ((reinterpret_cast<uintptr_t>(e.preact) & 15) == 0);
-  (void)osz;
+             ((reinterpret_cast<uintptr_t>(e.D) & amask) == 0);
+  if (e.resid) vec = vec && ((reinterpret_cast<uintptr_t>(e.resid) & amask) == 0);
+  if (e.preact) vec = vec && ((reinterpret_cast<uintptr_t>(e.preact) & amask) == 0);
   kp.vec_ok = vec ? 1 : 0;
   kp.m_tiles = (p.M + BM - 1) / BM;
   kp.n_tiles = (p.N + bn - 1) / bn;
   kp.total_tiles = static_cast<long long>(kp.m_tiles) * kp.n_tiles * kp.splits * p.zlo_n * p.zhi_n;
   kp.err = err_flag;
 
-  CUtensorMap ma, mb;
+  CUtensorMap ma, mb, me;
+  memset(&me, 0, sizeof(me));
+  // Epilogue operand through TMA when it is bf16 and the destination layout is a plain row-major matrix batch.
+  kp.e_tma = 0;
+  const bool plain = (e.rdiv <= 0 || e.rdiv >= (1 << 30)) && (e.ndiv <= 0 || e.ndiv >= (1 << 30));
+  if (e.resid && !e.out_f32 && plain && kp.vec_ok && e.d_zlo >= 0 && e.d_zhi >= 0) {
+    if (make_map_e(&me, e.resid, p.M, p.N, e.rs_lo, e.d_zlo, e.d_zhi, p.zlo_n, p.zhi_n, 128)) {
+      kp.e_tma = 1;
+      bn = 128;
+    }
+  }
+  kp.n_tiles = (p.N + bn - 1) / bn;
+  kp.total_tiles = static_cast<long long>(kp.m_tiles) * kp.n_tiles * kp.splits * p.zlo_n * p.zhi_n;
   if (!make_map(&ma, A, p.K, eb, p.zlo_n, p.zhi_n, BM)) return cudaErrorInvalidValue;
   if (!make_map(&mb, B, p.K, eb, p.zlo_n, p.zhi_n, bn)) return cudaErrorInvalidValue;
+  if (!kp.e_tma) me = ma;   // unused, but must be a valid descriptor
 
   if (eb == 2) {
-    if (bn == 256) return launch_t<256, 2>(ma, mb, kp, stream);
-    return launch_t<128, 2>(ma, mb, kp, stream);
+    if (bn == 256) return launch_t<256, 2>(ma, mb, me, kp, stream);
+    return launch_t<128, 2>(ma, mb, me, kp, stream);
   } else {
-    if (bn == 256) return launch_t<256, 4>(ma, mb, kp, stream);
-    return launch_t<128, 4>(ma, mb, kp, stream);
+    if (bn == 256) return launch_t<256, 4>(ma, mb, me, kp, stream);
+    return launch_t<128, 4>(ma, mb, me, kp, stream);
   }
 }
 

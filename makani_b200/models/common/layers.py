@@ -43,7 +43,8 @@ class PatchEmbed(nn.Module):
         super().__init__()
         self.img_size = img_size
         self.patch_size = patch_size
-        self.num_patches = (img_size[1] // patch_size[1]) * (img_size[0] // patch_size[0])
+        self.red_img_size = (img_size[0] // patch_size[0], img_size[1] // patch_size[1])
+        self.num_patches = self.red_img_size[0] * self.red_img_size[1]
         self.proj = nn.Conv2d(in_chans, embed_dim, kernel_size=patch_size, stride=patch_size)
         self.proj.weight.is_shared_mp = ["spatial"]
         self.proj.bias.is_shared_mp = ["spatial"]
