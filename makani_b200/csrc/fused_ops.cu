@@ -11,9 +11,21 @@ namespace {
 
 constexpr int NT = 512;
 
-__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
+// tanh-form GELU with the hardware tanh approximation (same function as the GEMM epilogues use, so forward and
+// backward stay consistent across kernels); differs from the erf form by < 1e-3 absolute
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float gelu_f(float x) {
+  const float hx = 0.5f * x;
+  return fmaf(hx, tanh_fast(x * fmaf(x * x, 0.0356774081f, 0.7978845608f)), hx);
+}
 __device__ __forceinline__ float dgelu_f(float x) {
-  return 0.5f * (1.0f + erff(x * 0.70710678118654752f)) + x * 0.3989422804014327f * __expf(-0.5f * x * x);
+  const float x2 = x * x;
+  const float t = tanh_fast(x * fmaf(x2, 0.0356774081f, 0.7978845608f));
+  return fmaf(0.5f * x * fmaf(-t, t, 1.0f), fmaf(x2, 0.1070322243f, 0.7978845608f), fmaf(0.5f, t, 0.5f));
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

@@ -1,0 +1,139 @@
+"""Micro-benchmarks of the individual sm_100a kernels with roofline fractions.
+
+    python -m makani_b200.utils.kernel_bench [--case NAME ...] [--hw H W] [--iters N] [--json]
+
+Each case times one kernel launch configuration with CUDA events (after warm-up, L2 flushed between
+iterations by writing a 256 MB buffer) and reports achieved bytes/s and FLOP/s against the measured peaks in
+`MEASURED_PEAKS.json` at the repository root (fallback 6.65 TB/s, 1.59 PFLOP/s when the file is absent).
+Cases mirror the launches of the SFNO-73ch training step so that a profiler can be pointed at exactly one
+of them (`--case conv_fc1 --iters 1`).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from ..ops import _ext
+from ..ops.conv import _conv_dgrad, _conv_fwd, _conv_wgrad, prep_weight
+from ..ops.gemm import ACT_DGELU, ACT_GELU, ACT_NONE, Operand, Output, gemm
+
+
+def _peaks():
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    path = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return d["hbm_gbs"] * 1e9, d["bf16_tflops"] * 1e12, "measured"
+    return 6.65e12, 1.59e15, "fallback"
+
+
+def _time(fn, iters, flush):
+    for _ in range(2):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    times.sort()
+    return times[len(times) // 2] * 1e-3
+
+
+def cases(H, W, dev, B=1):
+    hw = H * W * B
+    bf = torch.bfloat16
+    C, C2 = 384, 768
+    out = {}
+
+    def conv_case(ci, co, act, preact, resid):
+        x = torch.randn(B, ci, H, W, device=dev).to(bf)
+        w = prep_weight(torch.randn(co, ci, device=dev) * 0.05)
+        b = torch.zeros(co, device=dev)
+        r = torch.randn(B, co, H, W, device=dev).to(bf) if resid else None
+        nbytes = (ci + co * (2 if preact else 1) + (co if resid else 0)) * hw * 2
+        flops = 2.0 * ci * co * hw
+        return (lambda: _conv_fwd(x, w, ci, b, act, r, preact)), nbytes, flops
+
+    out["conv_fc1"] = lambda: conv_case(C, C2, ACT_GELU, True, False)          # MLP fc1: bias + GELU + saved pre-activation
+    out["conv_fc2"] = lambda: conv_case(C2, C, ACT_NONE, False, False)         # MLP fc2
+    out["conv_skip"] = lambda: conv_case(C, C, ACT_NONE, False, True)          # outer skip with fused residual add
+    out["conv_plain"] = lambda: conv_case(C, C, ACT_NONE, False, False)
+
+    def dgrad_gelu():
+        dy = torch.randn(1, C, H, W, device=dev).to(bf)
+        w = prep_weight(torch.randn(C, C2, device=dev) * 0.05)
+        pre = torch.randn(1, C2, H, W, device=dev).to(bf)
+        nbytes = (C + 2 * C2) * hw * 2
+        return (lambda: _conv_dgrad(dy, w, C2, act=ACT_DGELU, aux=pre)), nbytes, 2.0 * C * C2 * hw
+
+    out["conv_dgrad_gelu"] = dgrad_gelu
+
+    def wgrad():
+        dy = torch.randn(1, C, H, W, device=dev).to(bf)
+        x = torch.randn(1, C2, H, W, device=dev).to(bf)
+        return (lambda: _conv_wgrad(dy, x)), (C + C2) * hw * 2, 2.0 * C * C2 * hw
+
+    out["conv_wgrad"] = wgrad
+
+    def dft_fwd():
+        from ..ops.spectral import SHTPlan, dft_analysis
+        plan = SHTPlan.get(H, W, H // 3, W // 6 + 1, "equiangular", dev)
+        x = torch.randn(1, C, H, W, device=dev).to(bf)
+        nbytes = C * hw * 2 + plan.k2 * C * plan.hp * 2
+        return (lambda: dft_analysis(x, plan.f, False, plan.nlon, plan.k2, plan.hp)), nbytes, 2.0 * plan.k2 * W * C * H
+
+    out["dft_analysis"] = dft_fwd
+
+    def inorm():
+        from ..ops.norm import instance_norm
+        x = torch.randn(1, C, H, W, device=dev).to(bf)
+        w, b = torch.ones(C, device=dev), torch.zeros(C, device=dev)
+        return (lambda: instance_norm(x, w, b, 1e-6, "gelu")), 3 * C * hw * 2, 0.0
+
+    out["inorm_gelu"] = inorm
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case", nargs="*", default=None)
+    ap.add_argument("--hw", nargs=2, type=int, default=[721, 1440])
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--batch", type=int, default=1, help="images per launch for the conv cases")
+    ap.add_argument("--json", action="store_true")
+    args = ap.parse_args()
+    _ext.require()
+    dev = torch.device("cuda", 0)
+    hbm, flops_peak, src = _peaks()
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    all_cases = cases(args.hw[0], args.hw[1], dev, args.batch)
+    names = args.case or list(all_cases.keys())
+    results = []
+    for name in names:
+        fn, nbytes, flops = all_cases[name]()
+        t = _time(fn, args.iters, flush)
+        _ext.check_device_errors(dev)
+        roof = max(nbytes / hbm, flops / flops_peak)
+        res = dict(case=name, hw=args.hw, seconds=t, gbytes_per_s=nbytes / t / 1e9, tflops=flops / t / 1e12,
+                   roofline_seconds=roof, fraction_of_roofline=roof / t, peaks=src)
+        results.append(res)
+        if not args.json:
+            print(f"{name:18s} {t * 1e3:8.3f} ms  {res['gbytes_per_s']:8.1f} GB/s  {res['tflops']:7.1f} TFLOP/s  "
+                  f"{100 * res['fraction_of_roofline']:5.1f}% of {src} roofline")
+        del fn
+        torch.cuda.empty_cache()
+    if args.json:
+        print(json.dumps(results))
+
+
+if __name__ == "__main__":
+    main()
