@@ -160,6 +160,36 @@ void inorm_bwd(const Tensor& x, const Tensor& dy, c10::optional<Tensor> dx, cons
              "inorm_bwd");
 }
 
+// channels-last instance norm: x is [B, T, C] contiguous (a channels_last NCHW tensor viewed as tokens x channels)
+void inorm_cl_sums(const Tensor& x, const c10::optional<Tensor>& dy, const c10::optional<Tensor>& w, const c10::optional<Tensor>& b,
+                   const c10::optional<Tensor>& stats, Tensor& sums, c10::optional<Tensor> dw, c10::optional<Tensor> db, int64_t B,
+                   int64_t C, int64_t act, int64_t mode) {
+  MK_CHECK(x.is_cuda() && x.scalar_type() == torch::kBFloat16, "inorm_cl_sums: bf16 CUDA expected");
+  MK_CHECK(sums.scalar_type() == torch::kFloat32 && sums.is_contiguous() && sums.numel() == B * C * 2, "inorm_cl_sums: bad sums");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t T = x.numel() / (B * C);
+  auto fp = [](const c10::optional<Tensor>& t) -> float* { return (t.has_value() && t->defined()) ? t->data_ptr<float>() : nullptr; };
+  const __nv_bfloat16* dyp = (dy.has_value() && dy->defined()) ? reinterpret_cast<const __nv_bfloat16*>(dy->data_ptr()) : nullptr;
+  check_cuda(mk::inorm_cl_sums(reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), dyp, fp(w), fp(b), fp(stats), sums.data_ptr<float>(),
+                               fp(dw), fp(db), static_cast<int>(B), static_cast<int>(C), T, static_cast<int>(act), static_cast<int>(mode),
+                               cur_stream()),
+             "inorm_cl_sums");
+}
+
+void inorm_cl_apply(const Tensor& x, const c10::optional<Tensor>& dy, Tensor& out, const c10::optional<Tensor>& w,
+                    const c10::optional<Tensor>& b, const Tensor& sums, c10::optional<Tensor> stats, int64_t B, int64_t C, double count,
+                    double eps, int64_t act, int64_t mode) {
+  MK_CHECK(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && out.scalar_type() == torch::kBFloat16, "inorm_cl_apply: bf16 CUDA expected");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t T = x.numel() / (B * C);
+  auto fp = [](const c10::optional<Tensor>& t) -> float* { return (t.has_value() && t->defined()) ? t->data_ptr<float>() : nullptr; };
+  const __nv_bfloat16* dyp = (dy.has_value() && dy->defined()) ? reinterpret_cast<const __nv_bfloat16*>(dy->data_ptr()) : nullptr;
+  check_cuda(mk::inorm_cl_apply(reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), dyp, reinterpret_cast<__nv_bfloat16*>(out.data_ptr()),
+                                fp(w), fp(b), sums.data_ptr<float>(), fp(stats), static_cast<int>(B), static_cast<int>(C), T, count,
+                                static_cast<float>(eps), static_cast<int>(act), static_cast<int>(mode), cur_stream()),
+             "inorm_cl_apply");
+}
+
 int64_t lp_scratch_floats(int64_t planes, int64_t hw) { return planes * mk::lp_norms_chunks(hw) * 2 + planes; }
 
 void lp_norms(const Tensor& pred, const Tensor& tgt, const Tensor& qlat, Tensor& out, Tensor& scratch, int64_t P) {
@@ -290,6 +320,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("inorm_fwd", &inorm_fwd);
   m.def("inorm_partial_stats", &inorm_partial_stats);
   m.def("inorm_bwd", &inorm_bwd);
+  m.def("inorm_cl_sums", &inorm_cl_sums);
+  m.def("inorm_cl_apply", &inorm_cl_apply);
   m.def("lp_scratch_floats", &lp_scratch_floats);
   m.def("lp_norms", &lp_norms);
   m.def("lp_norms_bwd", &lp_norms_bwd);

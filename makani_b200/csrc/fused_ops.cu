@@ -243,6 +243,154 @@ __global__ void __launch_bounds__(NT) inorm_bwd_kernel(const __nv_bfloat16* __re
   }
 }
 
+// ------------------------------------------------------------------------------------------ instance norm, channels-last
+// x: [B, T, C] with C contiguous (C % 8 == 0, C <= 1024).  Thread (v, r) = (tid % V, tid / V), V = C / 8, owns 8
+// channels and walks the tokens r, r + R, ... of its slab, so per-channel constants stay in registers.
+
+constexpr int CL_THREADS = 512;
+
+// mode 0: sums of (x, x^2).  mode 1: sums of (g, g * xhat) with g = dy * act'(xhat * w + b) for the backward pass.
+template <int MODE>
+__global__ void __launch_bounds__(CL_THREADS) inorm_cl_sums_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
+                                                                   const float* __restrict__ w, const float* __restrict__ b,
+                                                                   const float* __restrict__ stats, float* __restrict__ sums,
+                                                                   float* __restrict__ dw, float* __restrict__ db, int C, long long T,
+                                                                   int act, int slab) {
+  extern __shared__ float sh_acc[];   // [C][2]
+  const int V = C >> 3;
+  const int R = CL_THREADS / V;
+  const int v = threadIdx.x % V, r = threadIdx.x / V;
+  const int bidx = blockIdx.y;
+  for (int i = threadIdx.x; i < 2 * C; i += CL_THREADS) sh_acc[i] = 0.f;
+  __syncthreads();
+  if (r < R) {
+    float a0[8], a1[8], mean[8], rstd[8], wc[8], bc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      a0[j] = 0.f;
+      a1[j] = 0.f;
+      if (MODE == 1) {
+        const int c = v * 8 + j;
+        mean[j] = stats[(static_cast<long long>(bidx) * C + c) * 2];
+        rstd[j] = stats[(static_cast<long long>(bidx) * C + c) * 2 + 1];
+        wc[j] = w ? w[c] : 1.f;
+        bc[j] = b ? b[c] : 0.f;
+      }
+    }
+    const long long t0 = static_cast<long long>(blockIdx.x) * slab;
+    long long t1 = t0 + slab;
+    if (t1 > T) t1 = T;
+    const uint4* xv = reinterpret_cast<const uint4*>(x + static_cast<long long>(bidx) * T * C) + v;
+    const uint4* gv = MODE == 1 ? reinterpret_cast<const uint4*>(dy + static_cast<long long>(bidx) * T * C) + v : nullptr;
+    for (long long t = t0 + r; t < t1; t += R) {
+      float f[8];
+      unpack8(xv[t * V], f);
+      if (MODE == 0) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          a0[j] += f[j];
+          a1[j] += f[j] * f[j];
+        }
+      } else {
+        float g[8];
+        unpack8(gv[t * V], g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float xh = (f[j] - mean[j]) * rstd[j];
+          float gg = g[j];
+          if (act) gg *= dgelu_f(xh * wc[j] + bc[j]);
+          a0[j] += gg;
+          a1[j] += gg * xh;
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      atomicAdd(&sh_acc[(v * 8 + j) * 2], a0[j]);
+      atomicAdd(&sh_acc[(v * 8 + j) * 2 + 1], a1[j]);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < 2 * C; i += CL_THREADS) {
+    const float val = sh_acc[i];
+    atomicAdd(sums + static_cast<long long>(bidx) * 2 * C + i, val);
+    if (MODE == 1) {
+      const int c = i >> 1;
+      if ((i & 1) && dw) atomicAdd(dw + c, val);
+      if (!(i & 1) && db) atomicAdd(db + c, val);
+    }
+  }
+}
+
+// mode 0: y = act(xhat * w + b), statistics derived from `sums` (and stored to `stats`).
+// mode 1: dx = rstd * w * (g - s1/T - xhat * s2/T) with (s1, s2) in `sums`, (mean, rstd) in `stats`.
+template <int MODE>
+__global__ void __launch_bounds__(CL_THREADS) inorm_cl_apply_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
+                                                                    __nv_bfloat16* __restrict__ out, const float* __restrict__ w,
+                                                                    const float* __restrict__ b, const float* __restrict__ sums,
+                                                                    float* __restrict__ stats, int C, long long T, float inv_count,
+                                                                    float eps, int act, int slab) {
+  const int V = C >> 3;
+  const int R = CL_THREADS / V;
+  const int v = threadIdx.x % V, r = threadIdx.x / V;
+  const int bidx = blockIdx.y;
+  if (r >= R) return;
+  float k0[8], k1[8], k2[8], k3[8], kw[8], kb[8];   // per-channel constants
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int c = v * 8 + j;
+    const long long sc = (static_cast<long long>(bidx) * C + c) * 2;
+    const float wc = w ? w[c] : 1.f, bc = b ? b[c] : 0.f;
+    kw[j] = wc;
+    kb[j] = bc;
+    if (MODE == 0) {
+      const float mean = sums[sc] * inv_count;
+      const float var = fmaxf(sums[sc + 1] * inv_count - mean * mean, 0.f);
+      const float rstd = rsqrtf(var + eps);
+      k0[j] = wc * rstd;
+      k1[j] = bc - mean * k0[j];
+      if (stats && blockIdx.x == 0 && r == 0) {
+        stats[sc] = mean;
+        stats[sc + 1] = rstd;
+      }
+    } else {
+      k0[j] = stats[sc];          // mean
+      k1[j] = stats[sc + 1];      // rstd
+      k2[j] = sums[sc] * inv_count;
+      k3[j] = sums[sc + 1] * inv_count;
+    }
+  }
+  const long long t0 = static_cast<long long>(blockIdx.x) * slab;
+  long long t1 = t0 + slab;
+  if (t1 > T) t1 = T;
+  const long long base = static_cast<long long>(bidx) * T * C;
+  const uint4* xv = reinterpret_cast<const uint4*>(x + base) + v;
+  const uint4* gv = MODE == 1 ? reinterpret_cast<const uint4*>(dy + base) + v : nullptr;
+  uint4* ov = reinterpret_cast<uint4*>(out + base) + v;
+  for (long long t = t0 + r; t < t1; t += R) {
+    float f[8];
+    unpack8(xv[t * V], f);
+    if (MODE == 0) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float val = fmaf(f[j], k0[j], k1[j]);
+        f[j] = act ? gelu_f(val) : val;
+      }
+    } else {
+      float g[8];
+      unpack8(gv[t * V], g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xh = (f[j] - k0[j]) * k1[j];
+        float gg = g[j];
+        if (act) gg *= dgelu_f(fmaf(xh, kw[j], kb[j]));
+        f[j] = k1[j] * kw[j] * (gg - k2[j] - xh * k3[j]);
+      }
+    }
+    ov[t * V] = pack8(f);
+  }
+}
+
 // ------------------------------------------------------------------------------------------ Lp norms
 
 constexpr int LP_CHUNK = 1 << 16;   // elements of one plane handled by one CTA
@@ -528,6 +676,39 @@ cudaError_t inorm_bwd(const __nv_bfloat16* x, const __nv_bfloat16* dy, __nv_bflo
   const float inv = static_cast<float>(1.0 / count);
   if (vec) inorm_bwd_kernel<true><<<planes, NT, 0, s>>>(x, dy, dx, w, b, stats, dw, db, sums_io, C, hw, inv, act, ext_sums);
   else inorm_bwd_kernel<false><<<planes, NT, 0, s>>>(x, dy, dx, w, b, stats, dw, db, sums_io, C, hw, inv, act, ext_sums);
+  return cudaGetLastError();
+}
+
+static inline bool cl_ok(int C) { return C % 8 == 0 && C >= 8 && C <= 1024 && (CL_THREADS / (C / 8)) >= 1; }
+// tokens per CTA: enough CTAs to fill the machine a few times over, but at least a few passes of the row loop each
+static inline int cl_slab(int C, long long T, int B) {
+  const int R = CL_THREADS / (C / 8);
+  long long target = (4LL * 148 + B - 1) / B;
+  long long slab = (T + target - 1) / target;
+  if (slab < 4LL * R) slab = 4LL * R;
+  return static_cast<int>(slab);
+}
+
+cudaError_t inorm_cl_sums(const __nv_bfloat16* x, const __nv_bfloat16* dy, const float* w, const float* b, const float* stats,
+                          float* sums, float* dw, float* db, int B, int C, long long T, int act, int mode, cudaStream_t s) {
+  if (!cl_ok(C)) return cudaErrorInvalidValue;
+  const int slab = cl_slab(C, T, B);
+  dim3 grid(static_cast<unsigned>((T + slab - 1) / slab), B);
+  const size_t sh = 2 * C * sizeof(float);
+  if (mode == 0) inorm_cl_sums_kernel<0><<<grid, CL_THREADS, sh, s>>>(x, dy, w, b, stats, sums, dw, db, C, T, act, slab);
+  else inorm_cl_sums_kernel<1><<<grid, CL_THREADS, sh, s>>>(x, dy, w, b, stats, sums, dw, db, C, T, act, slab);
+  return cudaGetLastError();
+}
+
+cudaError_t inorm_cl_apply(const __nv_bfloat16* x, const __nv_bfloat16* dy, __nv_bfloat16* out, const float* w, const float* b,
+                           const float* sums, float* stats, int B, int C, long long T, double count, float eps, int act, int mode,
+                           cudaStream_t s) {
+  if (!cl_ok(C)) return cudaErrorInvalidValue;
+  const int slab = cl_slab(C, T, B);
+  dim3 grid(static_cast<unsigned>((T + slab - 1) / slab), B);
+  const float inv = static_cast<float>(1.0 / count);
+  if (mode == 0) inorm_cl_apply_kernel<0><<<grid, CL_THREADS, 0, s>>>(x, dy, out, w, b, sums, stats, C, T, inv, eps, act, slab);
+  else inorm_cl_apply_kernel<1><<<grid, CL_THREADS, 0, s>>>(x, dy, out, w, b, sums, stats, C, T, inv, eps, act, slab);
   return cudaGetLastError();
 }
 

@@ -22,6 +22,17 @@ cudaError_t inorm_bwd(const __nv_bfloat16* x, const __nv_bfloat16* dy, __nv_bflo
                       const float* b, const float* stats, float* dw, float* db, float* sums_io, int planes, int C,
                       long long hw, double count, int act, int ext_sums, cudaStream_t s);
 
+// ---- instance norm on channels-last data x[B, T, C] (C contiguous, C % 8 == 0, C <= 1024) ----
+// sums: [B, C, 2] fp32, zero-initialised by the caller, accumulated atomically.
+//   mode 0: (sum x, sum x^2);   mode 1: (sum g, sum g*xhat), also accumulated over B into dw / db.
+cudaError_t inorm_cl_sums(const __nv_bfloat16* x, const __nv_bfloat16* dy, const float* w, const float* b, const float* stats,
+                          float* sums, float* dw, float* db, int B, int C, long long T, int act, int mode, cudaStream_t s);
+// mode 0: out = act(xhat * w + b) with statistics from `sums` over `count` elements (stats [B, C, 2] written);
+// mode 1: out = dx from the merged backward sums.
+cudaError_t inorm_cl_apply(const __nv_bfloat16* x, const __nv_bfloat16* dy, __nv_bfloat16* out, const float* w, const float* b,
+                           const float* sums, float* stats, int B, int C, long long T, double count, float eps, int act, int mode,
+                           cudaStream_t s);
+
 // ---- quadrature-weighted Lp norms on the sphere ----
 // out[plane] = (sum_hw q[h] |p-t|^P, sum_hw q[h] |t|^P), P in {1,2}.  `scratch` holds
 // planes*chunks*2 floats + planes ints (zero-initialised once; the kernel leaves the counters at zero).

@@ -100,6 +100,19 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(map), "r"(src),
+               "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -213,7 +226,8 @@ __device__ __forceinline__ TileCoord decode_tile(const KParams& p, long long t) 
   return c;
 }
 
-constexpr int STG_BYTES = 0;
+constexpr int STG_WARP_BYTES = 2 * 32 * 128;          // two 32-row x 128-byte staging boxes per epilogue warp
+constexpr int STG_BYTES = 8 * STG_WARP_BYTES;          // specialised epilogues stage tiles here for TMA stores
 
 // EPI selects a compile-time specialised epilogue (bf16 output, 16-byte vector stores, row bias only):
 //   0 generic (all options decided at run time)      1 plain store
@@ -221,7 +235,8 @@ constexpr int STG_BYTES = 0;
 template <int BN, int EB, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-            const __grid_constant__ CUtensorMap map_e, const KParams p) {
+            const __grid_constant__ CUtensorMap map_e, const __grid_constant__ CUtensorMap map_d,
+            const __grid_constant__ CUtensorMap map_p, const KParams p) {
   constexpr int BK = 128 / EB;            // elements per 128-byte k-slab
   constexpr int UMMA_K = 32 / EB;         // elements per tcgen05.mma
   constexpr int B_STAGE_BYTES = BN * 128;
@@ -240,7 +255,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   // layout: [stages][E tile x2 (optional)][staging][barriers]
   const uint32_t e_off = STAGES * STAGE_BYTES;
   const uint32_t stg_off = e_off + (p.e_tma ? 2 * E_BYTES : 0);
-  const uint32_t bar_off = stg_off + STG_BYTES;
+  const uint32_t bar_off = stg_off + (EPI != 0 ? STG_BYTES : 0);
   uint8_t* bar_ptr = smem + bar_off;
   const uint32_t bar_base = smem_base + bar_off;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -425,6 +440,88 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         }
         esm = smem + e_off + ebuf * E_BYTES;
       }
+      if constexpr (EPI != 0) {
+        // ---------------- specialised bf16 epilogues: registers -> swizzled smem box -> TMA store (full lines, clipped
+        // at the matrix edge by the tensor map)
+        const uint32_t stg_base = smem_base + stg_off + (warp - 2) * STG_WARP_BYTES;
+        uint8_t* const stg_ptr = smem + stg_off + (warp - 2) * STG_WARP_BYTES;
+        int sb = 0;
+        for (int bx = half; bx < BN / 64; bx += 2) {
+          const int nb = n0 + bx * 64;
+          if (nb >= p.N) break;
+          uint32_t v[64];
+          if (!c.skip) {
+            const uint32_t taddr = tmem_base + buf * BN + bx * 64 + (static_cast<uint32_t>(q * 32) << 16);
+            tmem_ld32(taddr, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+            tmem_ld32(taddr + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+          } else {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] = 0u;
+          }
+          // the staging box written two stores ago (one for the two-output epilogue) must have been read out
+          if constexpr (EPI == 2) tma_store_wait_read<0>();
+          else tma_store_wait_read<1>();
+          __syncwarp();
+          uint8_t* const box_d = stg_ptr + (EPI == 2 ? 32 * 128 : sb * 32 * 128);
+          uint8_t* const box_p = stg_ptr;
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            const int n = nb + g * 8;
+            float f[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] = fmaf(__uint_as_float(v[g * 8 + j]), p.alpha, rbias);
+            if (p.bias_mode == 2) {
+              if (n + 8 <= p.N) {
+                const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.bias + n));
+                const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.bias + n) + 1);
+                f[0] += b0.x; f[1] += b0.y; f[2] += b0.z; f[3] += b0.w;
+                f[4] += b1.x; f[5] += b1.y; f[6] += b1.z; f[7] += b1.w;
+              } else {
+                for (int j = 0; j < 8 && n + j < p.N; ++j) f[j] += __ldg(p.bias + n + j);
+              }
+            }
+            const uint32_t sw = static_cast<uint32_t>((g ^ (lane & 7)) << 4) + lane * 128;
+            if constexpr (EPI == 2) {
+              __nv_bfloat162 h[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+              *reinterpret_cast<uint4*>(box_p + sw) = *reinterpret_cast<uint4*>(h);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) f[j] = gelu_erf(f[j]);
+            }
+            if constexpr (EPI == 3 || EPI == 4) {
+              const uint4 ev = *reinterpret_cast<const uint4*>(esm + bx * (BM * 128) + rt * 128 + ((g ^ (rt & 7)) << 4));
+              const __nv_bfloat162* eh = reinterpret_cast<const __nv_bfloat162*>(&ev);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 x = __bfloat1622float2(eh[j]);
+                if constexpr (EPI == 3) {
+                  f[2 * j] += x.x;
+                  f[2 * j + 1] += x.y;
+                } else {
+                  f[2 * j] *= gelu_grad(x.x);
+                  f[2 * j + 1] *= gelu_grad(x.y);
+                }
+              }
+            }
+            __nv_bfloat162 h[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+            *reinterpret_cast<uint4*>(box_d + sw) = *reinterpret_cast<uint4*>(h);
+          }
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const int r0 = c.mt * BM + q * 32;
+            if (r0 < p.M) {
+              if constexpr (EPI == 2) tma_store_4d(&map_p, stg_base, nb, r0, c.zlo, c.zhi);
+              tma_store_4d(&map_d, stg_base + (EPI == 2 ? 32 * 128 : sb * 32 * 128), nb, r0, c.zlo, c.zhi);
+            }
+            tma_store_commit();
+          }
+          sb ^= 1;
+        }
+      } else
       for (int cc = half; cc < BN / 32; cc += 2) {
         const int nc = n0 + cc * 32;
         if (nc >= p.N) break;       // uniform across the warp
@@ -437,71 +534,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           for (int j = 0; j < 32; ++j) v[j] = 0u;
         }
         if (!row_ok) continue;
-        if constexpr (EPI != 0) {
-          // ---------------- specialised bf16 epilogues
-          __nv_bfloat16* const dptr = static_cast<__nv_bfloat16*>(p.D);
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const int n = nc + g * 8;
-            if (n >= p.N) break;
-            const long long off = row_off + (p.plain_cols ? static_cast<long long>(n)
-                                                          : static_cast<long long>(n / p.ndiv) * p.ns_hi + (n % p.ndiv));
-            float f[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) f[j] = fmaf(__uint_as_float(v[g * 8 + j]), p.alpha, rbias);
-            float e8[8];
-            if constexpr (EPI == 3 || EPI == 4) {
-              const int col = cc * 32 + g * 8;
-              const int box = col >> 6, chunk = (col & 63) >> 3;
-              const uint4 ev = *reinterpret_cast<const uint4*>(esm + box * (BM * 128) + rt * 128 + ((chunk ^ (rt & 7)) << 4));
-              const __nv_bfloat162* eh = reinterpret_cast<const __nv_bfloat162*>(&ev);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const float2 x = __bfloat1622float2(eh[j]);
-                e8[2 * j] = x.x;
-                e8[2 * j + 1] = x.y;
-              }
-            }
-            if (n + 8 <= p.N) {
-              if constexpr (EPI == 2) {
-                __nv_bfloat162 h[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
-                *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.preact) + off) = *reinterpret_cast<uint4*>(h);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) f[j] = gelu_erf(f[j]);
-              }
-              if constexpr (EPI == 3) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) f[j] += e8[j];
-              }
-              if constexpr (EPI == 4) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) f[j] *= gelu_grad(e8[j]);
-              }
-              __nv_bfloat162 h[4];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
-              *reinterpret_cast<uint4*>(dptr + off) = *reinterpret_cast<uint4*>(h);
-            } else {
-              // ragged right edge of the matrix
-              for (int j = 0; j < 8 && n + j < p.N; ++j) {
-                const int nj = n + j;
-                const long long o = row_off + (p.plain_cols ? static_cast<long long>(nj)
-                                                            : static_cast<long long>(nj / p.ndiv) * p.ns_hi + (nj % p.ndiv));
-                float x = f[j];
-                if constexpr (EPI == 2) {
-                  static_cast<__nv_bfloat16*>(p.preact)[o] = __float2bfloat16(x);
-                  x = gelu_erf(x);
-                }
-                if constexpr (EPI == 3) x += e8[j];
-                if constexpr (EPI == 4) x *= gelu_grad(e8[j]);
-                dptr[o] = __float2bfloat16(x);
-              }
-            }
-          }
-          continue;
-        }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           const int n = nc + g * 8;
@@ -628,6 +660,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   }
 
   // ------------------------------------------------------------------ teardown
+  if constexpr (EPI != 0) {
+    if (warp >= 2 && lane == 0) tma_store_wait_all();
+  }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -708,9 +743,10 @@ bool make_map(CUtensorMap* map, const GemmOperand& op, int K, int eb, int zlo_n,
 constexpr int SMEM_LIMIT = 232448;   // 227 KB per CTA on sm_100
 
 template <int BN, int EB, int EPI>
-cudaError_t launch_t(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& me, KParams& kp, cudaStream_t stream) {
+cudaError_t launch_t(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& me, const CUtensorMap& md,
+                     const CUtensorMap& mp, KParams& kp, cudaStream_t stream) {
   constexpr int STAGE = A_STAGE_BYTES + BN * 128;
-  constexpr int FIXED = STG_BYTES + 8 * (2 * MAX_STAGES + 8) + 16 + 1024;
+  constexpr int FIXED = (EPI != 0 ? STG_BYTES : 0) + 8 * (2 * MAX_STAGES + 8) + 16 + 1024;
   const int e_bytes = kp.e_tma ? 2 * BM * BN * 2 : 0;
   int stages = (SMEM_LIMIT - FIXED - e_bytes) / STAGE;
   if (stages > MAX_STAGES) stages = MAX_STAGES;
@@ -732,13 +768,13 @@ cudaError_t launch_t(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
   }
   long long grid = kp.total_tiles < num_sms ? kp.total_tiles : num_sms;
   if (grid < 1) grid = 1;
-  gemm_kernel<BN, EB, EPI><<<static_cast<unsigned>(grid), NUM_THREADS, smem, stream>>>(ma, mb, me, kp);
+  gemm_kernel<BN, EB, EPI><<<static_cast<unsigned>(grid), NUM_THREADS, smem, stream>>>(ma, mb, me, md, mp, kp);
   return cudaGetLastError();
 }
 
 // tensor map for the epilogue operand: plain [M rows][N contiguous] bf16 with two batch dimensions, no swizzle
 bool make_map_e(CUtensorMap* map, const void* ptr, int M, int N, long long row_stride, long long zs_lo, long long zs_hi,
-                int zlo_n, int zhi_n, int bn) {
+                int zlo_n, int zhi_n, int bn, int box_rows = BM) {
   EncodeTiledFn enc = get_encode();
   if (!enc) return false;
   cuuint64_t dims[4] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(M), static_cast<cuuint64_t>(zlo_n),
@@ -747,7 +783,7 @@ bool make_map_e(CUtensorMap* map, const void* ptr, int M, int N, long long row_s
                            static_cast<cuuint64_t>(zlo_n > 1 ? zs_lo : row_stride) * 2,
                            static_cast<cuuint64_t>(zhi_n > 1 ? zs_hi : row_stride) * 2};
   (void)bn;
-  cuuint32_t box[4] = {64, BM, 1, 1};   // 64 bf16 = one 128-byte swizzle row
+  cuuint32_t box[4] = {64, static_cast<cuuint32_t>(box_rows), 1, 1};   // 64 bf16 = one 128-byte swizzle row
   cuuint32_t estr[4] = {1, 1, 1, 1};
   if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (strides[0] & 15) || (strides[1] & 15) || (strides[2] & 15)) return false;
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
@@ -842,21 +878,31 @@ cudaError_t gemm_launch(const GemmProblem& p, const GemmOperand& A, const GemmOp
   if (!kp.e_tma) me = ma;   // unused, but must be a valid descriptor
 
   kp.plain_cols = (e.ndiv <= 0 || e.ndiv >= (1 << 30)) ? 1 : 0;
-  // pick a specialised epilogue when the launch fits one
+  // pick a specialised epilogue (TMA stores of bf16 tiles) when the launch fits one
   int epi = 0;
-  if (eb == 2 && !e.out_f32 && kp.vec_ok && !e.accumulate && kp.bias_mode != 2) {
+  CUtensorMap md, mp;
+  memset(&md, 0, sizeof(md));
+  md = ma;
+  mp = ma;
+  if (eb == 2 && !e.out_f32 && kp.vec_ok && !e.accumulate && plain && e.d_zlo >= 0 && e.d_zhi >= 0 &&
+      (kp.bias_mode != 2 || (reinterpret_cast<uintptr_t>(e.bias) & 15) == 0)) {
     if (!e.resid && !e.preact && e.act == 0) epi = 1;
     else if (!e.resid && e.preact && e.act == 1) epi = 2;
     else if (e.resid && kp.e_tma && !e.preact && e.act == 0) epi = 3;
     else if (e.resid && kp.e_tma && !e.preact && e.act == 2) epi = 4;
+    if (epi != 0) {
+      bool ok = make_map_e(&md, e.D, p.M, p.N, e.rs_lo, e.d_zlo, e.d_zhi, p.zlo_n, p.zhi_n, bn, 32);
+      if (ok && epi == 2) ok = make_map_e(&mp, e.preact, p.M, p.N, e.rs_lo, e.d_zlo, e.d_zhi, p.zlo_n, p.zhi_n, bn, 32);
+      if (!ok) epi = 0;
+    }
   }
   if (eb == 4) {
-    if (bn == 256) return launch_t<256, 4, 0>(ma, mb, me, kp, stream);
-    return launch_t<128, 4, 0>(ma, mb, me, kp, stream);
+    if (bn == 256) return launch_t<256, 4, 0>(ma, mb, me, md, mp, kp, stream);
+    return launch_t<128, 4, 0>(ma, mb, me, md, mp, kp, stream);
   }
 #define MK_DISPATCH(EPI_)                                                    \
-  if (bn == 256) return launch_t<256, 2, EPI_>(ma, mb, me, kp, stream);      \
-  return launch_t<128, 2, EPI_>(ma, mb, me, kp, stream);
+  if (bn == 256) return launch_t<256, 2, EPI_>(ma, mb, me, md, mp, kp, stream);      \
+  return launch_t<128, 2, EPI_>(ma, mb, me, md, mp, kp, stream);
   switch (epi) {
     case 1: { MK_DISPATCH(1) }
     case 2: { MK_DISPATCH(2) }

@@ -40,7 +40,7 @@ class InstanceNorm2d(nn.InstanceNorm2d):
 
     def forward(self, x, act: str = "none"):
         if x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 4:
-            return norm_ops.instance_norm(x.contiguous(), self.weight, self.bias, self.eps, act)
+            return norm_ops.instance_norm(x, self.weight, self.bias, self.eps, act)
         y = super().forward(x)
         if act == "gelu":
             y = torch.nn.functional.gelu(y)
@@ -313,7 +313,8 @@ class SphericalFourierNeuralOperatorNet(nn.Module):
         wd = self._working_dtype(x)
         if x.dtype != wd:
             x = x.to(wd)
-        x = x.contiguous()
+        if conv_ops.layout_of(x) is None:
+            x = x.contiguous()
 
         if self.big_skip:
             if self.out_shape != self.inp_shape:

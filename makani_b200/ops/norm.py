@@ -1,9 +1,14 @@
 """Instance normalisation over (H, W) with optional fused GELU, fp32 statistics, bf16 data.
 
 Replaces `nn.InstanceNorm2d(affine=True, eps=1e-6)` followed by the block activation
-(makani/models/networks/sfnonet.py:246-252,379).  Forward is one kernel (statistics pass + normalise pass of
-the same CTA, second pass served by L2 where the plane fits); backward is one kernel that recomputes the
-normalised value (and GELU') from the saved input and (mean, rstd) instead of storing them.
+(makani/models/networks/sfnonet.py:246-252,379).  Two layouts are served:
+
+  * channels-last (the internal fast format): a statistics kernel (per-channel sums accumulated in registers,
+    merged with atomics) and an apply kernel whose threads keep their channels' scale/shift in registers;
+  * NCHW: one kernel per (sample, channel) plane doing both passes.
+
+The backward pass recomputes the normalised value (and GELU') from the saved input and (mean, rstd) instead of
+storing them.
 """
 
 from __future__ import annotations
@@ -11,6 +16,10 @@ from __future__ import annotations
 import torch
 
 from . import _ext
+
+
+def _is_cl(x):
+    return x.dim() == 4 and (not x.is_contiguous()) and x.is_contiguous(memory_format=torch.channels_last)
 
 
 class _InstanceNorm(torch.autograd.Function):
@@ -43,10 +52,58 @@ class _InstanceNorm(torch.autograd.Function):
         return dx, dw, db, None, None
 
 
-def instance_norm(x: torch.Tensor, weight, bias, eps: float = 1e-6, act: str = "none") -> torch.Tensor:
-    """y = act(IN(x) * weight + bias) over the last two dims of NCHW `x`."""
-    if x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and x.dim() == 4:
-        return _InstanceNorm.apply(x, weight, bias, eps, 1 if act == "gelu" else 0)
+class _InstanceNormCL(torch.autograd.Function):
+    """Channels-last variant; `reduce_fn` (optional) merges the [B, C, 2] partial sums across a process group and
+    `count` is then the global number of grid points (spatially distributed instance norm)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, eps, act, count, reduce_fn):
+        ext = _ext.require()
+        B, C, H, W = x.shape
+        y = torch.empty_like(x)     # preserves channels_last
+        sums = torch.zeros(B, C, 2, dtype=torch.float32, device=x.device)
+        stats = torch.empty(B, C, 2, dtype=torch.float32, device=x.device)
+        wf = weight.detach().float().contiguous() if weight is not None else None
+        bf = bias.detach().float().contiguous() if bias is not None else None
+        ext.inorm_cl_sums(x, None, None, None, None, sums, None, None, B, C, 0, 0)
+        if reduce_fn is not None:
+            sums = reduce_fn(sums)
+        cnt = float(count if count else H * W)
+        ext.inorm_cl_apply(x, None, y, wf, bf, sums, stats, B, C, cnt, float(eps), int(act), 0)
+        ctx.save_for_backward(x, wf, bf, stats)
+        ctx.act, ctx.cnt, ctx.reduce_fn, ctx.affine = int(act), cnt, reduce_fn, weight is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        ext = _ext.require()
+        x, wf, bf, stats = ctx.saved_tensors
+        B, C, H, W = x.shape
+        if not _is_cl(dy):
+            dy = dy.contiguous(memory_format=torch.channels_last)
+        sums = torch.zeros(B, C, 2, dtype=torch.float32, device=x.device)
+        dw = torch.zeros(C, dtype=torch.float32, device=x.device) if ctx.affine else None
+        db = torch.zeros(C, dtype=torch.float32, device=x.device) if ctx.affine else None
+        ext.inorm_cl_sums(x, dy, wf, bf, stats, sums, dw, db, B, C, ctx.act, 1)
+        if ctx.reduce_fn is not None:
+            sums = ctx.reduce_fn(sums)
+        dx = torch.empty_like(x)
+        ext.inorm_cl_apply(x, dy, dx, wf, bf, sums, stats, B, C, ctx.cnt, 0.0, ctx.act, 1)
+        return dx, dw, db, None, None, None, None
+
+
+def cl_supported(x) -> bool:
+    return x.is_cuda and x.dtype == torch.bfloat16 and _is_cl(x) and x.shape[1] % 8 == 0 and x.shape[1] <= 1024
+
+
+def instance_norm(x: torch.Tensor, weight, bias, eps: float = 1e-6, act: str = "none", count=None, reduce_fn=None) -> torch.Tensor:
+    """y = act(IN(x) * weight + bias) over the last two dims of a 4-D activation `x`."""
+    a = 1 if act == "gelu" else 0
+    if cl_supported(x):
+        return _InstanceNormCL.apply(x, weight, bias, eps, a, count, reduce_fn)
+    if x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 4 and count is None and reduce_fn is None:
+        return _InstanceNorm.apply(x.contiguous(), weight, bias, eps, a)
+    assert count is None and reduce_fn is None, "distributed statistics need the channels-last CUDA path"
     xf = x.float()
     y = torch.nn.functional.instance_norm(xf, None, None, None if weight is None else weight.float(),
                                           None if bias is None else bias.float(), True, 0.0, eps)
@@ -56,7 +113,13 @@ def instance_norm(x: torch.Tensor, weight, bias, eps: float = 1e-6, act: str = "
 
 
 def channel_sums(x: torch.Tensor) -> torch.Tensor:
-    """sum over (batch, H, W) of a NCHW tensor in fp32 (bias gradients)."""
+    """sum over (batch, H, W) of a 4-D activation in fp32 (bias gradients)."""
+    if cl_supported(x):
+        ext = _ext.require()
+        B, C = x.shape[0], x.shape[1]
+        sums = torch.zeros(B, C, 2, dtype=torch.float32, device=x.device)
+        ext.inorm_cl_sums(x, None, None, None, None, sums, None, None, B, C, 0, 0)
+        return sums[..., 0].sum(0)
     if x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous():
         ext = _ext.require()
         B, C = x.shape[0], x.shape[1]

@@ -6,14 +6,14 @@ torch-harmonics RealSHT/InverseRealSHT it imports).  Here every stage is one lau
 engine, and each stage writes its result directly in the layout the next one reads, so no transpose or
 truncation pass ever touches HBM:
 
-    x  [B, C, H, W]                  real grid data (bf16)
-    S1 longitude DFT      -> T1 [B, m, ri, C, Hp]       A = DFT matrix [(m,ri), W]
+    x  [B, H, W, C]                  real grid data, channels-last (bf16)
+    S1 longitude DFT      -> T1 [B, H, (m,ri), C]       A = DFT matrix [(m,ri), W], batched over latitude rows
     S2 Legendre analysis  -> T2 [B, l, m, (ri, C)]      A = P_l^m(theta_k) w_k, batched over m, rows l < m skipped
     S3 complex contraction-> T3 [B, m, l, (ri, Co)]     B = W_l as a real 2x2-block matrix, batched over l, rows m > l skipped
-    S4 Legendre synthesis -> T4 [B, m, ri, Co, Hp']     k-loop restricted to l >= m
-    S5 inverse DFT        -> y  [B, Co, H', W']
+    S4 Legendre synthesis -> T4 [B, H', (m,ri), Co]     k-loop restricted to l >= m
+    S5 inverse DFT        -> y  [B, H', W', Co]
 
-(ri = real/imaginary part, Hp = H padded to a multiple of 8 elements for 16-byte TMA strides.)
+(ri = real/imaginary part; the Legendre tables are padded along latitude to 16-byte TMA strides.)
 The adjoints used by the backward pass are the same five launches with the constant operands read in the
 other major (no transposed copies of the tables are stored).
 """
@@ -81,49 +81,57 @@ class SHTPlan:
 
 
 # ------------------------------------------------------------------------------------------------ stages
-# Row index of the DFT side is j = 2*m + ri, which makes T1/T4 [B, (m,ri), C, Hp] contiguous in j.
+# Activations are channels-last: x is logically [B, C, H, W] and physically [B][k][i][c] (k latitude, i longitude).
+# Row index of the DFT side is j = 2*m + ri.  T1 / T4 are [B, H, 2*mmax, C]; T2 is [B, l, m, (ri, C)];
+# T3 is [B, m, l, (ri, Co)].
 
 
-def dft_analysis(x: torch.Tensor, mat: torch.Tensor, mat_mn: bool, mat_ld: int, k2: int, hp: int) -> torch.Tensor:
-    """T1[b, j, c, k] = sum_i M[j, i] x[b, c, k, i];  M given K-major ([j, i]) or MN-major ([i, j])."""
+def _to_cl(x: torch.Tensor) -> torch.Tensor:
+    if x.is_contiguous(memory_format=torch.channels_last) and not (x.is_contiguous() and x.shape[1] != 1):
+        return x
+    return x.contiguous(memory_format=torch.channels_last)
+
+
+def dft_analysis(x: torch.Tensor, mat: torch.Tensor, mat_mn: bool, mat_ld: int, k2: int) -> torch.Tensor:
+    """T1[b, k, j, c] = sum_i M[j, i] x[b, c, k, i];  M given K-major ([j, i]) or MN-major ([i, j])."""
     B, C, H, W = x.shape
-    t1 = torch.empty(B, k2, C, hp, dtype=x.dtype, device=x.device)
-    gemm(k2, H, W,
+    t1 = torch.empty(B, H, k2, C, dtype=x.dtype, device=x.device)
+    gemm(k2, C, W,
          Operand(mat, ld=mat_ld, mn_major=mat_mn),
-         Operand(x, ld=W, zs_lo=H * W, zs_hi=C * H * W),
-         Output(t1, rs_lo=C * hp, d_zlo=hp, d_zhi=k2 * C * hp),
-         zlo_n=C, zhi_n=B)
+         Operand(x, ld=C, mn_major=True, zs_lo=W * C, zs_hi=H * W * C),
+         Output(t1, rs_lo=C, d_zlo=k2 * C, d_zhi=H * k2 * C),
+         zlo_n=H, zhi_n=B, bn=128 if C <= 128 or C % 256 != 0 else 256)
     return t1
 
 
-def dft_synthesis(t4: torch.Tensor, mat: torch.Tensor, mat_mn: bool, mat_ld: int, H: int, W: int) -> torch.Tensor:
-    """y[b, c, k, i] = sum_j T4[b, j, c, k] M[i, j];  M given K-major ([i, j]) or MN-major ([j, i])."""
-    B, k2, C, hp = t4.shape
-    y = torch.empty(B, C, H, W, dtype=t4.dtype, device=t4.device)
-    gemm(H, W, k2,
-         Operand(t4, ld=C * hp, mn_major=True, zs_lo=hp, zs_hi=k2 * C * hp),
+def dft_synthesis(t4: torch.Tensor, mat: torch.Tensor, mat_mn: bool, mat_ld: int, W: int) -> torch.Tensor:
+    """y[b, c, k, i] = sum_j T4[b, k, j, c] M[i, j];  M given K-major ([i, j]) or MN-major ([j, i]).  y is channels-last."""
+    B, H, k2, C = t4.shape
+    y = torch.empty(B, C, H, W, dtype=t4.dtype, device=t4.device, memory_format=torch.channels_last)
+    gemm(W, C, k2,
          Operand(mat, ld=mat_ld, mn_major=mat_mn),
-         Output(y, rs_lo=W, d_zlo=H * W, d_zhi=C * H * W),
-         zlo_n=C, zhi_n=B)
+         Operand(t4, ld=C, mn_major=True, zs_lo=k2 * C, zs_hi=H * k2 * C),
+         Output(y, rs_lo=C, d_zlo=W * C, d_zhi=H * W * C),
+         zlo_n=H, zhi_n=B, bn=128 if C <= 128 or C % 256 != 0 else 256)
     return y
 
 
-def legendre_analysis(t1: torch.Tensor, table: torch.Tensor, H: int) -> torch.Tensor:
-    """T2[b, l, m, n] = sum_k table[m, l, k] T1[b, m, n, k], n = (ri, c);  zero for l < m."""
-    B, k2, C, hp = t1.shape
+def legendre_analysis(t1: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    """T2[b, l, m, n] = sum_k table[m, l, k] T1[b, k, m, n], n = (ri, c);  zero for l < m."""
+    B, H, k2, C = t1.shape
     mmax, lmax, hpt = table.shape
     n2 = 2 * C
     t2 = torch.empty(B, lmax, mmax, n2, dtype=t1.dtype, device=t1.device)
     gemm(lmax, n2, H,
          Operand(table, ld=hpt, zs_hi=lmax * hpt),
-         Operand(t1, ld=hp, zs_hi=n2 * hp, zs_lo=k2 * C * hp),
+         Operand(t1, ld=k2 * C, mn_major=True, zs_hi=n2, zs_lo=H * k2 * C),
          Output(t2, rs_lo=mmax * n2, d_zhi=n2, d_zlo=lmax * mmax * n2),
          zhi_n=mmax, zlo_n=B, tri=Tri(rmin_a=1))
     return t2
 
 
 def legendre_synthesis(t: torch.Tensor, lm_order: bool, table: torch.Tensor, H: int) -> torch.Tensor:
-    """T4[b, m, n, k] = sum_l T[b, ., ., n] table[m, l, k]  with T given as [b, m, l, n] (lm_order False)
+    """T4[b, k, m, n] = sum_l table[m, l, k] T[b, ., ., n]  with T given as [b, m, l, n] (lm_order False)
     or [b, l, m, n] (lm_order True); only l >= m contributes."""
     if lm_order:
         B, lmax, mmax, n2 = t.shape
@@ -132,12 +140,11 @@ def legendre_synthesis(t: torch.Tensor, lm_order: bool, table: torch.Tensor, H: 
         B, mmax, lmax, n2 = t.shape
         ld, zs_m = n2, lmax * n2
     hpt = table.shape[2]
-    hp = pad_to(H, 8)
-    t4 = torch.empty(B, mmax, n2, hp, dtype=t.dtype, device=t.device).view(B, 2 * mmax, n2 // 2, hp)
-    gemm(n2, H, lmax,
-         Operand(t, ld=ld, mn_major=True, zs_hi=zs_m, zs_lo=lmax * mmax * n2),
+    t4 = torch.empty(B, H, 2 * mmax, n2 // 2, dtype=t.dtype, device=t.device)
+    gemm(H, n2, lmax,
          Operand(table, ld=hpt, mn_major=True, zs_hi=lmax * hpt),
-         Output(t4, rs_lo=hp, d_zhi=n2 * hp, d_zlo=mmax * n2 * hp),
+         Operand(t, ld=ld, mn_major=True, zs_hi=zs_m, zs_lo=lmax * mmax * n2),
+         Output(t4, rs_lo=mmax * n2, d_zhi=n2, d_zlo=H * mmax * n2),
          zhi_n=mmax, zlo_n=B, tri=Tri(kmin_a=1))
     return t4
 
@@ -207,24 +214,25 @@ def fold_weight_grad(dwx: torch.Tensor) -> torch.Tensor:
 
 
 class _SpectralConv(torch.autograd.Function):
-    """y = iSHT_out(W . SHT_in(x)) and, when `want_resid`, r = iSHT_out(SHT_in(x)) (regridded residual)."""
+    """y = iSHT_out(W . SHT_in(x)) and, when `want_resid`, r = iSHT_out(SHT_in(x)) (regridded residual).
+    Input and outputs are channels-last."""
 
     @staticmethod
     def forward(ctx, x, w, plan_in: SHTPlan, plan_out: SHTPlan, want_resid: bool):
-        B, C, H, W = x.shape
+        x = _to_cl(x)
         wx = expand_weight(w, x.dtype)
-        t1 = dft_analysis(x, plan_in.f, False, plan_in.nlon, plan_in.k2, plan_in.hp)
-        t2 = legendre_analysis(t1, plan_in.pw, H)
+        t1 = dft_analysis(x, plan_in.f, False, plan_in.nlon, plan_in.k2)
+        t2 = legendre_analysis(t1, plan_in.pw)
         del t1
         t3 = contract(t2, wx, False)
         t4 = legendre_synthesis(t3, False, plan_out.p, plan_out.nlat)
         del t3
-        y = dft_synthesis(t4, plan_out.gt, False, plan_out.k2p, plan_out.nlat, plan_out.nlon)
+        y = dft_synthesis(t4, plan_out.gt, False, plan_out.k2p, plan_out.nlon)
         del t4
         r = None
         if want_resid:
             t4r = legendre_synthesis(t2, True, plan_out.p, plan_out.nlat)
-            r = dft_synthesis(t4r, plan_out.gt, False, plan_out.k2p, plan_out.nlat, plan_out.nlon)
+            r = dft_synthesis(t4r, plan_out.gt, False, plan_out.k2p, plan_out.nlon)
         ctx.save_for_backward(t2, wx)
         ctx.plans = (plan_in, plan_out)
         ctx.want_resid = want_resid
@@ -237,10 +245,10 @@ class _SpectralConv(torch.autograd.Function):
     def backward(ctx, dy, dr=None):
         t2, wx = ctx.saved_tensors
         plan_in, plan_out = ctx.plans
-        dy = dy.contiguous()
+        dy = _to_cl(dy)
         # adjoint of the inverse DFT / synthesis on the output grid
-        dt4 = dft_analysis(dy, plan_out.gt, True, plan_out.k2p, plan_out.k2, plan_out.hp)
-        dt3 = legendre_analysis(dt4, plan_out.p, plan_out.nlat)        # [B, l, m, (ri, o)]
+        dt4 = dft_analysis(dy, plan_out.gt, True, plan_out.k2p, plan_out.k2)
+        dt3 = legendre_analysis(dt4, plan_out.p)                       # [B, l, m, (ri, o)]
         del dt4
         dw = None
         if ctx.needs_input_grad[1]:
@@ -250,19 +258,19 @@ class _SpectralConv(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dt2 = contract(dt3, wx, True)                              # [B, m, l, (ri, c)]
             if ctx.want_resid and dr is not None:
-                dr = dr.contiguous()
-                dr4 = dft_analysis(dr, plan_out.gt, True, plan_out.k2p, plan_out.k2, plan_out.hp)
-                dr2 = legendre_analysis(dr4, plan_out.p, plan_out.nlat)     # [B, l, m, n]
+                dr = _to_cl(dr)
+                dr4 = dft_analysis(dr, plan_out.gt, True, plan_out.k2p, plan_out.k2)
+                dr2 = legendre_analysis(dr4, plan_out.p)               # [B, l, m, n]
                 dt2 = dt2 + dr2.transpose(1, 2)
                 del dr4, dr2
             dt1 = legendre_synthesis(dt2.contiguous(), False, plan_in.pw, plan_in.nlat)
-            dx = dft_synthesis(dt1, plan_in.f, True, plan_in.nlon, plan_in.nlat, plan_in.nlon)
+            dx = dft_synthesis(dt1, plan_in.f, True, plan_in.nlon, plan_in.nlon)
         return dx, dw, None, None, None
 
 
 def spectral_conv_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
-    return (x.dim() == 4 and x.dtype == torch.bfloat16 and x.is_contiguous() and x.shape[1] % 4 == 0
-            and w.dim() == 3 and w.shape[1] % 4 == 0 and x.shape[3] % 8 == 0)
+    return (x.dim() == 4 and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and w.dim() == 3 and w.shape[1] % 8 == 0
+            and x.shape[3] % 8 == 0)
 
 
 def spectral_conv_dhconv(x, w, plan_in: SHTPlan, plan_out: SHTPlan, want_resid: bool):

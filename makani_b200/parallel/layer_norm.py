@@ -90,19 +90,35 @@ class DistributedInstanceNorm2d(nn.Module):
     def __init__(self, num_features, eps=1e-05, affine=False):
         super().__init__()
         self.eps, self.affine, self.num_features = eps, affine, num_features
+        self._counts = {}
         if affine:
             self.weight = nn.Parameter(torch.ones(num_features))
             self.bias = nn.Parameter(torch.zeros(num_features))
             self.weight.is_shared_mp = ["spatial"]
             self.bias.is_shared_mp = ["spatial"]
 
-    def forward(self, x):
-        # global number of grid points per (sample, channel)
-        cnt = torch.tensor([float(x.shape[-2] * x.shape[-1])], dtype=torch.float64, device=x.device)
-        if comm.get_size("spatial") > 1:
-            dist.all_reduce(cnt, group=comm.get_group("spatial"))
-        return _DistInstanceNormFn.apply(x, self.weight if self.affine else None, self.bias if self.affine else None,
-                                         self.eps, float(cnt.item()))
+    def _global_count(self, x) -> float:
+        """Global number of grid points per (sample, channel); computed once per local tile shape."""
+        key = (x.shape[-2], x.shape[-1])
+        if key not in self._counts:
+            cnt = torch.tensor([float(key[0] * key[1])], dtype=torch.float64, device=x.device)
+            if comm.get_size("spatial") > 1:
+                dist.all_reduce(cnt, group=comm.get_group("spatial"))
+            self._counts[key] = float(cnt.item())
+        return self._counts[key]
+
+    def forward(self, x, act: str = "none"):
+        from ..ops import norm as norm_ops
+        w = self.weight if self.affine else None
+        b = self.bias if self.affine else None
+        cnt = self._global_count(x)
+        if norm_ops.cl_supported(x):
+            # fused channels-last kernels; only the [B, C, 2] partial sums cross the spatial group
+            return norm_ops.instance_norm(x, w, b, self.eps, act, count=cnt, reduce_fn=_allreduce_spatial)
+        y = _DistInstanceNormFn.apply(x, w, b, self.eps, cnt)
+        if act == "gelu":
+            y = torch.nn.functional.gelu(y)
+        return y
 
 
 class DistributedLayerNorm(nn.Module):

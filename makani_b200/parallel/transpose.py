@@ -20,6 +20,24 @@ from ..utils import comm
 from .helpers import compute_split_shapes, split_tensor_along_dim
 
 
+def _all_to_all(recv, send, group, name):
+    """all_to_all with a point-to-point fallback for backends without it (gloo)."""
+    if dist.get_backend(group) != "gloo":
+        dist.all_to_all(recv, send, group=group)
+        return
+    ranks = comm.get_group_ranks(name)
+    me = comm.get_rank(name)
+    recv[me].copy_(send[me])
+    reqs = []
+    for r, gr in enumerate(ranks):
+        if r == me:
+            continue
+        reqs.append(dist.isend(send[r], dst=gr, group=group))
+        reqs.append(dist.irecv(recv[r], src=gr, group=group))
+    for q in reqs:
+        q.wait()
+
+
 def _transpose(x: torch.Tensor, dim0: int, dim1: int, dim1_split_sizes: Sequence[int], name: str):
     size = comm.get_size(name)
     group = comm.get_group(name)
@@ -35,7 +53,7 @@ def _transpose(x: torch.Tensor, dim0: int, dim1: int, dim1_split_sizes: Sequence
         shp = list(send[my].shape)
         shp[dim1] = dim1_split_sizes[r]
         recv.append(torch.empty(shp, dtype=xr.dtype, device=xr.device))
-    dist.all_to_all(recv, send, group=group)
+    _all_to_all(recv, send, group, name)
     out = torch.cat(recv, dim=dim1)
     if is_complex:
         out = torch.view_as_complex(out)

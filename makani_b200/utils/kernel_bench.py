@@ -48,17 +48,18 @@ def _time(fn, iters, flush):
     return times[len(times) // 2] * 1e-3
 
 
-def cases(H, W, dev, B=1):
+def cases(H, W, dev, B=1, layout="cl"):
     hw = H * W * B
     bf = torch.bfloat16
     C, C2 = 384, 768
     out = {}
+    lay = (lambda t: t.contiguous(memory_format=torch.channels_last)) if layout == "cl" else (lambda t: t)
 
     def conv_case(ci, co, act, preact, resid):
-        x = torch.randn(B, ci, H, W, device=dev).to(bf)
+        x = lay(torch.randn(B, ci, H, W, device=dev).to(bf))
         w = prep_weight(torch.randn(co, ci, device=dev) * 0.05)
         b = torch.zeros(co, device=dev)
-        r = torch.randn(B, co, H, W, device=dev).to(bf) if resid else None
+        r = lay(torch.randn(B, co, H, W, device=dev).to(bf)) if resid else None
         nbytes = (ci + co * (2 if preact else 1) + (co if resid else 0)) * hw * 2
         flops = 2.0 * ci * co * hw
         return (lambda: _conv_fwd(x, w, ci, b, act, r, preact)), nbytes, flops
@@ -69,17 +70,17 @@ def cases(H, W, dev, B=1):
     out["conv_plain"] = lambda: conv_case(C, C, ACT_NONE, False, False)
 
     def dgrad_gelu():
-        dy = torch.randn(1, C, H, W, device=dev).to(bf)
+        dy = lay(torch.randn(1, C, H, W, device=dev).to(bf))
         w = prep_weight(torch.randn(C, C2, device=dev) * 0.05)
-        pre = torch.randn(1, C2, H, W, device=dev).to(bf)
+        pre = lay(torch.randn(1, C2, H, W, device=dev).to(bf))
         nbytes = (C + 2 * C2) * hw * 2
         return (lambda: _conv_dgrad(dy, w, C2, act=ACT_DGELU, aux=pre)), nbytes, 2.0 * C * C2 * hw
 
     out["conv_dgrad_gelu"] = dgrad_gelu
 
     def wgrad():
-        dy = torch.randn(1, C, H, W, device=dev).to(bf)
-        x = torch.randn(1, C2, H, W, device=dev).to(bf)
+        dy = lay(torch.randn(1, C, H, W, device=dev).to(bf))
+        x = lay(torch.randn(1, C2, H, W, device=dev).to(bf))
         return (lambda: _conv_wgrad(dy, x)), (C + C2) * hw * 2, 2.0 * C * C2 * hw
 
     out["conv_wgrad"] = wgrad
@@ -87,15 +88,15 @@ def cases(H, W, dev, B=1):
     def dft_fwd():
         from ..ops.spectral import SHTPlan, dft_analysis
         plan = SHTPlan.get(H, W, H // 3, W // 6 + 1, "equiangular", dev)
-        x = torch.randn(1, C, H, W, device=dev).to(bf)
-        nbytes = C * hw * 2 + plan.k2 * C * plan.hp * 2
-        return (lambda: dft_analysis(x, plan.f, False, plan.nlon, plan.k2, plan.hp)), nbytes, 2.0 * plan.k2 * W * C * H
+        x = torch.randn(1, C, H, W, device=dev).to(bf).contiguous(memory_format=torch.channels_last)
+        nbytes = C * hw * 2 + plan.k2 * C * H * 2
+        return (lambda: dft_analysis(x, plan.f, False, plan.nlon, plan.k2)), nbytes, 2.0 * plan.k2 * W * C * H
 
     out["dft_analysis"] = dft_fwd
 
     def inorm():
         from ..ops.norm import instance_norm
-        x = torch.randn(1, C, H, W, device=dev).to(bf)
+        x = lay(torch.randn(1, C, H, W, device=dev).to(bf))
         w, b = torch.ones(C, device=dev), torch.zeros(C, device=dev)
         return (lambda: instance_norm(x, w, b, 1e-6, "gelu")), 3 * C * hw * 2, 0.0
 
@@ -109,13 +110,14 @@ def main():
     ap.add_argument("--hw", nargs=2, type=int, default=[721, 1440])
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--batch", type=int, default=1, help="images per launch for the conv cases")
+    ap.add_argument("--layout", default="cl", choices=["cl", "nchw"], help="activation layout of the conv / norm cases")
     ap.add_argument("--json", action="store_true")
     args = ap.parse_args()
     _ext.require()
     dev = torch.device("cuda", 0)
     hbm, flops_peak, src = _peaks()
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
-    all_cases = cases(args.hw[0], args.hw[1], dev, args.batch)
+    all_cases = cases(args.hw[0], args.hw[1], dev, args.batch, args.layout)
     names = args.case or list(all_cases.keys())
     results = []
     for name in names:

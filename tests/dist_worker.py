@@ -1,0 +1,234 @@
+"""Worker body of the multi-process CPU (gloo) tests; launched by tests/test_distributed.py as
+`python tests/dist_worker.py <case> <h> <w> <fin> <fout>` with RANK/WORLD_SIZE/MASTER_* set."""
+
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from makani_b200.parallel.helpers import compute_split_shapes, gather_uneven, split_tensor_along_dim  # noqa: E402
+from makani_b200.utils import comm  # noqa: E402
+
+
+def _shard(x, dim, name):
+    return split_tensor_along_dim(x, dim, comm.get_size(name))[comm.get_rank(name)].contiguous()
+
+
+def _gather(x, dim, name):
+    return gather_uneven(x, dim, name)
+
+
+def _rel(a, b):
+    return ((a - b).norm() / (b.norm() + 1e-30)).item()
+
+
+def case_topology():
+    ws = comm.get_world_size()
+    sizes = {n: comm.get_size(n) for n in ["h", "w", "fin", "fout", "data", "model", "spatial", "matmul"]}
+    assert sizes["model"] == sizes["h"] * sizes["w"] * sizes["fin"] * sizes["fout"]
+    assert sizes["data"] * sizes["model"] == ws
+    t = torch.ones(1)
+    for name in ["h", "w", "fin", "fout", "data", "model", "spatial", "matmul"]:
+        if sizes[name] > 1:
+            u = t.clone()
+            dist.all_reduce(u, group=comm.get_group(name))
+            assert int(u.item()) == sizes[name], name
+    assert comm.get_root("model") == (comm.get_world_rank() // sizes["model"]) * sizes["model"]
+
+
+def case_sht():
+    from makani_b200.sht import DistributedInverseRealSHT, DistributedRealSHT, InverseRealSHT, RealSHT
+    torch.manual_seed(0)
+    nlat, nlon, L, M, B, C = 33, 64, 20, 21, 2, 6
+    x = torch.randn(B, C, nlat, nlon, dtype=torch.float64)
+    ref_f, ref_i = RealSHT(nlat, nlon, L, M, "equiangular").double(), InverseRealSHT(nlat, nlon, L, M, "equiangular").double()
+    df, di = DistributedRealSHT(nlat, nlon, L, M, "equiangular").double(), DistributedInverseRealSHT(nlat, nlon, L, M, "equiangular").double()
+    xl = _shard(_shard(x, -2, "h"), -1, "w").requires_grad_()
+    xr = x.clone().requires_grad_()
+    c_ref = ref_f(xr)
+    c_loc = df(xl)
+    c_full = _gather(_gather(c_loc, -2, "h"), -1, "w")
+    assert _rel(torch.view_as_real(c_full), torch.view_as_real(c_ref)) < 1e-6
+    # inverse + gradients
+    y_ref = ref_i(c_ref)
+    y_loc = di(c_loc)
+    y_full = _gather(_gather(y_loc, -2, "h"), -1, "w")
+    assert _rel(y_full, y_ref) < 1e-6
+    g = torch.randn_like(y_ref)
+    gl = _shard(_shard(g, -2, "h"), -1, "w")
+    y_ref.backward(g)
+    y_loc.backward(gl)
+    gx_full = _gather(_gather(xl.grad, -2, "h"), -1, "w")
+    assert _rel(gx_full, xr.grad) < 1e-6
+
+
+def case_fft():
+    from makani_b200.models.common.layers import InverseRealFFT2, RealFFT2
+    from makani_b200.parallel.fft3d import DistributedInverseRealFFT3, DistributedRealFFT3, InverseRealFFT3, RealFFT3
+    from makani_b200.parallel.layers import DistributedInverseRealFFT2, DistributedRealFFT2
+    torch.manual_seed(1)
+    for (H, W, B, C, L, M) in [(32, 64, 2, 8, 32, 33), (37, 72, 1, 10, 20, 25)]:
+        x = torch.randn(B, C, H, W, dtype=torch.float64)
+        f_ref, i_ref = RealFFT2(H, W, L, M), InverseRealFFT2(H, W, L, M)
+        f_d, i_d = DistributedRealFFT2(H, W, L, M), DistributedInverseRealFFT2(H, W, L, M)
+        xl = _shard(_shard(x, -2, "h"), -1, "w").requires_grad_()
+        xr = x.clone().requires_grad_()
+        c_ref, c_loc = f_ref(xr), f_d(xl)
+        c_full = _gather(_gather(c_loc, -2, "h"), -1, "w")
+        assert _rel(torch.view_as_real(c_full), torch.view_as_real(c_ref)) < 1e-6
+        y_ref, y_loc = i_ref(c_ref), i_d(c_loc)
+        assert _rel(_gather(_gather(y_loc, -2, "h"), -1, "w"), y_ref) < 1e-6
+        g = torch.randn_like(y_ref)
+        y_ref.backward(g)
+        y_loc.backward(_shard(_shard(g, -2, "h"), -1, "w"))
+        assert _rel(_gather(_gather(xl.grad, -2, "h"), -1, "w"), xr.grad) < 1e-6
+    D, H, W, B, C = 6, 16, 32, 1, 4
+    x = torch.randn(B, C, D, H, W, dtype=torch.float64)
+    f3, i3 = RealFFT3(D, H, W, 4, 10, 12), InverseRealFFT3(D, H, W, 4, 10, 12)
+    d3, di3 = DistributedRealFFT3(D, H, W, 4, 10, 12), DistributedInverseRealFFT3(D, H, W, 4, 10, 12)
+    xl = _shard(_shard(x, -2, "h"), -1, "w")
+    c_ref, c_loc = f3(x), d3(xl)
+    assert _rel(torch.view_as_real(_gather(_gather(c_loc, -2, "h"), -1, "w")), torch.view_as_real(c_ref)) < 1e-6
+    assert _rel(_gather(_gather(di3(c_loc), -2, "h"), -1, "w"), i3(c_ref)) < 1e-6
+
+
+def case_norm_and_loss():
+    from makani_b200.parallel.layer_norm import DistributedInstanceNorm2d
+    from makani_b200.utils.losses import LossHandler
+    from makani_b200.utils.YParams import ParamsBase
+    torch.manual_seed(2)
+    B, C, H, W = 2, 5, 33, 64
+    x = torch.randn(B, C, H, W) * 2 + 1
+    ref = torch.nn.InstanceNorm2d(C, eps=1e-6, affine=True)
+    dn = DistributedInstanceNorm2d(C, eps=1e-6, affine=True)
+    with torch.no_grad():
+        ref.weight.copy_(torch.rand(C) + 0.5); ref.bias.copy_(torch.randn(C))
+        dn.weight.copy_(ref.weight); dn.bias.copy_(ref.bias)
+    xl = _shard(_shard(x, -2, "h"), -1, "w").requires_grad_()
+    xr = x.clone().requires_grad_()
+    y_ref, y_loc = ref(xr), dn(xl)
+    assert _rel(_gather(_gather(y_loc, -2, "h"), -1, "w"), y_ref) < 1e-5
+    g = torch.randn_like(y_ref)
+    y_ref.backward(g)
+    y_loc.backward(_shard(_shard(g, -2, "h"), -1, "w"))
+    assert _rel(_gather(_gather(xl.grad, -2, "h"), -1, "w"), xr.grad) < 1e-4
+    # affine grads are partial sums on each tile: sum over the spatial group equals the serial gradient
+    gw = dn.weight.grad.clone()
+    dist.all_reduce(gw, group=comm.get_group("spatial"))
+    assert _rel(gw, ref.weight.grad) < 1e-4
+    # loss on local tiles == loss on the full field
+    sh = compute_split_shapes(H, comm.get_size("h")); sw = compute_split_shapes(W, comm.get_size("w"))
+    p = ParamsBase()
+    p.update_params(dict(loss="absolute squared geometric l2", n_future=0, img_shape_x=H, img_shape_y=W, img_crop_shape_x=H,
+                         img_crop_shape_y=W, img_crop_offset_x=0, img_crop_offset_y=0, N_out_channels=C, channel_weights="auto",
+                         model_grid_type="equiangular", img_local_shape_x=sh[comm.get_rank("h")], img_local_shape_y=sw[comm.get_rank("w")],
+                         img_local_offset_x=sum(sh[:comm.get_rank("h")]), img_local_offset_y=sum(sw[:comm.get_rank("w")])))
+    lh = LossHandler(p)
+    tgt = torch.randn(B, C, H, W)
+    l_loc = lh(_shard(_shard(x, -2, "h"), -1, "w"), _shard(_shard(tgt, -2, "h"), -1, "w"))
+    # serial reference
+    import makani_b200.utils.comm as cm
+    saved = dict(cm._SIZES); cm._SIZES.clear()
+    ws = cm._WORLD_SIZE; cm._WORLD_SIZE = 1
+    p2 = ParamsBase(); p2.update_params({k: v for k, v in p.to_dict().items() if not k.startswith("img_local")})
+    l_ref = LossHandler(p2)(x, tgt)
+    cm._WORLD_SIZE = ws; cm._SIZES.update(saved)
+    assert abs(l_loc.item() - l_ref.item()) < 1e-4 * abs(l_ref.item()), (l_loc.item(), l_ref.item())
+
+
+def case_matmul():
+    from makani_b200.parallel.layers import DistributedMLP
+    from makani_b200.parallel.mappings import gather_from_parallel_region, scatter_to_parallel_region
+    torch.manual_seed(3)
+    B, C, Hd, H, W = 2, 8, 12, 6, 10
+    x = torch.randn(B, C, H, W)
+    w1, b1, w2, b2 = torch.randn(Hd, C) * 0.3, torch.randn(Hd) * 0.1, torch.randn(C, Hd) * 0.3, torch.randn(C) * 0.1
+    mlp = DistributedMLP(C, Hd, C, comm_inp_name="fin", comm_hidden_name="fout")
+    fi, fo = comm.get_rank("fin"), comm.get_rank("fout")
+    nfi, nfo = comm.get_size("fin"), comm.get_size("fout")
+    with torch.no_grad():
+        mlp.fc1.weight.copy_(split_tensor_along_dim(split_tensor_along_dim(w1, 0, nfo)[fo], 1, nfi)[fi].reshape(mlp.fc1.weight.shape))
+        mlp.fc1.bias.copy_(split_tensor_along_dim(b1, 0, nfo)[fo].reshape(mlp.fc1.bias.shape))
+        mlp.fc2.weight.copy_(split_tensor_along_dim(split_tensor_along_dim(w2, 0, nfi)[fi], 1, nfo)[fo].reshape(mlp.fc2.weight.shape))
+        mlp.fc2.bias.copy_(split_tensor_along_dim(b2, 0, nfi)[fi].reshape(mlp.fc2.bias.shape))
+    xr = x.clone().requires_grad_()
+    f = torch.nn.functional
+    y_ref = f.conv2d(f.gelu(f.conv2d(xr, w1.view(Hd, C, 1, 1), b1)), w2.view(C, Hd, 1, 1), b2)
+    xl = x.clone().requires_grad_()
+    y_loc = mlp(scatter_to_parallel_region(xl, 1, "fin"))
+    y_full = gather_from_parallel_region(y_loc, 1, compute_split_shapes(C, nfi), "fin")
+    assert _rel(y_full, y_ref) < 1e-5
+    g = torch.randn_like(y_ref)
+    y_ref.backward(g)
+    y_full.backward(g)
+    assert _rel(xl.grad, xr.grad) < 1e-5
+
+
+def case_sfno_and_checkpoint():
+    """Spatially parallel SFNO == serial SFNO through a flexible checkpoint; gradient reduction over shared groups."""
+    import tempfile
+    from makani_b200.models.networks.sfnonet import SphericalFourierNeuralOperatorNet as SFNO
+    from makani_b200.parallel.grad_reduce import GradReducer
+    from makani_b200.utils import checkpoint as ckpt
+    torch.manual_seed(4)
+    kw = dict(inp_shape=(33, 64), out_shape=(33, 64), scale_factor=2, inp_chans=4, out_chans=4, embed_dim=8, num_layers=2)
+    path = os.path.join(os.environ["MK_TMP"], "flex_mp{mp_rank}.tar")
+    # serial model on rank 0 only (topology temporarily hidden), saved as a flexible checkpoint
+    import makani_b200.utils.comm as cm
+    saved, ws = dict(cm._SIZES), cm._WORLD_SIZE
+    cm._SIZES.clear(); cm._WORLD_SIZE = 1
+    torch.manual_seed(4)
+    serial = SFNO(**kw)
+    x = torch.randn(2, 4, 33, 64)
+    xr = x.clone().requires_grad_()
+    y_ref = serial(xr)
+    y_ref.square().mean().backward()
+    if comm.get_world_rank() == 0 or True:
+        st = {k: v.detach().clone() for k, v in serial.named_parameters()}
+    cm._WORLD_SIZE = ws; cm._SIZES.update(saved)
+    if comm.get_world_rank() == 0:
+        torch.save({"model_state": st, "iters": 0, "epoch": 0}, path.format(mp_rank=0))
+    dist.barrier()
+    par = SFNO(**kw)
+    ckpt.restore_checkpoint(path, par, mode="flexible")
+    xl = _shard(_shard(x, -2, "h"), -1, "w")
+    red = GradReducer(par, use_peer=False)
+    y_loc = par(xl)
+    y_full = _gather(_gather(y_loc, -2, "h"), -1, "w")
+    assert _rel(y_full, y_ref) < 1e-4, _rel(y_full, y_ref)
+    # same loss: mean over the global field
+    n_glob = y_ref.numel()
+    (y_loc.square().sum() / n_glob).backward()
+    red.reduce()
+    for (k, p), (_, q) in zip(par.named_parameters(), serial.named_parameters()):
+        g_full = p.grad
+        for d, grp in enumerate(getattr(p, "sharded_dims_mp", [])):
+            if grp is not None and comm.get_size(grp) > 1:
+                g_full = gather_uneven(g_full, d, grp)
+        a, b = (torch.view_as_real(g_full), torch.view_as_real(q.grad)) if g_full.is_complex() else (g_full, q.grad)
+        if b.norm() < 1e-7:
+            continue
+        assert _rel(a, b) < 1e-3, (k, _rel(a, b))
+    # flexible save from the parallel run reproduces the serial weights
+    out = os.path.join(os.environ["MK_TMP"], "flex2_mp{mp_rank}.tar")
+    ckpt.save_checkpoint(out, par, mode="flexible", world_rank=comm.get_world_rank())
+    dist.barrier()
+    full = ckpt.load_file(out.format(mp_rank=0))["model_state"]
+    for k, v in st.items():
+        assert torch.equal(full[k], v), k
+
+
+if __name__ == "__main__":
+    case = sys.argv[1]
+    sizes = [int(a) for a in sys.argv[2:6]]
+    comm.init(model_parallel_sizes=sizes, model_parallel_names=["h", "w", "fin", "fout"], timeout_s=120)
+    try:
+        globals()["case_" + case]()
+    finally:
+        dist.barrier()
+        comm.cleanup()
+    print("WORKER_OK")

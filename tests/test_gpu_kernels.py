@@ -233,6 +233,60 @@ def test_instance_norm_fwd_bwd():
                 assert _rel(a.float(), r_) < 2e-2
 
 
+def test_instance_norm_channels_last_fwd_bwd():
+    from makani_b200.ops.norm import instance_norm
+    dev = _dev()
+    torch.manual_seed(17)
+    for (B, C, H, W) in [(2, 16, 24, 40), (1, 384, 33, 64), (3, 8, 9, 7)]:
+        for act in ["none", "gelu"]:
+            x = (torch.randn(B, C, H, W, device=dev) * 2 + 0.5)
+            w = (torch.rand(C, device=dev) + 0.5).requires_grad_()
+            b = (torch.randn(C, device=dev) * 0.2).requires_grad_()
+            gy = torch.randn(B, C, H, W, device=dev).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+            xb = x.to(torch.bfloat16).contiguous(memory_format=torch.channels_last).requires_grad_()
+            y = instance_norm(xb, w, b, 1e-6, act)
+            assert y.is_contiguous(memory_format=torch.channels_last)
+            g = torch.autograd.grad(y, [xb, w, b], gy)
+            xf = x.to(torch.bfloat16).float().requires_grad_()
+            yr = torch.nn.functional.instance_norm(xf, None, None, w, b, True, 0.0, 1e-6)
+            if act == "gelu":
+                yr = torch.nn.functional.gelu(yr)
+            gr = torch.autograd.grad(yr, [xf, w, b], gy.float())
+            assert _rel(y.float(), yr) < 1e-2
+            for a, r_ in zip(g, gr):
+                assert _rel(a.float(), r_) < 2e-2
+    _ext.check_device_errors(dev)
+
+
+def test_conv_channels_last_chain():
+    """NCHW in -> channels-last hidden -> NCHW out, the layout path the SFNO encoder/decoder take."""
+    from makani_b200.ops.conv import CL, NCHW, layout_of, mlp2
+    dev = _dev()
+    torch.manual_seed(16)
+    B, Ci, Ch, Co, H, W = 2, 10, 64, 64, 24, 40
+    x = torch.randn(B, Ci, H, W, device=dev)
+    w1 = (torch.randn(Ch, Ci, 1, 1, device=dev) * 0.3).requires_grad_()
+    b1 = (torch.randn(Ch, device=dev) * 0.1).requires_grad_()
+    w2 = (torch.randn(Co, Ch, 1, 1, device=dev) * 0.2).requires_grad_()
+    w3 = (torch.randn(7, Co, 1, 1, device=dev) * 0.2).requires_grad_()
+    b3 = (torch.randn(Co, device=dev) * 0.1).requires_grad_()
+    xb = x.to(torch.bfloat16).requires_grad_()
+    h = mlp2(xb, w1, b1, w2, None)                      # NCHW -> CL
+    assert layout_of(h) == CL
+    y = mlp2(h, w2.detach().transpose(0, 1).contiguous().requires_grad_(), b3, w3, None)   # CL -> NCHW (7 channels)
+    assert layout_of(y) == NCHW and y.shape == (B, 7, H, W)
+    f = torch.nn.functional
+    xf = x.to(torch.bfloat16).float().requires_grad_()
+    hr = f.conv2d(f.gelu(f.conv2d(xf, w1, b1)), w2)
+    assert _rel(h.float(), hr) < 2e-2
+    gy = torch.randn_like(hr)
+    g = torch.autograd.grad(h, [xb, w1, b1, w2], gy.to(torch.bfloat16).contiguous(memory_format=torch.channels_last))
+    gr = torch.autograd.grad(hr, [xf, w1, b1, w2], gy)
+    for a, r_ in zip(g, gr):
+        assert _rel(a.float(), r_) < 3e-2
+    _ext.check_device_errors(dev)
+
+
 def test_lp_norms_fwd_bwd():
     from makani_b200.ops.loss import weighted_lp_norms
     dev = _dev()
@@ -297,7 +351,7 @@ def test_spectral_conv_fwd_bwd():
     from makani_b200.sht import InverseRealSHT, RealSHT
     dev = _dev()
     torch.manual_seed(11)
-    B, C, Co = 2, 8, 12
+    B, C, Co = 2, 8, 16
     nlat, nlon, L, M = 33, 64, 16, 17
     nlat2, nlon2 = 16, 32
     pin = SHTPlan.get(nlat, nlon, L, M, "equiangular", dev)
