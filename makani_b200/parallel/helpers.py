@@ -36,28 +36,35 @@ def get_memory_format(tensor: torch.Tensor):
     return torch.channels_last if tensor.is_contiguous(memory_format=torch.channels_last) else torch.contiguous_format
 
 
+def all_gather_uneven(t: torch.Tensor, dim: int, sizes: List[int], group) -> torch.Tensor:
+    """Concatenate along `dim` the tensors of all ranks, whose extents along `dim` are `sizes`.
+    Shards are padded to the largest extent for the collective (every backend supports equal-size all_gather)."""
+    dim = dim % t.dim()
+    is_complex = t.is_complex()
+    tr = torch.view_as_real(t) if is_complex else t
+    tr = tr.contiguous()
+    smax = max(sizes)
+    if tr.shape[dim] < smax:
+        pad_shape = list(tr.shape)
+        pad_shape[dim] = smax - tr.shape[dim]
+        tr = torch.cat([tr, torch.zeros(pad_shape, dtype=tr.dtype, device=tr.device)], dim=dim)
+    outs = [torch.empty_like(tr) for _ in sizes]
+    dist.all_gather(outs, tr, group=group)
+    out = torch.cat([o.narrow(dim, 0, s) for o, s in zip(outs, sizes)], dim=dim)
+    return torch.view_as_complex(out.contiguous()) if is_complex else out
+
+
 def gather_uneven(tensor: torch.Tensor, dim: int, comm_name: str) -> torch.Tensor:
     """All-gather `tensor` along `dim` over group `comm_name` when ranks hold different extents along `dim`."""
     size = comm.get_size(comm_name)
     if size == 1:
         return tensor
     group = comm.get_group(comm_name)
+    dim = dim % tensor.dim()
     my = torch.tensor([tensor.shape[dim]], dtype=torch.int64, device=tensor.device)
     sizes = [torch.empty_like(my) for _ in range(size)]
     dist.all_gather(sizes, my, group=group)
-    sizes = [int(s.item()) for s in sizes]
-    is_complex = tensor.is_complex()
-    t = torch.view_as_real(tensor) if is_complex else tensor
-    t = t.contiguous()
-    shape = list(t.shape)
-    outs = []
-    for s in sizes:
-        shp = list(shape)
-        shp[dim] = s
-        outs.append(torch.empty(shp, dtype=t.dtype, device=t.device))
-    dist.all_gather(outs, t, group=group)
-    out = torch.cat(outs, dim=dim)
-    return torch.view_as_complex(out) if is_complex else out
+    return all_gather_uneven(tensor, dim, [int(s.item()) for s in sizes], group)
 
 
 def sync_params(model: torch.nn.Module, mode: str = "broadcast") -> None:

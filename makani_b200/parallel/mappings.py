@@ -17,7 +17,7 @@ import torch
 import torch.distributed as dist
 
 from ..utils import comm
-from .helpers import compute_split_shapes, split_tensor_along_dim
+from .helpers import all_gather_uneven, compute_split_shapes, split_tensor_along_dim
 
 
 def _all_reduce(x: torch.Tensor, name: str) -> torch.Tensor:
@@ -43,22 +43,12 @@ def _gather(x: torch.Tensor, dim: int, shapes: Optional[List[int]], name: str) -
     if size == 1:
         return x
     dim = dim % x.dim()
-    x = x.contiguous()
-    is_complex = x.is_complex()
-    xr = torch.view_as_real(x) if is_complex else x
     if shapes is None:
         sz = torch.tensor([x.shape[dim]], dtype=torch.int64, device=x.device)
         all_sz = [torch.empty_like(sz) for _ in range(size)]
         dist.all_gather(all_sz, sz, group=comm.get_group(name))
         shapes = [int(s.item()) for s in all_sz]
-    outs = []
-    for s in shapes:
-        shp = list(xr.shape)
-        shp[dim] = s
-        outs.append(torch.empty(shp, dtype=xr.dtype, device=xr.device))
-    dist.all_gather(outs, xr, group=comm.get_group(name))
-    out = torch.cat(outs, dim=dim)
-    return torch.view_as_complex(out) if is_complex else out
+    return all_gather_uneven(x, dim, list(shapes), comm.get_group(name))
 
 
 class _CopyTo(torch.autograd.Function):
