@@ -22,7 +22,8 @@ from ..utils import comm
 
 
 class GradReducer:
-    def __init__(self, model: torch.nn.Module, use_peer: Optional[bool] = None, align: int = 64):
+    def __init__(self, model: torch.nn.Module, use_peer: Optional[bool] = None, align: int = 64, bucket_mb: float = 256.0,
+                 overlap: bool = True):
         self.params = [p for p in model.parameters() if p.requires_grad]
         dev = self.params[0].device
         self.device = dev
@@ -51,6 +52,39 @@ class GradReducer:
             else:
                 g = self.flat[off: off + n].view(p.shape)
             p.grad = g
+        # ---- buckets for overlapping the data-parallel reduction with the backward pass ----------------------
+        # Parameters are bucketed in reverse registration order (the order in which backward produces gradients);
+        # a bucket is a contiguous range of the flat buffer.  When the last gradient of a bucket has been
+        # accumulated, its all-reduce is queued on a side stream behind an event of the compute stream.
+        self.overlap = bool(overlap and self.sym is not None and self.data_size > 1)
+        self.buckets: List[List[int]] = []        # [start, end) element ranges of the flat buffer
+        self._bucket_of: Dict[int, int] = {}
+        self._pending: List[int] = []
+        if self.overlap:
+            limit = int(bucket_mb * 1024 * 1024 / 4)
+            end = total
+            cur_start = total
+            members: List[int] = []
+            for idx in range(len(self.params) - 1, -1, -1):
+                off, n = sizes[idx]
+                cur_start = off
+                members.append(idx)
+                if end - cur_start >= limit or idx == 0:
+                    b = len(self.buckets)
+                    self.buckets.append([cur_start, end])
+                    for m in members:
+                        self._bucket_of[m] = b
+                    members = []
+                    end = cur_start
+            self._pending = [0] * len(self.buckets)
+            self._counts = [0] * len(self.buckets)
+            for idx in range(len(self.params)):
+                self._counts[self._bucket_of[idx]] += 1
+            self._side = torch.cuda.Stream(device=dev)
+            self._launched = [False] * len(self.buckets)
+            for idx, p in enumerate(self.params):
+                p.register_post_accumulate_grad_hook(self._make_hook(idx))
+            self._reset_pending()
         # parameters whose gradient must additionally be summed over model-parallel groups
         self.shared: Dict[str, List[torch.nn.Parameter]] = {}
         for p in self.params:
@@ -58,13 +92,43 @@ class GradReducer:
                 if comm.get_size(g) > 1:
                     self.shared.setdefault(g, []).append(p)
 
+    def _reset_pending(self):
+        self._pending = list(self._counts)
+        self._launched = [False] * len(self.buckets)
+
+    def _make_hook(self, idx):
+        def hook(param):
+            b = self._bucket_of[idx]
+            self._pending[b] -= 1
+            if self._pending[b] == 0 and not self._launched[b]:
+                self._launch_bucket(b)
+        return hook
+
+    def _launch_bucket(self, b):
+        start, end = self.buckets[b]
+        self._launched[b] = True
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(self._side):
+            self._side.wait_event(ev)
+            self.sym.all_reduce_(end - start, torch.float32, scale=1.0 / self.data_size, byte_offset=start * 4)
+
     def zero_grad(self):
+        if self.overlap:
+            # the previous step's side-stream work must be finished before the buffer is cleared
+            torch.cuda.current_stream(self.device).wait_stream(self._side)
+            self._reset_pending()
         self.flat.zero_()
 
     def reduce(self):
         """Average over `data`, then sum over the model-parallel groups each parameter is shared on."""
         if self.data_size > 1:
-            if self.sym is not None:
+            if self.overlap:
+                for b in range(len(self.buckets)):     # buckets whose hooks did not all fire (unused parameters)
+                    if not self._launched[b]:
+                        self._launch_bucket(b)
+                torch.cuda.current_stream(self.device).wait_stream(self._side)
+            elif self.sym is not None:
                 self.sym.all_reduce_(self.total, torch.float32, scale=1.0 / self.data_size)
             else:
                 dist.all_reduce(self.flat, group=comm.get_group("data"))
