@@ -5,6 +5,7 @@
 #include <c10/cuda/CUDAGuard.h>
 
 #include <cstdint>
+#include <cstring>
 #include <map>
 #include <vector>
 
@@ -57,9 +58,66 @@ void clear_error_flag(int64_t device) {
 inline const char* base_ptr(const Tensor& t) { return static_cast<const char*>(t.data_ptr()); }
 
 // iparams layout: see makani_b200/ops/gemm.py (GemmSpec.pack)
+static bool parse_peer(mk::GemmPeer& g, const std::vector<int64_t>& seg, const std::vector<int64_t>& sync) {
+  memset(&g, 0, sizeof(g));
+  if (!seg.empty()) {
+    g.nseg = static_cast<int>(seg[0]);
+    MK_CHECK(g.nseg >= 1 && g.nseg <= 8 && seg.size() == static_cast<size_t>(1 + 4 * g.nseg), "gemm_peer: bad segment list");
+    for (int q = 0; q < g.nseg; ++q) {
+      g.seg_ptr[q] = reinterpret_cast<const void*>(seg[1 + 4 * q]);
+      g.seg_len[q] = static_cast<int>(seg[2 + 4 * q]);
+      g.seg_apos[q] = static_cast<int>(seg[3 + 4 * q]);
+      g.seg_gstart[q] = static_cast<int>(seg[4 + 4 * q]);
+    }
+  }
+  if (!sync.empty()) {
+    MK_CHECK(sync.size() == 28, "gemm_peer: sync descriptor must have 28 entries");
+    g.npeers = static_cast<int>(sync[0]);
+    g.nwait = static_cast<int>(sync[1]);
+    g.nsig = static_cast<int>(sync[2]);
+    g.done_ctr = reinterpret_cast<unsigned int*>(sync[3]);
+    for (int i = 0; i < 2; ++i) {
+      g.wait[i] = reinterpret_cast<const unsigned int*>(sync[4 + 4 * i]);
+      g.wait_exp[i] = reinterpret_cast<const unsigned int*>(sync[5 + 4 * i]);
+      g.wait_off[i] = static_cast<int>(sync[6 + 4 * i]);
+      g.bump[i] = reinterpret_cast<unsigned int*>(sync[7 + 4 * i]);
+      for (int q = 0; q < 8; ++q) g.sig[i][q] = reinterpret_cast<unsigned int*>(sync[12 + 8 * i + q]);
+    }
+  }
+  return !seg.empty() || !sync.empty();
+}
+
+void peer_sync(const std::vector<int64_t>& sync, int64_t phase, int64_t device) {
+  mk::GemmPeer g;
+  parse_peer(g, {}, sync);
+  c10::cuda::CUDAGuard guard(c10::Device(c10::kCUDA, static_cast<int>(device)));
+  Tensor dummy = torch::empty({1}, torch::dtype(torch::kUInt8).device(torch::kCUDA, static_cast<int>(device)));
+  Tensor ef = err_flag_for(dummy);
+  check_cuda(mk::peer_sync_launch(g, static_cast<int>(phase), ef.data_ptr<int>(), cur_stream()), "peer_sync");
+}
+
+void gemm_impl(const Tensor& a, const Tensor& b, Tensor& d, const c10::optional<Tensor>& bias,
+               const c10::optional<Tensor>& resid, const c10::optional<Tensor>& preact, const std::vector<int64_t>& ip,
+               double alpha, const mk::GemmPeer* peer);
+
 void gemm(const Tensor& a, const Tensor& b, Tensor& d, const c10::optional<Tensor>& bias,
           const c10::optional<Tensor>& resid, const c10::optional<Tensor>& preact, const std::vector<int64_t>& ip,
           double alpha) {
+  gemm_impl(a, b, d, bias, resid, preact, ip, alpha, nullptr);
+}
+
+// GEMM whose B operand is gathered from peer devices along k and/or that takes part in cross-device handshakes
+void gemm_peer(const Tensor& a, const Tensor& b, Tensor& d, const c10::optional<Tensor>& bias,
+               const c10::optional<Tensor>& resid, const c10::optional<Tensor>& preact, const std::vector<int64_t>& ip,
+               double alpha, const std::vector<int64_t>& seg, const std::vector<int64_t>& sync) {
+  mk::GemmPeer g;
+  parse_peer(g, seg, sync);
+  gemm_impl(a, b, d, bias, resid, preact, ip, alpha, &g);
+}
+
+void gemm_impl(const Tensor& a, const Tensor& b, Tensor& d, const c10::optional<Tensor>& bias,
+               const c10::optional<Tensor>& resid, const c10::optional<Tensor>& preact, const std::vector<int64_t>& ip,
+               double alpha, const mk::GemmPeer* peer) {
   MK_CHECK(ip.size() == 40, "gemm: expected 40 integer parameters, got ", ip.size());
   MK_CHECK(a.is_cuda() && b.is_cuda() && d.is_cuda(), "gemm: tensors must be CUDA");
   MK_CHECK(a.scalar_type() == b.scalar_type(), "gemm: A and B dtypes differ");
@@ -113,7 +171,7 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& d, const c10::optional<Tenso
     e.preact = const_cast<char*>(base_ptr(*preact)) + preact_off * osz;
   }
   Tensor ef = err_flag_for(a);
-  check_cuda(mk::gemm_launch(p, A, B, e, ef.data_ptr<int>(), cur_stream()), "gemm launch");
+  check_cuda(mk::gemm_launch(p, A, B, e, ef.data_ptr<int>(), cur_stream(), peer), "gemm launch");
 }
 
 void inorm_fwd(const Tensor& x, Tensor& y, const c10::optional<Tensor>& w, const c10::optional<Tensor>& b, Tensor& stats,
@@ -315,6 +373,8 @@ void peer_allreduce(const std::vector<int64_t>& data_ptrs, const std::vector<int
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, "tcgen05 GEMM with fused epilogue");
+  m.def("gemm_peer", &gemm_peer, "tcgen05 GEMM reading its B operand from peer devices");
+  m.def("peer_sync", &peer_sync);
   m.def("read_error_flag", &read_error_flag);
   m.def("clear_error_flag", &clear_error_flag);
   m.def("inorm_fwd", &inorm_fwd);

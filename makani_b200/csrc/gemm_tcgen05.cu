@@ -22,6 +22,26 @@ constexpr int BM = 128;
 constexpr int A_STAGE_BYTES = BM * 128;
 constexpr int NUM_THREADS = 320;   // TMA warp + MMA warp + 8 epilogue warps
 constexpr int MAX_STAGES = 6;
+constexpr int MAX_SEG = 8;
+
+// Handshake of a kernel that reads operands from peer GPUs and/or writes a buffer that peers read.
+//   wait[i]   : local flag array (one slot per peer) that must reach *wait_exp[i] + wait_off[i] before the first load
+//   bump[i]   : local counter incremented by one when the whole grid has finished
+//   sig[i][p] : flag slot in peer p's memory incremented by one when the whole grid has finished
+struct PeerSync {
+  int npeers;
+  int nwait, nsig;
+  const unsigned int* wait[2];
+  const unsigned int* wait_exp[2];
+  int wait_off[2];
+  unsigned int* bump[2];
+  unsigned int* sig[2][MAX_SEG];
+  unsigned int* done_ctr;
+};
+
+struct BMaps {
+  CUtensorMap m[MAX_SEG];
+};
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;   // 2 s per barrier wait
 
 struct KParams {
@@ -45,6 +65,13 @@ struct KParams {
   long long total_tiles;
   int stages, e_tma, plain_cols;
   int* err;
+  // ---- B operand gathered from several devices: segment s of the k axis lives on peer s
+  int nseg;                       // 1: ordinary single-map operand
+  int seg_len[MAX_SEG];           // local k extent of each segment
+  int seg_apos[MAX_SEG];          // k coordinate of the segment start in the A operand (padded layout)
+  int seg_gstart[MAX_SEG];        // global k index of the segment start (for the kmin/kmax structure)
+  // ---- cross-device handshakes (all counters are monotonic and live in device memory)
+  PeerSync sync;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -222,7 +249,7 @@ __device__ __forceinline__ TileCoord decode_tile(const KParams& p, long long t) 
   c.k_begin = kb;
   c.k_end = ke;
   const int r0 = c.mt * BM;
-  c.skip = (r0 + BM <= rmin) || (r0 >= rmax) || (kb >= ke);
+  c.skip = (r0 + BM <= rmin) || (r0 >= rmax) || (p.nseg == 1 && kb >= ke);
   return c;
 }
 
@@ -232,11 +259,27 @@ constexpr int STG_BYTES = 8 * STG_WARP_BYTES;          // specialised epilogues 
 // EPI selects a compile-time specialised epilogue (bf16 output, 16-byte vector stores, row bias only):
 //   0 generic (all options decided at run time)      1 plain store
 //   2 GELU + saved pre-activation                     3 + residual (TMA-prefetched)      4 * GELU'(aux) (TMA-prefetched)
+// local k range [lb, le) of segment `sg` for tile `c` (multi-device B operand)
+template <int BK>
+__device__ __forceinline__ void seg_range(const KParams& p, const TileCoord& c, int sg, int& lb, int& le) {
+  int kmin = p.kmin_a * c.zhi + p.kmin_b - p.seg_gstart[sg];
+  int kmax = p.kmax_a * c.zhi + p.kmax_b - p.seg_gstart[sg];
+  lb = kmin > 0 ? (kmin / BK) * BK : 0;
+  le = kmax < p.seg_len[sg] ? kmax : p.seg_len[sg];
+}
+
+__device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int* ptr) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+  return v;
+}
+
 template <int BN, int EB, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ BMaps maps_b,
             const __grid_constant__ CUtensorMap map_e, const __grid_constant__ CUtensorMap map_d,
             const __grid_constant__ CUtensorMap map_p, const KParams p) {
+  const CUtensorMap& map_b = maps_b.m[0];
   constexpr int BK = 128 / EB;            // elements per 128-byte k-slab
   constexpr int UMMA_K = 32 / EB;         // elements per tcgen05.mma
   constexpr int B_STAGE_BYTES = BN * 128;
@@ -282,6 +325,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    // operands on peer devices (and the buffer this kernel overwrites) must be ready: bounded wait on local flags.
+    // The whole CTA waits (not only the producer) so that no epilogue store of an all-zero tile can run early.
+    bool ok = true;
+    for (int w = 0; w < p.sync.nwait && ok; ++w) {
+      const unsigned int need = *p.sync.wait_exp[w] + static_cast<unsigned int>(p.sync.wait_off[w]);
+      for (int peer = 0; peer < p.sync.npeers && ok; ++peer) {
+        uint64_t t0 = 0;
+        for (uint32_t it = 0;; ++it) {
+          if (static_cast<int>(ld_acquire_sys_u32(p.sync.wait[w] + peer) - need) >= 0) break;
+          if ((it & 255u) == 255u) {
+            const uint64_t now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_LIMIT_NS) {
+              atomicExch(p.err, 32 + w);
+              ok = false;
+              break;
+            }
+          }
+        }
+      }
+    }
+    tmem_slot[1] = ok ? 1u : 0u;
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -294,13 +359,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const bool peers_ready = tmem_slot[1] != 0u;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       int s = 0;
       uint32_t ph = 0, epi_it = 0;
-      bool ok = true;
+      bool ok = peers_ready;
+      if (p.sync.nwait > 0) asm volatile("fence.proxy.async;" ::: "memory");   // flags acquired in the prologue order the TMA loads below
       for (long long t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
         const TileCoord c = decode_tile<BK>(p, t);
         const int m0 = c.mt * BM, n0 = c.nt * BN;
@@ -321,32 +388,42 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         if (c.skip) continue;
         const int azl = p.a_zlo ? c.zlo : 0, azh = p.a_zhi ? c.zhi : 0;
         const int bzl = p.b_zlo ? c.zlo : 0, bzh = p.b_zhi ? c.zhi : 0;
-        for (int k = c.k_begin; k < c.k_end; k += BK) {
-          if (!mbar_wait(empty_bar(s), ph ^ 1u)) {
-            atomicExch(p.err, 1);
-            ok = false;
-            break;
+        for (int sg = 0; sg < p.nseg && ok; ++sg) {
+          int lb = c.k_begin, le = c.k_end, apos = 0;
+          const CUtensorMap* mb = &map_b;
+          if (p.nseg > 1) {
+            seg_range<BK>(p, c, sg, lb, le);
+            apos = p.seg_apos[sg];
+            mb = &maps_b.m[sg];
           }
-          mbar_expect_tx(full_bar(s), STAGE_BYTES);
-          const uint32_t sa = smem_base + s * STAGE_BYTES;
-          const uint32_t sb = sa + A_STAGE_BYTES;
-          if (!p.a_mn) {
-            tma_load_4d(sa, &map_a, full_bar(s), k, m0, azl, azh);
-          } else {
+          for (int k = lb; k < le; k += BK) {
+            if (!mbar_wait(empty_bar(s), ph ^ 1u)) {
+              atomicExch(p.err, 1);
+              ok = false;
+              break;
+            }
+            mbar_expect_tx(full_bar(s), STAGE_BYTES);
+            const uint32_t sa = smem_base + s * STAGE_BYTES;
+            const uint32_t sb = sa + A_STAGE_BYTES;
+            const int ka = apos + k;
+            if (!p.a_mn) {
+              tma_load_4d(sa, &map_a, full_bar(s), ka, m0, azl, azh);
+            } else {
 #pragma unroll
-            for (int j = 0; j < BM / MN_BOX; ++j)
-              tma_load_4d(sa + j * (BK * 128), &map_a, full_bar(s), m0 + j * MN_BOX, k, azl, azh);
-          }
-          if (!p.b_mn) {
-            tma_load_4d(sb, &map_b, full_bar(s), k, n0, bzl, bzh);
-          } else {
+              for (int j = 0; j < BM / MN_BOX; ++j)
+                tma_load_4d(sa + j * (BK * 128), &map_a, full_bar(s), m0 + j * MN_BOX, ka, azl, azh);
+            }
+            if (!p.b_mn) {
+              tma_load_4d(sb, mb, full_bar(s), k, n0, bzl, bzh);
+            } else {
 #pragma unroll
-            for (int j = 0; j < BN / MN_BOX; ++j)
-              tma_load_4d(sb + j * (BK * 128), &map_b, full_bar(s), n0 + j * MN_BOX, k, bzl, bzh);
-          }
-          if (++s == STAGES) {
-            s = 0;
-            ph ^= 1u;
+              for (int j = 0; j < BN / MN_BOX; ++j)
+                tma_load_4d(sb + j * (BK * 128), mb, full_bar(s), n0 + j * MN_BOX, k, bzl, bzh);
+            }
+            if (++s == STAGES) {
+              s = 0;
+              ph ^= 1u;
+            }
           }
         }
       }
@@ -365,7 +442,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       const uint32_t b_kstep = p.b_mn ? UMMA_K * 128 : 32;
       int s = 0;
       uint32_t ph = 0, acc_it = 0;
-      bool ok = true;
+      bool ok = peers_ready;
       for (long long t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
         const TileCoord c = decode_tile<BK>(p, t);
         if (c.skip) continue;
@@ -377,7 +454,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + buf * BN;
         uint32_t accum = 0;
-        for (int k = c.k_begin; k < c.k_end; k += BK) {
+        int nblocks = 0;
+        if (p.nseg > 1) {
+          for (int sg = 0; sg < p.nseg; ++sg) {
+            int lb, le;
+            seg_range<BK>(p, c, sg, lb, le);
+            if (le > lb) nblocks += (le - lb + BK - 1) / BK;
+          }
+        } else {
+          nblocks = (c.k_end - c.k_begin + BK - 1) / BK;
+        }
+        for (int kb = 0; kb < nblocks; ++kb) {
           if (!mbar_wait(full_bar(s), ph)) {
             atomicExch(p.err, 3);
             ok = false;
@@ -410,7 +497,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
     uint32_t acc_it = 0, epi_it = 0;
-    bool ok = true;
+    bool ok = peers_ready;
     for (long long t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
       const TileCoord c = decode_tile<BK>(p, t);
       if (c.skip && p.accumulate) continue;
@@ -661,10 +748,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 
   // ------------------------------------------------------------------ teardown
   if constexpr (EPI != 0) {
-    if (warp >= 2 && lane == 0) tma_store_wait_all();
+    if (warp >= 2 && lane == 0) {
+      tma_store_wait_all();
+      asm volatile("fence.proxy.async;" ::: "memory");   // order the bulk stores before the generic-proxy signalling below
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (p.sync.done_ctr != nullptr && threadIdx.x == 0) {
+    // last CTA of the grid: everything this kernel wrote is complete and everything it read from peers is consumed
+    __threadfence_system();
+    const unsigned int prev = atomicAdd(p.sync.done_ctr, 1u);
+    if (prev == gridDim.x - 1) {
+      *p.sync.done_ctr = 0;
+      for (int i = 0; i < p.sync.nwait; ++i)
+        if (p.sync.bump[i]) atomicAdd(p.sync.bump[i], 1u);
+      __threadfence_system();
+      for (int i = 0; i < p.sync.nsig; ++i)
+        for (int peer = 0; peer < p.sync.npeers; ++peer)
+          if (p.sync.sig[i][peer]) atomicAdd_system(p.sync.sig[i][peer], 1u);
+    }
+  }
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
@@ -743,7 +847,7 @@ bool make_map(CUtensorMap* map, const GemmOperand& op, int K, int eb, int zlo_n,
 constexpr int SMEM_LIMIT = 232448;   // 227 KB per CTA on sm_100
 
 template <int BN, int EB, int EPI>
-cudaError_t launch_t(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& me, const CUtensorMap& md,
+cudaError_t launch_t(const CUtensorMap& ma, const BMaps& mb, const CUtensorMap& me, const CUtensorMap& md,
                      const CUtensorMap& mp, KParams& kp, cudaStream_t stream) {
   constexpr int STAGE = A_STAGE_BYTES + BN * 128;
   constexpr int FIXED = (EPI != 0 ? STG_BYTES : 0) + 8 * (2 * MAX_STAGES + 8) + 16 + 1024;
@@ -796,8 +900,63 @@ bool make_map_e(CUtensorMap* map, const void* ptr, int M, int N, long long row_s
 
 const char* gemm_last_error() { return g_err; }
 
+namespace {
+__global__ void peer_sync_kernel(const PeerSync sy, int phase, int* err) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  if (phase == 0) {
+    for (int w = 0; w < sy.nwait; ++w) {
+      const unsigned int need = *sy.wait_exp[w] + static_cast<unsigned int>(sy.wait_off[w]);
+      for (int peer = 0; peer < sy.npeers; ++peer) {
+        uint64_t t0 = 0;
+        for (uint32_t it = 0;; ++it) {
+          if (static_cast<int>(ld_acquire_sys_u32(sy.wait[w] + peer) - need) >= 0) break;
+          if ((it & 255u) == 255u) {
+            const uint64_t now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_LIMIT_NS) {
+              atomicExch(err, 48 + w);
+              return;
+            }
+          }
+        }
+      }
+    }
+  } else {
+    for (int i = 0; i < sy.nwait; ++i)
+      if (sy.bump[i]) atomicAdd(sy.bump[i], 1u);
+    __threadfence_system();
+    for (int i = 0; i < sy.nsig; ++i)
+      for (int peer = 0; peer < sy.npeers; ++peer)
+        if (sy.sig[i][peer]) atomicAdd_system(sy.sig[i][peer], 1u);
+  }
+}
+
+void fill_sync(PeerSync& sy, const GemmPeer* g) {
+  memset(&sy, 0, sizeof(sy));
+  if (!g) return;
+  sy.npeers = g->npeers;
+  sy.nwait = g->nwait;
+  sy.nsig = g->nsig;
+  for (int i = 0; i < 2; ++i) {
+    sy.wait[i] = g->wait[i];
+    sy.wait_exp[i] = g->wait_exp[i];
+    sy.wait_off[i] = g->wait_off[i];
+    sy.bump[i] = g->bump[i];
+    for (int q = 0; q < MAX_SEG; ++q) sy.sig[i][q] = g->sig[i][q];
+  }
+  sy.done_ctr = g->done_ctr;
+}
+}  // namespace
+
+cudaError_t peer_sync_launch(const GemmPeer& g, int phase, int* err_flag, cudaStream_t stream) {
+  PeerSync sy;
+  fill_sync(sy, &g);
+  peer_sync_kernel<<<1, 32, 0, stream>>>(sy, phase, err_flag);
+  return cudaGetLastError();
+}
+
 cudaError_t gemm_launch(const GemmProblem& p, const GemmOperand& A, const GemmOperand& B, const GemmEpilogue& e,
-                        int* err_flag, cudaStream_t stream) {
+                        int* err_flag, cudaStream_t stream, const GemmPeer* peer) {
   g_err[0] = 0;
   if (p.M <= 0 || p.N <= 0 || p.zlo_n <= 0 || p.zhi_n <= 0) return cudaSuccess;
   // cuTensorMapEncodeTiled is a driver call: make sure this host thread has the primary context bound (threads
@@ -859,6 +1018,20 @@ cudaError_t gemm_launch(const GemmProblem& p, const GemmOperand& A, const GemmOp
   kp.n_tiles = (p.N + bn - 1) / bn;
   kp.total_tiles = static_cast<long long>(kp.m_tiles) * kp.n_tiles * kp.splits * p.zlo_n * p.zhi_n;
   kp.err = err_flag;
+  kp.nseg = 1;
+  fill_sync(kp.sync, peer);
+  if (peer && peer->nseg > 1) {
+    if (kp.splits != 1 || peer->nseg > MAX_SEG) {
+      snprintf(g_err, sizeof(g_err), "multi-device operand: split-k not supported, at most %d segments", MAX_SEG);
+      return cudaErrorInvalidValue;
+    }
+    kp.nseg = peer->nseg;
+    for (int q = 0; q < peer->nseg; ++q) {
+      kp.seg_len[q] = peer->seg_len[q];
+      kp.seg_apos[q] = peer->seg_apos[q];
+      kp.seg_gstart[q] = peer->seg_gstart[q];
+    }
+  }
 
   CUtensorMap ma, mb, me;
   memset(&me, 0, sizeof(me));
@@ -874,7 +1047,18 @@ cudaError_t gemm_launch(const GemmProblem& p, const GemmOperand& A, const GemmOp
   kp.n_tiles = (p.N + bn - 1) / bn;
   kp.total_tiles = static_cast<long long>(kp.m_tiles) * kp.n_tiles * kp.splits * p.zlo_n * p.zhi_n;
   if (!make_map(&ma, A, p.K, eb, p.zlo_n, p.zhi_n, BM)) return cudaErrorInvalidValue;
-  if (!make_map(&mb, B, p.K, eb, p.zlo_n, p.zhi_n, bn)) return cudaErrorInvalidValue;
+  BMaps mbs;
+  if (kp.nseg > 1) {
+    for (int q = 0; q < kp.nseg; ++q) {
+      GemmOperand Bq = B;
+      Bq.ptr = peer->seg_ptr[q];
+      if (!make_map(&mbs.m[q], Bq, peer->seg_len[q], eb, p.zlo_n, p.zhi_n, bn)) return cudaErrorInvalidValue;
+    }
+    for (int q = kp.nseg; q < MAX_SEG; ++q) mbs.m[q] = mbs.m[0];
+  } else {
+    if (!make_map(&mb, B, p.K, eb, p.zlo_n, p.zhi_n, bn)) return cudaErrorInvalidValue;
+    for (int q = 0; q < MAX_SEG; ++q) mbs.m[q] = mb;
+  }
   if (!kp.e_tma) me = ma;   // unused, but must be a valid descriptor
 
   kp.plain_cols = (e.ndiv <= 0 || e.ndiv >= (1 << 30)) ? 1 : 0;
@@ -897,12 +1081,12 @@ cudaError_t gemm_launch(const GemmProblem& p, const GemmOperand& A, const GemmOp
     }
   }
   if (eb == 4) {
-    if (bn == 256) return launch_t<256, 4, 0>(ma, mb, me, md, mp, kp, stream);
-    return launch_t<128, 4, 0>(ma, mb, me, md, mp, kp, stream);
+    if (bn == 256) return launch_t<256, 4, 0>(ma, mbs, me, md, mp, kp, stream);
+    return launch_t<128, 4, 0>(ma, mbs, me, md, mp, kp, stream);
   }
 #define MK_DISPATCH(EPI_)                                                    \
-  if (bn == 256) return launch_t<256, 2, EPI_>(ma, mb, me, md, mp, kp, stream);      \
-  return launch_t<128, 2, EPI_>(ma, mb, me, md, mp, kp, stream);
+  if (bn == 256) return launch_t<256, 2, EPI_>(ma, mbs, me, md, mp, kp, stream);      \
+  return launch_t<128, 2, EPI_>(ma, mbs, me, md, mp, kp, stream);
   switch (epi) {
     case 1: { MK_DISPATCH(1) }
     case 2: { MK_DISPATCH(2) }

@@ -57,10 +57,28 @@ struct GemmProblem {
   int bn;               // tile width: 128 or 256 (0 = choose)
 };
 
+// Optional: B operand gathered from several devices and cross-device handshakes (see gemm_tcgen05.cu).
+struct GemmPeer {
+  int nseg;                        // 0/1: B is the ordinary single operand
+  const void* seg_ptr[8];          // base pointer of segment s (peer memory mapped into this process)
+  int seg_len[8], seg_apos[8], seg_gstart[8];
+  int npeers, nwait, nsig;
+  const unsigned int* wait[2];
+  const unsigned int* wait_exp[2];
+  int wait_off[2];
+  unsigned int* bump[2];
+  unsigned int* sig[2][8];
+  unsigned int* done_ctr;
+};
+
+// Waits (bounded) and/or signals of the same handshake protocol without a GEMM, for buffers produced or consumed by
+// other kernels.  phase 0: wait only; phase 1: bump + signal only.
+cudaError_t peer_sync_launch(const GemmPeer& g, int phase, int* err_flag, cudaStream_t stream);
+
 // Returns cudaSuccess or an error; never throws.  `err_flag` is a device int that the kernel sets to a
 // non-zero code when a bounded barrier wait runs out (the launch still terminates).
 cudaError_t gemm_launch(const GemmProblem& p, const GemmOperand& A, const GemmOperand& B,
-                        const GemmEpilogue& e, int* err_flag, cudaStream_t stream);
+                        const GemmEpilogue& e, int* err_flag, cudaStream_t stream, const GemmPeer* peer = nullptr);
 
 const char* gemm_last_error();
 
