@@ -71,18 +71,25 @@ static bool parse_peer(mk::GemmPeer& g, const std::vector<int64_t>& seg, const s
     }
   }
   if (!sync.empty()) {
-    MK_CHECK(sync.size() == 28, "gemm_peer: sync descriptor must have 28 entries");
-    g.npeers = static_cast<int>(sync[0]);
-    g.nwait = static_cast<int>(sync[1]);
-    g.nsig = static_cast<int>(sync[2]);
-    g.done_ctr = reinterpret_cast<unsigned int*>(sync[3]);
+    // [nwait, nsig, done_ctr, {wait, wait_exp, wait_off, bump, np_wait} x2, {np_sig, sig[8]} x2]
+    MK_CHECK(sync.size() == 31, "gemm_peer: sync descriptor must have 31 entries");
+    g.nwait = static_cast<int>(sync[0]);
+    g.nsig = static_cast<int>(sync[1]);
+    g.done_ctr = reinterpret_cast<unsigned int*>(sync[2]);
     for (int i = 0; i < 2; ++i) {
-      g.wait[i] = reinterpret_cast<const unsigned int*>(sync[4 + 4 * i]);
-      g.wait_exp[i] = reinterpret_cast<const unsigned int*>(sync[5 + 4 * i]);
-      g.wait_off[i] = static_cast<int>(sync[6 + 4 * i]);
-      g.bump[i] = reinterpret_cast<unsigned int*>(sync[7 + 4 * i]);
-      for (int q = 0; q < 8; ++q) g.sig[i][q] = reinterpret_cast<unsigned int*>(sync[12 + 8 * i + q]);
+      const size_t o = 3 + 5 * i;
+      g.wait[i] = reinterpret_cast<const unsigned int*>(sync[o]);
+      g.wait_exp[i] = reinterpret_cast<const unsigned int*>(sync[o + 1]);
+      g.wait_off[i] = static_cast<int>(sync[o + 2]);
+      g.bump[i] = reinterpret_cast<unsigned int*>(sync[o + 3]);
+      g.np_wait[i] = static_cast<int>(sync[o + 4]);
+      MK_CHECK(g.np_wait[i] >= 0 && g.np_wait[i] <= 8, "gemm_peer: at most 8 peers");
+      const size_t q0 = 13 + 9 * i;
+      g.np_sig[i] = static_cast<int>(sync[q0]);
+      MK_CHECK(g.np_sig[i] >= 0 && g.np_sig[i] <= 8, "gemm_peer: at most 8 peers");
+      for (int q = 0; q < 8; ++q) g.sig[i][q] = reinterpret_cast<unsigned int*>(sync[q0 + 1 + q]);
     }
+    MK_CHECK(g.nwait >= 0 && g.nwait <= 2 && g.nsig >= 0 && g.nsig <= 2, "gemm_peer: at most two wait and two signal lists");
   }
   return !seg.empty() || !sync.empty();
 }

@@ -29,7 +29,7 @@ constexpr int MAX_SEG = 8;
 //   bump[i]   : local counter incremented by one when the whole grid has finished
 //   sig[i][p] : flag slot in peer p's memory incremented by one when the whole grid has finished
 struct PeerSync {
-  int npeers;
+  int np_wait[2], np_sig[2];      // number of peers of the group each wait / signal list refers to
   int nwait, nsig;
   const unsigned int* wait[2];
   const unsigned int* wait_exp[2];
@@ -330,7 +330,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
     bool ok = true;
     for (int w = 0; w < p.sync.nwait && ok; ++w) {
       const unsigned int need = *p.sync.wait_exp[w] + static_cast<unsigned int>(p.sync.wait_off[w]);
-      for (int peer = 0; peer < p.sync.npeers && ok; ++peer) {
+      for (int peer = 0; peer < p.sync.np_wait[w] && ok; ++peer) {
         uint64_t t0 = 0;
         for (uint32_t it = 0;; ++it) {
           if (static_cast<int>(ld_acquire_sys_u32(p.sync.wait[w] + peer) - need) >= 0) break;
@@ -765,7 +765,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
         if (p.sync.bump[i]) atomicAdd(p.sync.bump[i], 1u);
       __threadfence_system();
       for (int i = 0; i < p.sync.nsig; ++i)
-        for (int peer = 0; peer < p.sync.npeers; ++peer)
+        for (int peer = 0; peer < p.sync.np_sig[i]; ++peer)
           if (p.sync.sig[i][peer]) atomicAdd_system(p.sync.sig[i][peer], 1u);
     }
   }
@@ -906,7 +906,7 @@ __global__ void peer_sync_kernel(const PeerSync sy, int phase, int* err) {
   if (phase == 0) {
     for (int w = 0; w < sy.nwait; ++w) {
       const unsigned int need = *sy.wait_exp[w] + static_cast<unsigned int>(sy.wait_off[w]);
-      for (int peer = 0; peer < sy.npeers; ++peer) {
+      for (int peer = 0; peer < sy.np_wait[w]; ++peer) {
         uint64_t t0 = 0;
         for (uint32_t it = 0;; ++it) {
           if (static_cast<int>(ld_acquire_sys_u32(sy.wait[w] + peer) - need) >= 0) break;
@@ -926,7 +926,7 @@ __global__ void peer_sync_kernel(const PeerSync sy, int phase, int* err) {
       if (sy.bump[i]) atomicAdd(sy.bump[i], 1u);
     __threadfence_system();
     for (int i = 0; i < sy.nsig; ++i)
-      for (int peer = 0; peer < sy.npeers; ++peer)
+      for (int peer = 0; peer < sy.np_sig[i]; ++peer)
         if (sy.sig[i][peer]) atomicAdd_system(sy.sig[i][peer], 1u);
   }
 }
@@ -934,7 +934,10 @@ __global__ void peer_sync_kernel(const PeerSync sy, int phase, int* err) {
 void fill_sync(PeerSync& sy, const GemmPeer* g) {
   memset(&sy, 0, sizeof(sy));
   if (!g) return;
-  sy.npeers = g->npeers;
+  for (int i = 0; i < 2; ++i) {
+    sy.np_wait[i] = g->np_wait[i];
+    sy.np_sig[i] = g->np_sig[i];
+  }
   sy.nwait = g->nwait;
   sy.nsig = g->nsig;
   for (int i = 0; i < 2; ++i) {

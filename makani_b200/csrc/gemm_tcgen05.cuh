@@ -62,7 +62,7 @@ struct GemmPeer {
   int nseg;                        // 0/1: B is the ordinary single operand
   const void* seg_ptr[8];          // base pointer of segment s (peer memory mapped into this process)
   int seg_len[8], seg_apos[8], seg_gstart[8];
-  int npeers, nwait, nsig;
+  int np_wait[2], np_sig[2], nwait, nsig;   // peers per wait list / signal list; number of lists in use
   const unsigned int* wait[2];
   const unsigned int* wait_exp[2];
   int wait_off[2];

@@ -19,6 +19,7 @@ import torch
 import torch.nn as nn
 
 from ...ops import spectral as spectral_ops
+from ...ops import spectral_dist as spectral_dist_ops
 from ...sht import DistributedInverseRealSHT, DistributedRealSHT, InverseRealSHT, RealSHT
 from ...utils import comm
 from .activations import ComplexReLU
@@ -86,6 +87,21 @@ class SpectralConv(nn.Module):
                 and type(self.forward_transform) is RealSHT and type(self.inverse_transform) is InverseRealSHT
                 and spectral_ops.spectral_conv_supported(x, self.weight))
 
+    def _fast_dist_ok(self, x) -> bool:
+        """Sharded grids: GEMM chain whose k loops read the peers' buffers directly (needs peer-mapped memory, i.e.
+        NCCL ranks on one node, and l/m truncations common to both transforms)."""
+        f, i = self.forward_transform, self.inverse_transform
+        return (x.is_cuda and self.operator_type == "dhconv" and not self.separable
+                and type(f) is DistributedRealSHT and type(i) is DistributedInverseRealSHT
+                and f.lmax == i.lmax and f.mmax == i.mmax and comm.get_size("h") * comm.get_size("w") <= 8
+                and spectral_dist_ops.dist_spectral_conv_supported(x, self.weight))
+
+    def _dist_plans(self, device, dtype):
+        f, i = self.forward_transform, self.inverse_transform
+        ph, pw, rh, rw = comm.get_size("h"), comm.get_size("w"), comm.get_rank("h"), comm.get_rank("w")
+        return (spectral_dist_ops.DistSHTPlan.get(f.nlat, f.nlon, f.lmax, f.mmax, f.grid, ph, pw, rh, rw, device, dtype),
+                spectral_dist_ops.DistSHTPlan.get(i.nlat, i.nlon, i.lmax, i.mmax, i.grid, ph, pw, rh, rw, device, dtype))
+
     def _plans(self, device, dtype):
         f, i = self.forward_transform, self.inverse_transform
         return (spectral_ops.SHTPlan.get(f.nlat, f.nlon, f.lmax, f.mmax, f.grid, device, dtype),
@@ -98,6 +114,15 @@ class SpectralConv(nn.Module):
                 y, residual = spectral_ops.spectral_conv_dhconv(x, self.weight, pin, pout, True)
             else:
                 y, residual = spectral_ops.spectral_conv_dhconv(x, self.weight, pin, pout, False), x
+            if hasattr(self, "bias"):
+                y = y + self.bias.to(y.dtype)
+            return y, residual
+        if self._fast_dist_ok(x):
+            pin, pout = self._dist_plans(x.device, x.dtype)
+            if self.scale_residual:
+                y, residual = spectral_dist_ops.dist_spectral_conv_dhconv(x, self.weight, pin, pout, True)
+            else:
+                y, residual = spectral_dist_ops.dist_spectral_conv_dhconv(x, self.weight, pin, pout, False), x
             if hasattr(self, "bias"):
                 y = y + self.bias.to(y.dtype)
             return y, residual

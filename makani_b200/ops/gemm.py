@@ -69,6 +69,22 @@ class Tri:
     kmax_b: int = _BIG
 
 
+@dataclass
+class Segment:
+    """One k-range of a B operand that is spread over several devices.
+
+    `source` is the tensor holding the range on CPU (emulation) or the device address of the peer's buffer as an
+    int on CUDA; all segments share the strides of the `Operand` they replace.  `length` is the k extent of the
+    range, `a_pos` the k coordinate at which the matching columns of A start (a multiple of 64 elements so that
+    TMA coordinates stay 16-byte aligned), `g_start` the global k index of the range for `Tri.kmin/kmax`.
+    """
+
+    source: object
+    length: int
+    a_pos: int
+    g_start: int
+
+
 def _flat(t: torch.Tensor) -> torch.Tensor:
     """1-D view over the whole storage extent used by `t` (t must be non-overlapping and dense or a slice)."""
     if t.is_contiguous():
@@ -79,21 +95,30 @@ def _flat(t: torch.Tensor) -> torch.Tensor:
 
 
 def _emulate(M, N, K, A: Operand, B: Operand, D: Output, zlo_n, zhi_n, alpha, bias, bias_mode, act, resid, resid_offset,
-             preact, preact_offset, accumulate, tri: Tri):
+             preact, preact_offset, accumulate, tri: Tri, segments=None):
     fa, fb, fd = _flat(A.tensor), _flat(B.tensor), _flat(D.tensor)
     cdt = torch.float64 if fa.dtype == torch.float64 else torch.float32
 
-    def view(op: Operand, flat, rows):
+    def view(op: Operand, flat, rows, kext):
         rs, ks = (1, op.ld) if op.mn_major else (op.ld, 1)
-        return flat[op.offset:].as_strided((zhi_n, zlo_n, rows, K), (op.zs_hi, op.zs_lo, rs, ks)).to(cdt)
+        return flat[op.offset:].as_strided((zhi_n, zlo_n, rows, kext), (op.zs_hi, op.zs_lo, rs, ks)).to(cdt)
 
-    a = view(A, fa, M)
-    b = view(B, fb, N)
+    a = view(A, fa, M, K)
     dev = fa.device
+    if segments:
+        # B gathered from several sources; columns of A outside every segment meet zeros (TMA out-of-bounds fill)
+        b = torch.zeros(zhi_n, zlo_n, N, K, dtype=cdt, device=dev)
+        k = torch.full((K,), -1, dtype=torch.long, device=dev)
+        for sg in segments:
+            b[..., sg.a_pos: sg.a_pos + sg.length] = view(B, _flat(sg.source), N, sg.length)
+            k[sg.a_pos: sg.a_pos + sg.length] = torch.arange(sg.g_start, sg.g_start + sg.length, device=dev)
+        k = k.view(1, 1, 1, -1)
+    else:
+        b = view(B, fb, N, K)
+        k = torch.arange(K, device=dev).view(1, 1, 1, -1)
     zh = torch.arange(zhi_n, device=dev).view(-1, 1, 1, 1)
     r = torch.arange(M, device=dev).view(1, 1, -1, 1)
-    k = torch.arange(K, device=dev).view(1, 1, 1, -1)
-    kmask = (k >= tri.kmin_a * zh + tri.kmin_b) & (k < tri.kmax_a * zh + tri.kmax_b)
+    kmask = (k >= tri.kmin_a * zh + tri.kmin_b) & (k < tri.kmax_a * zh + tri.kmax_b) & (k >= 0)
     a = a * kmask.to(cdt)
     acc = torch.matmul(a, b.transpose(-1, -2))  # [zh, zl, M, N]
     rmask = (r >= tri.rmin_a * zh + tri.rmin_b) & (r < tri.rmax_a * zh + tri.rmax_b)
@@ -131,14 +156,19 @@ def _emulate(M, N, K, A: Operand, B: Operand, D: Output, zlo_n, zhi_n, alpha, bi
 def gemm(M: int, N: int, K: int, A: Operand, B: Operand, D: Output, *, zlo_n: int = 1, zhi_n: int = 1, alpha: float = 1.0,
          bias: Optional[torch.Tensor] = None, bias_mode: int = BIAS_NONE, act: int = ACT_NONE,
          resid: Optional[torch.Tensor] = None, resid_offset: int = 0, preact: Optional[torch.Tensor] = None,
-         preact_offset: int = 0, accumulate: bool = False, splits: int = 1, tri: Optional[Tri] = None, bn: int = 0) -> None:
-    """Run the batched GEMM described above, writing into `D.tensor` in place."""
+         preact_offset: int = 0, accumulate: bool = False, splits: int = 1, tri: Optional[Tri] = None, bn: int = 0,
+         segments=None, sync=None) -> None:
+    """Run the batched GEMM described above, writing into `D.tensor` in place.
+
+    `segments` (list of `Segment`) spreads the k axis of B over several devices: `K` is then the padded k extent
+    of A and `B.tensor` only supplies dtype and strides.  `sync` is the 31-entry handshake descriptor built by
+    `makani_b200.parallel.peer.sync_descriptor` (CUDA only)."""
     tri = tri or Tri()
     if bias is None:
         bias_mode = BIAS_NONE
     if not A.tensor.is_cuda:
         _emulate(M, N, K, A, B, D, zlo_n, zhi_n, alpha, bias, bias_mode, act, resid, resid_offset, preact, preact_offset,
-                 accumulate, tri)
+                 accumulate, tri, segments)
         return
     ext = _ext.require()
     ip = [M, N, K, zlo_n, zhi_n, splits, bn,
@@ -147,6 +177,17 @@ def gemm(M: int, N: int, K: int, A: Operand, B: Operand, D: Output, *, zlo_n: in
           B.offset, int(B.mn_major), B.ld, B.zs_lo, B.zs_hi,
           D.offset, int(accumulate), D.d_zlo, D.d_zhi, D.rdiv, D.rs_hi, D.rs_lo, D.ndiv, D.ns_hi,
           bias_mode, act, resid_offset, preact_offset, 0, 0]
+    if segments or sync:
+        seg = []
+        if segments and len(segments) > 1:
+            seg = [len(segments)]
+            for sg in segments:
+                assert sg.a_pos % 64 == 0, "segment start in A must be a multiple of 64 elements"
+                seg += [int(sg.source), int(sg.length), int(sg.a_pos), int(sg.g_start)]
+        elif segments:
+            raise ValueError("a single-segment operand is an ordinary operand: pass it as B")
+        ext.gemm_peer(A.tensor, B.tensor, D.tensor, bias, resid, preact, ip, float(alpha), seg, list(sync or []))
+        return
     ext.gemm(A.tensor, B.tensor, D.tensor, bias, resid, preact, ip, float(alpha))
 
 

@@ -19,13 +19,18 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _launch(case, sizes, world):
+def _launch(case, sizes, world, cuda=False):
     port = _free_port()
     procs = []
     tmp = tempfile.mkdtemp()
     for r in range(world):
         env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1",
-                   MASTER_PORT=str(port), OMP_NUM_THREADS="1", MK_TMP=tmp, CUDA_VISIBLE_DEVICES="")
+                   MASTER_PORT=str(port), OMP_NUM_THREADS="1", MK_TMP=tmp)
+        if cuda:
+            # one GPU per rank; in-switch reductions off so that a failing rank cannot disturb its peers' GPUs
+            env.update(MK_DEVICE="cuda", NCCL_NVLS_ENABLE="0")
+        else:
+            env.update(CUDA_VISIBLE_DEVICES="")
         procs.append(subprocess.Popen([sys.executable, os.path.join(HERE, "dist_worker.py"), case] + [str(s) for s in sizes],
                                       env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
     outs = []
@@ -85,3 +90,8 @@ def test_channel_parallel_mlp(sizes):
 @pytest.mark.parametrize("sizes", [(2, 1, 1, 1), (2, 2, 1, 1)])
 def test_spatially_parallel_sfno_matches_serial(sizes):
     _launch("sfno_and_checkpoint", sizes, sizes[0] * sizes[1])
+
+
+@pytest.mark.parametrize("sizes", [(2, 1, 1, 1), (1, 2, 1, 1), (2, 2, 1, 1), (3, 1, 1, 1)])
+def test_fused_distributed_spectral_conv(sizes):
+    _launch("fused_spectral", sizes, sizes[0] * sizes[1])

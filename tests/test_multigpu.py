@@ -1,0 +1,25 @@
+"""Multi-GPU tests (one process per GPU, NCCL + peer memory): the fused compute+communication kernels against their
+serial counterparts.  Skipped when the machine has fewer GPUs than the case needs."""
+
+import pytest
+import torch
+
+from test_distributed import _launch
+
+pytestmark = pytest.mark.gpu
+
+
+def _need(n):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+
+
+@pytest.mark.parametrize("sizes", [(1, 2, 1, 1), (2, 1, 1, 1)])
+def test_fused_distributed_spectral_conv_2gpu(sizes):
+    _need(2)
+    _launch("fused_spectral", sizes, 2, cuda=True)
+
+
+def test_fused_distributed_spectral_conv_4gpu():
+    _need(4)
+    _launch("fused_spectral", (2, 2, 1, 1), 4, cuda=True)
