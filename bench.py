@@ -35,6 +35,8 @@ def parse():
     ap.add_argument("--impl", type=str, default="native", choices=["native", "reference"])
     ap.add_argument("--small", action="store_true", help="reduced grid for profiling captures (not a bench value)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--h", type=int, default=1, help="latitude-parallel ranks per model instance (default: pure data parallel)")
+    ap.add_argument("--w", type=int, default=1, help="longitude-parallel ranks per model instance")
     return ap.parse_args()
 
 
@@ -129,10 +131,10 @@ def main():
     assert world == args.gpus or world == 1, f"--gpus {args.gpus} but WORLD_SIZE={world}"
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    comm.init(model_parallel_sizes=[1, 1, 1, 1])
+    comm.init(model_parallel_sizes=[args.h, args.w, 1, 1])
     _ext.require()
 
-    cfg = FlagshipConfig(small=args.small)
+    cfg = FlagshipConfig(small=args.small, h=args.h, w=args.w)
     runner = build_flagship(cfg, dev)
 
     def barrier():
@@ -164,7 +166,8 @@ def main():
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_per_step = t.item() / args.steps
-    global_batch = cfg.batch_per_gpu * world
+    dp = world // (args.h * args.w)
+    global_batch = cfg.batch_per_gpu * dp
     value = global_batch / (ms_per_step / 1e3)
     _ext.check_device_errors(dev)
     final_loss = float(loss)
@@ -181,7 +184,7 @@ def main():
             "scaling": "weak", "vs_baseline": (value / BASELINE_VALUE) if BASELINE_VALUE else None, "dtype": "bf16",
             "data": "synthetic N(0,1), random-init weights", "impl": "native",
             "config": {"model": cfg.name, "global_batch": global_batch, "seq_len": f"{cfg.nlat}x{cfg.nlon}",
-                       "parallelism": f"dp{world}", "l2_policy": "inputs+activations per step (>2 GB) exceed the 126 MB L2",
+                       "parallelism": f"dp{dp}" + (f"xh{args.h}w{args.w}" if args.h * args.w > 1 else ""), "l2_policy": "inputs+activations per step (>2 GB) exceed the 126 MB L2",
                        "loss": cfg.loss, "optimizer": "AdamW (fused)", "final_loss": final_loss},
             "clocks": clocks, "gpu_launches": launches,
         }
@@ -189,6 +192,8 @@ def main():
             out["e2e"] = e2e
         print(json.dumps(out))
     if world > 1:
+        from makani_b200.parallel import peer
+        peer.release_slots()
         dist.barrier(device_ids=[local_rank])
         dist.destroy_process_group()
     return 0

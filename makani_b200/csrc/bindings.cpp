@@ -116,10 +116,32 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& d, const c10::optional<Tenso
 // GEMM whose B operand is gathered from peer devices along k and/or that takes part in cross-device handshakes
 void gemm_peer(const Tensor& a, const Tensor& b, Tensor& d, const c10::optional<Tensor>& bias,
                const c10::optional<Tensor>& resid, const c10::optional<Tensor>& preact, const std::vector<int64_t>& ip,
-               double alpha, const std::vector<int64_t>& seg, const std::vector<int64_t>& sync) {
+               double alpha, const std::vector<int64_t>& seg, const std::vector<int64_t>& sync,
+               const std::vector<int64_t>& dests) {
   mk::GemmPeer g;
   parse_peer(g, seg, sync);
+  MK_CHECK(dests.size() <= 7, "gemm_peer: at most 7 additional destinations");
+  g.ndx = static_cast<int>(dests.size());
+  const int64_t d_off = ip[25];
+  const int64_t osz = d.element_size();
+  for (size_t q = 0; q < dests.size(); ++q) g.Dx[q] = reinterpret_cast<char*>(dests[q]) + d_off * osz;
   gemm_impl(a, b, d, bias, resid, preact, ip, alpha, &g);
+}
+
+// src: local tensor whose data pointer is the first row; dsts: device addresses (this rank's copy and its peers')
+void peer_publish(const Tensor& src, int64_t rows, int64_t row_bytes, int64_t src_stride_bytes, int64_t dst_stride_bytes,
+                  const std::vector<int64_t>& dsts, const std::vector<int64_t>& sync) {
+  MK_CHECK(src.is_cuda(), "peer_publish: CUDA tensor expected");
+  MK_CHECK(!dsts.empty() && dsts.size() <= 8, "peer_publish: 1..8 destinations");
+  mk::GemmPeer g;
+  parse_peer(g, {}, sync);
+  c10::cuda::CUDAGuard guard(src.device());
+  Tensor ef = err_flag_for(src);
+  void* dp[8];
+  for (size_t q = 0; q < dsts.size(); ++q) dp[q] = reinterpret_cast<void*>(dsts[q]);
+  check_cuda(mk::peer_publish_launch(src.data_ptr(), rows, row_bytes, src_stride_bytes, dst_stride_bytes, dp,
+                                     static_cast<int>(dsts.size()), g, ef.data_ptr<int>(), cur_stream()),
+             "peer_publish");
 }
 
 void gemm_impl(const Tensor& a, const Tensor& b, Tensor& d, const c10::optional<Tensor>& bias,
@@ -382,6 +404,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, "tcgen05 GEMM with fused epilogue");
   m.def("gemm_peer", &gemm_peer, "tcgen05 GEMM reading its B operand from peer devices");
   m.def("peer_sync", &peer_sync);
+  m.def("peer_publish", &peer_publish, "strided copy into this rank's and its peers' buffers with the producer handshake");
   m.def("read_error_flag", &read_error_flag);
   m.def("clear_error_flag", &clear_error_flag);
   m.def("inorm_fwd", &inorm_fwd);

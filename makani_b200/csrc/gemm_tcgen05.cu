@@ -42,6 +42,10 @@ struct PeerSync {
 struct BMaps {
   CUtensorMap m[MAX_SEG];
 };
+// tensor maps of the additional destinations (the same output written into peers' memory)
+struct DMaps {
+  CUtensorMap m[MAX_SEG - 1];
+};
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;   // 2 s per barrier wait
 
 struct KParams {
@@ -70,6 +74,9 @@ struct KParams {
   int seg_len[MAX_SEG];           // local k extent of each segment
   int seg_apos[MAX_SEG];          // k coordinate of the segment start in the A operand (padded layout)
   int seg_gstart[MAX_SEG];        // global k index of the segment start (for the kmin/kmax structure)
+  // ---- output replicated into peers' memory: ndx additional destinations with the layout of D
+  int ndx;
+  void* Dx[MAX_SEG - 1];
   // ---- cross-device handshakes (all counters are monotonic and live in device memory)
   PeerSync sync;
 };
@@ -278,7 +285,7 @@ template <int BN, int EB, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ BMaps maps_b,
             const __grid_constant__ CUtensorMap map_e, const __grid_constant__ CUtensorMap map_d,
-            const __grid_constant__ CUtensorMap map_p, const KParams p) {
+            const __grid_constant__ CUtensorMap map_p, const __grid_constant__ DMaps maps_dx, const KParams p) {
   const CUtensorMap& map_b = maps_b.m[0];
   constexpr int BK = 128 / EB;            // elements per 128-byte k-slab
   constexpr int UMMA_K = 32 / EB;         // elements per tcgen05.mma
@@ -603,6 +610,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
             if (r0 < p.M) {
               if constexpr (EPI == 2) tma_store_4d(&map_p, stg_base, nb, r0, c.zlo, c.zhi);
               tma_store_4d(&map_d, stg_base + (EPI == 2 ? 32 * 128 : sb * 32 * 128), nb, r0, c.zlo, c.zhi);
+              if constexpr (EPI == 1) {
+                for (int dq = 0; dq < p.ndx; ++dq)   // the same box goes to every peer's copy (plain stores over NVLink)
+                  tma_store_4d(&maps_dx.m[dq], stg_base + sb * 32 * 128, nb, r0, c.zlo, c.zhi);
+              }
             }
             tma_store_commit();
           }
@@ -701,6 +712,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
 #pragma unroll
               for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
               *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.D) + off) = *reinterpret_cast<uint4*>(h);
+              for (int dq = 0; dq < p.ndx; ++dq)
+                *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.Dx[dq]) + off) = *reinterpret_cast<uint4*>(h);
             }
           } else {
             // ---- scalar path (ragged edge, unaligned layouts, atomic accumulation)
@@ -726,7 +739,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
                   x = (p.act == 2) ? x * gelu_grad(rr) : x + rr;
                 }
                 if (p.out_f32) static_cast<float*>(p.D)[o] = x;
-                else static_cast<__nv_bfloat16*>(p.D)[o] = __float2bfloat16(x);
+                else {
+                  static_cast<__nv_bfloat16*>(p.D)[o] = __float2bfloat16(x);
+                  for (int dq = 0; dq < p.ndx; ++dq) static_cast<__nv_bfloat16*>(p.Dx[dq])[o] = __float2bfloat16(x);
+                }
               }
             }
           }
@@ -848,7 +864,7 @@ constexpr int SMEM_LIMIT = 232448;   // 227 KB per CTA on sm_100
 
 template <int BN, int EB, int EPI>
 cudaError_t launch_t(const CUtensorMap& ma, const BMaps& mb, const CUtensorMap& me, const CUtensorMap& md,
-                     const CUtensorMap& mp, KParams& kp, cudaStream_t stream) {
+                     const CUtensorMap& mp, const DMaps& mdx, KParams& kp, cudaStream_t stream) {
   constexpr int STAGE = A_STAGE_BYTES + BN * 128;
   constexpr int FIXED = (EPI != 0 ? STG_BYTES : 0) + 8 * (2 * MAX_STAGES + 8) + 16 + 1024;
   const int e_bytes = kp.e_tma ? 2 * BM * BN * 2 : 0;
@@ -872,7 +888,7 @@ cudaError_t launch_t(const CUtensorMap& ma, const BMaps& mb, const CUtensorMap& 
   }
   long long grid = kp.total_tiles < num_sms ? kp.total_tiles : num_sms;
   if (grid < 1) grid = 1;
-  gemm_kernel<BN, EB, EPI><<<static_cast<unsigned>(grid), NUM_THREADS, smem, stream>>>(ma, mb, me, md, mp, kp);
+  gemm_kernel<BN, EB, EPI><<<static_cast<unsigned>(grid), NUM_THREADS, smem, stream>>>(ma, mb, me, md, mp, mdx, kp);
   return cudaGetLastError();
 }
 
@@ -931,6 +947,64 @@ __global__ void peer_sync_kernel(const PeerSync sy, int phase, int* err) {
   }
 }
 
+// Copies `rows` rows of `row_bytes` (multiple of 16) from local memory into the same place of up to 8 destination
+// buffers (this device's and its peers'), with the producer handshake folded in: every block waits until all
+// peers have consumed the previous contents, the last block to finish publishes the new generation.
+__global__ void __launch_bounds__(256) peer_publish_kernel(const uint4* __restrict__ src, long long rows, int row_vec,
+                                                           long long src_stride_vec, long long dst_stride_vec, int ndst,
+                                                           const PeerSync sy, int* err) {
+  struct Dst {
+    uint4* p[MAX_SEG];
+  };
+  __shared__ int ok_s;
+  if (threadIdx.x == 0) {
+    bool ok = true;
+    for (int w = 0; w < sy.nwait && ok; ++w) {
+      const unsigned int need = *sy.wait_exp[w] + static_cast<unsigned int>(sy.wait_off[w]);
+      for (int peer = 0; peer < sy.np_wait[w] && ok; ++peer) {
+        uint64_t t0 = 0;
+        for (uint32_t it = 0;; ++it) {
+          if (static_cast<int>(ld_acquire_sys_u32(sy.wait[w] + peer) - need) >= 0) break;
+          if ((it & 255u) == 255u) {
+            const uint64_t now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_LIMIT_NS) {
+              atomicExch(err, 40 + w);
+              ok = false;
+              break;
+            }
+          }
+        }
+      }
+    }
+    ok_s = ok ? 1 : 0;
+  }
+  __syncthreads();
+  if (ok_s) {
+    const long long total = rows * row_vec;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+      const long long r = i / row_vec;
+      const int c = static_cast<int>(i - r * row_vec);
+      const uint4 v = src[r * src_stride_vec + c];
+      for (int q = 0; q < ndst; ++q) reinterpret_cast<uint4*>(sy.sig[1][q])[r * dst_stride_vec + c] = v;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && sy.done_ctr != nullptr) {
+    __threadfence_system();
+    const unsigned int prev = atomicAdd(sy.done_ctr, 1u);
+    if (prev == gridDim.x - 1) {
+      *sy.done_ctr = 0;
+      for (int i = 0; i < sy.nwait; ++i)
+        if (sy.bump[i]) atomicAdd(sy.bump[i], 1u);
+      __threadfence_system();
+      for (int peer = 0; peer < sy.np_sig[0]; ++peer)
+        if (sy.sig[0][peer]) atomicAdd_system(sy.sig[0][peer], 1u);
+    }
+  }
+}
+
 void fill_sync(PeerSync& sy, const GemmPeer* g) {
   memset(&sy, 0, sizeof(sy));
   if (!g) return;
@@ -955,6 +1029,28 @@ cudaError_t peer_sync_launch(const GemmPeer& g, int phase, int* err_flag, cudaSt
   PeerSync sy;
   fill_sync(sy, &g);
   peer_sync_kernel<<<1, 32, 0, stream>>>(sy, phase, err_flag);
+  return cudaGetLastError();
+}
+
+cudaError_t peer_publish_launch(const void* src, long long rows, long long row_bytes, long long src_stride_bytes,
+                                long long dst_stride_bytes, void* const* dsts, int ndst, const GemmPeer& g, int* err_flag,
+                                cudaStream_t stream) {
+  if (rows <= 0 || row_bytes <= 0) return cudaSuccess;
+  if ((row_bytes & 15) || (src_stride_bytes & 15) || (dst_stride_bytes & 15) || (reinterpret_cast<uintptr_t>(src) & 15) ||
+      ndst < 1 || ndst > MAX_SEG || g.nsig > 1)
+    return cudaErrorInvalidValue;
+  PeerSync sy;
+  fill_sync(sy, &g);
+  // the second signal list carries the destination base pointers (the protocol itself needs one list only)
+  for (int q = 0; q < MAX_SEG; ++q) sy.sig[1][q] = q < ndst ? static_cast<unsigned int*>(dsts[q]) : nullptr;
+  for (int q = 0; q < ndst; ++q)
+    if (reinterpret_cast<uintptr_t>(dsts[q]) & 15) return cudaErrorInvalidValue;
+  const long long total = rows * (row_bytes / 16);
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  peer_publish_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+      static_cast<const uint4*>(src), rows, static_cast<int>(row_bytes / 16), src_stride_bytes / 16, dst_stride_bytes / 16,
+      ndst, sy, err_flag);
   return cudaGetLastError();
 }
 
@@ -1022,7 +1118,16 @@ cudaError_t gemm_launch(const GemmProblem& p, const GemmOperand& A, const GemmOp
   kp.total_tiles = static_cast<long long>(kp.m_tiles) * kp.n_tiles * kp.splits * p.zlo_n * p.zhi_n;
   kp.err = err_flag;
   kp.nseg = 1;
+  kp.ndx = 0;
   fill_sync(kp.sync, peer);
+  if (peer && peer->ndx > 0) {
+    if (peer->ndx > MAX_SEG - 1 || e.out_f32 || e.accumulate || kp.splits != 1 || e.preact) {
+      snprintf(g_err, sizeof(g_err), "replicated output: bf16 plain stores only, at most %d extra destinations", MAX_SEG - 1);
+      return cudaErrorInvalidValue;
+    }
+    kp.ndx = peer->ndx;
+    for (int q = 0; q < peer->ndx; ++q) kp.Dx[q] = peer->Dx[q];
+  }
   if (peer && peer->nseg > 1) {
     if (kp.splits != 1 || peer->nseg > MAX_SEG) {
       snprintf(g_err, sizeof(g_err), "multi-device operand: split-k not supported, at most %d segments", MAX_SEG);
@@ -1071,6 +1176,8 @@ cudaError_t gemm_launch(const GemmProblem& p, const GemmOperand& A, const GemmOp
   memset(&md, 0, sizeof(md));
   md = ma;
   mp = ma;
+  DMaps mdx;
+  for (int q = 0; q < MAX_SEG - 1; ++q) mdx.m[q] = ma;   // placeholders: always valid descriptors
   if (eb == 2 && !e.out_f32 && kp.vec_ok && !e.accumulate && plain && e.d_zlo >= 0 && e.d_zhi >= 0 &&
       (kp.bias_mode != 2 || (reinterpret_cast<uintptr_t>(e.bias) & 15) == 0)) {
     if (!e.resid && !e.preact && e.act == 0) epi = 1;
@@ -1080,16 +1187,21 @@ cudaError_t gemm_launch(const GemmProblem& p, const GemmOperand& A, const GemmOp
     if (epi != 0) {
       bool ok = make_map_e(&md, e.D, p.M, p.N, e.rs_lo, e.d_zlo, e.d_zhi, p.zlo_n, p.zhi_n, bn, 32);
       if (ok && epi == 2) ok = make_map_e(&mp, e.preact, p.M, p.N, e.rs_lo, e.d_zlo, e.d_zhi, p.zlo_n, p.zhi_n, bn, 32);
+      if (ok && kp.ndx > 0) {
+        if (epi != 1) ok = false;   // replicated output goes through the plain-store epilogue or the generic one
+        for (int q = 0; ok && q < kp.ndx; ++q)
+          ok = make_map_e(&mdx.m[q], kp.Dx[q], p.M, p.N, e.rs_lo, e.d_zlo, e.d_zhi, p.zlo_n, p.zhi_n, bn, 32);
+      }
       if (!ok) epi = 0;
     }
   }
   if (eb == 4) {
-    if (bn == 256) return launch_t<256, 4, 0>(ma, mbs, me, md, mp, kp, stream);
-    return launch_t<128, 4, 0>(ma, mbs, me, md, mp, kp, stream);
+    if (bn == 256) return launch_t<256, 4, 0>(ma, mbs, me, md, mp, mdx, kp, stream);
+    return launch_t<128, 4, 0>(ma, mbs, me, md, mp, mdx, kp, stream);
   }
 #define MK_DISPATCH(EPI_)                                                    \
-  if (bn == 256) return launch_t<256, 2, EPI_>(ma, mbs, me, md, mp, kp, stream);      \
-  return launch_t<128, 2, EPI_>(ma, mbs, me, md, mp, kp, stream);
+  if (bn == 256) return launch_t<256, 2, EPI_>(ma, mbs, me, md, mp, mdx, kp, stream); \
+  return launch_t<128, 2, EPI_>(ma, mbs, me, md, mp, mdx, kp, stream);
   switch (epi) {
     case 1: { MK_DISPATCH(1) }
     case 2: { MK_DISPATCH(2) }

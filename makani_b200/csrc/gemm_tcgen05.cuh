@@ -69,7 +69,15 @@ struct GemmPeer {
   unsigned int* bump[2];
   unsigned int* sig[2][8];
   unsigned int* done_ctr;
+  int ndx;                         // additional destinations of the output (peers' copies of the same buffer)
+  void* Dx[7];                     // base pointers matching GemmEpilogue::D (offset already applied)
 };
+
+// Copy of a strided 2-D block into the same place of `ndst` destination buffers (this device's and its peers'),
+// with the producer side of the handshake in `g` (wait list 0, signal list 0) executed by the same kernel.
+cudaError_t peer_publish_launch(const void* src, long long rows, long long row_bytes, long long src_stride_bytes,
+                                long long dst_stride_bytes, void* const* dsts, int ndst, const GemmPeer& g, int* err_flag,
+                                cudaStream_t stream);
 
 // Waits (bounded) and/or signals of the same handshake protocol without a GEMM, for buffers produced or consumed by
 // other kernels.  phase 0: wait only; phase 1: bump + signal only.

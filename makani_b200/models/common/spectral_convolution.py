@@ -91,7 +91,7 @@ class SpectralConv(nn.Module):
         """Sharded grids: GEMM chain whose k loops read the peers' buffers directly (needs peer-mapped memory, i.e.
         NCCL ranks on one node, and l/m truncations common to both transforms)."""
         f, i = self.forward_transform, self.inverse_transform
-        return (x.is_cuda and self.operator_type == "dhconv" and not self.separable
+        return (x.is_cuda and spectral_dist_ops.ENABLED and self.operator_type == "dhconv" and not self.separable
                 and type(f) is DistributedRealSHT and type(i) is DistributedInverseRealSHT
                 and f.lmax == i.lmax and f.mmax == i.mmax and comm.get_size("h") * comm.get_size("w") <= 8
                 and spectral_dist_ops.dist_spectral_conv_supported(x, self.weight))

@@ -157,12 +157,13 @@ def gemm(M: int, N: int, K: int, A: Operand, B: Operand, D: Output, *, zlo_n: in
          bias: Optional[torch.Tensor] = None, bias_mode: int = BIAS_NONE, act: int = ACT_NONE,
          resid: Optional[torch.Tensor] = None, resid_offset: int = 0, preact: Optional[torch.Tensor] = None,
          preact_offset: int = 0, accumulate: bool = False, splits: int = 1, tri: Optional[Tri] = None, bn: int = 0,
-         segments=None, sync=None) -> None:
+         segments=None, sync=None, dests=None) -> None:
     """Run the batched GEMM described above, writing into `D.tensor` in place.
 
     `segments` (list of `Segment`) spreads the k axis of B over several devices: `K` is then the padded k extent
     of A and `B.tensor` only supplies dtype and strides.  `sync` is the 31-entry handshake descriptor built by
-    `makani_b200.parallel.peer.sync_descriptor` (CUDA only)."""
+    `makani_b200.parallel.peer.sync_descriptor` (CUDA only).  `dests` lists device addresses of additional copies of
+    the output buffer (peers' memory) that receive the same bf16 stores as `D.tensor`."""
     tri = tri or Tri()
     if bias is None:
         bias_mode = BIAS_NONE
@@ -177,7 +178,7 @@ def gemm(M: int, N: int, K: int, A: Operand, B: Operand, D: Output, *, zlo_n: in
           B.offset, int(B.mn_major), B.ld, B.zs_lo, B.zs_hi,
           D.offset, int(accumulate), D.d_zlo, D.d_zhi, D.rdiv, D.rs_hi, D.rs_lo, D.ndiv, D.ns_hi,
           bias_mode, act, resid_offset, preact_offset, 0, 0]
-    if segments or sync:
+    if segments or sync or dests:
         seg = []
         if segments and len(segments) > 1:
             seg = [len(segments)]
@@ -186,7 +187,8 @@ def gemm(M: int, N: int, K: int, A: Operand, B: Operand, D: Output, *, zlo_n: in
                 seg += [int(sg.source), int(sg.length), int(sg.a_pos), int(sg.g_start)]
         elif segments:
             raise ValueError("a single-segment operand is an ordinary operand: pass it as B")
-        ext.gemm_peer(A.tensor, B.tensor, D.tensor, bias, resid, preact, ip, float(alpha), seg, list(sync or []))
+        ext.gemm_peer(A.tensor, B.tensor, D.tensor, bias, resid, preact, ip, float(alpha), seg, list(sync or []),
+                      [int(d) for d in (dests or [])])
         return
     ext.gemm(A.tensor, B.tensor, D.tensor, bias, resid, preact, ip, float(alpha))
 

@@ -14,16 +14,19 @@ tcgen05 GEMM whose k loop walks over the peers of one group:
     S4  T4[b, k_loc, (m_loc, ri), o] = sum_{h-peers q} sum_{l in l(q)} P[m, l, k] T3_q[b, m, l, (ri, o)]
     S5  y[b, k_loc, i_loc, o]        = sum_{w-peers q} sum_{m in m(q)} G[i, (m, ri)] T4_q[b, k_loc, (m, ri), o]
 
-The B operand of a stage is fetched tile by tile from the producing ranks' memory with TMA loads over NVLink
-(plain tiled loads, no multicast) while the tensor cores work on earlier tiles, so the transfer overlaps the math
-and each rank only ever computes the output slice it owns.  Producer/consumer ordering between ranks uses the
-monotonic device counters of `makani_b200.parallel.peer` and is part of the same kernels.  On CPU (gloo) the
-same code runs with an all-gather standing in for the peer reads, which is how the layout algebra is tested
-without GPUs.
+The stage that produces a buffer which peers need (x, T1, T3, T4) stores every finished tile from its epilogue
+into its segment of every peer's copy of that buffer (plain stores / TMA stores over NVLink, no multicast), so
+the all-gather happens tile by tile while the tensor cores work on the next tiles and each byte crosses NVLink
+once per destination.  The consuming stage then walks its k loop over the segments of its own local copy
+(re-reads hit local HBM / L2) and only computes the output slice it owns.  Producer/consumer ordering between
+ranks uses the monotonic device counters of `makani_b200.parallel.peer` and is part of the same kernels.  On CPU
+(gloo) the same code runs with an all-gather standing in for the peer stores, which is how the layout algebra is
+tested without GPUs.
 """
 
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Tuple
 
 import numpy as np
@@ -37,6 +40,8 @@ from .gemm import Operand, Output, Segment, Tri, gemm, pad_to
 from .spectral import _to_cl, expand_weight, fold_weight_grad
 
 SEG_ALIGN = 64   # elements: one 128-byte k-slab of bf16
+# MAKANI_B200_FUSED_DIST_SHT=0 falls back to the all-to-all formulation (for A/B timing of the two designs)
+ENABLED = os.environ.get("MAKANI_B200_FUSED_DIST_SHT", "1") != "0"
 
 
 def _seg_layout(shapes: List[int]) -> Tuple[List[int], int]:
@@ -139,6 +144,10 @@ def _slot(name, group, nbytes, device, size):
     return peer.get_slot(name, group, nbytes, device) if size > 1 else None
 
 
+def _dests(slot):
+    return slot.dests() if slot is not None else None
+
+
 def _segments(slot, shapes, pos, starts):
     return [Segment(src, n, p, g) for src, n, p, g in zip(slot.sources(), shapes, pos, starts)]
 
@@ -171,9 +180,7 @@ def stage_grid_to_slot(x: torch.Tensor, plan: DistSHTPlan):
         return None, x
     slot = peer.get_slot("xw", "w", B * plan.hmax * plan.wmax * C * _esz(x.dtype), x.device)
     view = slot.tensor(x.dtype, (B, hl, plan.wmax, C))
-    peer.begin_produce(slot)
-    view[:, :, :wl, :].copy_(x.permute(0, 2, 3, 1))
-    peer.end_produce(slot)
+    slot.publish(x, B * hl, wl * C, wl * C, plan.wmax * C)
     return slot, view
 
 
@@ -194,12 +201,12 @@ def stage_dft_analysis(xslot, xv, table, plan: DistSHTPlan, B, C):
     if xslot is None:
         W = plan.nlon
         gemm(k2, C, W, Operand(table, ld=plan.kw), Operand(xv, ld=C, mn_major=True, zs_lo=W * C, zs_hi=hl * W * C),
-             out, zlo_n=hl, zhi_n=B, bn=_bn(C), sync=sync)
+             out, zlo_n=hl, zhi_n=B, bn=_bn(C), sync=sync, dests=_dests(t1slot))
     else:
         segs = _segments(xslot, plan.lon_shapes, plan.lon_pos, _starts(plan.lon_shapes))
         gemm(k2, C, plan.kw, Operand(table, ld=plan.kw),
              Operand(xv, ld=C, mn_major=True, zs_lo=plan.wmax * C, zs_hi=hl * plan.wmax * C),
-             out, zlo_n=hl, zhi_n=B, bn=_bn(C), segments=segs, sync=sync)
+             out, zlo_n=hl, zhi_n=B, bn=_bn(C), segments=segs, sync=sync, dests=_dests(t1slot))
     return t1slot, t1, hstride
 
 
@@ -242,7 +249,8 @@ def stage_contract(t2, wx, transpose_w, plan: DistSHTPlan, private: bool = False
          Operand(t2, ld=kin, zs_hi=ml * kin, zs_lo=ll * ml * kin),
          Operand(wx, ld=npp, mn_major=transpose_w, zs_hi=nq * npp),
          Output(t3, rs_lo=lstride * nout, d_zhi=nout, d_zlo=ml * lstride * nout),
-         zhi_n=ll, zlo_n=B, tri=Tri(rmax_a=1, rmax_b=1 + plan.l0 - plan.m0), sync=peer.sync_descriptor(produce=slot))
+         zhi_n=ll, zlo_n=B, tri=Tri(rmax_a=1, rmax_b=1 + plan.l0 - plan.m0), sync=peer.sync_descriptor(produce=slot),
+         dests=_dests(slot))
     return slot, t3, lstride
 
 
@@ -253,9 +261,7 @@ def stage_lm_to_slot(t2: torch.Tensor, plan: DistSHTPlan):
     if slot is None:
         return None, t2, ll
     view = slot.tensor(t2.dtype, (B, plan.llmax, ml, n2))
-    peer.begin_produce(slot)
-    view[:, :ll].copy_(t2)
-    peer.end_produce(slot)
+    slot.publish(t2, B, ll * ml * n2, ll * ml * n2, plan.llmax * ml * n2)
     return slot, view, plan.llmax
 
 
@@ -281,10 +287,10 @@ def stage_legendre_synthesis(tslot, t, lstride, lm_order, table, plan: DistSHTPl
     tri = Tri(kmin_a=1, kmin_b=plan.m0)
     sync = peer.sync_descriptor(consume=tslot, produce=t4slot)
     if tslot is None:
-        gemm(hl, n2, plan.lmax, aop, bop, out, zhi_n=ml, zlo_n=B, tri=tri, sync=sync)
+        gemm(hl, n2, plan.lmax, aop, bop, out, zhi_n=ml, zlo_n=B, tri=tri, sync=sync, dests=_dests(t4slot))
     else:
         segs = _segments(tslot, plan.l_shapes, plan.l_pos, _starts(plan.l_shapes))
-        gemm(hl, n2, plan.kl, aop, bop, out, zhi_n=ml, zlo_n=B, tri=tri, segments=segs, sync=sync)
+        gemm(hl, n2, plan.kl, aop, bop, out, zhi_n=ml, zlo_n=B, tri=tri, segments=segs, sync=sync, dests=_dests(t4slot))
     return t4slot, t4, jstride
 
 
@@ -364,11 +370,11 @@ class _DistSpectralConv(torch.autograd.Function):
                 _, priv, _ = stage_contract(dt3, wx, True, plan_in, private=True)
                 nout = wx.shape[2]
                 slot, t3v, ls = t3_buffer(plan_in, B, nout, dt3.dtype, dt3.device)
-                if slot is not None:
-                    peer.begin_produce(slot)
-                torch.add(priv, dr2.transpose(1, 2), out=t3v[:, :, : plan_in.ll])
-                if slot is not None:
-                    peer.end_produce(slot)
+                if slot is None:
+                    torch.add(priv, dr2.transpose(1, 2), out=t3v)
+                else:
+                    total = priv + dr2.transpose(1, 2)
+                    slot.publish(total, B * plan_in.ml, plan_in.ll * nout, plan_in.ll * nout, ls * nout)
             else:
                 slot, t3v, ls = stage_contract(dt3, wx, True, plan_in)
             dx = dist_sht_synthesis(slot, t3v, ls, False, plan_in, B, C, plan_in.pw_syn, plan_in.ft_syn)

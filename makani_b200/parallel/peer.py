@@ -73,13 +73,15 @@ class SymmetricBuffer:
 
 # ---------------------------------------------------------------------------------------------- handshake slots
 #
-# A slot is a symmetric buffer that one kernel on every rank of a group writes (its own copy) and a later kernel
-# on every rank reads (all copies, through peer pointers), again and again.  Ordering between ranks is kept by
-# monotonic counters in device memory, so no host synchronisation and no NCCL call is involved and the whole
-# sequence can be captured in a CUDA graph:
+# A slot is a symmetric buffer holding one segment per rank of a group.  A producing kernel on rank r writes
+# segment r of EVERY rank's copy (plain stores over NVLink from its epilogue: an all-gather done by the
+# producer, tile by tile, while it computes); a later kernel on every rank reads all segments from its own,
+# local copy.  Data therefore crosses NVLink exactly once per destination and is re-read from local HBM / L2.
+# Ordering between ranks is kept by monotonic counters in device memory, so no host synchronisation and no NCCL
+# call is involved and the whole sequence can be captured in a CUDA graph:
 #
-#   ready[p]  (on every rank)  incremented by rank p when its copy of generation g is complete
-#   free[p]   (on every rank)  incremented by rank p when it has finished reading generation g everywhere
+#   ready[p]  (on every rank)  incremented by rank p when its segment of generation g has been written everywhere
+#   free[p]   (on every rank)  incremented by rank p when it has finished reading generation g
 #   n_prod, n_read (local)     generations produced / consumed so far by this rank
 #
 # A producer waits for free[p] >= n_prod for all p, a consumer for ready[p] >= n_read + 1; both waits are bounded
@@ -89,27 +91,43 @@ CTRL_BYTES = 256
 _READY, _FREE, _NPROD, _NREAD, _DONE = 0, 32, 64, 68, 72   # byte offsets inside the control block
 
 
+def _numel(shape) -> int:
+    n = 1
+    for s in shape:
+        n *= int(s)
+    return n
+
+
 class PeerSlot:
-    """Symmetric buffer plus handshake counters over one named communicator group (CUDA, one node)."""
+    """Symmetric buffer of `world` segments plus handshake counters over one communicator group (CUDA, one node)."""
 
     is_peer = True
 
-    def __init__(self, nbytes: int, group=None, device: Optional[torch.device] = None):
-        self.buf = SymmetricBuffer(CTRL_BYTES + nbytes, group=group, device=device)
+    def __init__(self, seg_bytes: int, group=None, device: Optional[torch.device] = None):
+        world = dist.get_world_size(group)
+        self.seg_capacity = (int(seg_bytes) + 255) // 256 * 256
+        self.buf = SymmetricBuffer(CTRL_BYTES + world * self.seg_capacity, group=group, device=device)
         self.world, self.rank, self.device = self.buf.world, self.buf.rank, self.buf.device
-        self.capacity = self.buf.nbytes - CTRL_BYTES
-        self._hold = None
+        self.seg_stride = self.seg_capacity
+
+    def set_layout(self, seg_bytes: int) -> None:
+        """Segment stride for the next produce/consume pair (identical on every rank)."""
+        self.seg_stride = (int(seg_bytes) + 255) // 256 * 256
+        assert self.seg_stride <= self.seg_capacity
 
     # data ------------------------------------------------------------------------------------------
     def tensor(self, dtype, shape) -> torch.Tensor:
-        n = 1
-        for s in shape:
-            n *= int(s)
-        return self.buf.view(dtype, n, CTRL_BYTES).view(*shape)
+        """This rank's segment inside its own copy."""
+        return self.buf.view(dtype, _numel(shape), CTRL_BYTES + self.rank * self.seg_stride).view(*shape)
+
+    def dests(self, include_self: bool = False):
+        """Addresses of this rank's segment inside every peer's copy (written by this rank's kernels only)."""
+        off = CTRL_BYTES + self.rank * self.seg_stride
+        return [p + off for r, p in enumerate(self.buf.ptrs) if include_self or r != self.rank]
 
     def sources(self):
-        """Device addresses of every rank's copy (to be read by this rank's kernels only, never by library code)."""
-        return [p + CTRL_BYTES for p in self.buf.ptrs]
+        """Addresses of all segments inside this rank's own copy."""
+        return [self.buf.local_ptr + CTRL_BYTES + q * self.seg_stride for q in range(self.world)]
 
     # handshake pieces ------------------------------------------------------------------------------
     def consume_lists(self):
@@ -128,12 +146,20 @@ class PeerSlot:
     def done_ptr(self) -> int:
         return self.buf.local_ptr + _DONE
 
+    def publish(self, src: torch.Tensor, rows: int, row_elems: int, src_stride: int, dst_stride: int) -> None:
+        """Strided copy of `rows` x `row_elems` elements of `src` into this rank's segment of every copy, with the
+        producer handshake done by the same kernel."""
+        esz = src.element_size()
+        _ext.require().peer_publish(src, int(rows), int(row_elems) * esz, int(src_stride) * esz, int(dst_stride) * esz,
+                                    self.dests(include_self=True), sync_descriptor(produce=self))
+
     def close(self):
         self.buf.close()
 
 
 def sync_descriptor(consume: Optional[PeerSlot] = None, produce: Optional[PeerSlot] = None) -> Optional[List[int]]:
-    """Flat handshake descriptor for a kernel that reads `consume` from all peers and/or writes its copy of `produce`.
+    """Flat handshake descriptor for a kernel that reads all segments of `consume` and/or writes its segment of
+    `produce` on every rank.
 
     Layout: [nwait, nsig, done_ctr, {wait, expected, offset, bump, peers} x 2, {peers, signal[8]} x 2]."""
     lists = []
@@ -161,41 +187,36 @@ def sync_descriptor(consume: Optional[PeerSlot] = None, produce: Optional[PeerSl
     return out
 
 
-def begin_produce(slot) -> None:
-    """Before a non-GEMM kernel overwrites this rank's copy of `slot`: wait until every peer has read the last one."""
-    if getattr(slot, "is_peer", False):
-        d = sync_descriptor(produce=slot)
-        _ext.require().peer_sync(d, 0, slot.device.index)
-
-
-def end_produce(slot) -> None:
-    if getattr(slot, "is_peer", False):
-        d = sync_descriptor(produce=slot)
-        _ext.require().peer_sync(d, 1, slot.device.index)
-
-
 class GatherSlot:
     """Same interface on top of an all-gather, for CPU runs (gloo) and for ranks that cannot map each other's
-    memory: `sources()` returns every rank's copy as ordinary tensors."""
+    memory: the producer keeps its segment locally and `sources()` gathers every rank's segment."""
 
     is_peer = False
 
-    def __init__(self, nbytes: int, group=None, device: Optional[torch.device] = None):
+    def __init__(self, seg_bytes: int, group=None, device: Optional[torch.device] = None):
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.device = device or torch.device("cpu")
-        self.capacity = int(nbytes)
-        self.store = torch.zeros(self.capacity, dtype=torch.uint8, device=self.device)
+        self.seg_capacity = int(seg_bytes)
+        self.store = torch.zeros(self.seg_capacity, dtype=torch.uint8, device=self.device)
         self._last = None
 
+    def set_layout(self, seg_bytes: int) -> None:
+        assert seg_bytes <= self.seg_capacity
+
     def tensor(self, dtype, shape) -> torch.Tensor:
-        n = 1
-        for s in shape:
-            n *= int(s)
         esz = torch.empty((), dtype=dtype).element_size()
-        self._last = self.store[: n * esz].view(dtype).view(*shape)
+        self._last = self.store[: _numel(shape) * esz].view(dtype).view(*shape)
         return self._last
+
+    def dests(self, include_self: bool = False):
+        return None
+
+    def publish(self, src, rows, row_elems, src_stride, dst_stride) -> None:
+        flat_src = src.reshape(-1) if src.is_contiguous() else src.as_strided((src.untyped_storage().nbytes() // src.element_size() - src.storage_offset(),), (1,))
+        s = flat_src.as_strided((rows, row_elems), (src_stride, 1))
+        self._last.view(-1).as_strided((rows, row_elems), (dst_stride, 1)).copy_(s)
 
     def sources(self):
         t = self._last.contiguous()
@@ -211,22 +232,22 @@ class GatherSlot:
 _SLOTS = {}
 
 
-def get_slot(name: str, group_name: str, nbytes: int, device: torch.device):
-    """Process-wide slot `name` over communicator group `group_name`, grown (collectively) to at least `nbytes`.
-    Every rank of the group must request the same sizes in the same order."""
+def get_slot(name: str, group_name: str, seg_bytes: int, device: torch.device):
+    """Process-wide slot `name` over communicator group `group_name` with room for `seg_bytes` per rank, grown
+    collectively when a larger request comes.  Every rank of the group must request the same sizes in the same
+    order (sizes are therefore computed from group-wide maximum extents)."""
     from ..utils import comm
 
     key = (name, group_name, str(device))
     slot = _SLOTS.get(key)
-    if slot is not None and slot.capacity >= nbytes:
-        return slot
-    if slot is not None:
-        slot.close()
-    group = comm.get_group(group_name)
-    use_peer = device.type == "cuda" and dist.get_backend(group) == "nccl"
-    cls = PeerSlot if use_peer else GatherSlot
-    slot = cls(int(nbytes * 1.0), group=group, device=device)
-    _SLOTS[key] = slot
+    if slot is None or slot.seg_capacity < seg_bytes:
+        if slot is not None:
+            slot.close()
+        group = comm.get_group(group_name)
+        use_peer = device.type == "cuda" and dist.get_backend(group) == "nccl"
+        slot = (PeerSlot if use_peer else GatherSlot)(int(seg_bytes), group=group, device=device)
+        _SLOTS[key] = slot
+    slot.set_layout(seg_bytes)
     return slot
 
 

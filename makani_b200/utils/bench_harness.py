@@ -33,6 +33,8 @@ class FlagshipConfig:
     batch_per_gpu: int = 1
     loss: str = "absolute squared geometric l2"
     lr: float = 1e-3
+    h: int = 1              # latitude-parallel ranks
+    w: int = 1              # longitude-parallel ranks
 
     def __post_init__(self):
         if self.small:
@@ -43,6 +45,12 @@ class FlagshipConfig:
 class FlagshipRunner:
     def __init__(self, cfg: FlagshipConfig, device: torch.device):
         self.cfg, self.device = cfg, device
+        from ..parallel.helpers import compute_split_shapes
+        lat_shapes = compute_split_shapes(cfg.nlat, comm.get_size("h"))
+        lon_shapes = compute_split_shapes(cfg.nlon, comm.get_size("w"))
+        rh, rw = comm.get_rank("h"), comm.get_rank("w")
+        self.lat0, self.lon0 = sum(lat_shapes[:rh]), sum(lon_shapes[:rw])
+        self.hl, self.wl = lat_shapes[rh], lon_shapes[rw]
         torch.manual_seed(0)
         self.model = SphericalFourierNeuralOperatorNet(
             spectral_transform="sht", model_grid_type="equiangular", sht_grid_type="legendre-gauss", filter_type="linear",
@@ -55,21 +63,23 @@ class FlagshipRunner:
         p = ParamsBase()
         p.update_params(dict(loss=cfg.loss, n_future=0, img_shape_x=cfg.nlat, img_shape_y=cfg.nlon,
                              img_crop_shape_x=cfg.nlat, img_crop_shape_y=cfg.nlon, img_crop_offset_x=0, img_crop_offset_y=0,
-                             N_out_channels=cfg.out_chans, channel_weights="auto", model_grid_type="equiangular"))
+                             N_out_channels=cfg.out_chans, channel_weights="auto", model_grid_type="equiangular",
+                             img_local_shape_x=self.hl, img_local_shape_y=self.wl, img_local_offset_x=self.lat0,
+                             img_local_offset_y=self.lon0))
         self.loss_fn = LossHandler(p).to(device)
         self.reducer = GradReducer(self.model)
         self.optimizer = FusedAdamW(self.model.parameters(), lr=cfg.lr, weight_decay=0.0)
         self.train_step = TrainStep(self.model, self.loss_fn, self.optimizer, self.reducer)
-        lat = torch.linspace(math.pi / 2, -math.pi / 2, cfg.nlat, device=device)
-        self.coslat = torch.cos(lat).view(1, 1, -1, 1).expand(cfg.batch_per_gpu, 1, cfg.nlat, cfg.nlon)
+        lat = torch.linspace(math.pi / 2, -math.pi / 2, cfg.nlat, device=device)[self.lat0: self.lat0 + self.hl]
+        self.coslat = torch.cos(lat).view(1, 1, -1, 1).expand(cfg.batch_per_gpu, 1, self.hl, self.wl)
 
     def synthetic_batch(self, seed: int):
         cfg = self.cfg
         g = torch.Generator(device=self.device)
         g.manual_seed(seed)
-        x = torch.randn(cfg.batch_per_gpu, cfg.out_chans, cfg.nlat, cfg.nlon, device=self.device, generator=g)
+        x = torch.randn(cfg.batch_per_gpu, cfg.out_chans, self.hl, self.wl, device=self.device, generator=g)
         inp = torch.cat([x, self.coslat], dim=1).to(torch.bfloat16).contiguous()
-        tgt = torch.randn(cfg.batch_per_gpu, cfg.out_chans, cfg.nlat, cfg.nlon, device=self.device, generator=g).to(torch.bfloat16)
+        tgt = torch.randn(cfg.batch_per_gpu, cfg.out_chans, self.hl, self.wl, device=self.device, generator=g).to(torch.bfloat16)
         return inp, tgt
 
     def step(self, inp, tgt):
@@ -84,8 +94,8 @@ class FlagshipRunner:
         host = []
         for i in range(nb):
             gi = torch.Generator().manual_seed(100 + i + 17 * local_rank)
-            hi = torch.randn(cfg.batch_per_gpu, cfg.in_chans, cfg.nlat, cfg.nlon, generator=gi).to(torch.bfloat16).pin_memory()
-            ht = torch.randn(cfg.batch_per_gpu, cfg.out_chans, cfg.nlat, cfg.nlon, generator=gi).to(torch.bfloat16).pin_memory()
+            hi = torch.randn(cfg.batch_per_gpu, cfg.in_chans, self.hl, self.wl, generator=gi).to(torch.bfloat16).pin_memory()
+            ht = torch.randn(cfg.batch_per_gpu, cfg.out_chans, self.hl, self.wl, generator=gi).to(torch.bfloat16).pin_memory()
             host.append((hi, ht))
         dbuf = [(torch.empty_like(h[0], device=dev), torch.empty_like(h[1], device=dev)) for h in host]
         copy_stream = torch.cuda.Stream(device=dev)
@@ -132,7 +142,8 @@ class FlagshipRunner:
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = t.item() / steps
-        return {"value": cfg.batch_per_gpu * world / (ms / 1e3), "unit": "samples/s", "ms_per_step": ms,
+        dp = max(1, world // (comm.get_size("h") * comm.get_size("w")))
+        return {"value": cfg.batch_per_gpu * dp / (ms / 1e3), "unit": "samples/s", "ms_per_step": ms,
                 "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4}
 
 
