@@ -32,9 +32,12 @@ def parse():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", type=str, default="native", choices=["native", "reference"])
+    ap.add_argument("--impl", type=str, default="native", choices=["native", "reference", "restated"],
+                    help="native: this framework; reference: the unmodified upstream package from baseline/_ref; restated: the "
+                         "reference's op sequence on stock PyTorch kernels and NCCL, through this package's model code")
     ap.add_argument("--small", action="store_true", help="reduced grid for profiling captures (not a bench value)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying a CUDA graph")
     ap.add_argument("--h", type=int, default=1, help="latitude-parallel ranks per model instance (default: pure data parallel)")
     ap.add_argument("--w", type=int, default=1, help="longitude-parallel ranks per model instance")
     return ap.parse_args()
@@ -132,9 +135,15 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     comm.init(model_parallel_sizes=[args.h, args.w, 1, 1])
-    _ext.require()
+    native = args.impl == "native"
+    if native:
+        _ext.require()
+    else:
+        _ext.set_native(False)
+        torch.backends.cuda.matmul.allow_tf32 = True      # as makani/train.py:109-110
+        torch.backends.cudnn.allow_tf32 = True
 
-    cfg = FlagshipConfig(small=args.small, h=args.h, w=args.w)
+    cfg = FlagshipConfig(small=args.small, h=args.h, w=args.w, graph=(not args.no_graph) and native, native=native)
     runner = build_flagship(cfg, dev)
 
     def barrier():
@@ -169,7 +178,8 @@ def main():
     dp = world // (args.h * args.w)
     global_batch = cfg.batch_per_gpu * dp
     value = global_batch / (ms_per_step / 1e3)
-    _ext.check_device_errors(dev)
+    if native:
+        _ext.check_device_errors(dev)
     final_loss = float(loss)
 
     # ---------------------------------------------------------------- end to end through the public API
@@ -181,11 +191,12 @@ def main():
         out = {
             "metric": "SFNO-73ch 721x1440 bf16 train samples/s", "value": value, "unit": "samples/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": (value / BASELINE_VALUE) if BASELINE_VALUE else None, "dtype": "bf16",
-            "data": "synthetic N(0,1), random-init weights", "impl": "native",
+            "scaling": "weak", "vs_baseline": (value / BASELINE_VALUE) if BASELINE_VALUE else None, "dtype": "bf16" if native else "bf16 autocast (fp32 transforms, as the reference)",
+            "data": "synthetic N(0,1), random-init weights", "impl": "native" if native else "restated-torch",
             "config": {"model": cfg.name, "global_batch": global_batch, "seq_len": f"{cfg.nlat}x{cfg.nlon}",
                        "parallelism": f"dp{dp}" + (f"xh{args.h}w{args.w}" if args.h * args.w > 1 else ""), "l2_policy": "inputs+activations per step (>2 GB) exceed the 126 MB L2",
-                       "loss": cfg.loss, "optimizer": "AdamW (fused)", "final_loss": final_loss},
+                       "loss": cfg.loss, "optimizer": "AdamW (fused)" if native else "torch.optim.AdamW(foreach)",
+                       "cuda_graph": bool(cfg.graph), "final_loss": final_loss},
             "clocks": clocks, "gpu_launches": launches,
         }
         if e2e is not None:

@@ -1060,7 +1060,15 @@ cudaError_t gemm_launch(const GemmProblem& p, const GemmOperand& A, const GemmOp
   if (p.M <= 0 || p.N <= 0 || p.zlo_n <= 0 || p.zhi_n <= 0) return cudaSuccess;
   // cuTensorMapEncodeTiled is a driver call: make sure this host thread has the primary context bound (threads
   // that only inherited the device index, e.g. autograd workers, do not until their first runtime call)
-  cudaFree(nullptr);
+  // (once per host thread: the call is not allowed while a stream is capturing, and threads are reused)
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cs) == cudaSuccess && cs == cudaStreamCaptureStatusNone) {
+      cudaFree(nullptr);
+      ctx_bound = true;
+    }
+  }
   const int eb = p.elem_bytes;
   if (eb != 2 && eb != 4) {
     snprintf(g_err, sizeof(g_err), "elem_bytes must be 2 or 4");

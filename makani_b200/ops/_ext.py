@@ -36,6 +36,20 @@ def _load():
             _ERR = e
 
 
+# MAKANI_B200_NATIVE=0 (or `set_native(False)`) routes every op through its plain PyTorch formulation: the
+# op-for-op restatement of the reference's execution (cuDNN/cuBLAS/cuFFT/ATen/NCCL) used as the same-box comparison arm.
+_NATIVE = os.environ.get("MAKANI_B200_NATIVE", "1") != "0"
+
+
+def set_native(flag: bool) -> None:
+    global _NATIVE
+    _NATIVE = bool(flag)
+
+
+def native() -> bool:
+    return _NATIVE
+
+
 def available() -> bool:
     _load()
     return _MOD is not None
@@ -87,6 +101,12 @@ def require():
 
 def launch_count() -> int:
     return LAUNCHES
+
+
+def add_launches(n: int) -> None:
+    """Account for kernels of this extension that a CUDA-graph replay launched (counted once at capture time)."""
+    global LAUNCHES
+    LAUNCHES += int(n)
 
 
 def check_device_errors(device=None) -> None:

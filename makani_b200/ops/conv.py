@@ -39,7 +39,7 @@ def layout_of(x: torch.Tensor) -> Optional[str]:
 
 def fast_path_ok(x: torch.Tensor) -> bool:
     """True when the native GEMM path applies: CUDA/CPU-emulated bf16 4-D tensor in a supported layout with 16-byte strides."""
-    if x.dim() != 4 or x.dtype != torch.bfloat16:
+    if x.dim() != 4 or x.dtype != torch.bfloat16 or not _ext.native():
         return False
     lay = layout_of(x)
     if lay == NCHW:

@@ -13,7 +13,7 @@ from .gemm import ACT_DGELU, ACT_GELU, ACT_NONE, BIAS_COL, Operand, Output, gemm
 
 
 def fast_path_ok(x: torch.Tensor) -> bool:
-    return x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and x.shape[-1] % 8 == 0
+    return _ext.native() and x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and x.shape[-1] % 8 == 0
 
 
 def _wq(w):

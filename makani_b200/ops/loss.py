@@ -50,7 +50,7 @@ class _LpNorms(torch.autograd.Function):
 
 def weighted_lp_norms(pred: torch.Tensor, tgt: torch.Tensor, qlat: torch.Tensor, p: int = 2) -> torch.Tensor:
     """[B, C, 2] fp32: (int q |pred - tgt|^p, int q |tgt|^p) with latitude weights qlat[H] (longitude weight folded in)."""
-    if pred.is_cuda and pred.dtype in (torch.bfloat16, torch.float32):
+    if _ext.native() and pred.is_cuda and pred.dtype in (torch.bfloat16, torch.float32):
         tgt = tgt.to(pred.dtype).contiguous()
         return _LpNorms.apply(pred.contiguous(), tgt, qlat.float().contiguous(), p)
     q = qlat.to(torch.float32).view(1, 1, -1, 1)

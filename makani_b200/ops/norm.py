@@ -93,7 +93,8 @@ class _InstanceNormCL(torch.autograd.Function):
 
 
 def cl_supported(x) -> bool:
-    return x.is_cuda and x.dtype == torch.bfloat16 and _is_cl(x) and x.shape[1] % 8 == 0 and x.shape[1] <= 1024
+    return (_ext.native() and x.is_cuda and x.dtype == torch.bfloat16 and _is_cl(x) and x.shape[1] % 8 == 0
+            and x.shape[1] <= 1024)
 
 
 def instance_norm(x: torch.Tensor, weight, bias, eps: float = 1e-6, act: str = "none", count=None, reduce_fn=None) -> torch.Tensor:
@@ -101,7 +102,7 @@ def instance_norm(x: torch.Tensor, weight, bias, eps: float = 1e-6, act: str = "
     a = 1 if act == "gelu" else 0
     if cl_supported(x):
         return _InstanceNormCL.apply(x, weight, bias, eps, a, count, reduce_fn)
-    if x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 4 and count is None and reduce_fn is None:
+    if _ext.native() and x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 4 and count is None and reduce_fn is None:
         return _InstanceNorm.apply(x.contiguous(), weight, bias, eps, a)
     assert count is None and reduce_fn is None, "distributed statistics need the channels-last CUDA path"
     xf = x.float()

@@ -78,32 +78,58 @@ class FusedAdamW(torch.optim.Optimizer):
         if closure is not None:
             with torch.enable_grad():
                 loss = closure()
-        self._step_count += 1
-        for gi, group in enumerate(self.param_groups):
-            plist = [p for p in group["params"] if p.grad is not None]
-            if not plist:
-                continue
-            if plist[0].is_cuda:
-                self._step_cuda(gi, group, plist)
-            else:
-                self._step_torch(group, plist)
+        self.prepare_step()
+        self.launch_step()
         return loss
 
-    def _step_cuda(self, gi, group, plist):
-        ext = _ext.require()
+    # The update is split in two so that the kernel launches can live inside a CUDA graph: `prepare_step` advances
+    # the step counters and uploads the hyper-parameters (host work, outside the graph); `launch_step` only
+    # launches kernels that read them from device memory.
+    def _groups_with_grads(self):
+        for gi, group in enumerate(self.param_groups):
+            plist = [p for p in group["params"] if p.grad is not None]
+            if plist:
+                yield gi, group, plist
+
+    def prepare_step(self):
+        self._step_count += 1
+        self._prepared = True
+        for gi, group, plist in self._groups_with_grads():
+            if not plist[0].is_cuda:
+                continue          # the CPU path keeps its own step counters
+            tb = self._table_for(gi, group, plist)
+            for p in plist:
+                self.state[p]["step"] += 1
+            step = float(self.state[plist[0]]["step"])
+            b1, b2 = group["betas"]
+            host = tb.get("hyper_host")
+            if host is None:
+                host = tb["hyper_host"] = torch.zeros(8, dtype=torch.float32).pin_memory()
+            # the pinned staging vector is reused: wait for the previous upload before overwriting it
+            ev = tb.get("hyper_ev")
+            if ev is not None:
+                ev.synchronize()
+            host.copy_(torch.tensor([group["lr"], b1, b2, group["eps"], group["weight_decay"], step, self.grad_scale,
+                                     1.0 if self.adamw else 0.0], dtype=torch.float32))
+            tb["hyper"].copy_(host, non_blocking=True)
+            ev = tb["hyper_ev"] = torch.cuda.Event()
+            ev.record()
+
+    def launch_step(self):
+        for gi, group, plist in self._groups_with_grads():
+            if plist[0].is_cuda:
+                tb = self._table_for(gi, group, plist)
+                _ext.require().adamw_step(tb["table"], tb["ct"], tb["co"], _CHUNK, tb["hyper"])
+            else:
+                self._step_torch(group, plist)
+
+    def _table_for(self, gi, group, plist):
         sig = tuple((p.data_ptr(), p.grad.data_ptr()) for p in plist)
         tb = self._tables.get(gi)
         if tb is None or tb["sig"] != sig:
             tb = self._build_table(gi, group, plist)
             self._tables[gi] = tb
-        for p in plist:
-            self.state[p]["step"] += 1
-        step = float(self.state[plist[0]]["step"])
-        b1, b2 = group["betas"]
-        h = torch.tensor([group["lr"], b1, b2, group["eps"], group["weight_decay"], step, self.grad_scale,
-                          1.0 if self.adamw else 0.0], dtype=torch.float32).pin_memory()
-        tb["hyper"].copy_(h, non_blocking=True)
-        ext.adamw_step(tb["table"], tb["ct"], tb["co"], _CHUNK, tb["hyper"])
+        return tb
 
     def _step_torch(self, group, plist):
         b1, b2 = group["betas"]

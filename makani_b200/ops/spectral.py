@@ -269,7 +269,7 @@ class _SpectralConv(torch.autograd.Function):
 
 
 def spectral_conv_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
-    return (x.dim() == 4 and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and w.dim() == 3 and w.shape[1] % 8 == 0
+    return (_ext.native() and x.dim() == 4 and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and w.dim() == 3 and w.shape[1] % 8 == 0
             and x.shape[3] % 8 == 0)
 
 

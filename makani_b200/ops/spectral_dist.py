@@ -36,6 +36,7 @@ from ..parallel import peer
 from ..parallel.helpers import compute_split_shapes
 from ..sht.legendre import legendre_table
 from ..sht.quadrature import precompute_latitudes
+from . import _ext
 from .gemm import Operand, Output, Segment, Tri, gemm, pad_to
 from .spectral import _to_cl, expand_weight, fold_weight_grad
 
@@ -395,7 +396,7 @@ def _contract_wgrad_local(dt: torch.Tensor, t2: torch.Tensor, plan: DistSHTPlan)
 
 
 def dist_spectral_conv_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
-    return x.dim() == 4 and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and w.dim() == 3 and w.shape[1] % 8 == 0
+    return _ext.native() and x.dim() == 4 and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and w.dim() == 3 and w.shape[1] % 8 == 0
 
 
 def dist_spectral_conv_dhconv(x, w, plan_in: DistSHTPlan, plan_out: DistSHTPlan, want_resid: bool):

@@ -86,11 +86,17 @@ class GradReducer:
                 p.register_post_accumulate_grad_hook(self._make_hook(idx))
             self._reset_pending()
         # parameters whose gradient must additionally be summed over model-parallel groups
-        self.shared: Dict[str, List[torch.nn.Parameter]] = {}
-        for p in self.params:
+        # (kept as merged [start, end) ranges of the flat buffer, reduced in place: no staging copies)
+        self.shared: Dict[str, List[List[int]]] = {}
+        for p, (off, n) in zip(self.params, sizes):
             for g in getattr(p, "is_shared_mp", ["model"]):
                 if comm.get_size(g) > 1:
-                    self.shared.setdefault(g, []).append(p)
+                    ranges = self.shared.setdefault(g, [])
+                    end = off + (n + align - 1) // align * align
+                    if ranges and ranges[-1][1] == off:
+                        ranges[-1][1] = end
+                    else:
+                        ranges.append([off, end])
 
     def _reset_pending(self):
         self._pending = list(self._counts)
@@ -133,15 +139,10 @@ class GradReducer:
             else:
                 dist.all_reduce(self.flat, group=comm.get_group("data"))
                 self.flat.mul_(1.0 / self.data_size)
-        for gname, plist in self.shared.items():
+        for gname, ranges in self.shared.items():
             grp = comm.get_group(gname)
-            bufs = [torch.view_as_real(p.grad) if p.is_complex() else p.grad for p in plist]
-            flat = torch.cat([b.reshape(-1) for b in bufs])
-            dist.all_reduce(flat, group=grp)
-            off = 0
-            for b in bufs:
-                b.copy_(flat[off: off + b.numel()].view_as(b))
-                off += b.numel()
+            for start, end in ranges:
+                dist.all_reduce(self.flat[start:end], group=grp)
 
     def close(self):
         if self.sym is not None:

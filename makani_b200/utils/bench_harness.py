@@ -15,7 +15,7 @@ from ..parallel.grad_reduce import GradReducer
 from ..parallel.helpers import sync_params
 from ..utils import comm
 from .losses import LossHandler
-from .train_step import TrainStep
+from .train_step import GraphedTrainStep, TrainStep
 from .YParams import ParamsBase
 
 
@@ -35,6 +35,8 @@ class FlagshipConfig:
     lr: float = 1e-3
     h: int = 1              # latitude-parallel ranks
     w: int = 1              # longitude-parallel ranks
+    graph: bool = True      # replay the whole step from one CUDA graph after an eager warm-up
+    native: bool = True     # False: the reference's op sequence on stock PyTorch (cuDNN / cuFFT / cuBLAS / ATen / NCCL)
 
     def __post_init__(self):
         if self.small:
@@ -58,7 +60,8 @@ class FlagshipRunner:
             scale_factor=cfg.scale_factor, inp_chans=cfg.in_chans, out_chans=cfg.out_chans, embed_dim=cfg.embed_dim,
             num_layers=cfg.num_layers, use_mlp=True, mlp_ratio=2.0, activation_function="gelu", encoder_layers=1,
             pos_embed="none", normalization_layer="instance_norm", hard_thresholding_fraction=1.0, big_skip=True).to(device)
-        self.model.set_compute_dtype(torch.bfloat16)
+        if cfg.native:
+            self.model.set_compute_dtype(torch.bfloat16)
         sync_params(self.model)
         p = ParamsBase()
         p.update_params(dict(loss=cfg.loss, n_future=0, img_shape_x=cfg.nlat, img_shape_y=cfg.nlon,
@@ -67,9 +70,18 @@ class FlagshipRunner:
                              img_local_shape_x=self.hl, img_local_shape_y=self.wl, img_local_offset_x=self.lat0,
                              img_local_offset_y=self.lon0))
         self.loss_fn = LossHandler(p).to(device)
-        self.reducer = GradReducer(self.model)
-        self.optimizer = FusedAdamW(self.model.parameters(), lr=cfg.lr, weight_decay=0.0)
-        self.train_step = TrainStep(self.model, self.loss_fn, self.optimizer, self.reducer)
+        if cfg.native:
+            self.reducer = GradReducer(self.model)
+            self.optimizer = FusedAdamW(self.model.parameters(), lr=cfg.lr, weight_decay=0.0)
+            step_cls = GraphedTrainStep if cfg.graph else TrainStep
+            self.train_step = step_cls(self.model, self.loss_fn, self.optimizer, self.reducer)
+        else:
+            # what the reference runs: fp32 parameters and transforms, bf16 autocast for the convolutions, foreach
+            # AdamW, NCCL all-reduce of the gradients (makani/utils/trainer.py:429-433,683-754)
+            self.reducer = GradReducer(self.model, use_peer=False, overlap=False)
+            self.optimizer = torch.optim.AdamW(self.model.parameters(), lr=cfg.lr, weight_decay=0.0, foreach=True)
+            self.train_step = TrainStep(self.model, self.loss_fn, self.optimizer, self.reducer, amp_dtype=torch.bfloat16)
+        self.io_dtype = torch.bfloat16 if cfg.native else torch.float32
         lat = torch.linspace(math.pi / 2, -math.pi / 2, cfg.nlat, device=device)[self.lat0: self.lat0 + self.hl]
         self.coslat = torch.cos(lat).view(1, 1, -1, 1).expand(cfg.batch_per_gpu, 1, self.hl, self.wl)
 
@@ -78,8 +90,8 @@ class FlagshipRunner:
         g = torch.Generator(device=self.device)
         g.manual_seed(seed)
         x = torch.randn(cfg.batch_per_gpu, cfg.out_chans, self.hl, self.wl, device=self.device, generator=g)
-        inp = torch.cat([x, self.coslat], dim=1).to(torch.bfloat16).contiguous()
-        tgt = torch.randn(cfg.batch_per_gpu, cfg.out_chans, self.hl, self.wl, device=self.device, generator=g).to(torch.bfloat16)
+        inp = torch.cat([x, self.coslat], dim=1).to(self.io_dtype).contiguous()
+        tgt = torch.randn(cfg.batch_per_gpu, cfg.out_chans, self.hl, self.wl, device=self.device, generator=g).to(self.io_dtype)
         return inp, tgt
 
     def step(self, inp, tgt):
@@ -94,14 +106,14 @@ class FlagshipRunner:
         host = []
         for i in range(nb):
             gi = torch.Generator().manual_seed(100 + i + 17 * local_rank)
-            hi = torch.randn(cfg.batch_per_gpu, cfg.in_chans, self.hl, self.wl, generator=gi).to(torch.bfloat16).pin_memory()
-            ht = torch.randn(cfg.batch_per_gpu, cfg.out_chans, self.hl, self.wl, generator=gi).to(torch.bfloat16).pin_memory()
+            hi = torch.randn(cfg.batch_per_gpu, cfg.in_chans, self.hl, self.wl, generator=gi).to(self.io_dtype).pin_memory()
+            ht = torch.randn(cfg.batch_per_gpu, cfg.out_chans, self.hl, self.wl, generator=gi).to(self.io_dtype).pin_memory()
             host.append((hi, ht))
         dbuf = [(torch.empty_like(h[0], device=dev), torch.empty_like(h[1], device=dev)) for h in host]
         copy_stream = torch.cuda.Stream(device=dev)
         ready = [torch.cuda.Event() for _ in range(nb)]
         consumed = [torch.cuda.Event() for _ in range(nb)]
-        h2d = host[0][0].numel() * 2 + host[0][1].numel() * 2
+        h2d = host[0][0].numel() * host[0][0].element_size() + host[0][1].numel() * host[0][1].element_size()
         loss_host = torch.zeros(1, dtype=torch.float32).pin_memory()
 
         def issue(i):
