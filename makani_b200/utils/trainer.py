@@ -290,7 +290,11 @@ class Trainer:
             with torch.cuda.graph(self.graph, stream=side):
                 self.static_loss = self._forward_backward(self.static_inp, self.static_tar)
                 if self.graph_mode == "step":
-                    self.optimizer.step()
+                    # only the kernels go into the graph; step counters and hyper-parameters are uploaded per replay
+                    if hasattr(self.optimizer, "launch_step"):
+                        self.optimizer.launch_step()
+                    else:
+                        self.optimizer.step()
         torch.cuda.current_stream(self.device).wait_stream(side)
 
     def _train_step(self, inp, tar):
@@ -299,6 +303,8 @@ class Trainer:
                 self._capture(inp, tar)
             self.static_inp.copy_(inp)
             self.static_tar.copy_(tar)
+            if self.graph_mode == "step" and hasattr(self.optimizer, "prepare_step"):
+                self.optimizer.prepare_step()
             self.graph.replay()
             loss = self.static_loss
             if self.graph_mode != "step":
@@ -369,8 +375,18 @@ class Trainer:
         loss = torch.zeros((), device=self.device)
         accumulated = torch.zeros((2,), dtype=torch.float32, device=self.device)
         tstep = time.perf_counter_ns()
+        wd = self._watchdog()
         for data in self.train_dataloader:
             self.iters += 1
+            if wd is not None:
+                # host-side liveness check before this step's collectives: a lost peer ends the epoch with an exception
+                # (after an emergency checkpoint from the surviving ranks) instead of a hang inside NCCL
+                wd.begin_step(self.iters)
+                try:
+                    wd.check()
+                except Exception:
+                    self._emergency_checkpoint()
+                    raise
             inp, tar = self._prepare_batch(data)
             data_gb += (inp.numel() + tar.numel()) * 4 / 1e9
             loss = self._train_step(inp, tar)
@@ -395,6 +411,27 @@ class Trainer:
         train_time = time.perf_counter() - t0
         logs = {"loss": float(loss), "loss accumulated": float(acc[0] / max(acc[1], 1.0)), "train_steps": steps}
         return train_time, data_gb, logs
+
+    def _watchdog(self):
+        """Heartbeat watchdog (params: enable_watchdog, watchdog_timeout_s, step_deadline_s); None when disabled."""
+        if not self.params.get("enable_watchdog", False):
+            return None
+        if getattr(self, "_wd", None) is None:
+            from .watchdog import from_process_group
+            self._wd = from_process_group(interval=1.0, timeout=float(self.params.get("watchdog_timeout_s", 120.0)),
+                                          step_deadline=self.params.get("step_deadline_s", None))
+        return self._wd
+
+    def _emergency_checkpoint(self):
+        """Local, collective-free save of this rank's state (legacy per-rank format) when a peer is lost."""
+        try:
+            path = os.path.join(self.params.experiment_dir, f"emergency_rank{comm.get_world_rank()}.tar")
+            torch.save({"model_state": {k: v.detach().cpu() for k, v in self.model.state_dict().items()},
+                        "iters": self.iters, "epoch": self.epoch}, path)
+            if self.log_to_screen:
+                self.logger.info(f"peer lost: emergency checkpoint written to {path}")
+        except Exception as e:  # the job is going down anyway; do not mask the original failure
+            self.logger.info(f"emergency checkpoint failed: {e}")
 
     @torch.no_grad()
     def validate_one_epoch(self, epoch):

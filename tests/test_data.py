@@ -1,0 +1,96 @@
+"""Data path: loaders, metrics against direct numpy restatements, data tools (CPU)."""
+
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from makani_b200.utils.YParams import ParamsBase
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _stats(tmp_path, C):
+    np.save(tmp_path / "m.npy", np.arange(C, dtype=np.float32).reshape(1, C, 1, 1))
+    np.save(tmp_path / "s.npy", (1.0 + np.arange(C, dtype=np.float32)).reshape(1, C, 1, 1))
+    return str(tmp_path / "m.npy"), str(tmp_path / "s.npy")
+
+
+def test_zarr_style_loader_pairs_and_normalisation(tmp_path):
+    from makani_b200.utils.dataloaders.zarr_helper import get_data_loader
+    C = 5
+    m, s = _stats(tmp_path, C)
+    p = ParamsBase()
+    p.update_params(dict(global_means_path=m, global_stds_path=s, in_channels=[0, 1, 2], out_channels=[1, 2], dt=2, batch_size=2))
+    f = np.random.RandomState(0).rand(9, C, 6, 8).astype(np.float32)
+    loader, meta, sampler = get_data_loader(p, None, True, store=f)
+    assert sampler is None and len(loader.dataset) == 7 and (meta.img_shape_x, meta.img_shape_y) == (6, 8)
+    x, y = next(iter(loader))
+    mean, std = np.load(m)[0], np.load(s)[0]
+    np.testing.assert_allclose(x[1].numpy(), (f[1][[0, 1, 2]] - mean[[0, 1, 2]]) / std[[0, 1, 2]], rtol=1e-6)
+    np.testing.assert_allclose(y[1].numpy(), (f[3][[1, 2]] - mean[[1, 2]]) / std[[1, 2]], rtol=1e-6)
+    im, istd = loader.get_input_normalization()
+    assert im.shape == (1, 3, 1, 1) and istd.shape == (1, 3, 1, 1)
+
+
+def test_synthetic_loader_is_seeded_and_shaped():
+    from makani_b200.utils.dataloader import get_dataloader
+    p = ParamsBase()
+    p.update_params(dict(enable_synthetic_data=True, batch_size=2, in_channels=[0, 1, 2], out_channels=[0, 1], n_history=0,
+                         n_future=0, img_shape_x=16, img_shape_y=32, n_train_samples_per_epoch=6, dt=1, dhours=6,
+                         data_num_shards=1, data_shard_id=0, seed=3))
+    batches = []
+    for _ in range(2):
+        loader, dataset, _ = get_dataloader(p, None, torch.device("cpu"), train=True)
+        batches.append([tuple(t.clone() for t in b) for b in loader])
+    assert len(batches[0]) == 3
+    for a, b in zip(*batches):
+        assert a[0].shape[0] == 2 and a[0].shape[-2:] == (16, 32)
+        assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+
+
+def test_weighted_metrics_match_numpy():
+    from makani_b200.utils.grids import GridQuadrature
+    from makani_b200.utils.metrics import functions as F
+    torch.manual_seed(0)
+    H, W = 19, 36
+    quad = GridQuadrature("naive", (H, W), normalize=True)
+    q = quad.quad_weight.reshape(H, W).double().numpy()
+    assert abs(q.sum() - 1.0) < 1e-5
+    x, y = torch.randn(3, 4, H, W), torch.randn(3, 4, H, W)
+    rmse_ref = np.sqrt(((x - y).double().numpy() ** 2 * q).sum(axis=(-2, -1)))
+    rmse = F.GeometricRMSE("naive", (H, W), normalize=True, channel_reduction="none", batch_reduction="none")(x, y)
+    np.testing.assert_allclose(rmse.double().numpy(), rmse_ref, rtol=1e-4)
+    l1_ref = (np.abs((x - y).double().numpy()) * q).sum(axis=(-2, -1))
+    l1 = F.GeometricL1("naive", (H, W), normalize=True, channel_reduction="none", batch_reduction="none")(x, y)
+    np.testing.assert_allclose(l1.double().numpy(), l1_ref, rtol=1e-4)
+    # anomaly correlation of fields that are already anomalies: no re-centring (makani/utils/metrics/functions.py:87-92)
+    xa, ya = x.double().numpy(), y.double().numpy()
+    acc_ref = (xa * ya * q).sum(axis=(-2, -1)) / np.sqrt((xa ** 2 * q).sum(axis=(-2, -1)) * (ya ** 2 * q).sum(axis=(-2, -1)))
+    acc = F.GeometricACC("naive", (H, W), normalize=True, channel_reduction="none", batch_reduction="none")(x, y)
+    np.testing.assert_allclose(acc.double().numpy(), acc_ref, rtol=1e-4, atol=1e-6)
+
+
+def test_parallel_copy_tool(tmp_path):
+    src, dst = tmp_path / "in", tmp_path / "out"
+    src.mkdir()
+    for y in (2017, 2018, 2019):
+        (src / f"{y}.h5").write_bytes(os.urandom(1000 + y))
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "data_process", "parallel_copy.py"), "--input_dir", str(src),
+                        "--output_dir", str(dst), "--workers", "2"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    for y in (2017, 2018, 2019):
+        assert (dst / f"{y}.h5").read_bytes() == (src / f"{y}.h5").read_bytes()
+
+
+def test_h5_convert_chunk_parser():
+    sys.path.insert(0, os.path.join(ROOT, "data_process"))
+    import h5_convert
+    assert h5_convert.parse_chunks("auto", (10, 4, 8, 8), 4) is True
+    assert h5_convert.parse_chunks("none", (10, 4, 8, 8), 4) is None
+    assert h5_convert.parse_chunks("1MB", (2000, 4, 8, 8), 4) == (1024, 4, 8, 8)
+    with pytest.raises(ValueError):
+        h5_convert.parse_chunks("7", (1, 1, 1, 1), 4)
