@@ -202,7 +202,24 @@ def main():
         if e2e is not None:
             out["e2e"] = e2e
         print(json.dumps(out))
+    # Teardown.  CUDA graphs that hold NCCL kernels must be gone before the communicators are destroyed; a helper
+    # thread ends the process if the teardown of the communication libraries stalls, so that a finished measurement
+    # can never turn into a hung job.
+    sys.stdout.flush()
     if world > 1:
+        import gc
+        import threading
+
+        def _bail():
+            time.sleep(30.0)
+            os._exit(0)
+
+        threading.Thread(target=_bail, daemon=True).start()
+        torch.cuda.synchronize()
+        if getattr(runner.train_step, "graph", None) is not None:
+            runner.train_step.graph = None
+        gc.collect()
+        torch.cuda.synchronize()
         from makani_b200.parallel import peer
         peer.release_slots()
         dist.barrier(device_ids=[local_rank])

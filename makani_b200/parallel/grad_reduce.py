@@ -121,8 +121,10 @@ class GradReducer:
 
     def zero_grad(self):
         if self.overlap:
-            # the previous step's side-stream work must be finished before the buffer is cleared
-            torch.cuda.current_stream(self.device).wait_stream(self._side)
+            # the previous step's side-stream work must be finished before the buffer is cleared (`reduce` has joined
+            # it already; under stream capture a wait on the not yet captured side stream is not allowed)
+            if not torch.cuda.is_current_stream_capturing():
+                torch.cuda.current_stream(self.device).wait_stream(self._side)
             self._reset_pending()
         self.flat.zero_()
 
