@@ -248,32 +248,66 @@ void inorm_bwd(const Tensor& x, const Tensor& dy, c10::optional<Tensor> dx, cons
 }
 
 // channels-last instance norm: x is [B, T, C] contiguous (a channels_last NCHW tensor viewed as tokens x channels)
+// Builds the statistic-exchange descriptor from the first wait / signal list of a 31-entry handshake descriptor.
+static bool make_exchange(mk::StatExchange& xc, const std::vector<int64_t>& sync, const std::vector<int64_t>& addrs, bool producer,
+                          const Tensor& like) {
+  memset(&xc, 0, sizeof(xc));
+  if (sync.empty()) return false;
+  mk::GemmPeer g;
+  parse_peer(g, {}, sync);
+  MK_CHECK(g.nwait == 1 && g.nsig == 1, "instance norm exchange: one wait list and one signal list expected");
+  xc.npeers = g.np_wait[0];
+  xc.wait = g.wait[0];
+  xc.wait_exp = g.wait_exp[0];
+  xc.wait_off = g.wait_off[0];
+  xc.bump = g.bump[0];
+  for (int q = 0; q < 8; ++q) xc.sig[q] = g.sig[0][q];
+  xc.done_ctr = g.done_ctr;
+  xc.err = err_flag_for(like).data_ptr<int>();
+  MK_CHECK(!addrs.empty() && addrs.size() <= 8, "instance norm exchange: 1..8 segment addresses");
+  if (producer) {
+    xc.ndst = static_cast<int>(addrs.size());
+    for (size_t q = 0; q < addrs.size(); ++q) xc.dst[q] = reinterpret_cast<float*>(addrs[q]);
+  } else {
+    xc.nsrc = static_cast<int>(addrs.size());
+    xc.src = reinterpret_cast<const float*>(addrs[0]);
+    xc.src_stride = addrs.size() > 1 ? (addrs[1] - addrs[0]) / 4 : 0;
+    for (size_t q = 1; q < addrs.size(); ++q)
+      MK_CHECK(addrs[q] - addrs[q - 1] == addrs[1] - addrs[0], "instance norm exchange: segments must be equally spaced");
+  }
+  return true;
+}
+
 void inorm_cl_sums(const Tensor& x, const c10::optional<Tensor>& dy, const c10::optional<Tensor>& w, const c10::optional<Tensor>& b,
                    const c10::optional<Tensor>& stats, Tensor& sums, c10::optional<Tensor> dw, c10::optional<Tensor> db, int64_t B,
-                   int64_t C, int64_t act, int64_t mode) {
+                   int64_t C, int64_t act, int64_t mode, const std::vector<int64_t>& sync, const std::vector<int64_t>& dsts) {
   MK_CHECK(x.is_cuda() && x.scalar_type() == torch::kBFloat16, "inorm_cl_sums: bf16 CUDA expected");
   MK_CHECK(sums.scalar_type() == torch::kFloat32 && sums.is_contiguous() && sums.numel() == B * C * 2, "inorm_cl_sums: bad sums");
   c10::cuda::CUDAGuard guard(x.device());
   const int64_t T = x.numel() / (B * C);
   auto fp = [](const c10::optional<Tensor>& t) -> float* { return (t.has_value() && t->defined()) ? t->data_ptr<float>() : nullptr; };
   const __nv_bfloat16* dyp = (dy.has_value() && dy->defined()) ? reinterpret_cast<const __nv_bfloat16*>(dy->data_ptr()) : nullptr;
+  mk::StatExchange xc;
+  const bool ex = make_exchange(xc, sync, dsts, true, x);
   check_cuda(mk::inorm_cl_sums(reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), dyp, fp(w), fp(b), fp(stats), sums.data_ptr<float>(),
                                fp(dw), fp(db), static_cast<int>(B), static_cast<int>(C), T, static_cast<int>(act), static_cast<int>(mode),
-                               cur_stream()),
+                               cur_stream(), ex ? &xc : nullptr),
              "inorm_cl_sums");
 }
 
 void inorm_cl_apply(const Tensor& x, const c10::optional<Tensor>& dy, Tensor& out, const c10::optional<Tensor>& w,
                     const c10::optional<Tensor>& b, const Tensor& sums, c10::optional<Tensor> stats, int64_t B, int64_t C, double count,
-                    double eps, int64_t act, int64_t mode) {
+                    double eps, int64_t act, int64_t mode, const std::vector<int64_t>& sync, const std::vector<int64_t>& srcs) {
   MK_CHECK(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && out.scalar_type() == torch::kBFloat16, "inorm_cl_apply: bf16 CUDA expected");
   c10::cuda::CUDAGuard guard(x.device());
   const int64_t T = x.numel() / (B * C);
   auto fp = [](const c10::optional<Tensor>& t) -> float* { return (t.has_value() && t->defined()) ? t->data_ptr<float>() : nullptr; };
   const __nv_bfloat16* dyp = (dy.has_value() && dy->defined()) ? reinterpret_cast<const __nv_bfloat16*>(dy->data_ptr()) : nullptr;
+  mk::StatExchange xc;
+  const bool ex = make_exchange(xc, sync, srcs, false, x);
   check_cuda(mk::inorm_cl_apply(reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), dyp, reinterpret_cast<__nv_bfloat16*>(out.data_ptr()),
                                 fp(w), fp(b), sums.data_ptr<float>(), fp(stats), static_cast<int>(B), static_cast<int>(C), T, count,
-                                static_cast<float>(eps), static_cast<int>(act), static_cast<int>(mode), cur_stream()),
+                                static_cast<float>(eps), static_cast<int>(act), static_cast<int>(mode), cur_stream(), ex ? &xc : nullptr),
              "inorm_cl_apply");
 }
 
@@ -410,8 +444,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("inorm_fwd", &inorm_fwd);
   m.def("inorm_partial_stats", &inorm_partial_stats);
   m.def("inorm_bwd", &inorm_bwd);
-  m.def("inorm_cl_sums", &inorm_cl_sums);
-  m.def("inorm_cl_apply", &inorm_cl_apply);
+  m.def("inorm_cl_sums", &inorm_cl_sums, py::arg("x"), py::arg("dy"), py::arg("w"), py::arg("b"), py::arg("stats"), py::arg("sums"),
+        py::arg("dw"), py::arg("db"), py::arg("B"), py::arg("C"), py::arg("act"), py::arg("mode"),
+        py::arg("sync") = std::vector<int64_t>(), py::arg("dsts") = std::vector<int64_t>());
+  m.def("inorm_cl_apply", &inorm_cl_apply, py::arg("x"), py::arg("dy"), py::arg("out"), py::arg("w"), py::arg("b"), py::arg("sums"),
+        py::arg("stats"), py::arg("B"), py::arg("C"), py::arg("count"), py::arg("eps"), py::arg("act"), py::arg("mode"),
+        py::arg("sync") = std::vector<int64_t>(), py::arg("srcs") = std::vector<int64_t>());
   m.def("lp_scratch_floats", &lp_scratch_floats);
   m.def("lp_norms", &lp_norms);
   m.def("lp_norms_bwd", &lp_norms_bwd);

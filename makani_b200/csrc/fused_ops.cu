@@ -2,6 +2,7 @@
 // AdamW with bf16 shadow weights, spectral-weight re-layout.  Each kernel makes the minimum number of passes
 // over HBM (vectorised 16-byte accesses) and keeps reductions in fp32.
 #include "fused_ops.cuh"
+#include <cstring>
 
 #include <math.h>
 
@@ -250,12 +251,49 @@ __global__ void __launch_bounds__(NT) inorm_bwd_kernel(const __nv_bfloat16* __re
 constexpr int CL_THREADS = 512;
 
 // mode 0: sums of (x, x^2).  mode 1: sums of (g, g * xhat) with g = dy * act'(xhat * w + b) for the backward pass.
+__device__ __forceinline__ unsigned int xch_ld_acquire(const unsigned int* ptr) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long xch_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// bounded wait (2 s) of one thread on the peers' flags; false + error word on expiry
+__device__ bool xch_wait(const StatExchange& xc, int code) {
+  const unsigned int need = *xc.wait_exp + static_cast<unsigned int>(xc.wait_off);
+  for (int peer = 0; peer < xc.npeers; ++peer) {
+    unsigned long long t0 = 0;
+    for (unsigned int it = 0;; ++it) {
+      if (static_cast<int>(xch_ld_acquire(xc.wait + peer) - need) >= 0) break;
+      if ((it & 255u) == 255u) {
+        const unsigned long long now = xch_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > 2000000000ull) {
+          atomicExch(xc.err, code);
+          return false;
+        }
+      }
+    }
+  }
+  return true;
+}
+__device__ void xch_signal(const StatExchange& xc) {
+  *xc.done_ctr = 0;
+  atomicAdd(xc.bump, 1u);
+  __threadfence_system();
+  for (int peer = 0; peer < xc.npeers; ++peer)
+    if (xc.sig[peer]) atomicAdd_system(xc.sig[peer], 1u);
+}
+
 template <int MODE>
 __global__ void __launch_bounds__(CL_THREADS) inorm_cl_sums_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
                                                                    const float* __restrict__ w, const float* __restrict__ b,
                                                                    const float* __restrict__ stats, float* __restrict__ sums,
                                                                    float* __restrict__ dw, float* __restrict__ db, int C, long long T,
-                                                                   int act, int slab) {
+                                                                   int act, int slab, const StatExchange xc) {
   extern __shared__ float sh_acc[];   // [C][2]
   const int V = C >> 3;
   const int R = CL_THREADS / V;
@@ -320,6 +358,32 @@ __global__ void __launch_bounds__(CL_THREADS) inorm_cl_sums_kernel(const __nv_bf
       if (!(i & 1) && db) atomicAdd(db + c, val);
     }
   }
+  if (xc.npeers > 0) {
+    // the last CTA of the grid hands this rank's sums to every peer
+    __shared__ int last_s;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const unsigned int prev = atomicAdd(xc.done_ctr, 1u);
+      int last = (prev == gridDim.x * gridDim.y - 1) ? 1 : 0;
+      if (last && !xch_wait(xc, 56)) last = 2;     // peers still read the previous statistics: give up (error word set)
+      last_s = last;
+    }
+    __syncthreads();
+    if (last_s == 1) {
+      __threadfence();
+      const int n = static_cast<int>(gridDim.y) * 2 * C;
+      for (int i = threadIdx.x; i < n; i += CL_THREADS) {
+        const float val = __ldcg(sums + i);
+        for (int q = 0; q < xc.ndst; ++q) xc.dst[q][i] = val;
+      }
+      __threadfence_system();
+      __syncthreads();
+      if (threadIdx.x == 0) xch_signal(xc);
+    } else if (last_s == 2 && threadIdx.x == 0) {
+      *xc.done_ctr = 0;
+    }
+  }
 }
 
 // mode 0: y = act(xhat * w + b), statistics derived from `sums` (and stored to `stats`).
@@ -329,12 +393,22 @@ __global__ void __launch_bounds__(CL_THREADS) inorm_cl_apply_kernel(const __nv_b
                                                                     __nv_bfloat16* __restrict__ out, const float* __restrict__ w,
                                                                     const float* __restrict__ b, const float* __restrict__ sums,
                                                                     float* __restrict__ stats, int C, long long T, float inv_count,
-                                                                    float eps, int act, int slab) {
+                                                                    float eps, int act, int slab, const StatExchange xc) {
   const int V = C >> 3;
   const int R = CL_THREADS / V;
   const int v = threadIdx.x % V, r = threadIdx.x / V;
   const int bidx = blockIdx.y;
-  if (r >= R) return;
+  if (xc.npeers > 0) {
+    // every peer's sums must have arrived in the local buffer
+    __shared__ int ok_s;
+    if (threadIdx.x == 0) ok_s = xch_wait(xc, 57) ? 1 : 0;
+    __syncthreads();
+    if (!ok_s) return;
+  }
+  if (r >= R) {
+    if (xc.npeers > 0) __syncthreads();   // matches the barrier before the completion count below
+    return;
+  }
   float k0[8], k1[8], k2[8], k3[8], kw[8], kb[8];   // per-channel constants
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
@@ -343,9 +417,21 @@ __global__ void __launch_bounds__(CL_THREADS) inorm_cl_apply_kernel(const __nv_b
     const float wc = w ? w[c] : 1.f, bc = b ? b[c] : 0.f;
     kw[j] = wc;
     kb[j] = bc;
+    float s0, s1;
+    if (xc.npeers > 0) {
+      s0 = 0.f;
+      s1 = 0.f;
+      for (int q = 0; q < xc.nsrc; ++q) {    // fixed order: every rank computes bit-identical statistics
+        s0 += __ldcg(xc.src + q * xc.src_stride + sc);
+        s1 += __ldcg(xc.src + q * xc.src_stride + sc + 1);
+      }
+    } else {
+      s0 = sums[sc];
+      s1 = sums[sc + 1];
+    }
     if (MODE == 0) {
-      const float mean = sums[sc] * inv_count;
-      const float var = fmaxf(sums[sc + 1] * inv_count - mean * mean, 0.f);
+      const float mean = s0 * inv_count;
+      const float var = fmaxf(s1 * inv_count - mean * mean, 0.f);
       const float rstd = rsqrtf(var + eps);
       k0[j] = wc * rstd;
       k1[j] = bc - mean * k0[j];
@@ -356,8 +442,8 @@ __global__ void __launch_bounds__(CL_THREADS) inorm_cl_apply_kernel(const __nv_b
     } else {
       k0[j] = stats[sc];          // mean
       k1[j] = stats[sc + 1];      // rstd
-      k2[j] = sums[sc] * inv_count;
-      k3[j] = sums[sc + 1] * inv_count;
+      k2[j] = s0 * inv_count;
+      k3[j] = s1 * inv_count;
     }
   }
   const long long t0 = static_cast<long long>(blockIdx.x) * slab;
@@ -388,6 +474,14 @@ __global__ void __launch_bounds__(CL_THREADS) inorm_cl_apply_kernel(const __nv_b
       }
     }
     ov[t * V] = pack8(f);
+  }
+  if (xc.npeers > 0) {
+    // the last CTA tells the peers that this rank is done with their sums
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const unsigned int prev = atomicAdd(xc.done_ctr, 1u);
+      if (prev == gridDim.x * gridDim.y - 1) xch_signal(xc);
+    }
   }
 }
 
@@ -690,25 +784,32 @@ static inline int cl_slab(int C, long long T, int B) {
 }
 
 cudaError_t inorm_cl_sums(const __nv_bfloat16* x, const __nv_bfloat16* dy, const float* w, const float* b, const float* stats,
-                          float* sums, float* dw, float* db, int B, int C, long long T, int act, int mode, cudaStream_t s) {
+                          float* sums, float* dw, float* db, int B, int C, long long T, int act, int mode, cudaStream_t s,
+                          const StatExchange* xch) {
   if (!cl_ok(C)) return cudaErrorInvalidValue;
+  StatExchange xc;
+  memset(&xc, 0, sizeof(xc));
+  if (xch) xc = *xch;
   const int slab = cl_slab(C, T, B);
   dim3 grid(static_cast<unsigned>((T + slab - 1) / slab), B);
   const size_t sh = 2 * C * sizeof(float);
-  if (mode == 0) inorm_cl_sums_kernel<0><<<grid, CL_THREADS, sh, s>>>(x, dy, w, b, stats, sums, dw, db, C, T, act, slab);
-  else inorm_cl_sums_kernel<1><<<grid, CL_THREADS, sh, s>>>(x, dy, w, b, stats, sums, dw, db, C, T, act, slab);
+  if (mode == 0) inorm_cl_sums_kernel<0><<<grid, CL_THREADS, sh, s>>>(x, dy, w, b, stats, sums, dw, db, C, T, act, slab, xc);
+  else inorm_cl_sums_kernel<1><<<grid, CL_THREADS, sh, s>>>(x, dy, w, b, stats, sums, dw, db, C, T, act, slab, xc);
   return cudaGetLastError();
 }
 
 cudaError_t inorm_cl_apply(const __nv_bfloat16* x, const __nv_bfloat16* dy, __nv_bfloat16* out, const float* w, const float* b,
                            const float* sums, float* stats, int B, int C, long long T, double count, float eps, int act, int mode,
-                           cudaStream_t s) {
+                           cudaStream_t s, const StatExchange* xch) {
   if (!cl_ok(C)) return cudaErrorInvalidValue;
+  StatExchange xc;
+  memset(&xc, 0, sizeof(xc));
+  if (xch) xc = *xch;
   const int slab = cl_slab(C, T, B);
   dim3 grid(static_cast<unsigned>((T + slab - 1) / slab), B);
   const float inv = static_cast<float>(1.0 / count);
-  if (mode == 0) inorm_cl_apply_kernel<0><<<grid, CL_THREADS, 0, s>>>(x, dy, out, w, b, sums, stats, C, T, inv, eps, act, slab);
-  else inorm_cl_apply_kernel<1><<<grid, CL_THREADS, 0, s>>>(x, dy, out, w, b, sums, stats, C, T, inv, eps, act, slab);
+  if (mode == 0) inorm_cl_apply_kernel<0><<<grid, CL_THREADS, 0, s>>>(x, dy, out, w, b, sums, stats, C, T, inv, eps, act, slab, xc);
+  else inorm_cl_apply_kernel<1><<<grid, CL_THREADS, 0, s>>>(x, dy, out, w, b, sums, stats, C, T, inv, eps, act, slab, xc);
   return cudaGetLastError();
 }
 

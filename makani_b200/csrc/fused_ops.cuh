@@ -22,16 +22,38 @@ cudaError_t inorm_bwd(const __nv_bfloat16* x, const __nv_bfloat16* dy, __nv_bflo
                       const float* b, const float* stats, float* dw, float* db, float* sums_io, int planes, int C,
                       long long hw, double count, int act, int ext_sums, cudaStream_t s);
 
+// ---- cross-device exchange of the partial sums of a spatially sharded instance norm (peer memory, one node) ----
+// Producer side (sums kernel): the last CTA to finish waits (bounded) until `wait[p] >= *wait_exp + wait_off` for all
+// peers, stores the [B, C, 2] sums into `dst[q]` (this rank's segment in every rank's buffer), bumps `bump` and
+// increments `sig[p]` on every peer.  Consumer side (apply kernel): every CTA waits the same way, sums the `nsrc`
+// segments found at `src + q * src_stride`, and the last CTA bumps / signals.  All counters are monotonic.
+struct StatExchange {
+  int npeers;                      // 0: no exchange (single device or host-side reduction)
+  const unsigned int* wait;
+  const unsigned int* wait_exp;
+  int wait_off;
+  unsigned int* bump;
+  unsigned int* sig[8];
+  unsigned int* done_ctr;
+  int* err;
+  float* dst[8];                   // producer: destinations (ndst)
+  int ndst;
+  const float* src;                // consumer: base of segment 0 in the local buffer
+  long long src_stride;            // floats between segments
+  int nsrc;
+};
+
 // ---- instance norm on channels-last data x[B, T, C] (C contiguous, C % 8 == 0, C <= 1024) ----
 // sums: [B, C, 2] fp32, zero-initialised by the caller, accumulated atomically.
 //   mode 0: (sum x, sum x^2);   mode 1: (sum g, sum g*xhat), also accumulated over B into dw / db.
 cudaError_t inorm_cl_sums(const __nv_bfloat16* x, const __nv_bfloat16* dy, const float* w, const float* b, const float* stats,
-                          float* sums, float* dw, float* db, int B, int C, long long T, int act, int mode, cudaStream_t s);
+                          float* sums, float* dw, float* db, int B, int C, long long T, int act, int mode, cudaStream_t s,
+                          const StatExchange* xch = nullptr);
 // mode 0: out = act(xhat * w + b) with statistics from `sums` over `count` elements (stats [B, C, 2] written);
 // mode 1: out = dx from the merged backward sums.
 cudaError_t inorm_cl_apply(const __nv_bfloat16* x, const __nv_bfloat16* dy, __nv_bfloat16* out, const float* w, const float* b,
                            const float* sums, float* stats, int B, int C, long long T, double count, float eps, int act, int mode,
-                           cudaStream_t s);
+                           cudaStream_t s, const StatExchange* xch = nullptr);
 
 // ---- quadrature-weighted Lp norms on the sphere ----
 // out[plane] = (sum_hw q[h] |p-t|^P, sum_hw q[h] |t|^P), P in {1,2}.  `scratch` holds

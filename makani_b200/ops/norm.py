@@ -53,11 +53,13 @@ class _InstanceNorm(torch.autograd.Function):
 
 
 class _InstanceNormCL(torch.autograd.Function):
-    """Channels-last variant; `reduce_fn` (optional) merges the [B, C, 2] partial sums across a process group and
-    `count` is then the global number of grid points (spatially distributed instance norm)."""
+    """Channels-last variant.  For a spatially distributed instance norm `count` is the global number of grid points
+    and the [B, C, 2] partial sums are merged across the ranks either by `reduce_fn` (any collective) or, when `slot`
+    (a `makani_b200.parallel.peer.PeerSlot`) is given, inside the two kernels themselves: the last CTA of the
+    reduction stores this rank's sums into every peer's buffer and the normalising kernel adds the segments up."""
 
     @staticmethod
-    def forward(ctx, x, weight, bias, eps, act, count, reduce_fn):
+    def forward(ctx, x, weight, bias, eps, act, count, reduce_fn, slot=None):
         ext = _ext.require()
         B, C, H, W = x.shape
         y = torch.empty_like(x)     # preserves channels_last
@@ -65,13 +67,21 @@ class _InstanceNormCL(torch.autograd.Function):
         stats = torch.empty(B, C, 2, dtype=torch.float32, device=x.device)
         wf = weight.detach().float().contiguous() if weight is not None else None
         bf = bias.detach().float().contiguous() if bias is not None else None
-        ext.inorm_cl_sums(x, None, None, None, None, sums, None, None, B, C, 0, 0)
-        if reduce_fn is not None:
-            sums = reduce_fn(sums)
         cnt = float(count if count else H * W)
-        ext.inorm_cl_apply(x, None, y, wf, bf, sums, stats, B, C, cnt, float(eps), int(act), 0)
+        if slot is not None:
+            from ..parallel.peer import sync_descriptor
+            slot.set_layout(B * C * 8)
+            ext.inorm_cl_sums(x, None, None, None, None, sums, None, None, B, C, 0, 0,
+                              sync_descriptor(produce=slot), slot.dests(include_self=True))
+            ext.inorm_cl_apply(x, None, y, wf, bf, sums, stats, B, C, cnt, float(eps), int(act), 0,
+                               sync_descriptor(consume=slot), slot.sources())
+        else:
+            ext.inorm_cl_sums(x, None, None, None, None, sums, None, None, B, C, 0, 0)
+            if reduce_fn is not None:
+                sums = reduce_fn(sums)
+            ext.inorm_cl_apply(x, None, y, wf, bf, sums, stats, B, C, cnt, float(eps), int(act), 0)
         ctx.save_for_backward(x, wf, bf, stats)
-        ctx.act, ctx.cnt, ctx.reduce_fn, ctx.affine = int(act), cnt, reduce_fn, weight is not None
+        ctx.act, ctx.cnt, ctx.reduce_fn, ctx.affine, ctx.slot = int(act), cnt, reduce_fn, weight is not None, slot
         return y
 
     @staticmethod
@@ -84,12 +94,21 @@ class _InstanceNormCL(torch.autograd.Function):
         sums = torch.zeros(B, C, 2, dtype=torch.float32, device=x.device)
         dw = torch.zeros(C, dtype=torch.float32, device=x.device) if ctx.affine else None
         db = torch.zeros(C, dtype=torch.float32, device=x.device) if ctx.affine else None
-        ext.inorm_cl_sums(x, dy, wf, bf, stats, sums, dw, db, B, C, ctx.act, 1)
-        if ctx.reduce_fn is not None:
-            sums = ctx.reduce_fn(sums)
         dx = torch.empty_like(x)
-        ext.inorm_cl_apply(x, dy, dx, wf, bf, sums, stats, B, C, ctx.cnt, 0.0, ctx.act, 1)
-        return dx, dw, db, None, None, None, None
+        slot = ctx.slot
+        if slot is not None:
+            from ..parallel.peer import sync_descriptor
+            slot.set_layout(B * C * 8)
+            ext.inorm_cl_sums(x, dy, wf, bf, stats, sums, dw, db, B, C, ctx.act, 1,
+                              sync_descriptor(produce=slot), slot.dests(include_self=True))
+            ext.inorm_cl_apply(x, dy, dx, wf, bf, sums, stats, B, C, ctx.cnt, 0.0, ctx.act, 1,
+                               sync_descriptor(consume=slot), slot.sources())
+        else:
+            ext.inorm_cl_sums(x, dy, wf, bf, stats, sums, dw, db, B, C, ctx.act, 1)
+            if ctx.reduce_fn is not None:
+                sums = ctx.reduce_fn(sums)
+            ext.inorm_cl_apply(x, dy, dx, wf, bf, sums, stats, B, C, ctx.cnt, 0.0, ctx.act, 1)
+        return dx, dw, db, None, None, None, None, None
 
 
 def cl_supported(x) -> bool:
@@ -97,11 +116,12 @@ def cl_supported(x) -> bool:
             and x.shape[1] <= 1024)
 
 
-def instance_norm(x: torch.Tensor, weight, bias, eps: float = 1e-6, act: str = "none", count=None, reduce_fn=None) -> torch.Tensor:
+def instance_norm(x: torch.Tensor, weight, bias, eps: float = 1e-6, act: str = "none", count=None, reduce_fn=None,
+                  slot=None) -> torch.Tensor:
     """y = act(IN(x) * weight + bias) over the last two dims of a 4-D activation `x`."""
     a = 1 if act == "gelu" else 0
     if cl_supported(x):
-        return _InstanceNormCL.apply(x, weight, bias, eps, a, count, reduce_fn)
+        return _InstanceNormCL.apply(x, weight, bias, eps, a, count, reduce_fn, slot)
     if _ext.native() and x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 4 and count is None and reduce_fn is None:
         return _InstanceNorm.apply(x.contiguous(), weight, bias, eps, a)
     assert count is None and reduce_fn is None, "distributed statistics need the channels-last CUDA path"

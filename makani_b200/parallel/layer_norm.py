@@ -11,12 +11,18 @@ all-reduce of a [B, C, 2] fp32 tensor.
 
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 import torch.nn as nn
 
 from ..ops import _ext
 from ..utils import comm
+
+
+# MAKANI_B200_PEER_NORM_STATS=0: exchange the statistics with an NCCL all-reduce instead of in-kernel peer stores
+PEER_STATS = os.environ.get("MAKANI_B200_PEER_NORM_STATS", "1") != "0"
 
 
 def _allreduce_spatial(t: torch.Tensor) -> torch.Tensor:
@@ -107,14 +113,25 @@ class DistributedInstanceNorm2d(nn.Module):
             self._counts[key] = float(cnt.item())
         return self._counts[key]
 
+    def _slot(self, x):
+        """Peer-memory exchange buffer for the statistics (NCCL ranks of one node, at most 8), else None."""
+        n = comm.get_size("spatial")
+        if not (PEER_STATS and x.is_cuda and 1 < n <= 8 and dist.get_backend(comm.get_group("spatial")) == "nccl"):
+            return None
+        from .peer import get_slot
+        return get_slot("inorm", "spatial", x.shape[0] * x.shape[1] * 8, x.device)
+
     def forward(self, x, act: str = "none"):
         from ..ops import norm as norm_ops
         w = self.weight if self.affine else None
         b = self.bias if self.affine else None
         cnt = self._global_count(x)
         if norm_ops.cl_supported(x):
-            # fused channels-last kernels; only the [B, C, 2] partial sums cross the spatial group
-            return norm_ops.instance_norm(x, w, b, self.eps, act, count=cnt, reduce_fn=_allreduce_spatial)
+            # fused channels-last kernels; only the [B, C, 2] partial sums cross the spatial group: through peer memory
+            # from inside the two kernels when the ranks can map each other's memory, else through an all-reduce
+            slot = self._slot(x)
+            return norm_ops.instance_norm(x, w, b, self.eps, act, count=cnt,
+                                          reduce_fn=None if slot is not None else _allreduce_spatial, slot=slot)
         y = _DistInstanceNormFn.apply(x, w, b, self.eps, cnt)
         if act == "gelu":
             y = torch.nn.functional.gelu(y)

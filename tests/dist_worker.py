@@ -277,6 +277,43 @@ def case_fused_spectral():
     y2_full = _gather(_gather(y2.float().contiguous(), -2, "h"), -1, "w")
     assert _rel(y2_full, y_ref.float()) < tol
 
+def case_peer_instance_norm():
+    """Spatially sharded instance norm whose statistics cross the ranks inside the kernels (peer memory) == serial op;
+    forward (with fused GELU), input and affine gradients; used twice so that the handshake counters carry over."""
+    from makani_b200.ops import _ext, norm as norm_ops
+    from makani_b200.parallel.layer_norm import DistributedInstanceNorm2d
+    assert os.environ.get("MK_DEVICE") == "cuda"
+    dev = torch.device("cuda", comm.get_local_rank())
+    torch.manual_seed(11)
+    B, C, H, W = 2, 64, 45, 64
+    x = (torch.randn(B, C, H, W) * 2.0 + 0.5).to(dev, torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    g = torch.randn(B, C, H, W).to(dev, torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    mod = DistributedInstanceNorm2d(C, eps=1e-6, affine=True).to(dev)
+    with torch.no_grad():
+        mod.weight.copy_(torch.rand(C) + 0.5)
+        mod.bias.copy_(torch.randn(C) * 0.1)
+    for act in ("gelu", "none"):
+        xr = x.clone().requires_grad_()
+        wr, br = mod.weight.detach().clone().requires_grad_(), mod.bias.detach().clone().requires_grad_()
+        y_ref = norm_ops.instance_norm(xr, wr, br, 1e-6, act)
+        y_ref.backward(g)
+        xl = _shard(_shard(x, -2, "h"), -1, "w").contiguous(memory_format=torch.channels_last).requires_grad_()
+        gl = _shard(_shard(g, -2, "h"), -1, "w").contiguous(memory_format=torch.channels_last)
+        mod.weight.grad = None
+        mod.bias.grad = None
+        assert mod._slot(xl) is not None, "peer exchange path not taken"
+        y = mod(xl, act=act)
+        y.backward(gl)
+        _ext.check_device_errors(dev)
+        y_full = _gather(_gather(y.float().contiguous(), -2, "h"), -1, "w")
+        assert _rel(y_full, y_ref.float()) < 2e-2, _rel(y_full, y_ref.float())
+        dx_full = _gather(_gather(xl.grad.float().contiguous(), -2, "h"), -1, "w")
+        assert _rel(dx_full, xr.grad.float()) < 3e-2, _rel(dx_full, xr.grad.float())
+        dw, db = mod.weight.grad.clone(), mod.bias.grad.clone()
+        dist.all_reduce(dw, group=comm.get_group("spatial"))
+        dist.all_reduce(db, group=comm.get_group("spatial"))
+        assert _rel(dw, wr.grad) < 3e-2 and _rel(db, br.grad) < 3e-2, (_rel(dw, wr.grad), _rel(db, br.grad))
+
 
 if __name__ == "__main__":
     case = sys.argv[1]

@@ -23,3 +23,9 @@ def test_fused_distributed_spectral_conv_2gpu(sizes):
 def test_fused_distributed_spectral_conv_4gpu():
     _need(4)
     _launch("fused_spectral", (2, 2, 1, 1), 4, cuda=True)
+
+
+@pytest.mark.parametrize("sizes,world", [((2, 1, 1, 1), 2), ((2, 2, 1, 1), 4)])
+def test_peer_memory_instance_norm(sizes, world):
+    _need(world)
+    _launch("peer_instance_norm", sizes, world, cuda=True)
