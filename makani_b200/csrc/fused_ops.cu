@@ -398,12 +398,21 @@ __global__ void __launch_bounds__(CL_THREADS) inorm_cl_apply_kernel(const __nv_b
   const int R = CL_THREADS / V;
   const int v = threadIdx.x % V, r = threadIdx.x / V;
   const int bidx = blockIdx.y;
+  extern __shared__ float sh_sum[];   // [C][2] merged sums of this sample (exchange mode only)
   if (xc.npeers > 0) {
     // every peer's sums must have arrived in the local buffer
     __shared__ int ok_s;
     if (threadIdx.x == 0) ok_s = xch_wait(xc, 57) ? 1 : 0;
     __syncthreads();
     if (!ok_s) return;
+    // merge the segments once per CTA (coalesced, L1 bypassed: the buffer is rewritten by peers between launches);
+    // fixed order, so every rank computes bit-identical statistics
+    for (int i = threadIdx.x; i < 2 * C; i += CL_THREADS) {
+      float acc = 0.f;
+      for (int q = 0; q < xc.nsrc; ++q) acc += __ldcg(xc.src + q * xc.src_stride + static_cast<long long>(bidx) * 2 * C + i);
+      sh_sum[i] = acc;
+    }
+    __syncthreads();
   }
   if (r >= R) {
     if (xc.npeers > 0) __syncthreads();   // matches the barrier before the completion count below
@@ -419,12 +428,8 @@ __global__ void __launch_bounds__(CL_THREADS) inorm_cl_apply_kernel(const __nv_b
     kb[j] = bc;
     float s0, s1;
     if (xc.npeers > 0) {
-      s0 = 0.f;
-      s1 = 0.f;
-      for (int q = 0; q < xc.nsrc; ++q) {    // fixed order: every rank computes bit-identical statistics
-        s0 += __ldcg(xc.src + q * xc.src_stride + sc);
-        s1 += __ldcg(xc.src + q * xc.src_stride + sc + 1);
-      }
+      s0 = sh_sum[2 * c];
+      s1 = sh_sum[2 * c + 1];
     } else {
       s0 = sums[sc];
       s1 = sums[sc + 1];
@@ -808,8 +813,9 @@ cudaError_t inorm_cl_apply(const __nv_bfloat16* x, const __nv_bfloat16* dy, __nv
   const int slab = cl_slab(C, T, B);
   dim3 grid(static_cast<unsigned>((T + slab - 1) / slab), B);
   const float inv = static_cast<float>(1.0 / count);
-  if (mode == 0) inorm_cl_apply_kernel<0><<<grid, CL_THREADS, 0, s>>>(x, dy, out, w, b, sums, stats, C, T, inv, eps, act, slab, xc);
-  else inorm_cl_apply_kernel<1><<<grid, CL_THREADS, 0, s>>>(x, dy, out, w, b, sums, stats, C, T, inv, eps, act, slab, xc);
+  const size_t shx = xc.npeers > 0 ? 2 * C * sizeof(float) : 0;
+  if (mode == 0) inorm_cl_apply_kernel<0><<<grid, CL_THREADS, shx, s>>>(x, dy, out, w, b, sums, stats, C, T, inv, eps, act, slab, xc);
+  else inorm_cl_apply_kernel<1><<<grid, CL_THREADS, shx, s>>>(x, dy, out, w, b, sums, stats, C, T, inv, eps, act, slab, xc);
   return cudaGetLastError();
 }
 
