@@ -37,6 +37,8 @@ def parse():
                          "reference's op sequence on stock PyTorch kernels and NCCL, through this package's model code")
     ap.add_argument("--small", action="store_true", help="reduced grid for profiling captures (not a bench value)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--mode", default="train", choices=["train", "rollout"],
+                    help="train: samples/s of the optimisation step (headline); rollout: ms per autoregressive inference step")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying a CUDA graph")
     ap.add_argument("--h", type=int, default=1, help="latitude-parallel ranks per model instance (default: pure data parallel)")
     ap.add_argument("--w", type=int, default=1, help="longitude-parallel ranks per model instance")
@@ -63,17 +65,64 @@ def reference_arm(args):
 
 
 class ClockSampler:
-    """Samples SM clocks / throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks / throttle reasons of this rank's GPU while the timed region runs.
+
+    Primary: an NVML polling thread (read-only queries, 50 ms period, exactly between `start` and `stop`);
+    fallback: an `nvidia-smi --query-gpu ... -lms 200` child process."""
 
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index: int):
-        self.gpu_index = gpu_index
+    def __init__(self, gpu_index: int, uuid: str = None):
+        self.gpu_index, self.uuid = gpu_index, uuid
         self.proc = None
+        self.thread = None
+        self.samples = []
         self.path = os.path.join("/tmp", f"bench_clocks_{os.getpid()}.csv")
 
+    # ---- NVML
+    def _nvml_handle(self):
+        import pynvml
+        pynvml.nvmlInit()
+        if self.uuid:
+            try:
+                return pynvml, pynvml.nvmlDeviceGetHandleByUUID(self.uuid if self.uuid.startswith("GPU-") else "GPU-" + self.uuid)
+            except Exception:
+                pass
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+        idx = self.gpu_index
+        if vis:
+            ids = [v.strip() for v in vis.split(",") if v.strip()]
+            if self.gpu_index < len(ids) and ids[self.gpu_index].isdigit():
+                idx = int(ids[self.gpu_index])
+        return pynvml, pynvml.nvmlDeviceGetHandleByIndex(idx)
+
+    def _poll(self):
+        nv, h = self._nv, self._h
+        bits = {"hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+                "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+                "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+                "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4)}
+        while not self._stop.is_set():
+            try:
+                sm = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+                self.samples.append((float(sm), [n for n, b in bits.items() if mask & b]))
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
     def start(self):
+        import threading
+        try:
+            self._nv, self._h = self._nvml_handle()
+            self._max = float(self._nv.nvmlDeviceGetMaxClockInfo(self._h, self._nv.NVML_CLOCK_SM))
+            self._stop = threading.Event()
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
         try:
             self.fh = open(self.path, "w")
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
@@ -83,6 +132,16 @@ class ClockSampler:
 
     def stop(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.thread is not None:
+            self._stop.set()
+            self.thread.join(timeout=2.0)
+            if self.samples:
+                sm = sorted(s[0] for s in self.samples)
+                out["sm_mhz"] = sm[len(sm) // 2]
+                out["sm_max_mhz"] = self._max
+                out["reasons"] = sorted({r for s in self.samples for r in s[1]})
+                out["samples"] = len(sm)
+            return out
         if self.proc is None:
             return out
         self.proc.terminate()
@@ -114,6 +173,13 @@ class ClockSampler:
             out["sm_max_mhz"] = max(mx)
         out["reasons"] = sorted(reasons)
         return out
+
+
+def _gpu_uuid(torch, index):
+    try:
+        return str(torch.cuda.get_device_properties(index).uuid)
+    except Exception:
+        return None
 
 
 def main():
@@ -151,12 +217,45 @@ def main():
             dist.barrier(device_ids=[local_rank])
         torch.cuda.synchronize()
 
+    if args.mode == "rollout":
+        sampler = ClockSampler(local_rank, _gpu_uuid(torch, local_rank))
+        sampler.start()
+        ms, launches, finite = runner.rollout(args.steps, args.warmup, world, local_rank, graph=not args.no_graph)
+        clocks = sampler.stop()
+        _ext.check_device_errors(dev)
+        if rank == 0:
+            print(json.dumps({
+                "metric": "SFNO-73ch 721x1440 bf16 rollout ms/step", "value": ms, "unit": "ms/step", "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "strong",
+                "vs_baseline": None, "dtype": "bf16", "data": "synthetic N(0,1), random-init weights", "impl": "native",
+                "config": {"model": cfg.name, "global_batch": 1, "seq_len": f"{cfg.nlat}x{cfg.nlon}",
+                           "parallelism": f"h{args.h}w{args.w}", "cuda_graph": not args.no_graph, "state_finite": finite},
+                "clocks": clocks, "gpu_launches": launches}))
+        sys.stdout.flush()
+        if world > 1:
+            import threading
+
+            def _bail():
+                time.sleep(30.0)
+                os._exit(0)
+
+            threading.Thread(target=_bail, daemon=True).start()
+            runner._rollout_graph = None
+            import gc
+            gc.collect()
+            torch.cuda.synchronize()
+            from makani_b200.parallel import peer
+            peer.release_slots()
+            dist.barrier(device_ids=[local_rank])
+            dist.destroy_process_group()
+        return 0
+
     # ---------------------------------------------------------------- device-timed steps (inputs resident)
     inp, tgt = runner.synthetic_batch(seed=1234 + rank)
     for _ in range(args.warmup):
         runner.step(inp, tgt)
     barrier()
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(local_rank, _gpu_uuid(torch, local_rank))
     sampler.start()
     l0 = _ext.launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

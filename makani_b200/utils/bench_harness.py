@@ -159,5 +159,58 @@ class FlagshipRunner:
                 "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4}
 
 
+    @torch.no_grad()
+    def rollout(self, steps: int, warmup: int, world: int, local_rank: int, graph: bool = True):
+        """Autoregressive inference: state <- [model(state), static channel]; one step is captured in a CUDA graph (as
+        `Inferencer.rollout` does) and replayed.  Returns milliseconds per step (device-timed, max over ranks)."""
+        self.model.eval()
+        dev = self.device
+        state, _ = self.synthetic_batch(seed=99)
+        static = state.clone()
+
+        def one_step():
+            pred = self.model(static)
+            static[:, : pred.shape[1]].copy_(pred)        # prognostic channels advance; the static channel stays
+
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        g = None
+        with torch.cuda.stream(side):
+            for _ in range(max(2, warmup)):
+                one_step()
+            side.synchronize()
+            if graph:
+                g = torch.cuda.CUDAGraph()
+                n0 = _ext.launch_count()
+                with torch.cuda.graph(g, stream=side):
+                    one_step()
+                per_replay = _ext.launch_count() - n0
+                _ext.add_launches(-per_replay)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        static.copy_(state)
+        if world > 1:
+            dist.barrier(device_ids=[local_rank])
+        torch.cuda.synchronize()
+        l0 = _ext.launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            if g is not None:
+                g.replay()
+                _ext.add_launches(per_replay)
+            else:
+                one_step()
+        e1.record()
+        if world > 1:
+            dist.barrier(device_ids=[local_rank])
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        self._rollout_graph = g
+        finite = bool(torch.isfinite(static.float()).all())
+        return t.item() / steps, _ext.launch_count() - l0, finite
+
+
 def build_flagship(cfg: FlagshipConfig, device: torch.device) -> FlagshipRunner:
     return FlagshipRunner(cfg, device)
