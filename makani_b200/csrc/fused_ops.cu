@@ -320,9 +320,10 @@ __global__ void __launch_bounds__(CL_THREADS) inorm_cl_sums_kernel(const __nv_bf
     if (t1 > T) t1 = T;
     const uint4* xv = reinterpret_cast<const uint4*>(x + static_cast<long long>(bidx) * T * C) + v;
     const uint4* gv = MODE == 1 ? reinterpret_cast<const uint4*>(dy + static_cast<long long>(bidx) * T * C) + v : nullptr;
-    for (long long t = t0 + r; t < t1; t += R) {
+    // four rows in flight per thread: independent 16-byte loads cover the HBM latency
+    auto accum = [&](const uint4& xr, const uint4& gr) {
       float f[8];
-      unpack8(xv[t * V], f);
+      unpack8(xr, f);
       if (MODE == 0) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -331,7 +332,7 @@ __global__ void __launch_bounds__(CL_THREADS) inorm_cl_sums_kernel(const __nv_bf
         }
       } else {
         float g[8];
-        unpack8(gv[t * V], g);
+        unpack8(gr, g);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const float xh = (f[j] - mean[j]) * rstd[j];
@@ -341,6 +342,23 @@ __global__ void __launch_bounds__(CL_THREADS) inorm_cl_sums_kernel(const __nv_bf
           a1[j] += gg * xh;
         }
       }
+    };
+    long long t = t0 + r;
+    for (; t + 3LL * R < t1; t += 4LL * R) {
+      uint4 xr[4], gr[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        xr[u] = xv[(t + u * R) * V];
+        if (MODE == 1) gr[u] = gv[(t + u * R) * V];
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) accum(xr[u], gr[u]);
+    }
+    for (; t < t1; t += R) {
+      const uint4 xr = xv[t * V];
+      uint4 gr = xr;
+      if (MODE == 1) gr = gv[t * V];
+      accum(xr, gr);
     }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -458,9 +476,9 @@ __global__ void __launch_bounds__(CL_THREADS) inorm_cl_apply_kernel(const __nv_b
   const uint4* xv = reinterpret_cast<const uint4*>(x + base) + v;
   const uint4* gv = MODE == 1 ? reinterpret_cast<const uint4*>(dy + base) + v : nullptr;
   uint4* ov = reinterpret_cast<uint4*>(out + base) + v;
-  for (long long t = t0 + r; t < t1; t += R) {
+  auto transform = [&](const uint4& xr, const uint4& gr) -> uint4 {
     float f[8];
-    unpack8(xv[t * V], f);
+    unpack8(xr, f);
     if (MODE == 0) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -469,7 +487,7 @@ __global__ void __launch_bounds__(CL_THREADS) inorm_cl_apply_kernel(const __nv_b
       }
     } else {
       float g[8];
-      unpack8(gv[t * V], g);
+      unpack8(gr, g);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const float xh = (f[j] - k0[j]) * k1[j];
@@ -478,7 +496,25 @@ __global__ void __launch_bounds__(CL_THREADS) inorm_cl_apply_kernel(const __nv_b
         f[j] = k1[j] * kw[j] * (gg - k2[j] - xh * k3[j]);
       }
     }
-    ov[t * V] = pack8(f);
+    return pack8(f);
+  };
+  // four rows in flight per thread: independent 16-byte loads cover the HBM latency
+  long long t = t0 + r;
+  for (; t + 3LL * R < t1; t += 4LL * R) {
+    uint4 xr[4], gr[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      xr[u] = xv[(t + u * R) * V];
+      if (MODE == 1) gr[u] = gv[(t + u * R) * V];
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) ov[(t + u * R) * V] = transform(xr[u], gr[u]);
+  }
+  for (; t < t1; t += R) {
+    const uint4 xr = xv[t * V];
+    uint4 gr = xr;
+    if (MODE == 1) gr = gv[t * V];
+    ov[t * V] = transform(xr, gr);
   }
   if (xc.npeers > 0) {
     // the last CTA tells the peers that this rank is done with their sums
