@@ -364,13 +364,14 @@ void spectral_expand(const Tensor& w, Tensor& wx) {
              "spectral_expand");
 }
 
-void spectral_fold(const Tensor& dwx, Tensor& dw) {
+void spectral_fold(const Tensor& dwx, Tensor& dw, bool two_block, bool assign) {
   MK_CHECK(dw.is_cuda() && dw.is_contiguous() && dw.scalar_type() == torch::kComplexFloat && dw.dim() == 3, "spectral_fold: complex64 [Cin,Cout,L]");
   const int64_t Cin = dw.size(0), Cout = dw.size(1), L = dw.size(2);
-  MK_CHECK(dwx.is_contiguous() && dwx.scalar_type() == torch::kFloat32 && dwx.numel() == 4 * Cin * Cout * L, "spectral_fold: bad dwx");
+  MK_CHECK(dwx.is_contiguous() && dwx.scalar_type() == torch::kFloat32 && dwx.numel() == (two_block ? 2 : 4) * Cin * Cout * L,
+           "spectral_fold: bad dwx");
   c10::cuda::CUDAGuard guard(dw.device());
   check_cuda(mk::spectral_fold(dwx.data_ptr<float>(), reinterpret_cast<float*>(dw.data_ptr()), static_cast<int>(Cin),
-                               static_cast<int>(Cout), static_cast<int>(L), cur_stream()),
+                               static_cast<int>(Cout), static_cast<int>(L), cur_stream(), two_block ? 1 : 0, assign ? 1 : 0),
              "spectral_fold");
 }
 
@@ -456,7 +457,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("adamw_step", &adamw_step);
   m.def("adam_entry_bytes", &adam_entry_bytes);
   m.def("spectral_expand", &spectral_expand);
-  m.def("spectral_fold", &spectral_fold);
+  m.def("spectral_fold", &spectral_fold, py::arg("dwx"), py::arg("dw"), py::arg("two_block") = false, py::arg("assign") = false);
   m.def("cast_bf16", &cast_bf16);
   m.def("fill_normal", &fill_normal);
   m.def("peer_alloc", &peer_alloc);

@@ -724,17 +724,26 @@ __global__ void spectral_expand_kernel(const float2* __restrict__ w, __nv_bfloat
   }
 }
 
-__global__ void spectral_fold_kernel(const float* __restrict__ dwx, float2* __restrict__ dw, int Cin, int Cout, int L) {
+// two_block == 0: dwx is the full real 2x2-block gradient [L, 2Cout, 2Cin];  two_block == 1: dwx is [2][L][Cout][Cin]
+// holding (dWr, dWi) already.  assign != 0 overwrites dw instead of accumulating into it.
+__global__ void spectral_fold_kernel(const float* __restrict__ dwx, float2* __restrict__ dw, int Cin, int Cout, int L,
+                                     int two_block, int assign) {
   __shared__ float2 tile[32][33];
   const int c0 = blockIdx.x * 32, o = blockIdx.y, l0 = blockIdx.z * 32;
   for (int j = threadIdx.y; j < 32; j += 8) {
     const int l = l0 + j, c = c0 + threadIdx.x;
     float2 v = make_float2(0.f, 0.f);
     if (l < L && c < Cin) {
-      const float* base = dwx + static_cast<long long>(l) * 4 * Cout * Cin;
-      const long long r0 = static_cast<long long>(o) * 2 * Cin, r1 = static_cast<long long>(Cout + o) * 2 * Cin;
-      v.x = base[r0 + c] + base[r1 + Cin + c];   // dWr
-      v.y = base[r1 + c] - base[r0 + Cin + c];   // dWi
+      if (two_block) {
+        const long long e = (static_cast<long long>(l) * Cout + o) * Cin + c;
+        v.x = dwx[e];
+        v.y = dwx[e + static_cast<long long>(L) * Cout * Cin];
+      } else {
+        const float* base = dwx + static_cast<long long>(l) * 4 * Cout * Cin;
+        const long long r0 = static_cast<long long>(o) * 2 * Cin, r1 = static_cast<long long>(Cout + o) * 2 * Cin;
+        v.x = base[r0 + c] + base[r1 + Cin + c];   // dWr
+        v.y = base[r1 + c] - base[r0 + Cin + c];   // dWi
+      }
     }
     tile[j][threadIdx.x] = v;
   }
@@ -744,10 +753,14 @@ __global__ void spectral_fold_kernel(const float* __restrict__ dwx, float2* __re
     if (c < Cin && l < L) {
       float2* d = dw + (static_cast<long long>(c) * Cout + o) * L + l;
       const float2 v = tile[threadIdx.x][j];
-      float2 cur = *d;
-      cur.x += v.x;
-      cur.y += v.y;
-      *d = cur;
+      if (assign) {
+        *d = v;
+      } else {
+        float2 cur = *d;
+        cur.x += v.x;
+        cur.y += v.y;
+        *d = cur;
+      }
     }
   }
 }
@@ -903,9 +916,9 @@ cudaError_t spectral_expand(const float* w, __nv_bfloat16* wx, int Cin, int Cout
   return cudaGetLastError();
 }
 
-cudaError_t spectral_fold(const float* dwx, float* dw, int Cin, int Cout, int L, cudaStream_t s) {
+cudaError_t spectral_fold(const float* dwx, float* dw, int Cin, int Cout, int L, cudaStream_t s, int two_block, int assign) {
   dim3 grid((Cin + 31) / 32, Cout, (L + 31) / 32), block(32, 8);
-  spectral_fold_kernel<<<grid, block, 0, s>>>(dwx, reinterpret_cast<float2*>(dw), Cin, Cout, L);
+  spectral_fold_kernel<<<grid, block, 0, s>>>(dwx, reinterpret_cast<float2*>(dw), Cin, Cout, L, two_block, assign);
   return cudaGetLastError();
 }
 

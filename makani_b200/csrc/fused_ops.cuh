@@ -83,8 +83,10 @@ cudaError_t adamw_step(const AdamEntry* table, const int* chunk_tensor, const lo
 // ---- spectral weight re-layout ----
 // w: complex64 [Cin, Cout, L] (interleaved) -> wx: bf16 [L, 2*Cout, 2*Cin] real 2x2-block form
 cudaError_t spectral_expand(const float* w, __nv_bfloat16* wx, int Cin, int Cout, int L, cudaStream_t s);
-// dwx: fp32 [L, 2*Cout, 2*Cin] -> dw (complex64 [Cin, Cout, L]) += fold(dwx)
-cudaError_t spectral_fold(const float* dwx, float* dw, int Cin, int Cout, int L, cudaStream_t s);
+// dwx: fp32 [L, 2*Cout, 2*Cin] (two_block 0) or [2][L][Cout][Cin] = (dWr, dWi) (two_block 1)
+//   -> dw (complex64 [Cin, Cout, L]) += fold(dwx), or = fold(dwx) when `assign`
+cudaError_t spectral_fold(const float* dwx, float* dw, int Cin, int Cout, int L, cudaStream_t s, int two_block = 0,
+                          int assign = 0);
 
 // ---- small elementwise helpers ----
 cudaError_t cast_f32_bf16(const float* x, __nv_bfloat16* y, long long n, cudaStream_t s);

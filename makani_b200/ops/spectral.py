@@ -180,6 +180,38 @@ def contract_wgrad(dt: torch.Tensor, t2: torch.Tensor) -> torch.Tensor:
     return dwx
 
 
+def contract_wgrad2(dt: torch.Tensor, t2: torch.Tensor, l0: int = 0, m0: int = 0) -> torch.Tensor:
+    """(dWr, dWi)[l, o, c] as fp32 [2, L, Co, Ci] without forming the full real 2x2-block gradient:
+
+        dWr[l, o, c] = sum_{b, m <= l} dTr T2r + dTi T2i        dWi[l, o, c] = sum_{b, m <= l} dTi T2r - dTr T2i
+
+    Both are GEMMs over k = (m, ri) (the two parts sit side by side in memory); the second one reads a copy of dT
+    with its parts swapped and one sign flipped.  `l0`, `m0`: global offsets of the local (l, m) block."""
+    B, L, M, nq = dt.shape
+    co, ci = nq // 2, t2.shape[3] // 2
+    d5 = dt.view(B, L, M, 2, co)
+    dts = torch.cat([d5[..., 1:2, :], -d5[..., 0:1, :]], dim=-2).contiguous()
+    out = (torch.empty if B == 1 else torch.zeros)(2, L, co, ci, dtype=torch.float32, device=dt.device)
+    tri = Tri(kmax_a=2, kmax_b=2 * (1 + l0 - m0))
+    for part, a in enumerate((dt, dts)):
+        gemm(co, ci, 2 * M,
+             Operand(a, ld=co, mn_major=True, zs_hi=M * nq, zs_lo=L * M * nq),
+             Operand(t2, ld=ci, mn_major=True, zs_hi=M * 2 * ci, zs_lo=L * M * 2 * ci),
+             Output(out, rs_lo=ci, offset=part * L * co * ci, d_zhi=co * ci),
+             zhi_n=L, zlo_n=B, accumulate=(B > 1), tri=tri)
+    return out
+
+
+def fold_weight_grad2(dw2: torch.Tensor) -> torch.Tensor:
+    """fp32 [2, L, Co, Ci] = (dWr, dWi) -> complex64 [Ci, Co, L]."""
+    _, L, co, ci = dw2.shape
+    if dw2.is_cuda and _ext.native():
+        dw = torch.empty(ci, co, L, dtype=torch.complex64, device=dw2.device)
+        _ext.require().spectral_fold(dw2, dw, True, True)
+        return dw
+    return torch.complex(dw2[0], dw2[1]).permute(2, 1, 0).contiguous()
+
+
 # ------------------------------------------------------------------------------------------------ weights
 
 
@@ -252,8 +284,7 @@ class _SpectralConv(torch.autograd.Function):
         del dt4
         dw = None
         if ctx.needs_input_grad[1]:
-            dwx = contract_wgrad(dt3, t2)
-            dw = fold_weight_grad(dwx).reshape(ctx.wshape)
+            dw = fold_weight_grad2(contract_wgrad2(dt3, t2)).reshape(ctx.wshape)
         dx = None
         if ctx.needs_input_grad[0]:
             dt2 = contract(dt3, wx, True)                              # [B, m, l, (ri, c)]

@@ -38,7 +38,7 @@ from ..sht.legendre import legendre_table
 from ..sht.quadrature import precompute_latitudes
 from . import _ext
 from .gemm import Operand, Output, Segment, Tri, gemm, pad_to
-from .spectral import _to_cl, expand_weight, fold_weight_grad
+from .spectral import _to_cl, contract_wgrad2, expand_weight, fold_weight_grad2
 
 SEG_ALIGN = 64   # elements: one 128-byte k-slab of bf16
 # MAKANI_B200_FUSED_DIST_SHT=0 falls back to the all-to-all formulation (for A/B timing of the two designs)
@@ -361,8 +361,7 @@ class _DistSpectralConv(torch.autograd.Function):
         dt3 = dist_sht_analysis(dy, plan_out, plan_out.gt_an, plan_out.p_an)        # [B, l, m, (ri, o)]
         dw = None
         if ctx.needs_input_grad[1]:
-            dwx = _contract_wgrad_local(dt3, t2, plan_in)
-            dw = fold_weight_grad(dwx).reshape(ctx.wshape)
+            dw = fold_weight_grad2(contract_wgrad2(dt3, t2, plan_in.l0, plan_in.m0)).reshape(ctx.wshape)
         dx = None
         if ctx.needs_input_grad[0]:
             if ctx.want_resid and dr is not None:
@@ -380,19 +379,6 @@ class _DistSpectralConv(torch.autograd.Function):
                 slot, t3v, ls = stage_contract(dt3, wx, True, plan_in)
             dx = dist_sht_synthesis(slot, t3v, ls, False, plan_in, B, C, plan_in.pw_syn, plan_in.ft_syn)
         return dx, dw, None, None, None
-
-
-def _contract_wgrad_local(dt: torch.Tensor, t2: torch.Tensor, plan: DistSHTPlan) -> torch.Tensor:
-    """dWx[l_loc, q, p] = sum_{b, m_loc <= l} dT[b, l, m, q] T2[b, l, m, p]  (fp32; partial over the "w" group)."""
-    B, ll, ml, nq = dt.shape
-    npp = t2.shape[3]
-    dwx = (torch.empty if B == 1 else torch.zeros)(ll, nq, npp, dtype=torch.float32, device=dt.device)
-    gemm(nq, npp, ml,
-         Operand(dt, ld=nq, mn_major=True, zs_hi=ml * nq, zs_lo=ll * ml * nq),
-         Operand(t2, ld=npp, mn_major=True, zs_hi=ml * npp, zs_lo=ll * ml * npp),
-         Output(dwx, rs_lo=npp, d_zhi=nq * npp),
-         zhi_n=ll, zlo_n=B, accumulate=(B > 1), tri=Tri(kmax_a=1, kmax_b=1 + plan.l0 - plan.m0))
-    return dwx
 
 
 def dist_spectral_conv_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
