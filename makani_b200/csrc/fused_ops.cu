@@ -367,13 +367,20 @@ __global__ void __launch_bounds__(CL_THREADS) inorm_cl_sums_kernel(const __nv_bf
     }
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < 2 * C; i += CL_THREADS) {
-    const float val = sh_acc[i];
-    atomicAdd(sums + static_cast<long long>(bidx) * 2 * C + i, val);
+  // one 16-byte vector atomic per two channels (C is a multiple of 8, the buffer is 16-byte aligned)
+  for (int i = threadIdx.x * 4; i < 2 * C; i += CL_THREADS * 4) {
+    const float4 val = *reinterpret_cast<const float4*>(sh_acc + i);
+    atomicAdd(reinterpret_cast<float4*>(sums + static_cast<long long>(bidx) * 2 * C + i), val);
     if (MODE == 1) {
       const int c = i >> 1;
-      if ((i & 1) && dw) atomicAdd(dw + c, val);
-      if (!(i & 1) && db) atomicAdd(db + c, val);
+      if (db) {
+        atomicAdd(db + c, val.x);
+        atomicAdd(db + c + 1, val.z);
+      }
+      if (dw) {
+        atomicAdd(dw + c, val.y);
+        atomicAdd(dw + c + 1, val.w);
+      }
     }
   }
   if (xc.npeers > 0) {
@@ -829,9 +836,9 @@ cudaError_t inorm_bwd(const __nv_bfloat16* x, const __nv_bfloat16* dy, __nv_bflo
 
 static inline bool cl_ok(int C) { return C % 8 == 0 && C >= 8 && C <= 1024 && (CL_THREADS / (C / 8)) >= 1; }
 // tokens per CTA: enough CTAs to fill the machine a few times over, but at least a few passes of the row loop each
-static inline int cl_slab(int C, long long T, int B) {
+static inline int cl_slab(int C, long long T, int B, int ctas_per_sm = 4) {
   const int R = CL_THREADS / (C / 8);
-  long long target = (4LL * 148 + B - 1) / B;
+  long long target = (static_cast<long long>(ctas_per_sm) * 148 + B - 1) / B;
   long long slab = (T + target - 1) / target;
   if (slab < 4LL * R) slab = 4LL * R;
   return static_cast<int>(slab);
@@ -844,7 +851,8 @@ cudaError_t inorm_cl_sums(const __nv_bfloat16* x, const __nv_bfloat16* dy, const
   StatExchange xc;
   memset(&xc, 0, sizeof(xc));
   if (xch) xc = *xch;
-  const int slab = cl_slab(C, T, B);
+  // every CTA ends with 2C atomics on the same [B, C, 2] words: fewer, longer CTAs than the streaming pass
+  const int slab = cl_slab(C, T, B, 2);
   dim3 grid(static_cast<unsigned>((T + slab - 1) / slab), B);
   const size_t sh = 2 * C * sizeof(float);
   if (mode == 0) inorm_cl_sums_kernel<0><<<grid, CL_THREADS, sh, s>>>(x, dy, w, b, stats, sums, dw, db, C, T, act, slab, xc);
