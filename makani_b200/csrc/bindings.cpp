@@ -128,6 +128,23 @@ void gemm_peer(const Tensor& a, const Tensor& b, Tensor& d, const c10::optional<
   gemm_impl(a, b, d, bias, resid, preact, ip, alpha, &g);
 }
 
+// out (bf16, contiguous in memory) = sum of the segments at `srcs` (+ bias over the innermost `C` channels)
+void peer_sum(Tensor& out, const std::vector<int64_t>& srcs, const c10::optional<Tensor>& bias, int64_t C,
+              const std::vector<int64_t>& sync) {
+  MK_CHECK(out.is_cuda() && out.scalar_type() == torch::kBFloat16, "peer_sum: bf16 CUDA output expected");
+  MK_CHECK(!srcs.empty() && srcs.size() <= 8, "peer_sum: 1..8 segments");
+  mk::GemmPeer g;
+  parse_peer(g, {}, sync);
+  c10::cuda::CUDAGuard guard(out.device());
+  Tensor ef = err_flag_for(out);
+  const void* sp[8];
+  for (size_t q = 0; q < srcs.size(); ++q) sp[q] = reinterpret_cast<const void*>(srcs[q]);
+  const float* bp = (bias.has_value() && bias->defined()) ? bias->data_ptr<float>() : nullptr;
+  check_cuda(mk::peer_sum_launch(out.data_ptr(), out.numel(), sp, static_cast<int>(srcs.size()), bp, static_cast<int>(C), g,
+                                 ef.data_ptr<int>(), cur_stream()),
+             "peer_sum");
+}
+
 // src: local tensor whose data pointer is the first row; dsts: device addresses (this rank's copy and its peers')
 void peer_publish(const Tensor& src, int64_t rows, int64_t row_bytes, int64_t src_stride_bytes, int64_t dst_stride_bytes,
                   const std::vector<int64_t>& dsts, const std::vector<int64_t>& sync) {
@@ -439,6 +456,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, "tcgen05 GEMM with fused epilogue");
   m.def("gemm_peer", &gemm_peer, "tcgen05 GEMM reading its B operand from peer devices");
   m.def("peer_sync", &peer_sync);
+  m.def("peer_sum", &peer_sum, "sum of the local segments of a peer buffer with the consumer handshake");
   m.def("peer_publish", &peer_publish, "strided copy into this rank's and its peers' buffers with the producer handshake");
   m.def("read_error_flag", &read_error_flag);
   m.def("clear_error_flag", &clear_error_flag);

@@ -1005,6 +1005,78 @@ __global__ void __launch_bounds__(256) peer_publish_kernel(const uint4* __restri
   }
 }
 
+// out = sum over `nsrc` local segments (+ per-channel bias), 8 bf16 per thread step, with the consumer side of the
+// handshake folded in: every block waits until all peers have delivered their segment, the last block to finish tells
+// the peers that the buffer may be overwritten.  The second signal list carries the segment base pointers.
+__global__ void __launch_bounds__(256) peer_sum_kernel(uint4* __restrict__ out, long long nvec, int nsrc,
+                                                       const float* __restrict__ bias, int C, const PeerSync sy, int* err) {
+  __shared__ int ok_s;
+  if (threadIdx.x == 0) {
+    bool ok = true;
+    for (int w = 0; w < sy.nwait && ok; ++w) {
+      const unsigned int need = *sy.wait_exp[w] + static_cast<unsigned int>(sy.wait_off[w]);
+      for (int peer = 0; peer < sy.np_wait[w] && ok; ++peer) {
+        uint64_t t0 = 0;
+        for (uint32_t it = 0;; ++it) {
+          if (static_cast<int>(ld_acquire_sys_u32(sy.wait[w] + peer) - need) >= 0) break;
+          if ((it & 255u) == 255u) {
+            const uint64_t now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_LIMIT_NS) {
+              atomicExch(err, 44 + w);
+              ok = false;
+              break;
+            }
+          }
+        }
+      }
+    }
+    ok_s = ok ? 1 : 0;
+  }
+  __syncthreads();
+  if (ok_s) {
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      if (bias) {
+        const int c0 = static_cast<int>((i * 8) % C);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = __ldg(bias + c0 + j);
+      }
+      for (int q = 0; q < nsrc; ++q) {
+        // L1 is bypassed: peers rewrite these buffers between launches
+        const uint4 v = __ldcg(reinterpret_cast<const uint4*>(sy.sig[1][q]) + i);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(h[j]);
+          acc[2 * j] += f.x;
+          acc[2 * j + 1] += f.y;
+        }
+      }
+      __nv_bfloat162 o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+      out[i] = *reinterpret_cast<uint4*>(o);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && sy.done_ctr != nullptr) {
+    __threadfence_system();
+    const unsigned int prev = atomicAdd(sy.done_ctr, 1u);
+    if (prev == gridDim.x - 1) {
+      *sy.done_ctr = 0;
+      for (int i = 0; i < sy.nwait; ++i)
+        if (sy.bump[i]) atomicAdd(sy.bump[i], 1u);
+      __threadfence_system();
+      for (int peer = 0; peer < sy.np_sig[0]; ++peer)
+        if (sy.sig[0][peer]) atomicAdd_system(sy.sig[0][peer], 1u);
+    }
+  }
+}
+
 void fill_sync(PeerSync& sy, const GemmPeer* g) {
   memset(&sy, 0, sizeof(sy));
   if (!g) return;
@@ -1051,6 +1123,25 @@ cudaError_t peer_publish_launch(const void* src, long long rows, long long row_b
   peer_publish_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
       static_cast<const uint4*>(src), rows, static_cast<int>(row_bytes / 16), src_stride_bytes / 16, dst_stride_bytes / 16,
       ndst, sy, err_flag);
+  return cudaGetLastError();
+}
+
+cudaError_t peer_sum_launch(void* out, long long n_elems, const void* const* srcs, int nsrc, const float* bias, int C,
+                            const GemmPeer& g, int* err_flag, cudaStream_t stream) {
+  if (n_elems <= 0) return cudaSuccess;
+  if ((n_elems & 7) || nsrc < 1 || nsrc > MAX_SEG || g.nsig > 1 || (reinterpret_cast<uintptr_t>(out) & 15) ||
+      (bias && (C <= 0 || (C & 7))))
+    return cudaErrorInvalidValue;
+  PeerSync sy;
+  fill_sync(sy, &g);
+  for (int q = 0; q < MAX_SEG; ++q) {
+    if (q < nsrc && (reinterpret_cast<uintptr_t>(srcs[q]) & 15)) return cudaErrorInvalidValue;
+    sy.sig[1][q] = q < nsrc ? static_cast<unsigned int*>(const_cast<void*>(srcs[q])) : nullptr;
+  }
+  const long long nvec = n_elems / 8;
+  long long blocks = (nvec + 255) / 256;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  peer_sum_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(static_cast<uint4*>(out), nvec, nsrc, bias, C, sy, err_flag);
   return cudaGetLastError();
 }
 

@@ -79,6 +79,11 @@ cudaError_t peer_publish_launch(const void* src, long long rows, long long row_b
                                 long long dst_stride_bytes, void* const* dsts, int ndst, const GemmPeer& g, int* err_flag,
                                 cudaStream_t stream);
 
+// out[i] = sum_q srcs[q][i] (+ bias[i % C]) over `n_elems` bf16 values (multiple of 8), reading `nsrc` local segments that
+// peers have filled; consumer side of the handshake in `g` (wait list 0, signal list 0) executed by the same kernel.
+cudaError_t peer_sum_launch(void* out, long long n_elems, const void* const* srcs, int nsrc, const float* bias, int C,
+                            const GemmPeer& g, int* err_flag, cudaStream_t stream);
+
 // Waits (bounded) and/or signals of the same handshake protocol without a GEMM, for buffers produced or consumed by
 // other kernels.  phase 0: wait only; phase 1: bump + signal only.
 cudaError_t peer_sync_launch(const GemmPeer& g, int phase, int* err_flag, cudaStream_t stream);

@@ -95,39 +95,41 @@ def _out(y, lay):
     return Output(y, rs_lo=T, d_zlo=C * T)          # rows = channels
 
 
-def _conv_fwd(x, wq, ci, bias, act, resid, want_preact, out_layout=None):
+def _conv_fwd(x, wq, ci, bias, act, resid, want_preact, out_layout=None, out=None, sync=None, dests=None):
+    """`out` (optional) receives the result instead of a fresh tensor; `sync` / `dests` are handed to the GEMM
+    (handshake descriptor and additional copies of the output buffer in peers' memory)."""
     B, C, H, W = x.shape
     assert C == ci
     T = H * W
     co = wq.shape[0]
     lay = layout_of(x)
     out_layout = out_layout or (layout_of(resid) if resid is not None else default_out_layout(co))
-    y = empty_like_layout(B, co, H, W, out_layout, x.dtype, x.device)
+    y = out if out is not None else empty_like_layout(B, co, H, W, out_layout, x.dtype, x.device)
     pre = torch.empty_like(y) if want_preact else None
     if resid is not None:
         assert layout_of(resid) == out_layout, "residual must have the layout of the output"
     wop = Operand(wq, ld=wq.shape[1])
     if out_layout == CL:
         gemm(T, co, ci, _tok_rows(x, lay), wop, _out(y, CL), zlo_n=B, bias=bias, bias_mode=BIAS_COL, act=act,
-             resid=resid, preact=pre)
+             resid=resid, preact=pre, sync=sync, dests=dests)
     else:
         gemm(co, T, ci, wop, _tok_rows(x, lay), _out(y, NCHW), zlo_n=B, bias=bias, bias_mode=BIAS_ROW, act=act,
-             resid=resid, preact=pre)
+             resid=resid, preact=pre, sync=sync, dests=dests)
     return y, pre
 
 
-def _conv_dgrad(dy, wq, ci, act=ACT_NONE, aux=None, x_layout=None):
+def _conv_dgrad(dy, wq, ci, act=ACT_NONE, aux=None, x_layout=None, out=None, sync=None, dests=None):
     """dX[b, ci, hw] = sum_co W[co, ci] dY[b, co, hw]  (optionally times GELU'(aux)), produced in `x_layout`."""
     B, co, H, W = dy.shape
     T = H * W
     lay = layout_of(dy)
     x_layout = x_layout or (layout_of(aux) if aux is not None else lay)
-    dx = empty_like_layout(B, ci, H, W, x_layout, dy.dtype, dy.device)
+    dx = out if out is not None else empty_like_layout(B, ci, H, W, x_layout, dy.dtype, dy.device)
     wt = Operand(wq, ld=wq.shape[1], mn_major=True)     # rows = ci, K = co
     if x_layout == CL:
-        gemm(T, ci, co, _tok_rows(dy, lay), wt, _out(dx, CL), zlo_n=B, act=act, resid=aux)
+        gemm(T, ci, co, _tok_rows(dy, lay), wt, _out(dx, CL), zlo_n=B, act=act, resid=aux, sync=sync, dests=dests)
     else:
-        gemm(ci, T, co, wt, _tok_rows(dy, lay), _out(dx, NCHW), zlo_n=B, act=act, resid=aux)
+        gemm(ci, T, co, wt, _tok_rows(dy, lay), _out(dx, NCHW), zlo_n=B, act=act, resid=aux, sync=sync, dests=dests)
     return dx
 
 

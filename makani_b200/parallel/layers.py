@@ -122,6 +122,12 @@ class DistributedMatmul(nn.Module):
             self.bias.is_shared_mp = ["spatial", comm_inp_name]
 
     def forward(self, x):
+        if self.input_format == "nchw":
+            from ..ops import matmul_dist
+            w2 = self.weight.reshape(self.weight.shape[0], self.weight.shape[1])
+            if matmul_dist.supported(x, w2, self.comm_inp_name, self.comm_out_name):
+                # tcgen05 GEMM whose epilogue delivers the partial products to the group (no NCCL on this path)
+                return matmul_dist.fused_dist_matmul(x, w2, getattr(self, "bias", None), self.comm_inp_name, self.comm_out_name)
         x_cp = copy_to_parallel_region(x, self.comm_out_name)
         x_loc = self.matmul_handle(x_cp, self.weight.to(x_cp.dtype), bias=None)
         x_out = reduce_from_parallel_region(x_loc, self.comm_inp_name)

@@ -153,6 +153,11 @@ class PeerSlot:
         _ext.require().peer_publish(src, int(rows), int(row_elems) * esz, int(src_stride) * esz, int(dst_stride) * esz,
                                     self.dests(include_self=True), sync_descriptor(produce=self))
 
+    def reduce_into(self, out: torch.Tensor, bias: Optional[torch.Tensor] = None, channels: int = 0) -> None:
+        """out = sum over all ranks' segments (+ bias over the innermost `channels`), consumer handshake included.
+        `out` must be bf16 and dense in memory in the order of the segments' contents."""
+        _ext.require().peer_sum(out, self.sources(), bias, int(channels), sync_descriptor(consume=self))
+
     def close(self):
         self.buf.close()
 
@@ -217,6 +222,17 @@ class GatherSlot:
         flat_src = src.reshape(-1) if src.is_contiguous() else src.as_strided((src.untyped_storage().nbytes() // src.element_size() - src.storage_offset(),), (1,))
         s = flat_src.as_strided((rows, row_elems), (src_stride, 1))
         self._last.view(-1).as_strided((rows, row_elems), (dst_stride, 1)).copy_(s)
+
+    def reduce_into(self, out, bias=None, channels=0) -> None:
+        parts = self.sources()
+        acc = parts[0].float()
+        for p in parts[1:]:
+            acc = acc + p.float()
+        acc = acc.reshape(-1)
+        if bias is not None:
+            acc = (acc.view(-1, channels) + bias.float().view(1, channels)).reshape(-1)
+        flat = out.permute(0, 2, 3, 1).reshape(-1) if (out.dim() == 4 and not out.is_contiguous()) else out.reshape(-1)
+        flat.copy_(acc.to(out.dtype))
 
     def sources(self):
         t = self._last.contiguous()

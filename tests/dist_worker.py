@@ -314,6 +314,46 @@ def case_peer_instance_norm():
         dist.all_reduce(db, group=comm.get_group("spatial"))
         assert _rel(dw, wr.grad) < 3e-2 and _rel(db, br.grad) < 3e-2, (_rel(dw, wr.grad), _rel(db, br.grad))
 
+def case_fused_matmul():
+    """Channel-parallel 1x1 convolution whose partial products are exchanged by the GEMM epilogue (peer memory) ==
+    the full convolution: forward, input gradient (reduced over the other group), local weight and bias gradients."""
+    from makani_b200.ops import _ext, matmul_dist
+    from makani_b200.parallel.layers import DistributedMatmul
+    assert os.environ.get("MK_DEVICE") == "cuda"
+    dev = torch.device("cuda", comm.get_local_rank())
+    torch.manual_seed(5)
+    B, Ci, Co, H, W = 2, 64, 96, 24, 40
+    x = torch.randn(B, Ci, H, W)
+    w, b = torch.randn(Co, Ci) * 0.1, torch.randn(Co) * 0.1
+    g = torch.randn(B, Co, H, W)
+    nfi, nfo, fi, fo = comm.get_size("fin"), comm.get_size("fout"), comm.get_rank("fin"), comm.get_rank("fout")
+    xr, wr, br = x.clone().requires_grad_(), w.clone().requires_grad_(), b.clone().requires_grad_()
+    y_ref = torch.nn.functional.conv2d(xr, wr.view(Co, Ci, 1, 1), br)
+    y_ref.backward(g)
+    layer = DistributedMatmul(Ci, Co, comm_inp_name="fin", comm_out_name="fout", bias=True).to(dev)
+    w_loc = split_tensor_along_dim(split_tensor_along_dim(w, 0, nfo)[fo], 1, nfi)[fi]
+    with torch.no_grad():
+        layer.weight.copy_(w_loc.reshape(layer.weight.shape))
+        layer.bias.copy_(split_tensor_along_dim(b, 0, nfo)[fo].reshape(layer.bias.shape))
+    cl = lambda t: t.to(dev, torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    for it in range(2):
+        xl = cl(split_tensor_along_dim(x, 1, nfi)[fi]).requires_grad_()
+        gl = cl(split_tensor_along_dim(g, 1, nfo)[fo])
+        assert matmul_dist.supported(xl, layer.weight.reshape(w_loc.shape), "fin", "fout"), "fused path not taken"
+        layer.weight.grad = None
+        layer.bias.grad = None
+        y = layer(xl)
+        y.backward(gl)
+        _ext.check_device_errors(dev)
+        y_want = split_tensor_along_dim(y_ref.detach(), 1, nfo)[fo]
+        assert _rel(y.float().cpu(), y_want) < 2e-2, ("y", _rel(y.float().cpu(), y_want))
+        dx_want = split_tensor_along_dim(xr.grad, 1, nfi)[fi]
+        assert _rel(xl.grad.float().cpu(), dx_want) < 2e-2, ("dx", _rel(xl.grad.float().cpu(), dx_want))
+        dw_want = split_tensor_along_dim(split_tensor_along_dim(wr.grad, 0, nfo)[fo], 1, nfi)[fi]
+        assert _rel(layer.weight.grad.float().cpu().reshape(dw_want.shape), dw_want) < 2e-2
+        db_want = split_tensor_along_dim(br.grad, 0, nfo)[fo]
+        assert _rel(layer.bias.grad.float().cpu().reshape(-1), db_want) < 2e-2
+
 
 if __name__ == "__main__":
     case = sys.argv[1]

@@ -29,3 +29,9 @@ def test_fused_distributed_spectral_conv_4gpu():
 def test_peer_memory_instance_norm(sizes, world):
     _need(world)
     _launch("peer_instance_norm", sizes, world, cuda=True)
+
+
+@pytest.mark.parametrize("sizes,world", [((1, 1, 2, 1), 2), ((1, 1, 1, 2), 2), ((1, 1, 2, 2), 4)])
+def test_fused_channel_parallel_matmul(sizes, world):
+    _need(world)
+    _launch("fused_matmul", sizes, world, cuda=True)
