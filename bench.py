@@ -40,6 +40,9 @@ def parse():
     ap.add_argument("--mode", default="train", choices=["train", "rollout"],
                     help="train: samples/s of the optimisation step (headline); rollout: ms per autoregressive inference step")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying a CUDA graph")
+    ap.add_argument("--model", default="sfno", choices=["sfno", "afno"], help="sfno: the headline model; afno: FourCastNet v1 (720x1440x20)")
+    ap.add_argument("--fin", type=int, default=1, help="input-feature parallel ranks (channel parallelism)")
+    ap.add_argument("--fout", type=int, default=1, help="output-feature parallel ranks")
     ap.add_argument("--h", type=int, default=1, help="latitude-parallel ranks per model instance (default: pure data parallel)")
     ap.add_argument("--w", type=int, default=1, help="longitude-parallel ranks per model instance")
     return ap.parse_args()
@@ -200,7 +203,7 @@ def main():
     assert world == args.gpus or world == 1, f"--gpus {args.gpus} but WORLD_SIZE={world}"
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    comm.init(model_parallel_sizes=[args.h, args.w, 1, 1])
+    comm.init(model_parallel_sizes=[args.h, args.w, args.fin, args.fout])
     native = args.impl == "native"
     if native:
         _ext.require()
@@ -209,7 +212,7 @@ def main():
         torch.backends.cuda.matmul.allow_tf32 = True      # as makani/train.py:109-110
         torch.backends.cudnn.allow_tf32 = True
 
-    cfg = FlagshipConfig(small=args.small, h=args.h, w=args.w, graph=(not args.no_graph) and native, native=native)
+    cfg = FlagshipConfig(small=args.small, h=args.h, w=args.w, graph=(not args.no_graph) and native, native=native, model=args.model)
     runner = build_flagship(cfg, dev)
 
     def barrier():
@@ -274,7 +277,8 @@ def main():
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_per_step = t.item() / args.steps
-    dp = world // (args.h * args.w)
+    mp = args.h * args.w * args.fin * args.fout
+    dp = world // mp
     global_batch = cfg.batch_per_gpu * dp
     value = global_batch / (ms_per_step / 1e3)
     if native:
@@ -288,12 +292,14 @@ def main():
 
     if rank == 0:
         out = {
-            "metric": "SFNO-73ch 721x1440 bf16 train samples/s", "value": value, "unit": "samples/s", "n_gpus": world,
+            "metric": ("SFNO-73ch 721x1440 bf16 train samples/s" if args.model == "sfno" else "AFNO-20ch 720x1440 bf16 train samples/s"),
+            "value": value, "unit": "samples/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": (value / BASELINE_VALUE) if BASELINE_VALUE else None, "dtype": "bf16" if native else "bf16 autocast (fp32 transforms, as the reference)",
             "data": "synthetic N(0,1), random-init weights", "impl": "native" if native else "restated-torch",
             "config": {"model": cfg.name, "global_batch": global_batch, "seq_len": f"{cfg.nlat}x{cfg.nlon}",
-                       "parallelism": f"dp{dp}" + (f"xh{args.h}w{args.w}" if args.h * args.w > 1 else ""), "l2_policy": "inputs+activations per step (>2 GB) exceed the 126 MB L2",
+                       "parallelism": f"dp{dp}" + (f"xh{args.h}w{args.w}" if args.h * args.w > 1 else "")
+                       + (f"xfin{args.fin}fout{args.fout}" if args.fin * args.fout > 1 else ""), "l2_policy": "inputs+activations per step (>2 GB) exceed the 126 MB L2",
                        "loss": cfg.loss, "optimizer": "AdamW (fused)" if native else "torch.optim.AdamW(foreach)",
                        "cuda_graph": bool(cfg.graph), "final_loss": final_loss},
             "clocks": clocks, "gpu_launches": launches,

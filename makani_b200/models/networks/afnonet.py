@@ -193,7 +193,8 @@ class AdaptiveFourierNeuralOperatorNet(nn.Module):
         return x
 
     def forward(self, x):
-        if self.compute_dtype is not None and x.dtype != self.compute_dtype:
+        if self.compute_dtype is not None:
+            # parameters stay fp32; convolutions / linears run in the compute dtype whatever dtype the input has
             with torch.autocast(device_type=x.device.type, dtype=self.compute_dtype):
                 return self._forward(x)
         return self._forward(x)

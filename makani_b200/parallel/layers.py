@@ -128,6 +128,14 @@ class DistributedMatmul(nn.Module):
             if matmul_dist.supported(x, w2, self.comm_inp_name, self.comm_out_name):
                 # tcgen05 GEMM whose epilogue delivers the partial products to the group (no NCCL on this path)
                 return matmul_dist.fused_dist_matmul(x, w2, getattr(self, "bias", None), self.comm_inp_name, self.comm_out_name)
+        elif self.input_format == "traditional" and x.dim() == 4 and x.is_contiguous():
+            # token-major [B, h, w, C] is the channels-last memory layout of a [B, C, h, w] activation
+            from ..ops import matmul_dist
+            xv = x.permute(0, 3, 1, 2)
+            if matmul_dist.supported(xv, self.weight, self.comm_inp_name, self.comm_out_name):
+                y = matmul_dist.fused_dist_matmul(xv, self.weight, getattr(self, "bias", None), self.comm_inp_name,
+                                                  self.comm_out_name)
+                return y.permute(0, 2, 3, 1)
         x_cp = copy_to_parallel_region(x, self.comm_out_name)
         x_loc = self.matmul_handle(x_cp, self.weight.to(x_cp.dtype), bias=None)
         x_out = reduce_from_parallel_region(x_loc, self.comm_inp_name)

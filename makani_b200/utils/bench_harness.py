@@ -37,8 +37,13 @@ class FlagshipConfig:
     w: int = 1              # longitude-parallel ranks
     graph: bool = True      # replay the whole step from one CUDA graph after an eager warm-up
     native: bool = True     # False: the reference's op sequence on stock PyTorch (cuDNN / cuFFT / cuBLAS / ATen / NCCL)
+    model: str = "sfno"     # "sfno" (headline) or "afno" (FourCastNet v1: 720x1440x20, patch 8, embed 768, 12 layers, 8 blocks)
 
     def __post_init__(self):
+        if self.model == "afno":
+            self.name = "afno_20ch_p8_e768_l12_b8"
+            self.nlat, self.nlon, self.in_chans, self.out_chans = 720, 1440, 20, 20
+            self.loss = "l2"
         if self.small:
             self.name += "_small"
             self.nlat, self.nlon = 361, 720
@@ -54,12 +59,25 @@ class FlagshipRunner:
         self.lat0, self.lon0 = sum(lat_shapes[:rh]), sum(lon_shapes[:rw])
         self.hl, self.wl = lat_shapes[rh], lon_shapes[rw]
         torch.manual_seed(0)
-        self.model = SphericalFourierNeuralOperatorNet(
+        if cfg.model == "afno":
+            from ..models.networks.afnonet import AdaptiveFourierNeuralOperatorNet
+            self.model = AdaptiveFourierNeuralOperatorNet(
+                inp_shape=(cfg.nlat, cfg.nlon), patch_size=(8, 8), inp_chans=cfg.in_chans, out_chans=cfg.out_chans, embed_dim=768,
+                num_layers=12, mlp_ratio=4.0, num_blocks=8, sparsity_threshold=0.01, hard_thresholding_fraction=1.0).to(device)
+        else:
+            self.model = self._build_sfno(cfg, device)
+        self._finish_init(cfg, device)
+
+    @staticmethod
+    def _build_sfno(cfg, device):
+        return SphericalFourierNeuralOperatorNet(
             spectral_transform="sht", model_grid_type="equiangular", sht_grid_type="legendre-gauss", filter_type="linear",
             operator_type="dhconv", inp_shape=(cfg.nlat, cfg.nlon), out_shape=(cfg.nlat, cfg.nlon),
             scale_factor=cfg.scale_factor, inp_chans=cfg.in_chans, out_chans=cfg.out_chans, embed_dim=cfg.embed_dim,
             num_layers=cfg.num_layers, use_mlp=True, mlp_ratio=2.0, activation_function="gelu", encoder_layers=1,
             pos_embed="none", normalization_layer="instance_norm", hard_thresholding_fraction=1.0, big_skip=True).to(device)
+
+    def _finish_init(self, cfg, device):
         if cfg.native:
             self.model.set_compute_dtype(torch.bfloat16)
         sync_params(self.model)
@@ -90,7 +108,10 @@ class FlagshipRunner:
         g = torch.Generator(device=self.device)
         g.manual_seed(seed)
         x = torch.randn(cfg.batch_per_gpu, cfg.out_chans, self.hl, self.wl, device=self.device, generator=g)
-        inp = torch.cat([x, self.coslat], dim=1).to(self.io_dtype).contiguous()
+        if cfg.in_chans == cfg.out_chans:
+            inp = x.to(self.io_dtype).contiguous()
+        else:
+            inp = torch.cat([x, self.coslat], dim=1).to(self.io_dtype).contiguous()
         tgt = torch.randn(cfg.batch_per_gpu, cfg.out_chans, self.hl, self.wl, device=self.device, generator=g).to(self.io_dtype)
         return inp, tgt
 
@@ -154,7 +175,7 @@ class FlagshipRunner:
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = t.item() / steps
-        dp = max(1, world // (comm.get_size("h") * comm.get_size("w")))
+        dp = max(1, world // comm.get_size("model"))
         return {"value": cfg.batch_per_gpu * dp / (ms / 1e3), "unit": "samples/s", "ms_per_step": ms,
                 "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4}
 
