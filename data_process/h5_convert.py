@@ -18,11 +18,11 @@ def parse_chunks(spec, shape, itemsize):
     if spec == "none":
         return None
     if spec.endswith("MB"):
-        budget = int(spec[:-2]) * 1024 * 1024
+        limit = int(spec[:-2]) * 1024 * 1024
         per_step = itemsize
         for s in shape[1:]:
             per_step *= s
-        steps = max(1, min(shape[0], budget // max(per_step, 1)))
+        steps = max(1, min(shape[0], limit // max(per_step, 1)))
         return (steps,) + tuple(shape[1:])
     raise ValueError(f"chunksize {spec!r} not supported")
 
