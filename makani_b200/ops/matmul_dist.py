@@ -56,7 +56,7 @@ def _reduced_conv(name, group, run, B, C, H, W, dtype, device, bias=None):
 class _FusedDistMatmul(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, bias, inp_group, out_group):
-        wq = prep_weight(w)
+        wq = prep_weight(w, x.dtype)
         ci, co = w.shape[1], w.shape[0]
         B, _, H, W = x.shape
         bias_f = bias.detach().float().reshape(-1).contiguous() if bias is not None else None

@@ -92,6 +92,8 @@ class FusedAdamW(torch.optim.Optimizer):
                 yield gi, group, plist
 
     def prepare_step(self):
+        from .spectral import note_weights_changed
+        note_weights_changed()      # also covers updates replayed from a CUDA graph, which never re-enter `launch_step`
         self._step_count += 1
         self._prepared = True
         for gi, group, plist in self._groups_with_grads():
@@ -116,6 +118,8 @@ class FusedAdamW(torch.optim.Optimizer):
             ev.record()
 
     def launch_step(self):
+        from .spectral import note_weights_changed
+        note_weights_changed()      # the kernels write parameters through raw pointers: derived caches are stale now
         for gi, group, plist in self._groups_with_grads():
             if plist[0].is_cuda:
                 tb = self._table_for(gi, group, plist)

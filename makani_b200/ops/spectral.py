@@ -215,8 +215,33 @@ def fold_weight_grad2(dw2: torch.Tensor) -> torch.Tensor:
 # ------------------------------------------------------------------------------------------------ weights
 
 
+# Inference re-uses the expanded weights: they are cached per parameter while gradients are disabled and dropped when
+# the parameter is modified in place (`_version`) or by the fused optimiser, which writes through raw pointers and
+# announces every update through `note_weights_changed`.
+_WEIGHT_EPOCH = 0
+_EXPANDED = {}
+
+
+def note_weights_changed() -> None:
+    global _WEIGHT_EPOCH
+    _WEIGHT_EPOCH += 1
+    _EXPANDED.clear()
+
+
 def expand_weight(w: torch.Tensor, dtype=torch.bfloat16) -> torch.Tensor:
     """complex [Ci, Co, L] -> real [L, 2Co, 2Ci] with rows (ri', o), columns (ri, c):  [[Wr, -Wi], [Wi, Wr]]."""
+    if not torch.is_grad_enabled() and w.is_cuda:
+        key = (w.data_ptr(), tuple(w.shape), dtype)
+        hit = _EXPANDED.get(key)
+        if hit is not None and hit[0] == (w._version, _WEIGHT_EPOCH):
+            return hit[1]
+        wx = _expand_weight(w, dtype)
+        _EXPANDED[key] = ((w._version, _WEIGHT_EPOCH), wx)
+        return wx
+    return _expand_weight(w, dtype)
+
+
+def _expand_weight(w: torch.Tensor, dtype=torch.bfloat16) -> torch.Tensor:
     ci, co, L = w.shape
     if w.is_cuda and dtype == torch.bfloat16:
         wx = torch.empty(L, 2 * co, 2 * ci, dtype=dtype, device=w.device)

@@ -95,3 +95,8 @@ def test_spatially_parallel_sfno_matches_serial(sizes):
 @pytest.mark.parametrize("sizes", [(2, 1, 1, 1), (1, 2, 1, 1), (2, 2, 1, 1), (3, 1, 1, 1)])
 def test_fused_distributed_spectral_conv(sizes):
     _launch("fused_spectral", sizes, sizes[0] * sizes[1])
+
+
+@pytest.mark.parametrize("sizes", [(1, 1, 2, 1), (1, 1, 1, 2), (1, 1, 2, 2)])
+def test_fused_channel_parallel_matmul_algebra(sizes):
+    _launch("fused_matmul", sizes, sizes[2] * sizes[3])
