@@ -94,3 +94,31 @@ def test_h5_convert_chunk_parser():
     assert h5_convert.parse_chunks("1MB", (2000, 4, 8, 8), 4) == (1024, 4, 8, 8)
     with pytest.raises(ValueError):
         h5_convert.parse_chunks("7", (1, 1, 1, 1), 4)
+
+
+@pytest.mark.parametrize("shape", [(20, 101), (721, 1440)])
+@pytest.mark.parametrize("rule", ["naive", "clenshaw-curtiss", "legendre-gauss"])
+def test_quadrature_weights_integrate_to_one(rule, shape):
+    from makani_b200.utils.grids import GridQuadrature
+    quad = GridQuadrature(rule, shape, normalize=True)
+    ones = torch.ones(1, 1, *shape)
+    assert abs(float(quad(ones)) - 1.0) < 1e-5
+
+
+def test_registry_lists_every_network_family_and_registers_custom_models():
+    from makani_b200.models import model_registry as reg
+    names = set(reg.list_models())
+    assert {"AFNOv1", "AFNO", "FNO", "SFNO", "DebugNet", "ViT"} <= names
+
+    class Tiny(torch.nn.Module):
+        def __init__(self, inp_shape=(8, 16), inp_chans=2, out_chans=2, **kw):
+            super().__init__()
+            self.c = torch.nn.Conv2d(inp_chans, out_chans, 1)
+
+        def forward(self, x):
+            return self.c(x)
+
+    reg.register_model(Tiny, "TinyTestNet")
+    assert "TinyTestNet" in reg.list_models()
+    with pytest.raises(Exception):
+        reg.register_model(Tiny, "TinyTestNet")      # names are unique
