@@ -122,3 +122,34 @@ def test_registry_lists_every_network_family_and_registers_custom_models():
     assert "TinyTestNet" in reg.list_models()
     with pytest.raises(Exception):
         reg.register_model(Tiny, "TinyTestNet")      # names are unique
+
+
+def test_era5_time_axis_and_labelled_year(tmp_path):
+    import datetime
+    sys.path.insert(0, ROOT)
+    from datasets.era5 import open_year, time as era5_time
+    assert era5_time.filename_to_year("/data/out_of_sample/2018.h5") == 2018
+    rng = era5_time.datetime_range(2018, datetime.timedelta(hours=6), 5)
+    assert rng[0] == datetime.datetime(2018, 1, 1, tzinfo=datetime.timezone.utc) and (rng[4] - rng[0]).total_seconds() == 24 * 3600
+    arr = np.random.rand(6, 3, 5, 8).astype(np.float32)
+    np.save(tmp_path / "2017.npy", arr)
+    meta = tmp_path / "data.json"
+    meta.write_text('{"h5_path": "fields", "dhours": 6, "attrs": {"description": "t"}, "coords": {"grid_type": "equiangular", '
+                    '"lat": [2, 1, 0, -1, -2], "lon": [0, 1, 2, 3, 4, 5, 6, 7], "channel": ["a", "b", "c"]}}')
+    ya = open_year(str(tmp_path / "2017.npy"), metadata_path=str(meta))
+    assert tuple(ya.shape) == arr.shape and tuple(ya.dims) == ("time", "channel", "lat", "lon")
+    np.testing.assert_array_equal(np.asarray(ya[2]), arr[2])
+    assert len(ya.coords["time"]) == 6 and list(ya.coords["channel"]) == ["a", "b", "c"]
+
+
+def test_copernicus_request_plan():
+    sys.path.insert(0, ROOT)
+    from datasets.copernicus import get_data
+    jobs = get_data.plan("/out", [2019], [500, 850], 0.25, 6)
+    assert len(jobs) == 12 * 3
+    fname, req = jobs[0]
+    assert fname == "/out/raw/pl_500_2019-01.nc" and req["levtype"] == "pl" and req["levelist"] == "500"
+    assert req["time"] == ["00:00", "06:00", "12:00", "18:00"] and req["date"] == "2019-01-01/to/2019-01-31"
+    assert jobs[2][0] == "/out/raw/sfc_2019-01.nc" and jobs[2][1]["param"] == get_data.SFC_PARAMS
+    feb = [r for f, r in jobs if f.endswith("sfc_2019-02.nc")][0]
+    assert feb["date"].endswith("2019-02-28")
