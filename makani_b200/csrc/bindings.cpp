@@ -392,6 +392,16 @@ void spectral_fold(const Tensor& dwx, Tensor& dw, bool two_block, bool assign) {
              "spectral_fold");
 }
 
+void swap_ri(const Tensor& x, Tensor& y, int64_t C) {
+  MK_CHECK(x.is_cuda() && x.is_contiguous() && y.is_contiguous() && x.numel() == y.numel(), "swap_ri: bad tensors");
+  MK_CHECK(x.scalar_type() == torch::kBFloat16 && y.scalar_type() == torch::kBFloat16, "swap_ri: bf16 expected");
+  MK_CHECK(C > 0 && x.numel() % (2 * C) == 0, "swap_ri: the innermost extent must be (2, C)");
+  c10::cuda::CUDAGuard guard(x.device());
+  check_cuda(mk::swap_ri_bf16(reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), reinterpret_cast<__nv_bfloat16*>(y.data_ptr()),
+                              x.numel() / (2 * C), static_cast<int>(C), cur_stream()),
+             "swap_ri");
+}
+
 void cast_bf16(const Tensor& x, Tensor& y) {
   MK_CHECK(x.is_cuda() && x.is_contiguous() && y.is_contiguous() && x.numel() == y.numel(), "cast_bf16: bad tensors");
   MK_CHECK(x.scalar_type() == torch::kFloat32 && y.scalar_type() == torch::kBFloat16, "cast_bf16: fp32 -> bf16");
@@ -477,6 +487,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("spectral_expand", &spectral_expand);
   m.def("spectral_fold", &spectral_fold, py::arg("dwx"), py::arg("dw"), py::arg("two_block") = false, py::arg("assign") = false);
   m.def("cast_bf16", &cast_bf16);
+  m.def("swap_ri", &swap_ri, "rows of (re, im) -> (im, -re)");
   m.def("fill_normal", &fill_normal);
   m.def("peer_alloc", &peer_alloc);
   m.def("peer_open", &peer_open);

@@ -772,6 +772,26 @@ __global__ void spectral_fold_kernel(const float* __restrict__ dwx, float2* __re
   }
 }
 
+// rows of (re[C], im[C]) bf16 -> (im[C], -re[C]); C a multiple of 8 (16-byte vectors, sign flip on the bit pattern)
+__global__ void swap_ri_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, long long rows, int cv) {
+  const long long total = rows * 2 * cv;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long row = i / (2 * cv);
+    const int j = static_cast<int>(i - row * 2 * cv);
+    if (j < cv) {
+      out[i] = in[row * 2 * cv + cv + j];
+    } else {
+      uint4 v = in[row * 2 * cv + (j - cv)];
+      v.x ^= 0x80008000u;
+      v.y ^= 0x80008000u;
+      v.z ^= 0x80008000u;
+      v.w ^= 0x80008000u;
+      out[i] = v;
+    }
+  }
+}
+
 __global__ void cast_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ y, long long n) {
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<long long>(gridDim.x) * blockDim.x)
@@ -927,6 +947,18 @@ cudaError_t spectral_expand(const float* w, __nv_bfloat16* wx, int Cin, int Cout
 cudaError_t spectral_fold(const float* dwx, float* dw, int Cin, int Cout, int L, cudaStream_t s, int two_block, int assign) {
   dim3 grid((Cin + 31) / 32, Cout, (L + 31) / 32), block(32, 8);
   spectral_fold_kernel<<<grid, block, 0, s>>>(dwx, reinterpret_cast<float2*>(dw), Cin, Cout, L, two_block, assign);
+  return cudaGetLastError();
+}
+
+cudaError_t swap_ri_bf16(const __nv_bfloat16* in, __nv_bfloat16* out, long long rows, int C, cudaStream_t s) {
+  if (rows <= 0) return cudaSuccess;
+  if (C <= 0 || (C & 7) || (reinterpret_cast<uintptr_t>(in) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
+    return cudaErrorInvalidValue;
+  const long long total = rows * 2 * (C / 8);
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  swap_ri_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(reinterpret_cast<const uint4*>(in), reinterpret_cast<uint4*>(out),
+                                                               rows, C / 8);
   return cudaGetLastError();
 }
 

@@ -88,6 +88,9 @@ cudaError_t spectral_expand(const float* w, __nv_bfloat16* wx, int Cin, int Cout
 cudaError_t spectral_fold(const float* dwx, float* dw, int Cin, int Cout, int L, cudaStream_t s, int two_block = 0,
                           int assign = 0);
 
+// rows of (re[C], im[C]) -> (im[C], -re[C]) (bf16, C % 8 == 0): the operand of the imaginary-part weight gradient
+cudaError_t swap_ri_bf16(const __nv_bfloat16* in, __nv_bfloat16* out, long long rows, int C, cudaStream_t s);
+
 // ---- small elementwise helpers ----
 cudaError_t cast_f32_bf16(const float* x, __nv_bfloat16* y, long long n, cudaStream_t s);
 cudaError_t fill_normal_bf16(__nv_bfloat16* y, long long n, uint64_t seed, cudaStream_t s);

@@ -189,8 +189,12 @@ def contract_wgrad2(dt: torch.Tensor, t2: torch.Tensor, l0: int = 0, m0: int = 0
     with its parts swapped and one sign flipped.  `l0`, `m0`: global offsets of the local (l, m) block."""
     B, L, M, nq = dt.shape
     co, ci = nq // 2, t2.shape[3] // 2
-    d5 = dt.view(B, L, M, 2, co)
-    dts = torch.cat([d5[..., 1:2, :], -d5[..., 0:1, :]], dim=-2).contiguous()
+    if dt.is_cuda and dt.dtype == torch.bfloat16 and co % 8 == 0 and dt.is_contiguous() and _ext.native():
+        dts = torch.empty_like(dt)
+        _ext.require().swap_ri(dt, dts, co)
+    else:
+        d5 = dt.view(B, L, M, 2, co)
+        dts = torch.cat([d5[..., 1:2, :], -d5[..., 0:1, :]], dim=-2).contiguous()
     out = (torch.empty if B == 1 else torch.zeros)(2, L, co, ci, dtype=torch.float32, device=dt.device)
     tri = Tri(kmax_a=2, kmax_b=2 * (1 + l0 - m0))
     for part, a in enumerate((dt, dts)):

@@ -400,3 +400,28 @@ def test_sfno_bf16_vs_fp32_reference():
             continue
         assert _rel(g, r) < 0.15, n
     _ext.check_device_errors(dev)
+
+
+def test_swap_ri_and_two_block_weight_gradient():
+    """(re, im) -> (im, -re) re-layout and the (dWr, dWi) GEMM pair against the complex einsum they implement."""
+    from makani_b200.ops.spectral import contract_wgrad2, fold_weight_grad2
+    dev = _dev()
+    torch.manual_seed(21)
+    B, L, M, Co, Ci = 2, 12, 12, 16, 24
+    dt = torch.randn(B, L, M, 2 * Co, device=dev).to(torch.bfloat16)
+    t2 = torch.randn(B, L, M, 2 * Ci, device=dev).to(torch.bfloat16)
+    out = torch.empty_like(dt)
+    _ext.require().swap_ri(dt, out, Co)
+    d5 = dt.view(B, L, M, 2, Co)
+    want = torch.cat([d5[..., 1:2, :], -d5[..., 0:1, :]], dim=-2).reshape(dt.shape)
+    assert torch.equal(out, want)
+    # zero the (l, m) pairs with m > l, as the Legendre stages do
+    mask = (torch.arange(M, device=dev)[None, :] <= torch.arange(L, device=dev)[:, None]).view(1, L, M, 1)
+    dtm, t2m = dt * mask, t2 * mask
+    dw = fold_weight_grad2(contract_wgrad2(dtm.contiguous(), t2m.contiguous()))            # complex [Ci, Co, L]
+    dtc = torch.complex(dtm[..., :Co].float(), dtm[..., Co:].float())                     # [B, L, M, Co]
+    t2c = torch.complex(t2m[..., :Ci].float(), t2m[..., Ci:].float())
+    # y = W x  =>  dL/dW = sum conj(x) dy in torch's convention for complex parameters
+    ref = torch.einsum("blmo,blmc->col", dtc, t2c.conj())
+    assert _rel(torch.view_as_real(dw), torch.view_as_real(ref)) < 2e-2
+    _ext.check_device_errors(dev)
