@@ -333,7 +333,7 @@ class Trainer:
                 self.train_sampler.set_epoch(epoch)
             if hasattr(self.train_dataloader, "set_epoch"):
                 self.train_dataloader.set_epoch(epoch)
-            self.epoch = epoch
+            self.epoch = epoch + 1          # epochs started so far: a checkpoint written below resumes at the next one
             t0 = time.time()
             train_time, train_data_gb, train_logs = self.train_one_epoch()
             valid_logs = {"base": {}, "metrics": {}}
