@@ -112,3 +112,26 @@ def test_autoregression_self_test_with_debugnet(tmp_path):
     p = _params(tmp_path, nettype="DebugNet", n_history=1, valid_autoreg_steps=2, skip_validation=True, save_checkpoint="none")
     t = Trainer(p, 0)
     assert t.test_autoregression_pipeline()
+
+
+def test_model_package_round_trip(tmp_path):
+    """A finished run can be reloaded from its experiment directory alone and reproduces the trained model's output."""
+    import datetime
+    from makani_b200.models.model_package import LocalPackage, load_model_package
+    p = _params(tmp_path, add_zenith=True)
+    trainer = Trainer(p, 0)
+    trainer.train()
+    exp = p.experiment_dir
+    for name in ("config.json", "metadata.json", "global_means.npy", "global_stds.npy"):
+        assert os.path.isfile(os.path.join(exp, name)), name
+    wrapped = load_model_package(LocalPackage(exp), pretrained=True, device="cpu")
+    torch.manual_seed(0)
+    x = torch.randn(1, len(p.in_channels), p.img_shape_x, p.img_shape_y)
+    t = datetime.datetime(2018, 3, 1, 6, tzinfo=datetime.timezone.utc)
+    with torch.no_grad():
+        y = wrapped(x, t)
+    assert y.shape == (1, len(p.out_channels), p.img_shape_x, p.img_shape_y) and torch.isfinite(y).all()
+    # same weights as the trainer's best checkpoint
+    best = ckpt.load_file(p.best_checkpoint_path.format(mp_rank=0))["model_state"]
+    for k, v in wrapped.model.state_dict().items():
+        assert torch.equal(v, best[k.replace("module.", "")]), k
