@@ -425,3 +425,42 @@ def test_swap_ri_and_two_block_weight_gradient():
     ref = torch.einsum("blmo,blmc->col", dtc, t2c.conj())
     assert _rel(torch.view_as_real(dw), torch.view_as_real(ref)) < 2e-2
     _ext.check_device_errors(dev)
+
+
+def test_graphed_train_step_matches_eager_steps():
+    """Forward + backward + fused AdamW replayed from one CUDA graph follow the same trajectory as eager launches
+    (changing learning rate included: hyper-parameters are uploaded outside the graph)."""
+    from makani_b200.models.networks.sfnonet import SphericalFourierNeuralOperatorNet as SFNO
+    from makani_b200.ops.optim import FusedAdamW
+    from makani_b200.parallel.grad_reduce import GradReducer
+    from makani_b200.utils.train_step import GraphedTrainStep, TrainStep
+    dev = _dev()
+
+    def run(cls):
+        torch.manual_seed(5)
+        m = SFNO(inp_shape=(33, 64), out_shape=(33, 64), scale_factor=2, inp_chans=8, out_chans=8, embed_dim=16, num_layers=2).to(dev)
+        m.set_compute_dtype(torch.bfloat16)
+        red = GradReducer(m)
+        opt = FusedAdamW(m.parameters(), lr=1e-3)
+        step = cls(m, lambda p, t, i: (p.float() - t.float()).square().mean(), opt, red)
+        g = torch.Generator(device=dev).manual_seed(9)
+        losses = []
+        for it in range(7):
+            x = torch.randn(2, 8, 33, 64, device=dev, generator=g).to(torch.bfloat16)
+            t = torch.randn(2, 8, 33, 64, device=dev, generator=g).to(torch.bfloat16)
+            for grp in opt.param_groups:
+                grp["lr"] = 1e-3 * (0.5 if it >= 5 else 1.0)
+            losses.append(float(step(x, t)))
+        torch.cuda.synchronize()
+        return losses, [p.detach().clone() for p in m.parameters()], step
+
+    le, pe, _ = run(TrainStep)
+    lg, pg, gs = run(GraphedTrainStep)
+    assert gs.graph is not None, "the step was not captured"
+    for a, b in zip(le, lg):
+        assert abs(a - b) < 2e-2 * max(1.0, abs(a)), (le, lg)
+    num = sum(float((torch.view_as_real(a) if a.is_complex() else a).sub(torch.view_as_real(b) if b.is_complex() else b).square().sum())
+              for a, b in zip(pe, pg))
+    den = sum(float((torch.view_as_real(a) if a.is_complex() else a).square().sum()) for a in pe)
+    assert (num / den) ** 0.5 < 2e-2
+    _ext.check_device_errors(dev)
