@@ -94,15 +94,6 @@ static bool parse_peer(mk::GemmPeer& g, const std::vector<int64_t>& seg, const s
   return !seg.empty() || !sync.empty();
 }
 
-void peer_sync(const std::vector<int64_t>& sync, int64_t phase, int64_t device) {
-  mk::GemmPeer g;
-  parse_peer(g, {}, sync);
-  c10::cuda::CUDAGuard guard(c10::Device(c10::kCUDA, static_cast<int>(device)));
-  Tensor dummy = torch::empty({1}, torch::dtype(torch::kUInt8).device(torch::kCUDA, static_cast<int>(device)));
-  Tensor ef = err_flag_for(dummy);
-  check_cuda(mk::peer_sync_launch(g, static_cast<int>(phase), ef.data_ptr<int>(), cur_stream()), "peer_sync");
-}
-
 void gemm_impl(const Tensor& a, const Tensor& b, Tensor& d, const c10::optional<Tensor>& bias,
                const c10::optional<Tensor>& resid, const c10::optional<Tensor>& preact, const std::vector<int64_t>& ip,
                double alpha, const mk::GemmPeer* peer);
@@ -465,7 +456,6 @@ void peer_allreduce(const std::vector<int64_t>& data_ptrs, const std::vector<int
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, "tcgen05 GEMM with fused epilogue");
   m.def("gemm_peer", &gemm_peer, "tcgen05 GEMM reading its B operand from peer devices");
-  m.def("peer_sync", &peer_sync);
   m.def("peer_sum", &peer_sum, "sum of the local segments of a peer buffer with the consumer handshake");
   m.def("peer_publish", &peer_publish, "strided copy into this rank's and its peers' buffers with the producer handshake");
   m.def("read_error_flag", &read_error_flag);

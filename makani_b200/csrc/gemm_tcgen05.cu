@@ -715,6 +715,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
               for (int dq = 0; dq < p.ndx; ++dq)
                 *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.Dx[dq]) + off) = *reinterpret_cast<uint4*>(h);
             }
+          } else if (full && p.vec_ok && p.accumulate && p.out_f32 && !p.preact && p.act == 0) {
+            // ---- split-k / batch accumulation in fp32: two 16-byte vector atomics instead of eight scalar ones
+            float4* o = reinterpret_cast<float4*>(static_cast<float*>(p.D) + off);
+            atomicAdd(o, make_float4(f[0], f[1], f[2], f[3]));
+            atomicAdd(o + 1, make_float4(f[4], f[5], f[6], f[7]));
           } else {
             // ---- scalar path (ragged edge, unaligned layouts, atomic accumulation)
 #pragma unroll
@@ -917,36 +922,6 @@ bool make_map_e(CUtensorMap* map, const void* ptr, int M, int N, long long row_s
 const char* gemm_last_error() { return g_err; }
 
 namespace {
-__global__ void peer_sync_kernel(const PeerSync sy, int phase, int* err) {
-  if (threadIdx.x != 0 || blockIdx.x != 0) return;
-  if (phase == 0) {
-    for (int w = 0; w < sy.nwait; ++w) {
-      const unsigned int need = *sy.wait_exp[w] + static_cast<unsigned int>(sy.wait_off[w]);
-      for (int peer = 0; peer < sy.np_wait[w]; ++peer) {
-        uint64_t t0 = 0;
-        for (uint32_t it = 0;; ++it) {
-          if (static_cast<int>(ld_acquire_sys_u32(sy.wait[w] + peer) - need) >= 0) break;
-          if ((it & 255u) == 255u) {
-            const uint64_t now = global_ns();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > WAIT_LIMIT_NS) {
-              atomicExch(err, 48 + w);
-              return;
-            }
-          }
-        }
-      }
-    }
-  } else {
-    for (int i = 0; i < sy.nwait; ++i)
-      if (sy.bump[i]) atomicAdd(sy.bump[i], 1u);
-    __threadfence_system();
-    for (int i = 0; i < sy.nsig; ++i)
-      for (int peer = 0; peer < sy.np_sig[i]; ++peer)
-        if (sy.sig[i][peer]) atomicAdd_system(sy.sig[i][peer], 1u);
-  }
-}
-
 // Copies `rows` rows of `row_bytes` (multiple of 16) from local memory into the same place of up to 8 destination
 // buffers (this device's and its peers'), with the producer handshake folded in: every block waits until all
 // peers have consumed the previous contents, the last block to finish publishes the new generation.
@@ -1096,13 +1071,6 @@ void fill_sync(PeerSync& sy, const GemmPeer* g) {
   sy.done_ctr = g->done_ctr;
 }
 }  // namespace
-
-cudaError_t peer_sync_launch(const GemmPeer& g, int phase, int* err_flag, cudaStream_t stream) {
-  PeerSync sy;
-  fill_sync(sy, &g);
-  peer_sync_kernel<<<1, 32, 0, stream>>>(sy, phase, err_flag);
-  return cudaGetLastError();
-}
 
 cudaError_t peer_publish_launch(const void* src, long long rows, long long row_bytes, long long src_stride_bytes,
                                 long long dst_stride_bytes, void* const* dsts, int ndst, const GemmPeer& g, int* err_flag,

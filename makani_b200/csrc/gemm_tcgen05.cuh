@@ -84,10 +84,6 @@ cudaError_t peer_publish_launch(const void* src, long long rows, long long row_b
 cudaError_t peer_sum_launch(void* out, long long n_elems, const void* const* srcs, int nsrc, const float* bias, int C,
                             const GemmPeer& g, int* err_flag, cudaStream_t stream);
 
-// Waits (bounded) and/or signals of the same handshake protocol without a GEMM, for buffers produced or consumed by
-// other kernels.  phase 0: wait only; phase 1: bump + signal only.
-cudaError_t peer_sync_launch(const GemmPeer& g, int phase, int* err_flag, cudaStream_t stream);
-
 // Returns cudaSuccess or an error; never throws.  `err_flag` is a device int that the kernel sets to a
 // non-zero code when a bounded barrier wait runs out (the launch still terminates).
 cudaError_t gemm_launch(const GemmProblem& p, const GemmOperand& A, const GemmOperand& B,

@@ -164,22 +164,6 @@ def contract(t2: torch.Tensor, wx: torch.Tensor, transpose_w: bool) -> torch.Ten
     return t3
 
 
-def contract_wgrad(dt: torch.Tensor, t2: torch.Tensor) -> torch.Tensor:
-    """dWx[l, q, p] = sum_{b, m<=l} dT[b, l, m, q] T2[b, l, m, p]  (fp32)."""
-    B, lmax, mmax, nq = dt.shape
-    npp = t2.shape[3]
-    if B == 1:
-        dwx = torch.empty(lmax, nq, npp, dtype=torch.float32, device=dt.device)
-    else:
-        dwx = torch.zeros(lmax, nq, npp, dtype=torch.float32, device=dt.device)
-    gemm(nq, npp, mmax,
-         Operand(dt, ld=nq, mn_major=True, zs_hi=mmax * nq, zs_lo=lmax * mmax * nq),
-         Operand(t2, ld=npp, mn_major=True, zs_hi=mmax * npp, zs_lo=lmax * mmax * npp),
-         Output(dwx, rs_lo=npp, d_zhi=nq * npp),
-         zhi_n=lmax, zlo_n=B, accumulate=(B > 1), tri=Tri(kmax_a=1, kmax_b=1))
-    return dwx
-
-
 def contract_wgrad2(dt: torch.Tensor, t2: torch.Tensor, l0: int = 0, m0: int = 0) -> torch.Tensor:
     """(dWr, dWi)[l, o, c] as fp32 [2, L, Co, Ci] without forming the full real 2x2-block gradient:
 
