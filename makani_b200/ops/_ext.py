@@ -109,6 +109,28 @@ def add_launches(n: int) -> None:
     LAUNCHES += int(n)
 
 
+# Codes written to the per-device error word by kernels whose bounded waits (2 s) ran out.
+ERROR_CODES = {
+    1: "GEMM producer: shared-memory stage never freed (empty barrier)",
+    2: "GEMM MMA issuer: accumulator buffer never drained (TMEM-empty barrier)",
+    3: "GEMM MMA issuer: operands never arrived (full barrier / TMA load)",
+    4: "GEMM epilogue: accumulator never completed (TMEM-full barrier)",
+    5: "GEMM producer: epilogue-operand buffer never freed",
+    6: "GEMM epilogue: epilogue operand never arrived",
+    16: "peer all-reduce: a rank did not reach the barrier",
+    32: "GEMM: peers did not deliver / release the first handshake buffer",
+    33: "GEMM: peers did not deliver / release the second handshake buffer",
+    40: "publish kernel: peers still read the previous contents",
+    44: "segment-sum kernel: a peer's segment did not arrive",
+    56: "instance-norm statistics: peers still read the previous sums",
+    57: "instance-norm apply: a peer's sums did not arrive",
+}
+
+
+def describe_error(code: int) -> str:
+    return ERROR_CODES.get(int(code), "unknown code")
+
+
 def check_device_errors(device=None) -> None:
     """Raise if a kernel recorded an expired bounded wait on `device` (synchronises)."""
     import torch
@@ -119,4 +141,4 @@ def check_device_errors(device=None) -> None:
     code = _MOD.read_error_flag(int(dev))
     if code != 0:
         _MOD.clear_error_flag(int(dev))
-        raise RuntimeError(f"makani_b200: a device-side bounded wait expired (code {code})")
+        raise RuntimeError(f"makani_b200: a device-side bounded wait expired (code {code}: {describe_error(code)})")
