@@ -282,6 +282,7 @@ __device__ bool xch_wait(const StatExchange& xc, int code) {
 }
 __device__ void xch_signal(const StatExchange& xc) {
   *xc.done_ctr = 0;
+  if (*reinterpret_cast<volatile int*>(xc.err) != 0) return;   // nothing is published after an expired wait
   atomicAdd(xc.bump, 1u);
   __threadfence_system();
   for (int peer = 0; peer < xc.npeers; ++peer)

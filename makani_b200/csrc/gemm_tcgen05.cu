@@ -782,12 +782,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
     const unsigned int prev = atomicAdd(p.sync.done_ctr, 1u);
     if (prev == gridDim.x - 1) {
       *p.sync.done_ctr = 0;
-      for (int i = 0; i < p.sync.nwait; ++i)
-        if (p.sync.bump[i]) atomicAdd(p.sync.bump[i], 1u);
-      __threadfence_system();
-      for (int i = 0; i < p.sync.nsig; ++i)
-        for (int peer = 0; peer < p.sync.np_sig[i]; ++peer)
-          if (p.sync.sig[i][peer]) atomicAdd_system(p.sync.sig[i][peer], 1u);
+      // after an expired wait nothing is published: the counters keep describing the last complete generation
+      if (*reinterpret_cast<volatile int*>(p.err) == 0) {
+        for (int i = 0; i < p.sync.nwait; ++i)
+          if (p.sync.bump[i]) atomicAdd(p.sync.bump[i], 1u);
+        __threadfence_system();
+        for (int i = 0; i < p.sync.nsig; ++i)
+          for (int peer = 0; peer < p.sync.np_sig[i]; ++peer)
+            if (p.sync.sig[i][peer]) atomicAdd_system(p.sync.sig[i][peer], 1u);
+      }
     }
   }
   if (warp == 1) {
@@ -971,11 +974,13 @@ __global__ void __launch_bounds__(256) peer_publish_kernel(const uint4* __restri
     const unsigned int prev = atomicAdd(sy.done_ctr, 1u);
     if (prev == gridDim.x - 1) {
       *sy.done_ctr = 0;
-      for (int i = 0; i < sy.nwait; ++i)
-        if (sy.bump[i]) atomicAdd(sy.bump[i], 1u);
-      __threadfence_system();
-      for (int peer = 0; peer < sy.np_sig[0]; ++peer)
-        if (sy.sig[0][peer]) atomicAdd_system(sy.sig[0][peer], 1u);
+      if (*reinterpret_cast<volatile int*>(err) == 0) {   // nothing is published after an expired wait
+        for (int i = 0; i < sy.nwait; ++i)
+          if (sy.bump[i]) atomicAdd(sy.bump[i], 1u);
+        __threadfence_system();
+        for (int peer = 0; peer < sy.np_sig[0]; ++peer)
+          if (sy.sig[0][peer]) atomicAdd_system(sy.sig[0][peer], 1u);
+      }
     }
   }
 }
@@ -1043,11 +1048,13 @@ __global__ void __launch_bounds__(256) peer_sum_kernel(uint4* __restrict__ out, 
     const unsigned int prev = atomicAdd(sy.done_ctr, 1u);
     if (prev == gridDim.x - 1) {
       *sy.done_ctr = 0;
-      for (int i = 0; i < sy.nwait; ++i)
-        if (sy.bump[i]) atomicAdd(sy.bump[i], 1u);
-      __threadfence_system();
-      for (int peer = 0; peer < sy.np_sig[0]; ++peer)
-        if (sy.sig[0][peer]) atomicAdd_system(sy.sig[0][peer], 1u);
+      if (*reinterpret_cast<volatile int*>(err) == 0) {   // nothing is published after an expired wait
+        for (int i = 0; i < sy.nwait; ++i)
+          if (sy.bump[i]) atomicAdd(sy.bump[i], 1u);
+        __threadfence_system();
+        for (int peer = 0; peer < sy.np_sig[0]; ++peer)
+          if (sy.sig[0][peer]) atomicAdd_system(sy.sig[0][peer], 1u);
+      }
     }
   }
 }

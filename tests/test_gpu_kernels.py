@@ -464,3 +464,36 @@ def test_graphed_train_step_matches_eager_steps():
     den = sum(float((torch.view_as_real(a) if a.is_complex() else a).square().sum()) for a in pe)
     assert (num / den) ** 0.5 < 2e-2
     _ext.check_device_errors(dev)
+
+
+def test_bounded_wait_reports_instead_of_hanging():
+    """A consumer whose peer never signals gives up after its 2 s limit, sets the device error word and returns; the
+    host sees the code and the context stays usable.  (The "peer" is a flag in local memory that nothing sets.)"""
+    import time
+    dev = _dev()
+    ext = _ext.require()
+    _ext.check_device_errors(dev)
+    ctrl = torch.zeros(64, dtype=torch.int32, device=dev)            # ready[8] | free[8] | n_prod, n_read, done
+    base = ctrl.data_ptr()
+    ready, free_, n_read, done = base, base + 32, base + 68, base + 72
+    # [nwait, nsig, done_ctr, {wait, expected, offset, bump, peers} x 2, {peers, signal[8]} x 2]
+    sync = [1, 1, done, ready, n_read, 1, n_read, 1, 0, 0, 0, 0, 0, 1, free_] + [0] * 7 + [0] * 9
+    assert len(sync) == 31
+    src = torch.ones(4096, dtype=torch.bfloat16, device=dev)
+    out = torch.zeros_like(src)
+    t0 = time.time()
+    ext.peer_sum(out, [src.data_ptr()], None, 0, sync)
+    torch.cuda.synchronize()
+    waited = time.time() - t0
+    assert 1.5 < waited < 10.0, waited
+    with pytest.raises(RuntimeError, match="code 44"):
+        _ext.check_device_errors(dev)
+    assert float(out.float().abs().sum()) == 0.0                     # nothing was consumed
+    _ext.check_device_errors(dev)                                    # the error word is cleared by the report
+    # the same kernel proceeds as soon as the flag is there, and ordinary work still runs
+    ctrl[0] = 1
+    ext.peer_sum(out, [src.data_ptr()], None, 0, sync)
+    torch.cuda.synchronize()
+    _ext.check_device_errors(dev)
+    assert torch.equal(out, src)
+    assert int(ctrl[17]) == 1 and int(ctrl[8]) == 1                  # n_read bumped, "free" signalled
