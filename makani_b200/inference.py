@@ -1,8 +1,9 @@
 """Inference / scoring entry point: `python -m makani_b200.inference --yaml_config <file> --config <section>`.
 
 Requires the checkpoints of the run (or `--checkpoint_path`).  `--mode score` rolls the model out over the
-evaluation set and writes acc/rmse curves; `--mode ensemble` is declared by the reference CLI but not
-implemented there either (makani/inference.py:55,161-165).
+evaluation set and writes acc/rmse curves; `--mode ensemble` (declared but not implemented by the reference CLI,
+makani/inference.py:55,161-165) runs an initial-condition ensemble from one sample and writes the RMSE of the ensemble
+mean, the spread and their ratio per channel and lead time.
 """
 
 from __future__ import annotations
@@ -19,6 +20,9 @@ def main(argv=None):
     parser.add_argument("--enable_nhwc", action="store_true")
     parser.add_argument("--mode", default="score", type=str, choices=["score", "ensemble"])
     parser.add_argument("--checkpoint_format", default="legacy", choices=["flexible", "legacy"], type=str)
+    parser.add_argument("--ensemble_size", default=8, type=int)
+    parser.add_argument("--ensemble_noise_std", default=0.05, type=float, help="std of the initial-condition noise (normalised units)")
+    parser.add_argument("--ensemble_ic", default=0, type=int, help="index of the evaluation sample used as initial condition")
     args = parser.parse_args(argv)
     params, world_rank = bootstrap(args, inference=True)
     if not args.enable_synthetic_data:
@@ -33,7 +37,10 @@ def main(argv=None):
         inferencer = Inferencer(params, world_rank)
         inferencer.score_model()
         return inferencer
-    raise NotImplementedError("ensemble inference is not implemented")
+    inferencer = Inferencer(params, world_rank)
+    inferencer.ensemble_result = inferencer.inference_ensemble(ic=args.ensemble_ic, n_members=args.ensemble_size,
+                                                               noise_std=args.ensemble_noise_std)
+    return inferencer
 
 
 if __name__ == "__main__":

@@ -173,6 +173,50 @@ class Inferencer(Trainer):
                 outputs.append(self._static_pred.float().cpu())
         return (self._static_state, outputs) if keep_outputs else self._static_state
 
+    @torch.no_grad()
+    def inference_ensemble(self, ic=0, n_members=8, noise_std=0.05, seed=0):
+        """Initial-condition ensemble from sample `ic` of the evaluation set: `n_members` copies of the (normalised)
+        initial state perturbed with N(0, noise_std^2) noise are rolled out together as one batch; per channel and
+        lead time the quadrature-weighted RMSE of the ensemble mean, the ensemble spread and their ratio are returned
+        as a dict of `[C_out, steps + 1]` tensors (and saved to the experiment directory on rank 0).
+        The reference CLI declares this mode without implementing it (makani/inference.py:55,161-165)."""
+        from .metrics.functions import GeometricRMSE
+        self._set_eval()
+        p = self.params
+        data = [x.unsqueeze(0) for x in self.valid_dataset[ic]] if hasattr(self.valid_dataset, "__getitem__") else \
+            [x[:1] for x in next(iter(self.valid_dataloader))]
+        gdata = [x.to(self.device, dtype=torch.float32).expand(n_members, *x.shape[1:]).contiguous() for x in data]
+        inp, tar = self.preprocessor.cache_unpredicted_features(*gdata)
+        gen = torch.Generator(device=self.device).manual_seed(int(seed))
+        inp = inp + float(noise_std) * torch.randn(inp.shape, device=self.device, generator=gen)
+        state = self.preprocessor.flatten_history(inp)
+        local = dict(local_shape=None, local_offset=(0, 0))
+        if comm.get_size("spatial") > 1:
+            local = dict(local_shape=(p.img_local_shape_x, p.img_local_shape_y), local_offset=(p.img_local_offset_x, p.img_local_offset_y))
+        rule = "legendre-gauss" if p.get("model_grid_type", "equiangular") == "legendre-gauss" else "naive"
+        rmse = GeometricRMSE(rule, img_shape=(p.img_shape_x, p.img_shape_y), crop_shape=(p.img_crop_shape_x, p.img_crop_shape_y),
+                             crop_offset=(p.img_crop_offset_x, p.img_crop_offset_y), normalize=True, channel_reduction="none",
+                             batch_reduction="none", **local).to(self.device)
+        skill, spread = [], []
+        for idt, targ in enumerate(torch.split(tar, 1, dim=1)):
+            targ = self.preprocessor.flatten_history(targ)
+            with torch.autocast(device_type=self.device.type, dtype=self.amp_dtype, enabled=self.amp_enabled):
+                pred = self.model(state)
+            pf = pred.float()
+            mean = pf.mean(dim=0, keepdim=True)
+            skill.append(rmse(mean, targ[:1].float())[0])
+            # spread: root of the quadrature-weighted mean ensemble variance (unbiased over members)
+            var = pf.var(dim=0, unbiased=n_members > 1, keepdim=True) if n_members > 1 else torch.zeros_like(mean)
+            spread.append(rmse(torch.sqrt(var), torch.zeros_like(var))[0])
+            state = self.preprocessor.append_history(state.to(pred.dtype), pred, idt)
+        out = {"rmse": torch.stack(skill, dim=1).cpu(), "spread": torch.stack(spread, dim=1).cpu()}
+        out["spread_skill_ratio"] = out["spread"] / out["rmse"].clamp_min(1e-12)
+        if self.world_rank == 0 and p.get("experiment_dir") is not None:
+            os.makedirs(p.experiment_dir, exist_ok=True)
+            for k, v in out.items():
+                np.save(os.path.join(p.experiment_dir, f"ensemble_{k}.npy"), v.numpy())
+        return out
+
     def log_score(self, scoring_logs, scoring_time):
         if not self.log_to_screen:
             return

@@ -44,6 +44,13 @@ def test_train_cli_resumes_and_inference_scores(recipe):
     assert again.params.resuming and again.startEpoch >= 1
     inf = inference.main(_args(path, "tiny_sfno"))
     assert inf is not None
+    ens = inference.main(_args(path, "tiny_sfno", "--mode", "ensemble", "--ensemble_size", "4", "--ensemble_noise_std", "0.1"))
+    res = ens.ensemble_result
+    assert res["rmse"].shape == (4, 3) and res["spread"].shape == (4, 3)        # 4 channels, 2 rollout steps + 1
+    assert (res["spread"] > 0).all() and (res["rmse"] > 0).all()
+    assert os.path.isfile(os.path.join(ens.params.experiment_dir, "ensemble_spread_skill_ratio.npy"))
+    one = ens.inference_ensemble(ic=0, n_members=1, noise_std=0.0)
+    assert float(one["spread"].abs().sum()) == 0.0
 
 
 def test_self_test_mode(recipe):
