@@ -57,3 +57,13 @@ def test_self_test_mode(recipe):
     from makani_b200 import train
     path, _ = recipe
     train.main(_args(path, "tiny_sfno", "--mode", "test"))
+
+
+def test_quickstart_example_runs(tmp_path):
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("quickstart", os.path.join(ROOT, "examples", "quickstart.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    out = mod.main(["--workdir", str(tmp_path)])
+    assert out["acc"].shape == (4, 5) and out["pred"].shape[0] == 5
+    assert out["scores"]["base"]["validation steps"] > 0
