@@ -35,22 +35,37 @@ def supported(x: torch.Tensor, w: torch.Tensor, inp_group: str, out_group: str) 
     return comm.get_size(inp_group) > 1 or comm.get_size(out_group) > 1
 
 
-def _reduced_conv(name, group, run, B, C, H, W, dtype, device, bias=None):
-    """Runs `run(out, sync, dests)` (a GEMM that writes a [B, C, H, W] channels-last partial result) and returns the sum
-    of the partial results over `group`."""
+def _start_reduced_conv(name, group, run, B, C, H, W, dtype, device):
+    """Launches `run(out, sync, dests)` (a GEMM that writes a [B, C, H, W] channels-last partial result, delivering its
+    tiles to every member of `group`) and returns a handle for `_finish_reduced_conv`."""
     n = comm.get_size(group)
     if n == 1:
         y = torch.empty(B, C, H, W, dtype=dtype, device=device, memory_format=torch.channels_last)
         run(y, None, None)
-        if bias is not None:
-            y = y + bias.to(dtype).view(1, -1, 1, 1)
-        return y
+        return None, y
     slot = peer.get_slot(name, group, B * C * H * W * torch.empty((), dtype=dtype).element_size(), device)
     part = slot.tensor(dtype, (B, H, W, C)).permute(0, 3, 1, 2)          # channels-last view of this rank's segment
     run(part, peer.sync_descriptor(produce=slot), slot.dests())
+    return slot, (B, C, H, W, dtype, device)
+
+
+def _finish_reduced_conv(handle, bias=None):
+    """Sum of the partial results over the group (+ bias).  Work launched between start and finish overlaps the
+    arrival of the peers' tiles."""
+    slot, rest = handle
+    if slot is None:
+        y = rest
+        if bias is not None:
+            y = y + bias.to(y.dtype).view(1, -1, 1, 1)
+        return y
+    B, C, H, W, dtype, device = rest
     y = torch.empty(B, C, H, W, dtype=dtype, device=device, memory_format=torch.channels_last)
     slot.reduce_into(y, bias, C)
     return y
+
+
+def _reduced_conv(name, group, run, B, C, H, W, dtype, device, bias=None):
+    return _finish_reduced_conv(_start_reduced_conv(name, group, run, B, C, H, W, dtype, device), bias)
 
 
 class _FusedDistMatmul(torch.autograd.Function):
@@ -77,14 +92,17 @@ class _FusedDistMatmul(torch.autograd.Function):
         if layout_of(dy) != CL:
             dy = dy.contiguous(memory_format=torch.channels_last)
         B, _, H, W = dy.shape
-        dx = None
+        handle = None
         if ctx.needs_input_grad[0]:
             def run(out, sync, dests):
                 _conv_dgrad(dy, wq, ci, x_layout=CL, out=out, sync=sync, dests=dests)
 
-            dx = _reduced_conv("mm_bwd", out_group, run, B, ci, H, W, dy.dtype, dy.device)
+            handle = _start_reduced_conv("mm_bwd", out_group, run, B, ci, H, W, dy.dtype, dy.device)
+        # the weight and bias gradients are local: they run while the peers' input-gradient tiles are still arriving
+        # (what the reference's overlapped variant does with an asynchronous all-reduce, makani/mpu/layers.py:171-218)
         dw = _conv_wgrad(dy, x).reshape(wshape) if ctx.needs_input_grad[1] else None
         db = _chan_sum(dy).reshape(bshape) if has_bias and ctx.needs_input_grad[2] else None
+        dx = _finish_reduced_conv(handle) if handle is not None else None
         return dx, dw, db, None, None
 
 

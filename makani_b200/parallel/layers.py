@@ -144,6 +144,43 @@ class DistributedMatmul(nn.Module):
         return x_out
 
 
+class DistributedPatchEmbed(nn.Module):
+    """Patch embedding (strided convolution) whose output channels may be sharded over the `matmul` group; the input
+    is gathered first when it arrives channel-sharded.  Interface of makani/mpu/layers.py:403-450 (no network of the
+    reference uses it); the width must divide evenly over the spatial group."""
+
+    def __init__(self, img_size=(224, 224), patch_size=(16, 16), in_chans=3, embed_dim=768, input_is_matmul_parallel=False,
+                 output_is_matmul_parallel=True):
+        super().__init__()
+        self.input_parallel, self.output_parallel = input_is_matmul_parallel, output_is_matmul_parallel
+        msize, ssize = comm.get_size("matmul"), comm.get_size("spatial")
+        assert (img_size[1] // patch_size[1]) % ssize == 0, "the spatial group size must divide the number of patches along W"
+        self.img_size = (img_size[0], img_size[1] // ssize)
+        self.patch_size = patch_size
+        self.num_patches = ((img_size[1] // patch_size[1]) // ssize) * (img_size[0] // patch_size[0])
+        if self.output_parallel:
+            assert embed_dim % msize == 0, "embed_dim must be divisible by the matmul group size"
+            out_local = embed_dim // msize
+        else:
+            out_local = embed_dim
+        self.proj = nn.Conv2d(in_chans, out_local, kernel_size=patch_size, stride=patch_size)
+        self.proj.weight.is_shared_mp = ["spatial"]
+        self.proj.bias.is_shared_mp = ["spatial"]
+        if self.output_parallel:
+            self.proj.weight.sharded_dims_mp = ["matmul", None, None, None]
+            self.proj.bias.sharded_dims_mp = ["matmul"]
+        self.gather_shapes = compute_split_shapes(in_chans, msize)
+
+    def forward(self, x):
+        if self.input_parallel:
+            x = gather_from_parallel_region(x, 1, self.gather_shapes, "matmul")
+        if self.output_parallel:
+            x = copy_to_parallel_region(x, "matmul")
+        B, C, H, W = x.shape
+        assert H == self.img_size[0] and W == self.img_size[1], f"input size ({H}x{W}) does not match the model ({self.img_size})"
+        return self.proj(x).flatten(2)
+
+
 class DistributedEncoderDecoder(nn.Module):
     """Channel-parallel pointwise encoder/decoder; the in/out group names alternate from layer to layer."""
 

@@ -360,6 +360,30 @@ def case_fused_matmul():
         db_want = split_tensor_along_dim(br.grad, 0, nfo)[fo]
         assert _rel(layer.bias.grad.float().cpu().reshape(-1), db_want) < tol
 
+def case_patch_embed():
+    """Channel-parallel patch embedding == the serial strided convolution with the concatenated weights."""
+    from makani_b200.parallel.layers import DistributedPatchEmbed
+    torch.manual_seed(8)
+    B, C, H, W, E, P = 2, 6, 16, 32, 12, 4
+    msize, mrank = comm.get_size("matmul"), comm.get_rank("matmul")
+    x = torch.randn(B, C, H, W)
+    w, b = torch.randn(E, C, P, P) * 0.1, torch.randn(E) * 0.1
+    layer = DistributedPatchEmbed((H, W), (P, P), C, E, input_is_matmul_parallel=True, output_is_matmul_parallel=True)
+    e_loc = E // msize
+    with torch.no_grad():
+        layer.proj.weight.copy_(w[mrank * e_loc:(mrank + 1) * e_loc])
+        layer.proj.bias.copy_(b[mrank * e_loc:(mrank + 1) * e_loc])
+    xr = x.clone().requires_grad_()
+    y_ref = torch.nn.functional.conv2d(xr, w, b, stride=P).flatten(2)
+    xl = split_tensor_along_dim(x, 1, msize)[mrank].contiguous().requires_grad_()
+    y = layer(xl)
+    assert y.shape == (B, e_loc, (H // P) * (W // P))
+    assert _rel(y, y_ref[:, mrank * e_loc:(mrank + 1) * e_loc]) < 1e-5
+    g = torch.randn_like(y_ref)
+    y_ref.backward(g)
+    y.backward(g[:, mrank * e_loc:(mrank + 1) * e_loc].contiguous())
+    assert _rel(xl.grad, split_tensor_along_dim(xr.grad, 1, msize)[mrank]) < 1e-5
+
 
 if __name__ == "__main__":
     case = sys.argv[1]

@@ -100,3 +100,8 @@ def test_fused_distributed_spectral_conv(sizes):
 @pytest.mark.parametrize("sizes", [(1, 1, 2, 1), (1, 1, 1, 2), (1, 1, 2, 2)])
 def test_fused_channel_parallel_matmul_algebra(sizes):
     _launch("fused_matmul", sizes, sizes[2] * sizes[3])
+
+
+@pytest.mark.parametrize("sizes", [(1, 1, 2, 1), (1, 1, 2, 2)])
+def test_distributed_patch_embed(sizes):
+    _launch("patch_embed", sizes, sizes[2] * sizes[3])
