@@ -34,8 +34,9 @@ _REGISTRY: Dict[str, Union[str, Callable]] = dict(_BUILTIN)
 def _discover_entry_points():
     try:
         from importlib.metadata import entry_points
-        for ep in entry_points(group="makani.models"):
-            _REGISTRY.setdefault(ep.name, ep.value)
+        for group in ("makani_b200.models", "makani.models"):     # own group, and plug-ins written for the reference
+            for ep in entry_points(group=group):
+                _REGISTRY.setdefault(ep.name, ep.value)
     except Exception:
         pass
 
