@@ -67,3 +67,14 @@ def test_quickstart_example_runs(tmp_path):
     out = mod.main(["--workdir", str(tmp_path)])
     assert out["acc"].shape == (4, 5) and out["pred"].shape[0] == 5
     assert out["scores"]["base"]["validation steps"] > 0
+
+
+def test_profile_cli_runs_with_a_capture_window(recipe):
+    """The profiling entry point trains like the normal one; on CPU the profiler toggles are no-ops but the window
+    bookkeeping (start / stop step, ranks, modes) is exercised."""
+    from makani_b200 import train_profile
+    path, tmp = recipe
+    trainer = train_profile.main(_args(path, "tiny_sfno", "--capture_mode", "training", "validation", "--capture_range_start", "1",
+                                       "--capture_range_stop", "3", "--capture_ranks", "0"))
+    assert trainer.iters == 4
+    assert (tmp / "runs" / "tiny_sfno" / "t0" / "training_checkpoints" / "ckpt_mp0.tar").is_file()
