@@ -1,12 +1,21 @@
 // Persistent warp-specialised GEMM for sm_100a: TMA -> shared memory (128B swizzle) -> tcgen05.mma with
 // accumulators in tensor memory -> tcgen05.ld epilogue with fused bias / GELU / residual / scatter.
 //
-// Roles per CTA (192 threads, one CTA per SM):
+// Roles per CTA (320 threads, one CTA per SM):
 //   warp 0      : TMA producer (one elected lane)
 //   warp 1      : TMEM allocator + MMA issuer (one elected lane)
-//   warps 2..5  : epilogue; warp w reads TMEM lanes [32*(w%4), 32*(w%4)+32)
+//   warps 2..9  : epilogue; warp w reads TMEM lanes [32*(w%4), 32*(w%4)+32), the two warps that share a lane
+//                 quarter take alternating column chunks
 // Two accumulator buffers in TMEM let the epilogue of tile i overlap the main loop of tile i+1.
 // Every mbarrier wait is bounded; on expiry the kernel records a code in *err and drains.
+//
+// Multi-GPU use (one process per GPU, buffers mapped through CUDA IPC):
+//   * the k axis of the B operand may be cut into up to 8 segments with their own base pointers and tensor maps
+//     (the per-rank segments of a gathered buffer in this device's own memory);
+//   * the bf16 output may be replicated into up to 7 more buffers with the layout of D (the same segment of every
+//     peer's copy), by plain 16-byte stores or TMA stores over NVLink: no load ever targets peer memory;
+//   * producer / consumer ordering across devices uses monotonic counters (PeerSync) checked by the first thread of
+//     every CTA before any work and advanced by the last CTA of the grid.
 #include "gemm_tcgen05.cuh"
 
 #include <cuda.h>
@@ -24,7 +33,7 @@ constexpr int NUM_THREADS = 320;   // TMA warp + MMA warp + 8 epilogue warps
 constexpr int MAX_STAGES = 6;
 constexpr int MAX_SEG = 8;
 
-// Handshake of a kernel that reads operands from peer GPUs and/or writes a buffer that peers read.
+// Handshake of a kernel that consumes buffers its peers have filled and/or fills a buffer that its peers consume.
 //   wait[i]   : local flag array (one slot per peer) that must reach *wait_exp[i] + wait_off[i] before the first load
 //   bump[i]   : local counter incremented by one when the whole grid has finished
 //   sig[i][p] : flag slot in peer p's memory incremented by one when the whole grid has finished
@@ -69,7 +78,7 @@ struct KParams {
   long long total_tiles;
   int stages, e_tma, plain_cols;
   int* err;
-  // ---- B operand gathered from several devices: segment s of the k axis lives on peer s
+  // ---- B operand gathered from several devices: segment s of the k axis was written by rank s into the local buffer
   int nseg;                       // 1: ordinary single-map operand
   int seg_len[MAX_SEG];           // local k extent of each segment
   int seg_apos[MAX_SEG];          // k coordinate of the segment start in the A operand (padded layout)
@@ -332,7 +341,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    // operands on peer devices (and the buffer this kernel overwrites) must be ready: bounded wait on local flags.
+    // segments written by the peers (and the peers' copies this kernel overwrites) must be ready: bounded wait on local flags.
     // The whole CTA waits (not only the producer) so that no epilogue store of an all-zero tile can run early.
     bool ok = true;
     for (int w = 0; w < p.sync.nwait && ok; ++w) {
@@ -777,7 +786,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
   tc_fence_before();
   __syncthreads();
   if (p.sync.done_ctr != nullptr && threadIdx.x == 0) {
-    // last CTA of the grid: everything this kernel wrote is complete and everything it read from peers is consumed
+    // last CTA of the grid: everything this kernel wrote (here and into the peers' copies) is complete and everything it
+    // consumed may be overwritten
     __threadfence_system();
     const unsigned int prev = atomicAdd(p.sync.done_ctr, 1u);
     if (prev == gridDim.x - 1) {
