@@ -165,3 +165,79 @@ class FusedAdamW(torch.optim.Optimizer):
                 v.mul_(b2).addcmul_(g, g, value=1.0 - b2)
                 denom = v.sqrt() / math.sqrt(1.0 - b2 ** step) + eps
                 p.addcdiv_(m, denom, value=-lr / (1.0 - b1 ** step))
+
+
+class LAMB(torch.optim.Optimizer):
+    """Layer-wise adaptive moments (You et al., 2020), the update rule of apex `FusedLAMB` that the reference offers
+    as `optimizer_type: FusedLAMB` (makani/utils/trainer.py:434-448), written with multi-tensor (`_foreach`) ops so that
+    it needs no extra dependency and runs on CPU and GPU alike.
+
+        m = b1 m + (1 - b1) g          v = b2 v + (1 - b2) g^2          (g clipped to a global norm of `max_grad_norm`)
+        u = m_hat / (sqrt(v_hat) + eps) + wd * p        p -= lr * (||p|| / ||u||) * u      (trust ratio 1 if a norm is 0)
+
+    Complex parameters are updated through their interleaved real view.
+    """
+
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-6, weight_decay=0.01, bias_correction=True,
+                 max_grad_norm=1.0, use_nvlamb=False):
+        defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, bias_correction=bias_correction,
+                        max_grad_norm=max_grad_norm)
+        super().__init__(params, defaults)
+        self.use_nvlamb = use_nvlamb      # apply the trust ratio also to parameters without weight decay
+
+    @staticmethod
+    def _real(t):
+        return torch.view_as_real(t) if t.is_complex() else t
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        # global gradient norm over all groups (fp32)
+        grads = [self._real(p.grad) for g in self.param_groups for p in g["params"] if p.grad is not None]
+        if not grads:
+            return loss
+        gnorm = torch.linalg.vector_norm(torch.stack(torch._foreach_norm(grads)))
+        for group in self.param_groups:
+            plist = [p for p in group["params"] if p.grad is not None]
+            if not plist:
+                continue
+            b1, b2 = group["betas"]
+            clip = torch.clamp(gnorm / group["max_grad_norm"], min=1.0) if group["max_grad_norm"] > 0 else torch.ones_like(gnorm)
+            ps, gs, ms, vs = [], [], [], []
+            for p in plist:
+                st = self.state[p]
+                if len(st) == 0:
+                    st["step"] = 0
+                    st["exp_avg"] = torch.zeros_like(self._real(p))
+                    st["exp_avg_sq"] = torch.zeros_like(self._real(p))
+                st["step"] += 1
+                ps.append(self._real(p))
+                gs.append(self._real(p.grad))
+                ms.append(st["exp_avg"])
+                vs.append(st["exp_avg_sq"])
+            step = self.state[plist[0]]["step"]
+            gs = torch._foreach_div(gs, clip)
+            torch._foreach_mul_(ms, b1)
+            torch._foreach_add_(ms, gs, alpha=1.0 - b1)
+            torch._foreach_mul_(vs, b2)
+            torch._foreach_addcmul_(vs, gs, gs, value=1.0 - b2)
+            bc1 = 1.0 - b1 ** step if group["bias_correction"] else 1.0
+            bc2 = 1.0 - b2 ** step if group["bias_correction"] else 1.0
+            denom = torch._foreach_sqrt(torch._foreach_div(vs, bc2))
+            torch._foreach_add_(denom, group["eps"])
+            upd = torch._foreach_div(torch._foreach_div(ms, bc1), denom)
+            wd = group["weight_decay"]
+            if wd != 0.0:
+                torch._foreach_add_(upd, ps, alpha=wd)
+            pn = torch._foreach_norm(ps)
+            un = torch._foreach_norm(upd)
+            for p_, u_, a, b in zip(ps, upd, pn, un):
+                if wd != 0.0 or self.use_nvlamb:
+                    ratio = torch.where((a > 0) & (b > 0), a / b, torch.ones_like(a))
+                else:
+                    ratio = torch.ones_like(a)
+                p_.add_(u_ * ratio, alpha=-group["lr"])
+        return loss

@@ -216,8 +216,9 @@ class Trainer:
             return cls(params, betas=betas, lr=p.lr, weight_decay=p.weight_decay)
         if ot == "SGD":
             return torch.optim.SGD(params, lr=p.lr, weight_decay=p.weight_decay, momentum=p.get("momentum", 0.0))
-        if ot == "FusedLAMB":
-            raise ValueError("FusedLAMB needs NVIDIA apex, which this framework does not depend on; use AdamW")
+        if ot in ("FusedLAMB", "LAMB"):
+            from ..ops.optim import LAMB
+            return LAMB(params, lr=p.lr, betas=betas, weight_decay=p.weight_decay, max_grad_norm=p.get("optimizer_max_grad_norm", 1.0))
         raise ValueError(f"Unknown optimizer type {ot}")
 
     def _make_scheduler(self, p):

@@ -111,3 +111,35 @@ def test_complex_modulus_second_moment():
     # first step of Adam: update = lr * g / (|g| + eps)
     expect = p0 - 1e-2 * g / (g.abs() + 1e-8)
     assert torch.allclose(p.detach(), expect, atol=1e-5)
+
+
+def test_lamb_matches_a_direct_restatement():
+    import math
+    from makani_b200.ops.optim import LAMB
+    torch.manual_seed(0)
+    ps = [torch.randn(5, 3, requires_grad=True), torch.randn(4, dtype=torch.complex64, requires_grad=True), torch.zeros(3, requires_grad=True)]
+    ref = [p.detach().clone() for p in ps]
+    opt = LAMB(ps, lr=1e-2, betas=(0.9, 0.95), eps=1e-6, weight_decay=0.1, max_grad_norm=0.5)
+    m = [torch.zeros_like(torch.view_as_real(r) if r.is_complex() else r) for r in ref]
+    v = [torch.zeros_like(x) for x in m]
+    for step in range(1, 4):
+        gs = [torch.randn_like(p) for p in ps]
+        for p, g in zip(ps, gs):
+            p.grad = g.clone()
+        opt.step()
+        gr = [torch.view_as_real(g) if g.is_complex() else g for g in gs]
+        gnorm = math.sqrt(sum(float(g.square().sum()) for g in gr))
+        clip = max(1.0, gnorm / 0.5)
+        for i, r in enumerate(ref):
+            rr = torch.view_as_real(r) if r.is_complex() else r
+            g = gr[i] / clip
+            m[i] = 0.9 * m[i] + 0.1 * g
+            v[i] = 0.95 * v[i] + 0.05 * g * g
+            u = (m[i] / (1 - 0.9 ** step)) / ((v[i] / (1 - 0.95 ** step)).sqrt() + 1e-6) + 0.1 * rr
+            pn, un = float(rr.norm()), float(u.norm())
+            ratio = pn / un if pn > 0 and un > 0 else 1.0
+            rr.sub_(1e-2 * ratio * u)
+        for p, r in zip(ps, ref):
+            a = torch.view_as_real(p.detach()) if p.is_complex() else p.detach()
+            b = torch.view_as_real(r) if r.is_complex() else r
+            assert torch.allclose(a, b, rtol=1e-5, atol=1e-6)
