@@ -190,7 +190,9 @@ class VisualizationWrapper:
         self.lat, self.lon = lat, lon
         self.scale = np.asarray(scale, dtype=np.float32).reshape(-1, 1, 1) if np.ndim(scale) else scale
         self.bias = np.asarray(bias, dtype=np.float32).reshape(-1, 1, 1) if np.ndim(bias) else bias
-        self.executor = ProcessPoolExecutor(max_workers=max(1, num_workers))
+        # spawned (not forked) workers: the parent is multi-threaded and usually holds a CUDA context
+        import multiprocessing
+        self.executor = ProcessPoolExecutor(max_workers=max(1, num_workers), mp_context=multiprocessing.get_context("spawn"))
         self.requests = []
 
     def reset(self):

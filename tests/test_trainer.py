@@ -135,3 +135,14 @@ def test_model_package_round_trip(tmp_path):
     best = ckpt.load_file(p.best_checkpoint_path.format(mp_rank=0))["model_state"]
     for k, v in wrapped.model.state_dict().items():
         assert torch.equal(v, best[k.replace("module.", "")]), k
+
+
+def test_validation_video_is_written(tmp_path):
+    """`log_video` renders the first validation rollout (prediction vs target per step) into a GIF."""
+    pytest.importorskip("PIL")
+    p = _params(tmp_path, log_video=1)
+    trainer = Trainer(p, 0)
+    assert trainer.visualizer is not None
+    trainer.train()
+    gifs = [f for f in os.listdir(p.experiment_dir) if f.endswith(".gif")]
+    assert gifs, os.listdir(p.experiment_dir)
