@@ -83,6 +83,11 @@ class GraphedTrainStep(TrainStep):
         self._calls += 1
         if self._calls <= self.warmup_steps:
             return super().__call__(inp, tgt)        # eager warm-up: allocator pools, peer buffers, plan caches
+        if self.graph is not None and (inp.shape != self.static_inp.shape or tgt.shape != self.static_tgt.shape
+                                       or inp.dtype != self.static_inp.dtype or tgt.dtype != self.static_tgt.dtype):
+            # a different batch geometry (e.g. the last, shorter batch of an epoch): this call runs eagerly and the
+            # captured graph stays valid for the usual shape
+            return super().__call__(inp, tgt)
         if self.graph is None:
             self._capture(inp, tgt)
         self.static_inp.copy_(inp, non_blocking=True)
