@@ -153,3 +153,44 @@ def test_copernicus_request_plan():
     assert jobs[2][0] == "/out/raw/sfc_2019-01.nc" and jobs[2][1]["param"] == get_data.SFC_PARAMS
     feb = [r for f, r in jobs if f.endswith("sfc_2019-02.nc")][0]
     assert feb["date"].endswith("2019-02-28")
+
+
+def _run_tool(name, *args):
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "data_process", name), *args], capture_output=True, text=True,
+                       cwd=os.path.join(ROOT, "data_process"), env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
+    assert r.returncode == 0, r.stdout + r.stderr
+    return r.stdout
+
+
+def test_statistics_and_histogram_tools(tmp_path):
+    rng = np.random.default_rng(3)
+    src = tmp_path / "train"
+    src.mkdir()
+    years = {2016: rng.standard_normal((10, 3, 9, 16)) * np.array([1.0, 2.0, 0.5])[None, :, None, None] + np.array([0.0, 3.0, -1.0])[None, :, None, None],
+             2017: rng.standard_normal((7, 3, 9, 16)) + 0.25}
+    for y, a in years.items():
+        np.save(src / f"{y}.npy", a.astype(np.float32))
+    out = tmp_path / "stats"
+    _run_tool("get_stats.py", "--input_path", str(src), "--output_path", str(out), "--batch", "4", "--dt", "2")
+    full = np.concatenate([years[2016], years[2017]]).astype(np.float32).astype(np.float64)
+    lat = np.linspace(0, np.pi, 9)
+    q = np.clip(np.sin(lat), 0, None)[:, None] * np.ones((1, 16))
+    q = q / q.sum()
+    mean = (full * q).sum(axis=(2, 3)).mean(axis=0)
+    std = np.sqrt((((full - mean[None, :, None, None]) ** 2) * q).sum(axis=(2, 3)).mean(axis=0))
+    np.testing.assert_allclose(np.load(out / "global_means.npy").reshape(-1), mean, rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(np.load(out / "global_stds.npy").reshape(-1), std, rtol=1e-4)
+    np.testing.assert_allclose(np.load(out / "mins.npy").reshape(-1), full.min(axis=(0, 2, 3)), rtol=1e-6)
+    np.testing.assert_allclose(np.load(out / "maxs.npy").reshape(-1), full.max(axis=(0, 2, 3)), rtol=1e-6)
+    np.testing.assert_allclose(np.load(out / "time_means.npy")[0], full.mean(axis=0), rtol=1e-4, atol=1e-5)
+    # differences x[t+dt] - x[t] never cross a file boundary
+    diffs = np.concatenate([a[2:] - a[:-2] for a in (years[2016].astype(np.float32).astype(np.float64), years[2017].astype(np.float32).astype(np.float64))])
+    dmean = (diffs * q).sum(axis=(2, 3)).mean(axis=0)
+    dstd = np.sqrt((((diffs - dmean[None, :, None, None]) ** 2) * q).sum(axis=(2, 3)).mean(axis=0))
+    np.testing.assert_allclose(np.load(out / "time_diff_means.npy").reshape(-1), dmean, rtol=1e-3, atol=1e-4)
+    np.testing.assert_allclose(np.load(out / "time_diff_stds.npy").reshape(-1), dstd, rtol=1e-4)
+    hist = tmp_path / "hist"
+    _run_tool("get_histograms.py", "--input_path", str(src), "--output_path", str(hist), "--stats_path", str(out), "--nbins", "20")
+    h = np.load(hist / "histograms.npz")
+    assert h["counts"].shape == (3, 20) and h["edges"].shape == (3, 21)
+    assert np.all(h["counts"].sum(axis=1) == 17 * 9 * 16)
