@@ -117,6 +117,13 @@ class FusedAdamW(torch.optim.Optimizer):
             ev = tb["hyper_ev"] = torch.cuda.Event()
             ev.record()
 
+    def prepare_tables(self):
+        """Builds the device-side pointer tables (host-to-device copies) ahead of a stream capture; gradients must
+        exist already."""
+        for gi, group, plist in self._groups_with_grads():
+            if plist[0].is_cuda:
+                self._table_for(gi, group, plist)
+
     def launch_step(self):
         from .spectral import note_weights_changed
         note_weights_changed()      # the kernels write parameters through raw pointers: derived caches are stale now

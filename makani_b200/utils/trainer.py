@@ -286,6 +286,8 @@ class Trainer:
         with torch.cuda.stream(side):
             for _ in range(num_warmup_steps):
                 self._forward_backward(self.static_inp, self.static_tar)
+            if self.graph_mode == "step" and hasattr(self.optimizer, "prepare_tables"):
+                self.optimizer.prepare_tables()      # pointer tables are uploaded before the capture starts
             side.synchronize()
             self.graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(self.graph, stream=side):
