@@ -471,7 +471,7 @@ class Trainer:
         if not self.log_to_screen:
             return
         lr = self.optimizer.param_groups[0]["lr"]
-        self.logger.info(f"Epoch {self.epoch + 1} summary:")
+        self.logger.info(f"Epoch {self.epoch} summary:")
         self.logger.info(f"Performance Parameters:")
         if self.device.type == "cuda":
             free, total = torch.cuda.mem_get_info(self.device)
