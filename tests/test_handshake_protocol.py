@@ -144,3 +144,25 @@ def test_a_missing_wait_is_caught_by_the_model():
         for k in seq0:
             while not k.advance(world):
                 pass
+
+
+def test_norm_and_matmul_exchanges_interleaved_with_the_transform_chain():
+    """All slot users of one SFNO block on a 2 x 2 grid: instance-norm statistics over the whole spatial group
+    (produce, consume), the transform chain, and a second norm; several blocks back to back."""
+    n, hgroup, wgroup = _grid(2, 2)
+    everyone = {r: list(range(n)) for r in range(n)}
+    slot_group = {"xw": wgroup, "t1": hgroup, "t3": hgroup, "t4": wgroup, "inorm": everyone}
+    block = [(None, "inorm"), ("inorm", None),                                    # norm 0
+             (None, "xw"), ("xw", "t1"), ("t1", None), (None, "t3"), ("t3", "t4"), ("t4", None),
+             (None, "inorm"), ("inorm", None)]                                    # norm 1
+    for seed in range(200):
+        rng = random.Random(1000 + seed)
+        world = {name: {r: SlotState(groups[r]) for r in range(n)} for name, groups in slot_group.items()}
+        queues = {r: [Kernel(r, c, p) for _ in range(4) for c, p in block] for r in range(n)}
+        while any(queues.values()):
+            runnable = [r for r, q in queues.items() if q and q[0].enabled(world)]
+            assert runnable, f"deadlock (seed {seed})"
+            r = rng.choice(runnable)
+            if queues[r][0].advance(world):
+                queues[r].pop(0)
+        assert all(s.n_prod == s.n_read == 8 for s in world["inorm"].values())
