@@ -1,6 +1,6 @@
 """Headline benchmark: SFNO-73ch 721x1440 bf16 training throughput (samples/s), weak scaling, pure data parallel.
 
-    python bench.py --gpus N --steps K --warmup W [--impl native|reference]
+    python bench.py --gpus N --steps K --warmup W [--impl native|reference|restated]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
         bench.py --gpus N --steps K --warmup W
 
@@ -8,7 +8,15 @@ Model ("sfno_linear_73chq_sc3_layers8_edim384", reference recipe config/sfnonet.
 equiangular grid, 73 prognostic channels + 1 static cos(latitude) channel in, 73 out, embed_dim 384, 8 blocks,
 scale_factor 3, dhconv spectral weights, MLP ratio 2, GELU, instance norm; random-init weights, synthetic
 N(0,1) data, batch 1 per GPU; loss "absolute squared geometric l2"; AdamW.  One step = forward + backward +
-gradient reduction + optimiser step.  Prints one JSON line on rank 0.
+gradient reduction + optimiser step, replayed from one CUDA graph after an eager warm-up (`--no-graph`: eager).
+Prints one JSON line on rank 0: the device-timed value (CUDA events, max over ranks), the end-to-end value (every
+step's batch copied from pinned host memory, every step's loss read back), clocks sampled during the timed region and
+the number of this package's kernels launched in it.
+
+Other configurations of the same harness: `--h/--w` (one sample split over latitude / longitude ranks with the fused
+distributed transforms), `--fin/--fout` (channel parallelism), `--model afno`, `--mode rollout` (autoregressive
+inference, ms per step), `--impl restated` (the reference's op sequence on stock PyTorch kernels and NCCL),
+`--impl reference` (the unmodified upstream package, if importable).
 """
 
 from __future__ import annotations
