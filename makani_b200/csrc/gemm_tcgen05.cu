@@ -21,6 +21,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 namespace mk {
@@ -77,6 +78,7 @@ struct KParams {
   int m_tiles, n_tiles;
   long long total_tiles;
   int stages, e_tma, plain_cols;
+  int n_fast;                     // tile order: 1 = n-tile index fastest, 0 = m-tile index fastest
   int* err;
   // ---- B operand gathered from several devices: segment s of the k axis was written by rank s into the local buffer
   int nseg;                       // 1: ordinary single-map operand
@@ -242,10 +244,20 @@ struct TileCoord {
 template <int BK>
 __device__ __forceinline__ TileCoord decode_tile(const KParams& p, long long t) {
   TileCoord c;
-  c.mt = static_cast<int>(t % p.m_tiles);
-  t /= p.m_tiles;
-  c.nt = static_cast<int>(t % p.n_tiles);
-  t /= p.n_tiles;
+  // The index that varies fastest walks over the tiles that share the larger operand, so that the CTAs of one wave
+  // fetch that operand's tile from DRAM once and hit L2 for the rest (token-major convolutions: many m-tiles of
+  // activations against two to six n-tiles of weights -> n fastest).
+  if (p.n_fast) {
+    c.nt = static_cast<int>(t % p.n_tiles);
+    t /= p.n_tiles;
+    c.mt = static_cast<int>(t % p.m_tiles);
+    t /= p.m_tiles;
+  } else {
+    c.mt = static_cast<int>(t % p.m_tiles);
+    t /= p.m_tiles;
+    c.nt = static_cast<int>(t % p.n_tiles);
+    t /= p.n_tiles;
+  }
   c.split = static_cast<int>(t % p.splits);
   t /= p.splits;
   c.zlo = static_cast<int>(t % p.zlo_n);
@@ -904,6 +916,12 @@ cudaError_t launch_t(const CUtensorMap& ma, const BMaps& mb, const CUtensorMap& 
     cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
     configured = true;
   }
+  // tile order (MAKANI_B200_TILE_ORDER=m|n forces one order for A/B timing)
+  static const int forced_order = [] {
+    const char* e = getenv("MAKANI_B200_TILE_ORDER");
+    return (e && e[0] == 'm') ? 0 : ((e && e[0] == 'n') ? 1 : -1);
+  }();
+  kp.n_fast = forced_order >= 0 ? forced_order : (kp.m_tiles > kp.n_tiles ? 1 : 0);
   long long grid = kp.total_tiles < num_sms ? kp.total_tiles : num_sms;
   if (grid < 1) grid = 1;
   gemm_kernel<BN, EB, EPI><<<static_cast<unsigned>(grid), NUM_THREADS, smem, stream>>>(ma, mb, me, md, mp, mdx, kp);
