@@ -53,26 +53,22 @@ def parse():
     ap.add_argument("--fout", type=int, default=1, help="output-feature parallel ranks")
     ap.add_argument("--h", type=int, default=1, help="latitude-parallel ranks per model instance (default: pure data parallel)")
     ap.add_argument("--w", type=int, default=1, help="longitude-parallel ranks per model instance")
+    ap.add_argument("--multistep", type=int, default=1, help="multistep_count: autoregressive steps per training sample (loss over all of them)")
+    ap.add_argument("--ref-graph", default="fwdbwd", choices=["none", "fwdbwd"], help="reference arm: its --cuda_graph_mode")
+    ap.add_argument("--tiny", action="store_true", help="32x64 plumbing configuration (CPU friendly; not a bench value)")
     return ap.parse_args()
 
 
 def reference_arm(args):
-    """Runs the unmodified reference from baseline/_ref when it can be imported, else reports why not."""
-    ref = os.path.join(ROOT, "baseline", "_ref")
-    why = None
-    if not os.path.isdir(os.path.join(ref, "makani")):
-        why = "reference not installed under baseline/_ref"
-    else:
-        sys.path.insert(0, ref)
-        try:
-            import makani  # noqa: F401
-        except Exception as e:  # missing torch_harmonics / modulus / ruamel / h5py in this image
-            why = f"reference import fails offline: {type(e).__name__}: {e}"
-        else:
-            why = "reference imported but its synthetic data path is not runnable offline"
-    if int(os.environ.get("RANK", "0")) == 0:
-        print(json.dumps({"impl": "reference", "unavailable": why}))
-    return 0
+    """Times the unmodified upstream package from baseline/_ref (see baseline/reference_arm.py)."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    try:
+        import reference_arm as arm
+    except Exception as e:
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"impl": "reference", "unavailable": f"baseline/reference_arm.py not importable: {type(e).__name__}: {e}"}))
+        return 0
+    return arm.run(args, clock_sampler_cls=ClockSampler)
 
 
 class ClockSampler:

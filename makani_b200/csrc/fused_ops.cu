@@ -906,6 +906,10 @@ cudaError_t lp_norms(const void* pred, const void* tgt, int is_f32, const float*
   const int chunks = lp_norms_chunks(hw);
   float* partial = scratch;
   int* counters = reinterpret_cast<int*>(scratch + static_cast<long long>(planes) * chunks * 2);
+  // The counters' position depends on (planes, chunks): a scratch buffer that served another shape holds partial sums
+  // there.  They are cleared on the stream before every launch (a memset node under graph capture).
+  cudaError_t me = cudaMemsetAsync(counters, 0, sizeof(int) * static_cast<size_t>(planes), s);
+  if (me != cudaSuccess) return me;
   dim3 grid(chunks, planes);
   if (is_f32) {
     if (P == 2) lp_norms_kernel<float, 2><<<grid, NT, 0, s>>>((const float*)pred, (const float*)tgt, qlat, out, partial, counters, W, hw, chunks);

@@ -311,6 +311,21 @@ def test_lp_norms_fwd_bwd():
             assert torch.equal(out, out2)
 
 
+def test_lp_norms_scratch_reuse_across_shapes():
+    """The cached scratch buffer serves calls of different (planes, chunks): large, small, larger again, each checked."""
+    from makani_b200.ops.loss import weighted_lp_norms
+    dev = _dev()
+    torch.manual_seed(18)
+    for (B, C, H, W) in [(2, 6, 130, 1024), (1, 3, 33, 64), (3, 6, 130, 1024), (1, 7, 70, 1000), (2, 6, 130, 1024)]:
+        q = torch.rand(H, device=dev) / (H * W)
+        pr = (torch.randn(B, C, H, W, device=dev) + 3.0).to(torch.bfloat16)
+        tg = torch.randn(B, C, H, W, device=dev).to(torch.bfloat16)
+        out = weighted_lp_norms(pr, tg, q, 2)
+        d = ((pr.float() - tg.float()) ** 2 * q.view(1, 1, -1, 1)).sum(dim=(-2, -1))
+        t = (tg.float() ** 2 * q.view(1, 1, -1, 1)).sum(dim=(-2, -1))
+        assert _rel(out[..., 0], d) < 1e-4 and _rel(out[..., 1], t) < 1e-4, (B, C, H, W)
+
+
 def test_fused_adamw_matches_torch():
     from makani_b200.ops.optim import FusedAdamW
     dev = _dev()
