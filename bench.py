@@ -292,6 +292,10 @@ def main():
     if native:
         _ext.check_device_errors(dev)
     final_loss = float(loss)
+    if os.environ.get("MAKANI_B200_DP_DIAG") == "timeline" and getattr(runner, "reducer", None) is not None:
+        rep = runner.reducer.timeline_report()
+        if rep is not None and rank == 0:
+            print("timeline " + json.dumps(rep), file=sys.stderr)
 
     # ---------------------------------------------------------------- end to end through the public API
     e2e = None
@@ -309,7 +313,8 @@ def main():
                        "parallelism": f"dp{dp}" + (f"xh{args.h}w{args.w}" if args.h * args.w > 1 else "")
                        + (f"xfin{args.fin}fout{args.fout}" if args.fin * args.fout > 1 else ""), "l2_policy": "inputs+activations per step (>2 GB) exceed the 126 MB L2",
                        "loss": cfg.loss, "optimizer": "AdamW (fused)" if native else "torch.optim.AdamW(foreach)",
-                       "cuda_graph": bool(cfg.graph), "final_loss": final_loss},
+                       "cuda_graph": bool(cfg.graph), "final_loss": final_loss,
+                       **({"diag": os.environ["MAKANI_B200_DP_DIAG"] + " (not a bench value)"} if os.environ.get("MAKANI_B200_DP_DIAG") else {})},
             "clocks": clocks, "gpu_launches": launches,
         }
         if e2e is not None:

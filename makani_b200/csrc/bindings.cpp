@@ -10,6 +10,7 @@
 #include <vector>
 
 #include "fused_ops.cuh"
+#include "gelu.cuh"
 #include "gemm_tcgen05.cuh"
 #include "peer.cuh"
 
@@ -191,7 +192,13 @@ void gemm_impl(const Tensor& a, const Tensor& b, Tensor& d, const c10::optional<
   e.act = ip[k++];
   const int64_t resid_off = ip[k++];
   const int64_t preact_off = ip[k++];
-  // remaining slots reserved
+  {
+    // bit pattern of the activation parameter (fp32), then one reserved slot
+    const uint32_t bits = static_cast<uint32_t>(ip[k++]);
+    float f;
+    memcpy(&f, &bits, sizeof(f));
+    e.act_param = f;
+  }
   e.bias = nullptr;
   if (bias.has_value() && bias->defined()) {
     MK_CHECK(bias->is_cuda() && bias->scalar_type() == torch::kFloat32 && bias->is_contiguous(), "gemm: bias must be contiguous fp32 CUDA");
@@ -354,9 +361,10 @@ void adamw_step(const Tensor& table, const Tensor& chunk_tensor, const Tensor& c
   static_assert(sizeof(mk::AdamEntry) == 56 || sizeof(mk::AdamEntry) == 64, "AdamEntry layout");
   MK_CHECK(table.size(1) * 8 == (int64_t)sizeof(mk::AdamEntry), "adamw: table row must be ", sizeof(mk::AdamEntry), " bytes");
   c10::cuda::CUDAGuard guard(table.device());
+  Tensor ef = err_flag_for(table);
   check_cuda(mk::adamw_step(reinterpret_cast<const mk::AdamEntry*>(table.data_ptr()), chunk_tensor.data_ptr<int>(),
                             reinterpret_cast<const long long*>(chunk_off.data_ptr<int64_t>()), static_cast<int>(chunk_tensor.numel()),
-                            chunk, hyper.data_ptr<float>(), cur_stream()),
+                            chunk, hyper.data_ptr<float>(), ef.data_ptr<int>(), cur_stream()),
              "adamw_step");
 }
 
@@ -435,7 +443,7 @@ Tensor tensor_from_ptr(int64_t ptr, int64_t bytes, int64_t device) {
 
 // in-place sum over ranks of `data` (fp32 or bf16) living in symmetric memory: ptrs[r] = rank r's copy.
 void peer_allreduce(const std::vector<int64_t>& data_ptrs, const std::vector<int64_t>& flag_ptrs, int64_t rank, int64_t n,
-                    int64_t is_bf16, double scale, int64_t epoch, int64_t device) {
+                    int64_t is_bf16, double scale, double wait_seconds, int64_t device) {
   const int world = static_cast<int>(data_ptrs.size());
   MK_CHECK(world >= 1 && world <= mk::PEER_MAX, "peer_allreduce: world size out of range");
   c10::cuda::CUDAGuard guard(c10::Device(c10::kCUDA, static_cast<int>(device)));
@@ -447,7 +455,7 @@ void peer_allreduce(const std::vector<int64_t>& data_ptrs, const std::vector<int
   Tensor dummy = torch::empty({1}, torch::dtype(torch::kUInt8).device(torch::kCUDA, static_cast<int>(device)));
   Tensor ef = err_flag_for(dummy);
   check_cuda(mk::peer_allreduce(pp, world, static_cast<int>(rank), n, static_cast<int>(is_bf16), static_cast<float>(scale),
-                                static_cast<unsigned int>(epoch), ef.data_ptr<int>(), cur_stream()),
+                                wait_seconds, ef.data_ptr<int>(), cur_stream()),
              "peer_allreduce");
 }
 
@@ -458,6 +466,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_peer", &gemm_peer, "tcgen05 GEMM reading its B operand from peer devices");
   m.def("peer_sum", &peer_sum, "sum of the local segments of a peer buffer with the consumer handshake");
   m.def("peer_publish", &peer_publish, "strided copy into this rank's and its peers' buffers with the producer handshake");
+  m.def("set_gelu_tanh", [](int64_t on) { mk::set_gelu_tanh(static_cast<int>(on)); });
   m.def("read_error_flag", &read_error_flag);
   m.def("clear_error_flag", &clear_error_flag);
   m.def("inorm_fwd", &inorm_fwd);

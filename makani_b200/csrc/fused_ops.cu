@@ -2,6 +2,7 @@
 // AdamW with bf16 shadow weights, spectral-weight re-layout.  Each kernel makes the minimum number of passes
 // over HBM (vectorised 16-byte accesses) and keeps reductions in fp32.
 #include "fused_ops.cuh"
+#include "gelu.cuh"
 #include <cstring>
 
 #include <math.h>
@@ -9,25 +10,32 @@
 namespace mk {
 
 namespace {
+int g_gelu_tanh = 0;
+}
+void set_gelu_tanh(int on) { g_gelu_tanh = on ? 1 : 0; }
+int gelu_tanh() { return g_gelu_tanh; }
+
+// number of SMs of the current device (cached per device index)
+int sm_count() {
+  static int cache[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cache[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cache[dev] = n;
+  }
+  return cache[dev];
+}
+
+namespace {
 
 constexpr int NT = 512;
 
-// tanh-form GELU with the hardware tanh approximation (same function as the GEMM epilogues use, so forward and
-// backward stay consistent across kernels); differs from the erf form by < 1e-3 absolute
-__device__ __forceinline__ float tanh_fast(float x) {
-  float y;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-__device__ __forceinline__ float gelu_f(float x) {
-  const float hx = 0.5f * x;
-  return fmaf(hx, tanh_fast(x * fmaf(x * x, 0.0356774081f, 0.7978845608f)), hx);
-}
-__device__ __forceinline__ float dgelu_f(float x) {
-  const float x2 = x * x;
-  const float t = tanh_fast(x * fmaf(x2, 0.0356774081f, 0.7978845608f));
-  return fmaf(0.5f * x * fmaf(-t, t, 1.0f), fmaf(x2, 0.1070322243f, 0.7978845608f), fmaf(0.5f, t, 0.5f));
-}
+// act: 0 none, 1 GELU (exact erf form), 2 GELU (tanh form); the launchers map the caller's on/off flag to 1 or 2
+// according to the process-wide setting
+__device__ __forceinline__ float gelu_f(float x, int act) { return gelu_fwd(x, act == 2); }
+__device__ __forceinline__ float dgelu_f(float x, int act) { return gelu_bwd(x, act == 2); }
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -146,14 +154,14 @@ __global__ void __launch_bounds__(NT) inorm_fwd_kernel(const __nv_bfloat16* __re
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         float v = f[j] * ga + be;
-        f[j] = act ? gelu_f(v) : v;
+        f[j] = act ? gelu_f(v, act) : v;
       }
       yv[i] = pack8(f);
     }
   } else {
     for (long long i = threadIdx.x; i < hw; i += NT) {
       float v = __bfloat162float(xp[i]) * ga + be;
-      yp[i] = __float2bfloat16(act ? gelu_f(v) : v);
+      yp[i] = __float2bfloat16(act ? gelu_f(v, act) : v);
     }
   }
 }
@@ -185,7 +193,7 @@ __global__ void __launch_bounds__(NT) inorm_bwd_kernel(const __nv_bfloat16* __re
         for (int j = 0; j < 8; ++j) {
           const float xh = (f[j] - mean) * rstd;
           float gg = g[j];
-          if (act) gg *= dgelu_f(xh * wc + bc);
+          if (act) gg *= dgelu_f(xh * wc + bc, act);
           s1 += gg;
           s2 += gg * xh;
         }
@@ -194,7 +202,7 @@ __global__ void __launch_bounds__(NT) inorm_bwd_kernel(const __nv_bfloat16* __re
       for (long long i = threadIdx.x; i < hw; i += NT) {
         const float xh = (__bfloat162float(xp[i]) - mean) * rstd;
         float gg = __bfloat162float(gp[i]);
-        if (act) gg *= dgelu_f(xh * wc + bc);
+        if (act) gg *= dgelu_f(xh * wc + bc, act);
         s1 += gg;
         s2 += gg * xh;
       }
@@ -229,7 +237,7 @@ __global__ void __launch_bounds__(NT) inorm_bwd_kernel(const __nv_bfloat16* __re
       for (int j = 0; j < 8; ++j) {
         const float xh = (f[j] - mean) * rstd;
         float gg = g[j];
-        if (act) gg *= dgelu_f(xh * wc + bc);
+        if (act) gg *= dgelu_f(xh * wc + bc, act);
         f[j] = sc * (gg - m1 - xh * m2);
       }
       ov[i] = pack8(f);
@@ -238,7 +246,7 @@ __global__ void __launch_bounds__(NT) inorm_bwd_kernel(const __nv_bfloat16* __re
     for (long long i = threadIdx.x; i < hw; i += NT) {
       const float xh = (__bfloat162float(xp[i]) - mean) * rstd;
       float gg = __bfloat162float(gp[i]);
-      if (act) gg *= dgelu_f(xh * wc + bc);
+      if (act) gg *= dgelu_f(xh * wc + bc, act);
       op[i] = __float2bfloat16(sc * (gg - m1 - xh * m2));
     }
   }
@@ -338,7 +346,7 @@ __global__ void __launch_bounds__(CL_THREADS) inorm_cl_sums_kernel(const __nv_bf
         for (int j = 0; j < 8; ++j) {
           const float xh = (f[j] - mean[j]) * rstd[j];
           float gg = g[j];
-          if (act) gg *= dgelu_f(xh * wc[j] + bc[j]);
+          if (act) gg *= dgelu_f(xh * wc[j] + bc[j], act);
           a0[j] += gg;
           a1[j] += gg * xh;
         }
@@ -491,7 +499,7 @@ __global__ void __launch_bounds__(CL_THREADS) inorm_cl_apply_kernel(const __nv_b
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const float val = fmaf(f[j], k0[j], k1[j]);
-        f[j] = act ? gelu_f(val) : val;
+        f[j] = act ? gelu_f(val, act) : val;
       }
     } else {
       float g[8];
@@ -500,7 +508,7 @@ __global__ void __launch_bounds__(CL_THREADS) inorm_cl_apply_kernel(const __nv_b
       for (int j = 0; j < 8; ++j) {
         const float xh = (f[j] - k0[j]) * k1[j];
         float gg = g[j];
-        if (act) gg *= dgelu_f(fmaf(xh, kw[j], kb[j]));
+        if (act) gg *= dgelu_f(fmaf(xh, kw[j], kb[j]), act);
         f[j] = k1[j] * kw[j] * (gg - k2[j] - xh * k3[j]);
       }
     }
@@ -629,7 +637,11 @@ __global__ void __launch_bounds__(NT) lp_bwd_kernel(const T* __restrict__ pred, 
 
 __global__ void __launch_bounds__(256) adamw_kernel(const AdamEntry* __restrict__ table, const int* __restrict__ chunk_tensor,
                                                     const long long* __restrict__ chunk_off, long long chunk,
-                                                    const float* __restrict__ hyper) {
+                                                    const float* __restrict__ hyper, const int* __restrict__ err) {
+  // A bounded wait that ran out earlier in this step (a lost peer in the gradient all-reduce, a handshake that timed
+  // out) leaves gradients that are incomplete: the update is skipped, so that the replicas stay identical until the
+  // host reads the error word and raises.
+  if (err != nullptr && *reinterpret_cast<const volatile int*>(err) != 0) return;
   const AdamEntry e = table[chunk_tensor[blockIdx.x]];
   const long long off = chunk_off[blockIdx.x];
   long long n = e.n - off;
@@ -828,6 +840,7 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 cudaError_t inorm_fwd(const __nv_bfloat16* x, __nv_bfloat16* y, const float* w, const float* b, float* stats, int planes,
                       int C, long long hw, float eps, int act, int ext_stats, cudaStream_t s) {
+  if (act) act = gelu_tanh() ? 2 : 1;
   if (planes <= 0) return cudaSuccess;
   const bool vec = (hw % 8 == 0) && aligned16(x) && aligned16(y);
   const int mode = ext_stats ? 2 : 0;
@@ -847,6 +860,7 @@ cudaError_t inorm_partial_stats(const __nv_bfloat16* x, float* sums, int planes,
 cudaError_t inorm_bwd(const __nv_bfloat16* x, const __nv_bfloat16* dy, __nv_bfloat16* dx, const float* w, const float* b,
                       const float* stats, float* dw, float* db, float* sums_io, int planes, int C, long long hw,
                       double count, int act, int ext_sums, cudaStream_t s) {
+  if (act) act = gelu_tanh() ? 2 : 1;
   if (planes <= 0) return cudaSuccess;
   const bool vec = (hw % 8 == 0) && aligned16(x) && aligned16(dy) && (dx == nullptr || aligned16(dx));
   const float inv = static_cast<float>(1.0 / count);
@@ -859,7 +873,7 @@ static inline bool cl_ok(int C) { return C % 8 == 0 && C >= 8 && C <= 1024 && (C
 // tokens per CTA: enough CTAs to fill the machine a few times over, but at least a few passes of the row loop each
 static inline int cl_slab(int C, long long T, int B, int ctas_per_sm = 4) {
   const int R = CL_THREADS / (C / 8);
-  long long target = (static_cast<long long>(ctas_per_sm) * 148 + B - 1) / B;
+  long long target = (static_cast<long long>(ctas_per_sm) * sm_count() + B - 1) / B;
   long long slab = (T + target - 1) / target;
   if (slab < 4LL * R) slab = 4LL * R;
   return static_cast<int>(slab);
@@ -868,6 +882,7 @@ static inline int cl_slab(int C, long long T, int B, int ctas_per_sm = 4) {
 cudaError_t inorm_cl_sums(const __nv_bfloat16* x, const __nv_bfloat16* dy, const float* w, const float* b, const float* stats,
                           float* sums, float* dw, float* db, int B, int C, long long T, int act, int mode, cudaStream_t s,
                           const StatExchange* xch) {
+  if (act) act = gelu_tanh() ? 2 : 1;
   if (!cl_ok(C)) return cudaErrorInvalidValue;
   StatExchange xc;
   memset(&xc, 0, sizeof(xc));
@@ -884,6 +899,7 @@ cudaError_t inorm_cl_sums(const __nv_bfloat16* x, const __nv_bfloat16* dy, const
 cudaError_t inorm_cl_apply(const __nv_bfloat16* x, const __nv_bfloat16* dy, __nv_bfloat16* out, const float* w, const float* b,
                            const float* sums, float* stats, int B, int C, long long T, double count, float eps, int act, int mode,
                            cudaStream_t s, const StatExchange* xch) {
+  if (act) act = gelu_tanh() ? 2 : 1;
   if (!cl_ok(C)) return cudaErrorInvalidValue;
   StatExchange xc;
   memset(&xc, 0, sizeof(xc));
@@ -937,9 +953,9 @@ cudaError_t lp_norms_bwd(const void* pred, const void* tgt, int is_f32, const fl
 }
 
 cudaError_t adamw_step(const AdamEntry* table, const int* chunk_tensor, const long long* chunk_off, int nchunks,
-                       long long chunk, const float* hyper, cudaStream_t s) {
+                       long long chunk, const float* hyper, const int* err, cudaStream_t s) {
   if (nchunks <= 0) return cudaSuccess;
-  adamw_kernel<<<nchunks, 256, 0, s>>>(table, chunk_tensor, chunk_off, chunk, hyper);
+  adamw_kernel<<<nchunks, 256, 0, s>>>(table, chunk_tensor, chunk_off, chunk, hyper, err);
   return cudaGetLastError();
 }
 
@@ -961,7 +977,7 @@ cudaError_t swap_ri_bf16(const __nv_bfloat16* in, __nv_bfloat16* out, long long 
     return cudaErrorInvalidValue;
   const long long total = rows * 2 * (C / 8);
   long long blocks = (total + 255) / 256;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks > sm_count() * 8) blocks = sm_count() * 8;
   swap_ri_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(reinterpret_cast<const uint4*>(in), reinterpret_cast<uint4*>(out),
                                                                rows, C / 8);
   return cudaGetLastError();
@@ -970,7 +986,7 @@ cudaError_t swap_ri_bf16(const __nv_bfloat16* in, __nv_bfloat16* out, long long 
 cudaError_t cast_f32_bf16(const float* x, __nv_bfloat16* y, long long n, cudaStream_t s) {
   if (n <= 0) return cudaSuccess;
   long long blocks = (n + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > sm_count() * 16) blocks = sm_count() * 16;
   cast_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(x, y, n);
   return cudaGetLastError();
 }
@@ -978,7 +994,7 @@ cudaError_t cast_f32_bf16(const float* x, __nv_bfloat16* y, long long n, cudaStr
 cudaError_t fill_normal_bf16(__nv_bfloat16* y, long long n, uint64_t seed, cudaStream_t s) {
   if (n <= 0) return cudaSuccess;
   long long blocks = ((n + 1) / 2 + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > sm_count() * 16) blocks = sm_count() * 16;
   fill_normal_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(y, n, seed);
   return cudaGetLastError();
 }

@@ -7,6 +7,9 @@
 
 namespace mk {
 
+// number of SMs of the current device
+int sm_count();
+
 // ---- instance norm over the last `hw` elements of each of `planes` = B*C rows (channel = plane % C) ----
 // stats: [planes, 2] fp32 (mean, rstd) written by fwd, read by bwd.  act: 0 none, 1 GELU applied after the affine.
 // If `ext_stats` is non-zero the forward skips the reduction and uses the (mean, rstd) already in `stats`
@@ -77,8 +80,9 @@ struct AdamEntry {
   int pair_mode;           // 1: elements are (re, im) pairs sharing one second moment |g|^2
 };
 // hyper (device, fp32[8]): lr, beta1, beta2, eps, weight_decay, step, grad_scale, adamw(1)/adam-L2(0)
+// err (optional): the device error word; the update is skipped while it is non-zero
 cudaError_t adamw_step(const AdamEntry* table, const int* chunk_tensor, const long long* chunk_off, int nchunks,
-                       long long chunk, const float* hyper, cudaStream_t s);
+                       long long chunk, const float* hyper, const int* err, cudaStream_t s);
 
 // ---- spectral weight re-layout ----
 // w: complex64 [Cin, Cout, L] (interleaved) -> wx: bf16 [L, 2*Cout, 2*Cin] real 2x2-block form

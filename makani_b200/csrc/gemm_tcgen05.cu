@@ -9,6 +9,13 @@
 // Two accumulator buffers in TMEM let the epilogue of tile i overlap the main loop of tile i+1.
 // Every mbarrier wait is bounded; on expiry the kernel records a code in *err and drains.
 //
+// CTA pairs (template parameter CG = 2, single-GPU launches only): two CTAs of a thread-block cluster share one
+// 256-row tile.  Each CTA loads its own 128 rows of A and HALF of the B tile (plain TMA loads, no multicast, whose
+// completion is counted on the leader CTA's barrier); the leader issues tcgen05.mma.cta_group::2, which reads both
+// CTAs' shared memory and writes 128 accumulator rows into each CTA's TMEM; tcgen05.commit multicasts the
+// "stage free" and "accumulator full" signals to both CTAs.  Per tensor-core cycle every SM then takes a third less
+// data from L2 (two thirds with 128-wide tiles), which is what bounds these GEMMs.
+//
 // Multi-GPU use (one process per GPU, buffers mapped through CUDA IPC):
 //   * the k axis of the B operand may be cut into up to 8 segments with their own base pointers and tensor maps
 //     (the per-rank segments of a gathered buffer in this device's own memory);
@@ -17,6 +24,8 @@
 //   * producer / consumer ordering across devices uses monotonic counters (PeerSync) checked by the first thread of
 //     every CTA before any work and advanced by the last CTA of the grid.
 #include "gemm_tcgen05.cuh"
+#include "gelu.cuh"
+#include "fused_ops.cuh"
 
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -70,7 +79,8 @@ struct KParams {
   int ndiv; long long ns_hi;
   float alpha;
   const float* bias;
-  int bias_mode, act;
+  int bias_mode, act, gelu_tanh;
+  float act_param;
   const void* resid;
   void* preact;
   void* D;
@@ -145,6 +155,34 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
+// CTA-pair form: the destination is this CTA's shared memory, the barrier that counts the bytes lives in the leader CTA
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int c0, int c1,
+                                                 int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(map), "r"(leader_bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+// address of the same shared-memory offset in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 __device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3) {
   asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(map), "r"(src),
                "r"(c0), "r"(c1), "r"(c2), "r"(c3)
@@ -164,10 +202,26 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+// pair form: arrives on the barrier at this offset in both CTAs of the pair
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+  const unsigned short mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+               "h"(mask)
+               : "memory");
+}
 
-template <int EB>
+template <int EB, int CG>
 __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accum) {
-  if constexpr (EB == 2) {
+  if constexpr (EB == 2 && CG == 2) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "l"(da), "l"(db), "r"(idesc), "r"(accum)
+        : "memory");
+  } else if constexpr (EB == 2) {
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
@@ -213,36 +267,16 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes
   return d;
 }
 
-// GELU in its tanh form, 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))), evaluated with the hardware
-// tanh.approx instruction.  It differs from the erf form by < 1e-3 absolute, below the bf16 rounding of the outputs
-// it feeds, and costs 6 instructions per element instead of ~20, which keeps the epilogue off the critical path.
-__device__ __forceinline__ float tanh_fast(float x) {
-  float y;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-__device__ __forceinline__ float gelu_erf(float x) {
-  const float u = x * fmaf(x * x, 0.0356774081f, 0.7978845608f);
-  const float hx = 0.5f * x;
-  return fmaf(hx, tanh_fast(u), hx);
-}
-// derivative of the same function
-__device__ __forceinline__ float gelu_grad(float x) {
-  const float x2 = x * x;
-  const float t = tanh_fast(x * fmaf(x2, 0.0356774081f, 0.7978845608f));
-  const float dt = fmaf(-t, t, 1.0f);
-  const float du = fmaf(x2, 0.1070322243f, 0.7978845608f);
-  return fmaf(0.5f * x * dt, du, fmaf(0.5f, t, 0.5f));
-}
-
 struct TileCoord {
   int zhi, zlo, split, mt, nt;
   int k_begin, k_end;   // element range, k_begin multiple of BK
   bool skip;
 };
 
-template <int BK>
-__device__ __forceinline__ TileCoord decode_tile(const KParams& p, long long t) {
+// CG = 2: `t` counts 256-row pair tiles (p.m_tiles is then the number of pair tiles) and `half` (0 / 1) selects this
+// CTA's 128 rows; skip decisions are taken for the pair as a whole because the MMA is issued once for both CTAs.
+template <int BK, int CG = 1>
+__device__ __forceinline__ TileCoord decode_tile(const KParams& p, long long t, int half = 0) {
   TileCoord c;
   // The index that varies fastest walks over the tiles that share the larger operand, so that the CTAs of one wave
   // fetch that operand's tile from DRAM once and hit L2 for the rest (token-major convolutions: many m-tiles of
@@ -276,8 +310,9 @@ __device__ __forceinline__ TileCoord decode_tile(const KParams& p, long long t) 
   if (ke > kmax) ke = kmax;
   c.k_begin = kb;
   c.k_end = ke;
-  const int r0 = c.mt * BM;
-  c.skip = (r0 + BM <= rmin) || (r0 >= rmax) || (p.nseg == 1 && kb >= ke);
+  const int r0 = c.mt * (BM * CG);
+  c.skip = (r0 + BM * CG <= rmin) || (r0 >= rmax) || (p.nseg == 1 && kb >= ke);
+  if constexpr (CG == 2) c.mt = c.mt * 2 + half;   // from here on: this CTA's own 128-row block
   return c;
 }
 
@@ -302,7 +337,7 @@ __device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int* p
   return v;
 }
 
-template <int BN, int EB, int EPI>
+template <int BN, int EB, int EPI, int CG>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ BMaps maps_b,
             const __grid_constant__ CUtensorMap map_e, const __grid_constant__ CUtensorMap map_d,
@@ -310,7 +345,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
   const CUtensorMap& map_b = maps_b.m[0];
   constexpr int BK = 128 / EB;            // elements per 128-byte k-slab
   constexpr int UMMA_K = 32 / EB;         // elements per tcgen05.mma
-  constexpr int B_STAGE_BYTES = BN * 128;
+  constexpr int BNL = BN / CG;            // rows of the B tile this CTA loads (a pair splits the tile)
+  constexpr int B_STAGE_BYTES = BNL * 128;
   constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
   constexpr int MN_BOX = 128 / EB;        // extent of an MN-major box along the contiguous dimension
   constexpr uint32_t TMEM_COLS = 2 * BN;
@@ -339,6 +375,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // pair geometry: `crank` = rank inside the cluster (the leader is rank 0), tiles are dealt out per cluster
+  const int crank = (CG == 2) ? static_cast<int>(cluster_ctarank()) : 0;
+  const long long tile0 = (CG == 2) ? (blockIdx.x >> 1) : blockIdx.x;
+  const long long tile_step = (CG == 2) ? (gridDim.x >> 1) : gridDim.x;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -347,7 +387,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(tfull_bar(b), 1);
-      mbar_init(tempty_bar(b), 8);
+      mbar_init(tempty_bar(b), 8 * CG);
       mbar_init(efull_bar(b), 1);
       mbar_init(eempty_bar(b), 8);
     }
@@ -377,14 +417,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
     tmem_slot[1] = ok ? 1u : 0u;
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                     smem_u32(const_cast<uint32_t*>(tmem_slot))),
-                 "r"(TMEM_COLS)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if constexpr (CG == 2) {
+      // the same warp of both CTAs allocates, with the same destination offset
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                       smem_u32(const_cast<uint32_t*>(tmem_slot))),
+                   "r"(TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                       smem_u32(const_cast<uint32_t*>(tmem_slot))),
+                   "r"(TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (CG == 2) cluster_sync_all();   // the partner's barriers are initialised before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const bool peers_ready = tmem_slot[1] != 0u;
@@ -396,8 +446,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
       uint32_t ph = 0, epi_it = 0;
       bool ok = peers_ready;
       if (p.sync.nwait > 0) asm volatile("fence.proxy.async;" ::: "memory");   // flags acquired in the prologue order the TMA loads below
-      for (long long t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
-        const TileCoord c = decode_tile<BK>(p, t);
+      // pair: every load of both CTAs is counted on the leader's "full" barrier
+      const uint32_t leader_full0 = (CG == 2) ? mapa_u32(full_bar(0), 0) : 0u;
+      for (long long t = tile0; t < p.total_tiles && ok; t += tile_step) {
+        const TileCoord c = decode_tile<BK, CG>(p, t, crank);
         const int m0 = c.mt * BM, n0 = c.nt * BN;
         if (p.e_tma && !(c.skip && p.accumulate)) {
           // epilogue operand (residual / saved pre-activation) for this tile
@@ -430,23 +482,45 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
               ok = false;
               break;
             }
-            mbar_expect_tx(full_bar(s), STAGE_BYTES);
             const uint32_t sa = smem_base + s * STAGE_BYTES;
             const uint32_t sb = sa + A_STAGE_BYTES;
             const int ka = apos + k;
-            if (!p.a_mn) {
-              tma_load_4d(sa, &map_a, full_bar(s), ka, m0, azl, azh);
-            } else {
+            if constexpr (CG == 2) {
+              // the leader announces the bytes of both CTAs; the partner's loads may land first (the barrier's byte
+              // count goes negative for a moment, its phase cannot complete before the leader's arrival)
+              if (crank == 0) mbar_expect_tx(full_bar(s), 2 * STAGE_BYTES);
+              const uint32_t lbar = leader_full0 + 8u * s;
+              const int nb0 = n0 + crank * BNL;
+              if (!p.a_mn) {
+                tma_load_4d_pair(sa, &map_a, lbar, ka, m0, azl, azh);
+              } else {
 #pragma unroll
-              for (int j = 0; j < BM / MN_BOX; ++j)
-                tma_load_4d(sa + j * (BK * 128), &map_a, full_bar(s), m0 + j * MN_BOX, ka, azl, azh);
-            }
-            if (!p.b_mn) {
-              tma_load_4d(sb, mb, full_bar(s), k, n0, bzl, bzh);
-            } else {
+                for (int j = 0; j < BM / MN_BOX; ++j)
+                  tma_load_4d_pair(sa + j * (BK * 128), &map_a, lbar, m0 + j * MN_BOX, ka, azl, azh);
+              }
+              if (!p.b_mn) {
+                tma_load_4d_pair(sb, mb, lbar, k, nb0, bzl, bzh);
+              } else {
 #pragma unroll
-              for (int j = 0; j < BN / MN_BOX; ++j)
-                tma_load_4d(sb + j * (BK * 128), mb, full_bar(s), n0 + j * MN_BOX, k, bzl, bzh);
+                for (int j = 0; j < BNL / MN_BOX; ++j)
+                  tma_load_4d_pair(sb + j * (BK * 128), mb, lbar, nb0 + j * MN_BOX, k, bzl, bzh);
+              }
+            } else {
+              mbar_expect_tx(full_bar(s), STAGE_BYTES);
+              if (!p.a_mn) {
+                tma_load_4d(sa, &map_a, full_bar(s), ka, m0, azl, azh);
+              } else {
+#pragma unroll
+                for (int j = 0; j < BM / MN_BOX; ++j)
+                  tma_load_4d(sa + j * (BK * 128), &map_a, full_bar(s), m0 + j * MN_BOX, ka, azl, azh);
+              }
+              if (!p.b_mn) {
+                tma_load_4d(sb, mb, full_bar(s), k, n0, bzl, bzh);
+              } else {
+#pragma unroll
+                for (int j = 0; j < BN / MN_BOX; ++j)
+                  tma_load_4d(sb + j * (BK * 128), mb, full_bar(s), n0 + j * MN_BOX, k, bzl, bzh);
+              }
             }
             if (++s == STAGES) {
               s = 0;
@@ -458,12 +532,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      // instruction descriptor: fp32 accumulate, operand format, majors, N, M
+    if (lane == 0 && crank == 0) {
+      // instruction descriptor: fp32 accumulate, operand format, majors, N, M (256 rows for a CTA pair)
       const uint32_t fmt = (EB == 2) ? 1u : 2u;   // BF16 : TF32
       const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(p.a_mn) << 15) |
                              (static_cast<uint32_t>(p.b_mn) << 16) | (static_cast<uint32_t>(BN >> 3) << 17) |
-                             (static_cast<uint32_t>(BM >> 4) << 24);
+                             (static_cast<uint32_t>((BM * CG) >> 4) << 24);
       const uint32_t a_lbo = p.a_mn ? BK * 128 : 16, a_sbo = 1024;
       const uint32_t b_lbo = p.b_mn ? BK * 128 : 16, b_sbo = 1024;
       const uint32_t a_kstep = p.a_mn ? UMMA_K * 128 : 32;
@@ -471,8 +545,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
       int s = 0;
       uint32_t ph = 0, acc_it = 0;
       bool ok = peers_ready;
-      for (long long t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
-        const TileCoord c = decode_tile<BK>(p, t);
+      for (long long t = tile0; t < p.total_tiles && ok; t += tile_step) {
+        const TileCoord c = decode_tile<BK, CG>(p, t, crank);
         if (c.skip) continue;
         const int buf = acc_it & 1;
         if (!mbar_wait(tempty_bar(buf), ((acc_it >> 1) & 1u) ^ 1u)) {
@@ -505,16 +579,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
           for (int kk = 0; kk < BK / UMMA_K; ++kk) {
             const uint64_t da = make_desc(sa + kk * a_kstep, a_lbo, a_sbo);
             const uint64_t db = make_desc(sb + kk * b_kstep, b_lbo, b_sbo);
-            tc_mma<EB>(tmem_d, da, db, idesc, accum);
+            tc_mma<EB, CG>(tmem_d, da, db, idesc, accum);
             accum = 1;
           }
-          tc_commit(empty_bar(s));   // frees the smem stage once these MMAs have read it
+          // frees the smem stage (in both CTAs of a pair) once these MMAs have read it
+          if constexpr (CG == 2) tc_commit_pair(empty_bar(s));
+          else tc_commit(empty_bar(s));
           if (++s == STAGES) {
             s = 0;
             ph ^= 1u;
           }
         }
-        tc_commit(tfull_bar(buf));   // accumulator complete
+        if constexpr (CG == 2) tc_commit_pair(tfull_bar(buf));   // accumulator complete (both halves)
+        else tc_commit(tfull_bar(buf));
         ++acc_it;
       }
     }
@@ -526,8 +603,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
     const int half = (warp - 2) >> 2;
     uint32_t acc_it = 0, epi_it = 0;
     bool ok = peers_ready;
-    for (long long t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
-      const TileCoord c = decode_tile<BK>(p, t);
+    // the "accumulator drained" barrier of a pair lives in the leader and counts the warps of both CTAs
+    const uint32_t leader_tempty0 = (CG == 2) ? mapa_u32(tempty_bar(0), 0) : 0u;
+    for (long long t = tile0; t < p.total_tiles; t += tile_step) {
+      const TileCoord c = decode_tile<BK, CG>(p, t, crank);
       if (c.skip && p.accumulate) continue;
       const int rt = q * 32 + lane;                 // row inside the tile
       const int r = c.mt * BM + rt;
@@ -596,13 +675,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
               }
             }
             const uint32_t sw = static_cast<uint32_t>((g ^ (lane & 7)) << 4) + lane * 128;
+            if constexpr (EPI == 1) {
+              if (p.act != 0) {      // ReLU / soft shrinkage (uniform over the launch)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = act_fwd(f[j], p.act, p.act_param, p.gelu_tanh);
+              }
+            }
             if constexpr (EPI == 2) {
               __nv_bfloat162 h[4];
 #pragma unroll
               for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
               *reinterpret_cast<uint4*>(box_p + sw) = *reinterpret_cast<uint4*>(h);
 #pragma unroll
-              for (int j = 0; j < 8; ++j) f[j] = gelu_erf(f[j]);
+              for (int j = 0; j < 8; ++j) f[j] = gelu_fwd(f[j], p.gelu_tanh);
             }
             if constexpr (EPI == 3 || EPI == 4) {
               const uint4 ev = *reinterpret_cast<const uint4*>(esm + bx * (BM * 128) + rt * 128 + ((g ^ (rt & 7)) << 4));
@@ -614,8 +699,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
                   f[2 * j] += x.x;
                   f[2 * j + 1] += x.y;
                 } else {
-                  f[2 * j] *= gelu_grad(x.x);
-                  f[2 * j + 1] *= gelu_grad(x.y);
+                  f[2 * j] *= act_bwd(x.x, p.act, p.gelu_tanh);
+                  f[2 * j + 1] *= act_bwd(x.y, p.act, p.gelu_tanh);
                 }
               }
             }
@@ -699,9 +784,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
                 *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.preact) + off) = *reinterpret_cast<uint4*>(h);
               }
             }
-            if (p.act == 1) {
+            if (p.act & 1) {
 #pragma unroll
-              for (int j = 0; j < 8; ++j) f[j] = gelu_erf(f[j]);
+              for (int j = 0; j < 8; ++j) f[j] = act_fwd(f[j], p.act, p.act_param, p.gelu_tanh);
             }
             if (p.resid) {
               if (!p.e_tma) {
@@ -722,7 +807,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
                 }
               }
 #pragma unroll
-              for (int j = 0; j < 8; ++j) f[j] = (p.act == 2) ? f[j] * gelu_grad(e8[j]) : f[j] + e8[j];
+              for (int j = 0; j < 8; ++j) f[j] = (p.act != 0 && !(p.act & 1)) ? f[j] * act_bwd(e8[j], p.act, p.gelu_tanh) : f[j] + e8[j];
             }
             if (p.out_f32) {
               float4* o = reinterpret_cast<float4*>(static_cast<float*>(p.D) + off);
@@ -753,7 +838,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
                 if (p.out_f32) static_cast<float*>(p.preact)[o] = x;
                 else static_cast<__nv_bfloat16*>(p.preact)[o] = __float2bfloat16(x);
               }
-              if (p.act == 1) x = gelu_erf(x);
+              if (p.act & 1) x = act_fwd(x, p.act, p.act_param, p.gelu_tanh);
               if (p.accumulate) {
                 atomicAdd(static_cast<float*>(p.D) + o, x);
               } else {
@@ -762,7 +847,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
                   if (p.e_tma) rr = e8[j];
                   else rr = p.out_f32 ? static_cast<const float*>(p.resid)[o]
                                       : __bfloat162float(static_cast<const __nv_bfloat16*>(p.resid)[o]);
-                  x = (p.act == 2) ? x * gelu_grad(rr) : x + rr;
+                  x = (p.act != 0 && !(p.act & 1)) ? x * act_bwd(rr, p.act, p.gelu_tanh) : x + rr;
                 }
                 if (p.out_f32) static_cast<float*>(p.D)[o] = x;
                 else {
@@ -777,7 +862,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
       if (!c.skip) {
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(tempty_bar(buf));
+        if (lane == 0) {
+          if constexpr (CG == 2) mbar_arrive_cluster(leader_tempty0 + 8u * buf);
+          else mbar_arrive(tempty_bar(buf));
+        }
         ++acc_it;
       }
       if (p.e_tma) {
@@ -815,9 +903,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
       }
     }
   }
+  if constexpr (CG == 2) cluster_sync_all();   // neither CTA leaves (or frees TMEM) while its partner may still touch it
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    if constexpr (CG == 2)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
@@ -892,10 +984,10 @@ bool make_map(CUtensorMap* map, const GemmOperand& op, int K, int eb, int zlo_n,
 
 constexpr int SMEM_LIMIT = 232448;   // 227 KB per CTA on sm_100
 
-template <int BN, int EB, int EPI>
+template <int BN, int EB, int EPI, int CG>
 cudaError_t launch_t(const CUtensorMap& ma, const BMaps& mb, const CUtensorMap& me, const CUtensorMap& md,
                      const CUtensorMap& mp, const DMaps& mdx, KParams& kp, cudaStream_t stream) {
-  constexpr int STAGE = A_STAGE_BYTES + BN * 128;
+  constexpr int STAGE = A_STAGE_BYTES + (BN / CG) * 128;
   constexpr int FIXED = (EPI != 0 ? STG_BYTES : 0) + 8 * (2 * MAX_STAGES + 8) + 16 + 1024;
   const int e_bytes = kp.e_tma ? 2 * BM * BN * 2 : 0;
   int stages = (SMEM_LIMIT - FIXED - e_bytes) / STAGE;
@@ -907,24 +999,61 @@ cudaError_t launch_t(const CUtensorMap& ma, const BMaps& mb, const CUtensorMap& 
   kp.stages = stages;
   const int smem = stages * STAGE + e_bytes + FIXED;
   static bool configured = false;
-  static int num_sms = 0;
+  static int pair_clusters = 0;     // CTA pairs that can be resident at once (CG = 2)
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN, EB, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
+    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN, EB, EPI, CG>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
     if (e != cudaSuccess) return e;
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (CG == 2) {
+      cudaLaunchConfig_t qc;
+      memset(&qc, 0, sizeof(qc));
+      cudaLaunchAttribute qa[1];
+      qa[0].id = cudaLaunchAttributeClusterDimension;
+      qa[0].val.clusterDim.x = 2;
+      qa[0].val.clusterDim.y = 1;
+      qa[0].val.clusterDim.z = 1;
+      qc.gridDim = dim3(2 * (sm_count() / 2), 1, 1);
+      qc.blockDim = dim3(NUM_THREADS, 1, 1);
+      qc.dynamicSmemBytes = SMEM_LIMIT;
+      qc.attrs = qa;
+      qc.numAttrs = 1;
+      int n = 0;
+      e = cudaOccupancyMaxActiveClusters(&n, gemm_kernel<BN, EB, EPI, CG>, &qc);
+      if (e != cudaSuccess || n < 1) {
+        (void)cudaGetLastError();
+        n = sm_count() / 2;
+      }
+      pair_clusters = n;
+    }
     configured = true;
   }
+  const int num_sms = sm_count();
   // tile order (MAKANI_B200_TILE_ORDER=m|n forces one order for A/B timing)
   static const int forced_order = [] {
     const char* e = getenv("MAKANI_B200_TILE_ORDER");
     return (e && e[0] == 'm') ? 0 : ((e && e[0] == 'n') ? 1 : -1);
   }();
   kp.n_fast = forced_order >= 0 ? forced_order : (kp.m_tiles > kp.n_tiles ? 1 : 0);
+  if (CG == 2) {
+    long long clusters = kp.total_tiles < pair_clusters ? kp.total_tiles : pair_clusters;
+    if (clusters < 1) clusters = 1;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters), 1, 1);
+    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gemm_kernel<BN, EB, EPI, CG>, ma, mb, me, md, mp, mdx, kp);
+  }
   long long grid = kp.total_tiles < num_sms ? kp.total_tiles : num_sms;
   if (grid < 1) grid = 1;
-  gemm_kernel<BN, EB, EPI><<<static_cast<unsigned>(grid), NUM_THREADS, smem, stream>>>(ma, mb, me, md, mp, mdx, kp);
+  gemm_kernel<BN, EB, EPI, CG><<<static_cast<unsigned>(grid), NUM_THREADS, smem, stream>>>(ma, mb, me, md, mp, mdx, kp);
   return cudaGetLastError();
 }
 
@@ -1122,7 +1251,7 @@ cudaError_t peer_publish_launch(const void* src, long long rows, long long row_b
     if (reinterpret_cast<uintptr_t>(dsts[q]) & 15) return cudaErrorInvalidValue;
   const long long total = rows * (row_bytes / 16);
   long long blocks = (total + 255) / 256;
-  if (blocks > 148 * 4) blocks = 148 * 4;
+  if (blocks > sm_count() * 4LL) blocks = sm_count() * 4LL;
   peer_publish_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
       static_cast<const uint4*>(src), rows, static_cast<int>(row_bytes / 16), src_stride_bytes / 16, dst_stride_bytes / 16,
       ndst, sy, err_flag);
@@ -1143,7 +1272,7 @@ cudaError_t peer_sum_launch(void* out, long long n_elems, const void* const* src
   }
   const long long nvec = n_elems / 8;
   long long blocks = (nvec + 255) / 256;
-  if (blocks > 148 * 4) blocks = 148 * 4;
+  if (blocks > sm_count() * 4LL) blocks = sm_count() * 4LL;
   peer_sum_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(static_cast<uint4*>(out), nvec, nsrc, bias, C, sy, err_flag);
   return cudaGetLastError();
 }
@@ -1203,7 +1332,7 @@ cudaError_t gemm_launch(const GemmProblem& p, const GemmOperand& A, const GemmOp
   kp.d_zlo = e.d_zlo; kp.d_zhi = e.d_zhi;
   kp.rdiv = e.rdiv > 0 ? e.rdiv : 1 << 30; kp.rs_hi = e.rs_hi; kp.rs_lo = e.rs_lo;
   kp.ndiv = e.ndiv > 0 ? e.ndiv : 1 << 30; kp.ns_hi = e.ns_hi;
-  kp.alpha = e.alpha; kp.bias = e.bias; kp.bias_mode = e.bias ? e.bias_mode : 0; kp.act = e.act;
+  kp.alpha = e.alpha; kp.bias = e.bias; kp.bias_mode = e.bias ? e.bias_mode : 0; kp.act = e.act; kp.gelu_tanh = gelu_tanh(); kp.act_param = e.act_param;
   kp.resid = e.resid; kp.preact = e.preact; kp.D = e.D;
   kp.out_f32 = e.out_f32; kp.accumulate = e.accumulate;
   // 16-byte vector accesses need every stride (and the bases) aligned
@@ -1254,19 +1383,30 @@ cudaError_t gemm_launch(const GemmProblem& p, const GemmOperand& A, const GemmOp
       bn = 128;
     }
   }
+  // CTA pairs (256-row tiles, each CTA loads half of the B tile): single-device bf16 launches without row-triangular
+  // structure and with at least two row blocks.  MAKANI_B200_CTA_PAIRS=0 keeps every launch on single CTAs.
+  static const int pairs_enabled = [] {
+    const char* e = getenv("MAKANI_B200_CTA_PAIRS");
+    return (e && e[0] == '0') ? 0 : 1;
+  }();
+  const bool no_peer = (peer == nullptr) || (peer->nseg <= 1 && peer->ndx == 0 && peer->nwait == 0 && peer->nsig == 0 &&
+                                              peer->done_ctr == nullptr);
+  const int cg = (pairs_enabled && eb == 2 && no_peer && p.M > BM && p.rmin_a == 0 && p.rmax_a == 0) ? 2 : 1;
+  kp.m_tiles = (p.M + BM * cg - 1) / (BM * cg);
   kp.n_tiles = (p.N + bn - 1) / bn;
   kp.total_tiles = static_cast<long long>(kp.m_tiles) * kp.n_tiles * kp.splits * p.zlo_n * p.zhi_n;
   if (!make_map(&ma, A, p.K, eb, p.zlo_n, p.zhi_n, BM)) return cudaErrorInvalidValue;
+  const int bn_box = bn / cg;     // rows of B one CTA loads per stage
   BMaps mbs;
   if (kp.nseg > 1) {
     for (int q = 0; q < kp.nseg; ++q) {
       GemmOperand Bq = B;
       Bq.ptr = peer->seg_ptr[q];
-      if (!make_map(&mbs.m[q], Bq, peer->seg_len[q], eb, p.zlo_n, p.zhi_n, bn)) return cudaErrorInvalidValue;
+      if (!make_map(&mbs.m[q], Bq, peer->seg_len[q], eb, p.zlo_n, p.zhi_n, bn_box)) return cudaErrorInvalidValue;
     }
     for (int q = kp.nseg; q < MAX_SEG; ++q) mbs.m[q] = mbs.m[0];
   } else {
-    if (!make_map(&mb, B, p.K, eb, p.zlo_n, p.zhi_n, bn)) return cudaErrorInvalidValue;
+    if (!make_map(&mb, B, p.K, eb, p.zlo_n, p.zhi_n, bn_box)) return cudaErrorInvalidValue;
     for (int q = 0; q < MAX_SEG; ++q) mbs.m[q] = mb;
   }
   if (!kp.e_tma) me = ma;   // unused, but must be a valid descriptor
@@ -1282,10 +1422,10 @@ cudaError_t gemm_launch(const GemmProblem& p, const GemmOperand& A, const GemmOp
   for (int q = 0; q < MAX_SEG - 1; ++q) mdx.m[q] = ma;   // placeholders: always valid descriptors
   if (eb == 2 && !e.out_f32 && kp.vec_ok && !e.accumulate && plain && e.d_zlo >= 0 && e.d_zhi >= 0 &&
       (kp.bias_mode != 2 || (reinterpret_cast<uintptr_t>(e.bias) & 15) == 0)) {
-    if (!e.resid && !e.preact && e.act == 0) epi = 1;
+    if (!e.resid && !e.preact && (e.act == 0 || e.act == 3 || e.act == 5)) epi = 1;
     else if (!e.resid && e.preact && e.act == 1) epi = 2;
     else if (e.resid && kp.e_tma && !e.preact && e.act == 0) epi = 3;
-    else if (e.resid && kp.e_tma && !e.preact && e.act == 2) epi = 4;
+    else if (e.resid && kp.e_tma && !e.preact && (e.act == 2 || e.act == 4 || e.act == 6)) epi = 4;
     if (epi != 0) {
       bool ok = make_map_e(&md, e.D, p.M, p.N, e.rs_lo, e.d_zlo, e.d_zhi, p.zlo_n, p.zhi_n, bn, 32);
       if (ok && epi == 2) ok = make_map_e(&mp, e.preact, p.M, p.N, e.rs_lo, e.d_zlo, e.d_zhi, p.zlo_n, p.zhi_n, bn, 32);
@@ -1298,12 +1438,16 @@ cudaError_t gemm_launch(const GemmProblem& p, const GemmOperand& A, const GemmOp
     }
   }
   if (eb == 4) {
-    if (bn == 256) return launch_t<256, 4, 0>(ma, mbs, me, md, mp, mdx, kp, stream);
-    return launch_t<128, 4, 0>(ma, mbs, me, md, mp, mdx, kp, stream);
+    if (bn == 256) return launch_t<256, 4, 0, 1>(ma, mbs, me, md, mp, mdx, kp, stream);
+    return launch_t<128, 4, 0, 1>(ma, mbs, me, md, mp, mdx, kp, stream);
   }
-#define MK_DISPATCH(EPI_)                                                    \
-  if (bn == 256) return launch_t<256, 2, EPI_>(ma, mbs, me, md, mp, mdx, kp, stream); \
-  return launch_t<128, 2, EPI_>(ma, mbs, me, md, mp, mdx, kp, stream);
+#define MK_DISPATCH(EPI_)                                                                              \
+  if (cg == 2) {                                                                                       \
+    if (bn == 256) return launch_t<256, 2, EPI_, 2>(ma, mbs, me, md, mp, mdx, kp, stream);             \
+    return launch_t<128, 2, EPI_, 2>(ma, mbs, me, md, mp, mdx, kp, stream);                            \
+  }                                                                                                    \
+  if (bn == 256) return launch_t<256, 2, EPI_, 1>(ma, mbs, me, md, mp, mdx, kp, stream);               \
+  return launch_t<128, 2, EPI_, 1>(ma, mbs, me, md, mp, mdx, kp, stream);
   switch (epi) {
     case 1: { MK_DISPATCH(1) }
     case 2: { MK_DISPATCH(2) }

@@ -40,9 +40,12 @@ struct GemmEpilogue {
   float alpha;
   const float* bias;    // fp32, may be null
   int bias_mode;        // 1: per row r, 2: per column n
-  int act;              // 0: none, 1: exact (erf) GELU, 2: multiply by GELU'(resid) (backward through a GELU)
-  const void* resid;    // optional tensor added after the activation (act 0/1) or the saved pre-activation
-                        // (act 2); same addressing and dtype as D
+  int act;              // 0 none; 1 GELU, 3 ReLU, 5 soft shrinkage (threshold act_param); 2 / 4 / 6: multiply by the
+                        // derivative of GELU / ReLU / soft shrinkage evaluated at `resid` (see gelu.cuh)
+  float act_param;
+  const void* resid;    // optional tensor added after the activation (odd act or 0), or the operand of the derivative
+                        // (even act: saved pre-activation for GELU, saved output for ReLU / shrinkage); same
+                        // addressing and dtype as D
   // optional second output: the pre-activation value (alpha*acc + bias) in the same layout / dtype
   void* preact;
 };

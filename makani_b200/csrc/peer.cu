@@ -4,12 +4,12 @@
 
 #include <cuda_bf16.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 namespace mk {
 
 namespace {
 
-constexpr uint64_t PEER_WAIT_NS = 2000000000ull;
 
 __device__ __forceinline__ uint64_t gtime() {
   uint64_t t;
@@ -28,7 +28,7 @@ __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
 
 // All `world` ranks' CTA `blockIdx.x` meet here. Slot layout per rank: [block][PEER_MAX + 1].
 // Thread i < world signals peer i and waits for peer i's signal. Returns false if a wait ran out.
-__device__ __forceinline__ bool cta_barrier(const PeerPtrs& p, int world, int rank, unsigned int value) {
+__device__ __forceinline__ bool cta_barrier(const PeerPtrs& p, int world, int rank, unsigned int value, uint64_t wait_ns) {
   bool ok = true;
   __syncthreads();
   if (threadIdx.x < world) {
@@ -43,7 +43,7 @@ __device__ __forceinline__ bool cta_barrier(const PeerPtrs& p, int world, int ra
       if ((it & 255u) == 255u) {
         const uint64_t now = gtime();
         if (t0 == 0) t0 = now;
-        else if (now - t0 > PEER_WAIT_NS) {
+        else if (now - t0 > wait_ns) {
           ok = false;
           break;
         }
@@ -58,6 +58,9 @@ struct Vec16;
 template <>
 struct Vec16<float> {
   static constexpr int N = 4;
+  static __device__ __forceinline__ void add(const uint4& v, float (&a)[4]) {
+    a[0] += __uint_as_float(v.x); a[1] += __uint_as_float(v.y); a[2] += __uint_as_float(v.z); a[3] += __uint_as_float(v.w);
+  }
   static __device__ __forceinline__ void load(const float* p, float (&f)[4]) {
     const float4 v = *reinterpret_cast<const float4*>(p);
     f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
@@ -69,6 +72,15 @@ struct Vec16<float> {
 template <>
 struct Vec16<__nv_bfloat16> {
   static constexpr int N = 8;
+  static __device__ __forceinline__ void add(const uint4& v, float (&a)[8]) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 x = __bfloat1622float2(h[j]);
+      a[2 * j] += x.x;
+      a[2 * j + 1] += x.y;
+    }
+  }
   static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&f)[8]) {
     const uint4 v = *reinterpret_cast<const uint4*>(p);
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
@@ -88,53 +100,86 @@ struct Vec16<__nv_bfloat16> {
   }
 };
 
-template <typename T>
-__global__ void __launch_bounds__(512) allreduce_kernel(const PeerPtrs p, int world, int rank, long long n, float scale,
-                                                        int* err) {
+// 256 threads x at most 64 registers: a CTA of this kernel fits on an SM beside a persistent GEMM CTA (320 threads x up
+// to 144 registers), so that the reduction of a bucket really runs while backward continues.
+constexpr int AR_THREADS = 256;
+
+// WORLD is a template parameter so that the loops over the peers unroll completely: all WORLD loads of a vector (and U
+// vectors per thread) are in flight together, which is what it takes to fill an NVLink round trip (about 2 us) with
+// about a hundred CTAs; with a run-time peer loop each thread had a single 16-byte load outstanding and the pull ran at a third
+// of the link rate.
+template <typename T, int WORLD>
+__global__ void __maxnreg__(64) allreduce_kernel(const PeerPtrs p, int rank, long long n, float scale,
+                                                        uint64_t wait_ns, int* err) {
   constexpr int V = Vec16<T>::N;
+  constexpr int U = (WORLD <= 2) ? 4 : ((WORLD <= 4) ? 2 : 1);   // vectors per thread and trip: U * WORLD (about 8) loads in flight
   unsigned int* my_epoch = p.flags[rank] + blockIdx.x * (PEER_MAX + 1) + PEER_MAX;
   const unsigned int epoch = *my_epoch;
   const unsigned int v0 = 2 * epoch + 1, v1 = 2 * epoch + 2;
-  bool ok = cta_barrier(p, world, rank, v0);
+  bool ok = cta_barrier(p, WORLD, rank, v0, wait_ns);
   if (ok) {
+    // peers in staggered order (rank, rank + 1, ...), so that the ranks do not all hit the same peer at once
+    T* peer[WORLD];
+#pragma unroll
+    for (int r = 0; r < WORLD; ++r) peer[r] = static_cast<T*>(p.data[(rank + r) % WORLD]);
     // slice of this rank, in 16-byte vectors
     const long long nvec = n / V;
-    const long long per = (nvec + world - 1) / world;
+    const long long per = (nvec + WORLD - 1) / WORLD;
     const long long beg = per * rank;
     long long end = beg + per;
     if (end > nvec) end = nvec;
-    for (long long i = beg + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < end;
-         i += static_cast<long long>(gridDim.x) * blockDim.x) {
-      float acc[V];
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i0 = beg + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < end; i0 += stride * U) {
+      uint4 raw[U][WORLD];
 #pragma unroll
-      for (int j = 0; j < V; ++j) acc[j] = 0.f;
-      for (int r = 0; r < world; ++r) {
-        const int src = (rank + r) % world;   // stagger the peers
-        float f[V];
-        Vec16<T>::load(static_cast<const T*>(p.data[src]) + i * V, f);
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < end) {
 #pragma unroll
-        for (int j = 0; j < V; ++j) acc[j] += f[j];
+          for (int r = 0; r < WORLD; ++r) raw[u][r] = *reinterpret_cast<const uint4*>(peer[r] + i * V);
+        }
       }
 #pragma unroll
-      for (int j = 0; j < V; ++j) acc[j] *= scale;
-      for (int r = 0; r < world; ++r) {
-        const int dst = (rank + r) % world;
-        Vec16<T>::store(static_cast<T*>(p.data[dst]) + i * V, acc);
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < end) {
+          float acc[V];
+#pragma unroll
+          for (int j = 0; j < V; ++j) acc[j] = 0.f;
+#pragma unroll
+          for (int r = 0; r < WORLD; ++r) Vec16<T>::add(raw[u][r], acc);
+#pragma unroll
+          for (int j = 0; j < V; ++j) acc[j] *= scale;
+#pragma unroll
+          for (int r = 0; r < WORLD; ++r) Vec16<T>::store(peer[r] + i * V, acc);
+        }
       }
     }
     // ragged tail (n not a multiple of the vector width): the last rank handles it elementwise
-    if (rank == world - 1 && blockIdx.x == 0) {
+    if (rank == WORLD - 1 && blockIdx.x == 0) {
       for (long long i = nvec * V + threadIdx.x; i < n; i += blockDim.x) {
         float a = 0.f;
-        for (int r = 0; r < world; ++r) a += static_cast<float>(static_cast<const T*>(p.data[r])[i]);
+        for (int r = 0; r < WORLD; ++r) a += static_cast<float>(static_cast<const T*>(p.data[r])[i]);
         a *= scale;
-        for (int r = 0; r < world; ++r) static_cast<T*>(p.data[r])[i] = static_cast<T>(a);
+        for (int r = 0; r < WORLD; ++r) static_cast<T*>(p.data[r])[i] = static_cast<T>(a);
       }
     }
-    ok = cta_barrier(p, world, rank, v1);
+    ok = cta_barrier(p, WORLD, rank, v1, wait_ns);
   }
   if (!ok && threadIdx.x == 0) atomicExch(err, 16);
   if (threadIdx.x == 0) *my_epoch = epoch + 1;
+}
+
+template <typename T>
+cudaError_t launch_allreduce(int world, unsigned blocks, cudaStream_t s, const PeerPtrs& p, int rank, long long n, float scale,
+                             uint64_t wait_ns, int* err) {
+  switch (world) {
+#define MK_AR(W) case W: allreduce_kernel<T, W><<<blocks, AR_THREADS, 0, s>>>(p, rank, n, scale, wait_ns, err); break;
+    MK_AR(1) MK_AR(2) MK_AR(3) MK_AR(4) MK_AR(5) MK_AR(6) MK_AR(7) MK_AR(8)
+#undef MK_AR
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
 }
 
 }  // namespace
@@ -161,17 +206,25 @@ cudaError_t peer_open(const char* handle64, void** ptr) {
 cudaError_t peer_close(void* ptr) { return cudaIpcCloseMemHandle(ptr); }
 cudaError_t peer_free(void* ptr) { return cudaFree(ptr); }
 
-cudaError_t peer_allreduce(const PeerPtrs& p, int world, int rank, long long n, int is_bf16, float scale, unsigned int,
+cudaError_t peer_allreduce(const PeerPtrs& p, int world, int rank, long long n, int is_bf16, float scale, double wait_seconds,
                            int* err, cudaStream_t s) {
   if (n <= 0) return cudaSuccess;
+  if (!(wait_seconds > 0.0)) wait_seconds = 2.0;
+  const uint64_t wait_ns = static_cast<uint64_t>(wait_seconds * 1e9);
   const int V = is_bf16 ? 8 : 4;
   long long per = (n / V + world - 1) / world;
-  long long blocks = (per + 511) / 512;
+  long long blocks = (per + 255) / 256;
   if (blocks < 1) blocks = 1;
-  if (blocks > 64) blocks = 64;   // 64 CTAs x 512 threads x 16 B in flight saturate NVLink without starving compute
-  if (is_bf16) allreduce_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 512, 0, s>>>(p, world, rank, n, scale, err);
-  else allreduce_kernel<float><<<static_cast<unsigned>(blocks), 512, 0, s>>>(p, world, rank, n, scale, err);
-  return cudaGetLastError();
+  // 128 CTAs x 256 threads x 16 vectors of 16 B in flight saturate NVLink without starving compute (MAKANI_B200_AR_BLOCKS overrides,
+  // read once; every rank of a group must use the same value because CTA i pairs with CTA i of its peers)
+  static const int max_blocks = [] {
+    const char* e = getenv("MAKANI_B200_AR_BLOCKS");
+    int v = e ? atoi(e) : PEER_MAX_BLOCKS;
+    return (v >= 1 && v <= PEER_MAX_BLOCKS) ? v : PEER_MAX_BLOCKS;
+  }();
+  if (blocks > max_blocks) blocks = max_blocks;
+  if (is_bf16) return launch_allreduce<__nv_bfloat16>(world, static_cast<unsigned>(blocks), s, p, rank, n, scale, wait_ns, err);
+  return launch_allreduce<float>(world, static_cast<unsigned>(blocks), s, p, rank, n, scale, wait_ns, err);
 }
 
 }  // namespace mk

@@ -24,8 +24,10 @@ cudaError_t peer_free(void* ptr);
 
 // In-place sum over `world` ranks of n elements (fp32 or bf16, summed in fp32, scaled by `scale`).
 // Two-shot: every rank reduces its 1/world slice from all peers, then stores the result into every peer.
-// Cross-rank ordering uses per-CTA epoch flags in symmetric memory with bounded waits (*err = 16 on expiry).
+// Cross-rank ordering uses per-CTA epoch flags in symmetric memory with bounded waits: a rank that does not see its
+// peers within `wait_seconds` sets *err = 16 and leaves.  The limit is the tolerated skew between ranks (a slow data
+// loader, a rank writing a checkpoint), not a liveness check: dead ranks are the host watchdog's business.
 cudaError_t peer_allreduce(const PeerPtrs& p, int world, int rank, long long n, int is_bf16, float scale,
-                           unsigned int epoch_unused, int* err, cudaStream_t s);
+                           double wait_seconds, int* err, cudaStream_t s);
 
 }  // namespace mk

@@ -31,6 +31,7 @@ def _load():
             spec = importlib.util.spec_from_file_location("makani_b200.csrc._C", SO_PATH)
             mod = importlib.util.module_from_spec(spec)
             spec.loader.exec_module(mod)
+            mod.set_gelu_tanh(1 if _GELU_TANH else 0)
             _MOD = mod
         except Exception as e:  # pragma: no cover - depends on the machine
             _ERR = e
@@ -39,6 +40,7 @@ def _load():
 # MAKANI_B200_NATIVE=0 (or `set_native(False)`) routes every op through its plain PyTorch formulation: the
 # op-for-op restatement of the reference's execution (cuDNN/cuBLAS/cuFFT/ATen/NCCL) used as the same-box comparison arm.
 _NATIVE = os.environ.get("MAKANI_B200_NATIVE", "1") != "0"
+_GELU_TANH = os.environ.get("MAKANI_B200_GELU", "erf") == "tanh"
 
 
 def set_native(flag: bool) -> None:
@@ -58,7 +60,7 @@ def available() -> bool:
 # number of kernels of this extension launched by the current process (each binding call launches exactly one)
 LAUNCHES = 0
 _NON_KERNEL = {"read_error_flag", "clear_error_flag", "lp_scratch_floats", "adam_entry_bytes", "peer_alloc", "peer_open",
-               "peer_close", "peer_free", "tensor_from_ptr"}
+               "peer_close", "peer_free", "tensor_from_ptr", "set_gelu_tanh"}
 
 
 class _Counting:
@@ -97,6 +99,35 @@ def require():
     if _PROXY is None:
         _PROXY = _Counting(_MOD)
     return _PROXY
+
+
+_SM_COUNT = {}
+
+
+def sm_count(device=None) -> int:
+    """Number of SMs of `device` (148 on B200); used to size split-k factors and grids."""
+    import torch
+
+    if not torch.cuda.is_available():
+        return 148
+    idx = torch.cuda.current_device() if device is None else (torch.device(device).index or 0)
+    if idx not in _SM_COUNT:
+        _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _SM_COUNT[idx]
+
+
+def set_gelu_approximation(kind: str) -> None:
+    """"none" (default): GELU is the exact erf form everywhere, as torch.nn.GELU(); "tanh": the tanh approximation
+    (hardware tanh.approx in the kernels, `approximate="tanh"` in the torch fallbacks)."""
+    global _GELU_TANH
+    assert kind in ("none", "tanh")
+    _GELU_TANH = kind == "tanh"
+    if _MOD is not None or available():
+        _MOD.set_gelu_tanh(1 if _GELU_TANH else 0)
+
+
+def gelu_approximation() -> str:
+    return "tanh" if _GELU_TANH else "none"
 
 
 def launch_count() -> int:

@@ -142,7 +142,7 @@ def _conv_wgrad(dy, x, splits: Optional[int] = None):
     if splits is None:
         tiles = ((co + 127) // 128) * ((ci + 255) // 256) * B
         kblocks = (T + 63) // 64
-        splits = max(1, min(kblocks, (2 * 148 + tiles - 1) // tiles))
+        splits = max(1, min(kblocks, (2 * _ext.sm_count() + tiles - 1) // tiles))
     gemm(co, ci, T, _chan_rows(dy, layout_of(dy)), _chan_rows(x, layout_of(x)), Output(dw, rs_lo=ci), zlo_n=B,
          accumulate=True, splits=splits)
     return dw
@@ -238,7 +238,7 @@ def conv1x1(x, w, bias=None, resid=None, act: str = "none", out_layout: Optional
     w4 = w.reshape(w.shape[0], -1, 1, 1).to(x.dtype)
     y = torch.nn.functional.conv2d(x, w4, None if bias is None else bias.to(x.dtype))
     if act == "gelu":
-        y = torch.nn.functional.gelu(y)
+        y = torch.nn.functional.gelu(y, approximate=_ext.gelu_approximation())
     if resid is not None:
         y = y + resid
     return y
@@ -250,7 +250,8 @@ def mlp2(x, w1, b1, w2, b2, resid=None, out_layout: Optional[str] = None):
         _ext.require()
         return _MLP2.apply(x, w1, b1, w2, b2, resid, out_layout)
     f = torch.nn.functional
-    h = f.gelu(f.conv2d(x, w1.reshape(w1.shape[0], -1, 1, 1).to(x.dtype), None if b1 is None else b1.to(x.dtype)))
+    h = f.gelu(f.conv2d(x, w1.reshape(w1.shape[0], -1, 1, 1).to(x.dtype), None if b1 is None else b1.to(x.dtype)),
+               approximate=_ext.gelu_approximation())
     y = f.conv2d(h, w2.reshape(w2.shape[0], -1, 1, 1).to(x.dtype), None if b2 is None else b2.to(x.dtype))
     if resid is not None:
         y = y + resid

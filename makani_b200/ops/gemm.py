@@ -18,7 +18,7 @@ import torch
 
 from . import _ext
 
-ACT_NONE, ACT_GELU, ACT_DGELU = 0, 1, 2
+ACT_NONE, ACT_GELU, ACT_DGELU, ACT_RELU, ACT_DRELU, ACT_SHRINK, ACT_DSHRINK = 0, 1, 2, 3, 4, 5, 6
 BIAS_NONE, BIAS_ROW, BIAS_COL = 0, 1, 2
 _BIG = 1 << 30
 
@@ -95,7 +95,7 @@ def _flat(t: torch.Tensor) -> torch.Tensor:
 
 
 def _emulate(M, N, K, A: Operand, B: Operand, D: Output, zlo_n, zhi_n, alpha, bias, bias_mode, act, resid, resid_offset,
-             preact, preact_offset, accumulate, tri: Tri, segments=None):
+             preact, preact_offset, accumulate, tri: Tri, segments=None, act_param: float = 0.0):
     fa, fb, fd = _flat(A.tensor), _flat(B.tensor), _flat(D.tensor)
     cdt = torch.float64 if fa.dtype == torch.float64 else torch.float32
 
@@ -136,14 +136,27 @@ def _emulate(M, N, K, A: Operand, B: Operand, D: Output, zlo_n, zhi_n, alpha, bi
     if preact is not None:
         _flat(preact).index_put_((idx - D.offset + preact_offset,), acc.reshape(-1).to(preact.dtype))
     if act == ACT_GELU:
-        acc = torch.nn.functional.gelu(acc)
+        acc = torch.nn.functional.gelu(acc, approximate=_ext.gelu_approximation())
+    elif act == ACT_RELU:
+        acc = torch.relu(acc)
+    elif act == ACT_SHRINK:
+        acc = torch.nn.functional.softshrink(acc, lambd=float(act_param))
     if resid is not None:
         rv = _flat(resid)[idx - D.offset + resid_offset].to(cdt).view_as(acc)
-        if act == ACT_DGELU:
+        if act == ACT_DRELU:
+            acc = acc * (rv > 0).to(cdt)
+        elif act == ACT_DSHRINK:
+            acc = acc * (rv != 0).to(cdt)
+        elif act == ACT_DGELU:
             x = rv
-            cdf = 0.5 * (1.0 + torch.erf(x * 0.7071067811865476))
-            pdf = torch.exp(-0.5 * x * x) * 0.3989422804014327
-            acc = acc * (cdf + x * pdf)
+            if _ext.gelu_approximation() == "tanh":
+                u = 0.7978845608028654 * (x + 0.044715 * x ** 3)
+                t = torch.tanh(u)
+                acc = acc * (0.5 * (1.0 + t) + 0.5 * x * (1.0 - t * t) * 0.7978845608028654 * (1.0 + 3 * 0.044715 * x * x))
+            else:
+                cdf = 0.5 * (1.0 + torch.erf(x * 0.7071067811865476))
+                pdf = torch.exp(-0.5 * x * x) * 0.3989422804014327
+                acc = acc * (cdf + x * pdf)
         else:
             acc = acc + rv
     vals = acc.reshape(-1).to(fd.dtype)
@@ -157,7 +170,7 @@ def gemm(M: int, N: int, K: int, A: Operand, B: Operand, D: Output, *, zlo_n: in
          bias: Optional[torch.Tensor] = None, bias_mode: int = BIAS_NONE, act: int = ACT_NONE,
          resid: Optional[torch.Tensor] = None, resid_offset: int = 0, preact: Optional[torch.Tensor] = None,
          preact_offset: int = 0, accumulate: bool = False, splits: int = 1, tri: Optional[Tri] = None, bn: int = 0,
-         segments=None, sync=None, dests=None) -> None:
+         segments=None, sync=None, dests=None, act_param: float = 0.0) -> None:
     """Run the batched GEMM described above, writing into `D.tensor` in place.
 
     `segments` (list of `Segment`) spreads the k axis of B over several devices: `K` is then the padded k extent
@@ -169,7 +182,7 @@ def gemm(M: int, N: int, K: int, A: Operand, B: Operand, D: Output, *, zlo_n: in
         bias_mode = BIAS_NONE
     if not A.tensor.is_cuda:
         _emulate(M, N, K, A, B, D, zlo_n, zhi_n, alpha, bias, bias_mode, act, resid, resid_offset, preact, preact_offset,
-                 accumulate, tri, segments)
+                 accumulate, tri, segments, act_param)
         return
     ext = _ext.require()
     ip = [M, N, K, zlo_n, zhi_n, splits, bn,
@@ -177,7 +190,7 @@ def gemm(M: int, N: int, K: int, A: Operand, B: Operand, D: Output, *, zlo_n: in
           A.offset, int(A.mn_major), A.ld, A.zs_lo, A.zs_hi,
           B.offset, int(B.mn_major), B.ld, B.zs_lo, B.zs_hi,
           D.offset, int(accumulate), D.d_zlo, D.d_zhi, D.rdiv, D.rs_hi, D.rs_lo, D.ndiv, D.ns_hi,
-          bias_mode, act, resid_offset, preact_offset, 0, 0]
+          bias_mode, act, resid_offset, preact_offset, _f32_bits(act_param), 0]
     if segments or sync or dests:
         seg = []
         if segments and len(segments) > 1:
@@ -191,6 +204,11 @@ def gemm(M: int, N: int, K: int, A: Operand, B: Operand, D: Output, *, zlo_n: in
                       [int(d) for d in (dests or [])])
         return
     ext.gemm(A.tensor, B.tensor, D.tensor, bias, resid, preact, ip, float(alpha))
+
+
+def _f32_bits(x: float) -> int:
+    import struct
+    return struct.unpack("<I", struct.pack("<f", float(x)))[0]
 
 
 def pad_to(n: int, m: int) -> int:

@@ -43,7 +43,7 @@ def _lin_wgrad(dy, x2):
     C = x2.shape[1]
     dw = torch.zeros(O, C, dtype=torch.float32, device=dy.device)
     tiles = ((O + 127) // 128) * ((C + 255) // 256)
-    splits = max(1, min((T + 63) // 64, (2 * 148 + tiles - 1) // tiles))
+    splits = max(1, min((T + 63) // 64, (2 * _ext.sm_count() + tiles - 1) // tiles))
     # dW[o, c] = sum_t dY[t, o] X[t, c]: both operands row-contiguous in their own index, K = t
     gemm(O, C, T, Operand(dy, ld=O, mn_major=True), Operand(x2, ld=C, mn_major=True), Output(dw, rs_lo=C),
          accumulate=True, splits=splits)

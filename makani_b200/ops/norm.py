@@ -129,7 +129,7 @@ def instance_norm(x: torch.Tensor, weight, bias, eps: float = 1e-6, act: str = "
     y = torch.nn.functional.instance_norm(xf, None, None, None if weight is None else weight.float(),
                                           None if bias is None else bias.float(), True, 0.0, eps)
     if act == "gelu":
-        y = torch.nn.functional.gelu(y)
+        y = torch.nn.functional.gelu(y, approximate=_ext.gelu_approximation())
     return y.to(x.dtype)
 
 

@@ -13,6 +13,7 @@ fixed pointer table.
 
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional
 
 import torch
@@ -22,8 +23,10 @@ from ..utils import comm
 
 
 class GradReducer:
-    def __init__(self, model: torch.nn.Module, use_peer: Optional[bool] = None, align: int = 64, bucket_mb: float = 256.0,
-                 overlap: bool = True):
+    def __init__(self, model: torch.nn.Module, use_peer: Optional[bool] = None, align: int = 64,
+                 bucket_mb: Optional[float] = None, overlap: bool = True):
+        if bucket_mb is None:
+            bucket_mb = float(os.environ.get("MAKANI_B200_BUCKET_MB", "256"))
         self.params = [p for p in model.parameters() if p.requires_grad]
         dev = self.params[0].device
         self.device = dev
@@ -38,6 +41,18 @@ class GradReducer:
         if use_peer is None:
             use_peer = (dev.type == "cuda" and dist.is_initialized() and self.data_size > 1 and self.data_size <= 8
                         and dist.get_backend() == "nccl")
+        # diagnosis only: MAKANI_B200_DP_DIAG=noreduce leaves the data-parallel average out (replicas diverge), to tell
+        # the cost of the reduction apart from what running N ranks side by side costs by itself
+        self.diag_noreduce = os.environ.get("MAKANI_B200_DP_DIAG", "") == "noreduce"
+        # MAKANI_B200_DP_DIAG=timeline (eager steps only): CUDA events around every bucket's reduction and around the final
+        # join; `timeline_report()` returns when each bucket became ready, how long its reduction took and how long the
+        # compute stream waited at the end of backward
+        self.diag_timeline = os.environ.get("MAKANI_B200_DP_DIAG", "") == "timeline"
+        self._timeline = []
+        self._t_zero = None
+        self._t_join = None
+        if self.diag_noreduce:
+            use_peer = False
         self.sym = None
         if use_peer:
             from .peer import SymmetricBuffer
@@ -113,11 +128,16 @@ class GradReducer:
     def _launch_bucket(self, b):
         start, end = self.buckets[b]
         self._launched[b] = True
-        ev = torch.cuda.Event()
+        timeline = self.diag_timeline and not torch.cuda.is_current_stream_capturing()
+        ev = torch.cuda.Event(enable_timing=timeline)
         ev.record(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(self._side):
             self._side.wait_event(ev)
             self.sym.all_reduce_(end - start, torch.float32, scale=1.0 / self.data_size, byte_offset=start * 4)
+            if timeline:
+                done = torch.cuda.Event(enable_timing=True)
+                done.record(self._side)
+                self._timeline.append((b, (end - start) * 4, ev, done))
 
     def zero_grad(self):
         if self.overlap:
@@ -126,16 +146,28 @@ class GradReducer:
             if not torch.cuda.is_current_stream_capturing():
                 torch.cuda.current_stream(self.device).wait_stream(self._side)
             self._reset_pending()
+        if self.diag_timeline and not torch.cuda.is_current_stream_capturing():
+            self._timeline = []
+            self._t_zero = torch.cuda.Event(enable_timing=True)
+            self._t_zero.record(torch.cuda.current_stream(self.device))
         self.flat.zero_()
 
     def reduce(self):
         """Average over `data`, then sum over the model-parallel groups each parameter is shared on."""
-        if self.data_size > 1:
+        if self.data_size > 1 and not self.diag_noreduce:
             if self.overlap:
                 for b in range(len(self.buckets)):     # buckets whose hooks did not all fire (unused parameters)
                     if not self._launched[b]:
                         self._launch_bucket(b)
+                timeline = self.diag_timeline and not torch.cuda.is_current_stream_capturing()
+                if timeline:
+                    e0 = torch.cuda.Event(enable_timing=True)
+                    e0.record(torch.cuda.current_stream(self.device))
                 torch.cuda.current_stream(self.device).wait_stream(self._side)
+                if timeline:
+                    e1 = torch.cuda.Event(enable_timing=True)
+                    e1.record(torch.cuda.current_stream(self.device))
+                    self._t_join = (e0, e1)
             elif self.sym is not None:
                 self.sym.all_reduce_(self.total, torch.float32, scale=1.0 / self.data_size)
             else:
@@ -145,6 +177,16 @@ class GradReducer:
             grp = comm.get_group(gname)
             for start, end in ranges:
                 dist.all_reduce(self.flat[start:end], group=grp)
+
+    def timeline_report(self):
+        """Of the last eager step (MAKANI_B200_DP_DIAG=timeline): per bucket (index, MB, ms after the start of the step at
+        which it became ready, ms at which its reduction had finished) and the ms the compute stream waited at the join."""
+        if not (self.diag_timeline and self._t_zero is not None and self._t_join is not None):
+            return None
+        torch.cuda.synchronize(self.device)
+        rows = [(b, nbytes / 1e6, self._t_zero.elapsed_time(ev), self._t_zero.elapsed_time(done)) for b, nbytes, ev, done in self._timeline]
+        e0, e1 = self._t_join
+        return {"buckets": rows, "backward_end_ms": self._t_zero.elapsed_time(e0), "join_wait_ms": e0.elapsed_time(e1)}
 
     def close(self):
         if self.sym is not None:

@@ -134,7 +134,7 @@ class DistributedInstanceNorm2d(nn.Module):
                                           reduce_fn=None if slot is not None else _allreduce_spatial, slot=slot)
         y = _DistInstanceNormFn.apply(x, w, b, self.eps, cnt)
         if act == "gelu":
-            y = torch.nn.functional.gelu(y)
+            y = torch.nn.functional.gelu(y, approximate=_ext.gelu_approximation())
         return y
 
 

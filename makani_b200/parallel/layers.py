@@ -237,31 +237,6 @@ class DistributedMLP(nn.Module):
         return self.fwd(x)
 
 
-class DistributedPatchEmbed(nn.Module):
-    def __init__(self, img_size=(224, 224), patch_size=(16, 16), in_chans=3, embed_dim=768, input_is_matmul_parallel=False,
-                 output_is_matmul_parallel=True):
-        super().__init__()
-        self.input_parallel, self.output_parallel = input_is_matmul_parallel, output_is_matmul_parallel
-        self.img_size, self.patch_size = img_size, patch_size
-        self.num_patches = (img_size[1] // patch_size[1]) * (img_size[0] // patch_size[0])
-        msize = comm.get_size("matmul")
-        self.in_shapes = compute_split_shapes(in_chans, msize)
-        out_loc = compute_split_shapes(embed_dim, msize)[comm.get_rank("matmul")] if output_is_matmul_parallel else embed_dim
-        self.proj = nn.Conv2d(in_chans, out_loc, kernel_size=patch_size, stride=patch_size)
-        self.proj.weight.is_shared_mp = ["spatial"]
-        self.proj.bias.is_shared_mp = ["spatial"]
-        if output_is_matmul_parallel:
-            self.proj.weight.sharded_dims_mp = ["matmul", None, None, None]
-            self.proj.bias.sharded_dims_mp = ["matmul"]
-
-    def forward(self, x):
-        if self.input_parallel:
-            x = gather_from_parallel_region(x, 1, self.in_shapes, "matmul")
-        if self.output_parallel:
-            x = copy_to_parallel_region(x, "matmul")
-        return self.proj(x).flatten(2)
-
-
 class DistributedAttention(nn.Module):
     """Multi-head self attention with heads split over `comm_hidden_name` (sequence stays whole)."""
 

@@ -9,6 +9,7 @@ multicast).  The reference has no counterpart: all its communication goes throug
 
 from __future__ import annotations
 
+import os
 from typing import List, Optional
 
 import torch
@@ -17,6 +18,10 @@ import torch.distributed as dist
 from ..ops import _ext
 
 FLAG_BYTES = 128 * 9 * 4  # PEER_MAX_BLOCKS * (PEER_MAX + 1) * sizeof(uint32), see csrc/peer.cuh
+
+# How far apart the ranks of a data-parallel group may reach the gradient all-reduce (rank-0-only logging, a slow
+# first batch, a checkpoint write).  Lost ranks are detected on the host (utils/watchdog.py), so this is generous.
+PEER_SKEW_SECONDS = float(os.environ.get("MAKANI_B200_PEER_SKEW_SECONDS", "120"))
 
 
 class SymmetricBuffer:
@@ -49,12 +54,18 @@ class SymmetricBuffer:
         esz = torch.empty((), dtype=dtype).element_size()
         return self.local[byte_offset: byte_offset + numel * esz].view(dtype)
 
-    def all_reduce_(self, numel: int, dtype=torch.float32, scale: float = 1.0, byte_offset: int = 0) -> None:
-        """In-place sum (times `scale`) over the group of `numel` elements starting at `byte_offset`."""
+    def all_reduce_(self, numel: int, dtype=torch.float32, scale: float = 1.0, byte_offset: int = 0,
+                    wait_seconds: Optional[float] = None) -> None:
+        """In-place sum (times `scale`) over the group of `numel` elements starting at `byte_offset`.
+
+        `wait_seconds` bounds how long a rank waits for its peers inside the kernel (default: `PEER_SKEW_SECONDS`).
+        It is the tolerated skew between ranks, not a liveness check: when it runs out the kernel leaves with
+        error code 16 and the fused optimiser skips its update."""
         assert dtype in (torch.float32, torch.bfloat16)
         ptrs = [p + byte_offset for p in self.ptrs]
         self.ext.peer_allreduce(ptrs, self.flag_ptrs, self.rank, int(numel), 1 if dtype == torch.bfloat16 else 0,
-                                float(scale), 0, self.device.index)
+                                float(scale), float(PEER_SKEW_SECONDS if wait_seconds is None else wait_seconds),
+                                self.device.index)
 
     def close(self):
         if self._closed:

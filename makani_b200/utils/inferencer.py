@@ -115,6 +115,9 @@ class Inferencer(Trainer):
         self.metrics.zero_buffers()
         for data in self.valid_dataloader:
             self._autoregressive_inference(data, compute_metrics=True, output_data=False, output_channels=False)
+        if self.device.type == "cuda":
+            from ..ops import _ext
+            _ext.check_device_errors(self.device)    # expired bounded waits of the distributed kernels surface here
         logs, acc_curves, rmse_curves = self.metrics.finalize(final_inference=True)
         if self.world_rank == 0 and self.params.get("experiment_dir") is not None:
             os.makedirs(self.params.experiment_dir, exist_ok=True)
@@ -171,6 +174,9 @@ class Inferencer(Trainer):
             self._rollout_graph.replay()
             if keep_outputs:
                 outputs.append(self._static_pred.float().cpu())
+        if self.device.type == "cuda":
+            from ..ops import _ext
+            _ext.check_device_errors(self.device)
         return (self._static_state, outputs) if keep_outputs else self._static_state
 
     @torch.no_grad()

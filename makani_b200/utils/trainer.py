@@ -106,6 +106,11 @@ class Trainer:
         self._set_train()
         self.graph = None
         self.graph_mode = g("cuda_graph_mode", "none") if self.device.type == "cuda" else "none"
+        if self.graph_mode == "step" and self.amp_dtype == torch.float16:
+            # the captured optimiser launch cannot honour the loss scaler's inf/NaN check; keep the scaler on the host
+            if self.log_to_screen:
+                self.logger.info("amp_mode fp16: cuda_graph_mode 'step' falls back to 'fwdbwd' (the GradScaler steps on the host)")
+            self.graph_mode = "fwdbwd"
 
         self.visualizer = None
         if g("log_video", 0) and g("log_video", 0) > 0:
@@ -405,6 +410,15 @@ class Trainer:
                 tstep = now
             if p.get("log_weights_and_grads", 0) > 0 and self.iters % p.log_weights_and_grads == 0:
                 self.log_weights_and_grads(os.path.join(p.experiment_dir, "weights_and_grads"))
+                if dist.is_initialized() and comm.get_size("data") > 1:
+                    # only data rank 0 wrote files: re-align the ranks on the host so that the next step's in-kernel
+                    # handshakes do not have to absorb the skew
+                    dist.barrier(group=comm.get_group("data"))
+            # the device error word (expired bounded waits) is read every `check_device_errors_every` steps; the fused
+            # optimiser already skips its update while the word is set, so a late read loses no consistency
+            every = int(p.get("check_device_errors_every", 50))
+            if self.device.type == "cuda" and every > 0 and self.iters % every == 0:
+                _ext.check_device_errors(self.device)
         if self.device.type == "cuda":
             torch.cuda.synchronize()
             _ext.check_device_errors(self.device)
@@ -459,6 +473,8 @@ class Trainer:
                     self.visualizer.add(f"{epoch}_{idt}", pred[0].float().cpu().numpy(), targ[0].float().cpu().numpy())
                     viz_time += time.time() - tv
                 inpt = self.preprocessor.append_history(inpt.to(pred.dtype), pred, idt)
+        if self.device.type == "cuda":
+            _ext.check_device_errors(self.device)    # validation uses the same bounded handshakes as training
         logs = self.metrics.finalize()
         if self.visualizer is not None and self.world_rank == 0:
             tv = time.time()

@@ -314,6 +314,66 @@ def case_peer_instance_norm():
         dist.all_reduce(db, group=comm.get_group("spatial"))
         assert _rel(dw, wr.grad) < 3e-2 and _rel(db, br.grad) < 3e-2, (_rel(dw, wr.grad), _rel(db, br.grad))
 
+def case_peer_allreduce():
+    """In-kernel peer-memory all-reduce == NCCL all-reduce: fp32 and bf16, sizes that are not multiples of the vector
+    width or of the rank count, non-zero byte offsets, a scale factor, several calls in a row (epoch flags carry over);
+    then `GradReducer` with the peer path against the same module reduced with NCCL."""
+    from makani_b200.ops import _ext
+    from makani_b200.parallel.peer import SymmetricBuffer
+    from makani_b200.parallel.grad_reduce import GradReducer
+    assert os.environ.get("MK_DEVICE") == "cuda"
+    dev = torch.device("cuda", comm.get_local_rank())
+    world, rank = dist.get_world_size(), dist.get_rank()
+    buf = SymmetricBuffer(64 * 1024 * 1024, group=None, device=dev)
+    torch.manual_seed(100 + rank)
+    for dtype, tol in ((torch.float32, 1e-6), (torch.bfloat16, 1e-2)):
+        esz = 4 if dtype == torch.float32 else 2
+        for n, off, scale in ((1 << 20, 0, 1.0), (1000003, 256, 1.0 / world), (37, 1024, 0.5), (8 * 1024 * 1024 + 5, 4096, 1.0 / world)):
+            v = buf.view(dtype, n, off)
+            src = torch.randn(n, device=dev).to(dtype)
+            v.copy_(src)
+            ref = src.float().clone()
+            dist.all_reduce(ref)
+            ref *= scale
+            torch.cuda.synchronize()
+            dist.barrier()
+            buf.all_reduce_(n, dtype, scale=scale, byte_offset=off, wait_seconds=20.0)
+            torch.cuda.synchronize()
+            _ext.check_device_errors(dev)
+            err = _rel(v.float(), ref)
+            assert err < tol, (str(dtype), n, off, err)
+            dist.barrier()
+    buf.close()
+    # gradient reducer: peer path vs NCCL path on identical modules and identical (rank-dependent) gradients
+    torch.manual_seed(7)
+    def make():
+        m = torch.nn.Sequential(torch.nn.Linear(300, 257), torch.nn.Linear(257, 64)).to(dev)
+        m.register_parameter("cw", torch.nn.Parameter(torch.randn(33, 5, dtype=torch.complex64, device=dev)))
+        return m
+    ma = make()
+    mb = make()
+    mb.load_state_dict(ma.state_dict())
+    ra = GradReducer(ma, use_peer=True, bucket_mb=0.05)
+    rb = GradReducer(mb, use_peer=False)
+    assert ra.sym is not None and ra.overlap
+    for it in range(3):
+        ra.zero_grad(); rb.zero_grad()
+        g = torch.Generator(device=dev); g.manual_seed(1000 * it + rank)
+        x = torch.randn(16, 300, device=dev, generator=g)
+        for m in (ma, mb):
+            y = m(x)
+            loss = (y ** 2).mean() + (torch.view_as_real(m.cw) ** 2).sum() * (rank + 1)
+            loss.backward()
+        ra.reduce(); rb.reduce()
+        torch.cuda.synchronize()
+        _ext.check_device_errors(dev)
+        for pa, pb in zip(ma.parameters(), mb.parameters()):
+            ga = torch.view_as_real(pa.grad) if pa.grad.is_complex() else pa.grad
+            gb = torch.view_as_real(pb.grad) if pb.grad.is_complex() else pb.grad
+            assert _rel(ga, gb) < 1e-5, _rel(ga, gb)
+    ra.close()
+
+
 def case_fused_matmul():
     """Channel-parallel 1x1 convolution whose partial products are exchanged by the GEMM epilogue (peer memory) ==
     the full convolution: forward, input gradient (reduced over the other group), local weight and bias gradients."""

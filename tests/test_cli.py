@@ -78,3 +78,23 @@ def test_profile_cli_runs_with_a_capture_window(recipe):
                                        "--capture_range_stop", "3", "--capture_ranks", "0"))
     assert trainer.iters == 4
     assert (tmp / "runs" / "tiny_sfno" / "t0" / "training_checkpoints" / "ckpt_mp0.tar").is_file()
+
+
+def test_makani_alias_package_resolves_to_this_framework():
+    """`makani.*` imports give the very module objects of `makani_b200.*` (and `makani.mpu` the parallel layer); the
+    upstream command name `python -m makani.train` reaches the same CLI."""
+    import subprocess
+    import sys
+    import os
+    import makani
+    import makani.utils.comm as c1
+    import makani_b200.utils.comm as c2
+    import makani.mpu.helpers as h1
+    import makani_b200.parallel.helpers as h2
+    from makani.models import model_registry
+    assert c1 is c2 and h1 is h2
+    assert makani.Trainer.__module__ == "makani_b200.utils.trainer"
+    assert "SFNO" in model_registry.list_models()
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, "-m", "makani.train", "--help"], cwd=root, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0 and "--yaml_config" in out.stdout and "--cuda_graph_mode" in out.stdout

@@ -166,6 +166,48 @@ def test_gemm_many_tiles_persistent():
     assert _rel(d, ref) < 1e-2
 
 
+def test_gemm_cta_pairs_epilogues_ragged():
+    """Token-major shapes that run on CTA pairs (256-row tiles, M > 128): ragged M and N, both tile widths, every
+    TMA-store epilogue (plain, bias+GELU+saved pre-activation, +residual, *GELU'), batch of two, MN-major weight."""
+    dev = _dev()
+    torch.manual_seed(21)
+    Z, M, K = 2, 1000, 136
+    for N in (384, 200):
+        x = torch.randn(Z, M, K, device=dev).to(torch.bfloat16)
+        w = torch.randn(N, K, device=dev).to(torch.bfloat16)
+        wt = w.t().contiguous()                                   # [K, N]: the same weight read row-contiguous
+        bias = torch.randn(N, device=dev)
+        res = torch.randn(Z, M, N, device=dev).to(torch.bfloat16)
+        for bn in (128, 256):
+            for act, use_res, use_pre, wmn in [(ACT_NONE, False, False, False), (ACT_GELU, False, True, False),
+                                               (ACT_NONE, True, False, True), (ACT_DGELU, True, False, True)]:
+                d = torch.zeros(Z, M, N, device=dev, dtype=torch.bfloat16)
+                pre = torch.zeros_like(d) if use_pre else None
+                B = Operand(wt, ld=N, mn_major=True) if wmn else Operand(w, ld=K)
+                outs = _run_both(M, N, K, Operand(x, ld=K, zs_lo=M * K), B, Output(d, rs_lo=N, d_zlo=M * N), zlo_n=Z,
+                                 bias=bias if act != ACT_DGELU else None, bias_mode=BIAS_COL, act=act,
+                                 resid=res if use_res else None, preact=pre, bn=bn)
+                for got, ref in outs:
+                    assert _rel(got, ref) < 1e-2, (N, bn, act, use_res)
+
+
+def test_gemm_headline_token_count():
+    """One 1x1-convolution GEMM at the flagship resolution (M = 721 * 1440 tokens, 384 -> 384 channels) against
+    torch.matmul on a sample of row blocks, first, middle and last rows included."""
+    dev = _dev()
+    torch.manual_seed(22)
+    M, N, K = 721 * 1440, 384, 384
+    x = torch.randn(M, K, device=dev).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=dev) / math.sqrt(K)).to(torch.bfloat16)
+    d = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    gemm(M, N, K, Operand(x, ld=K), Operand(w, ld=K), Output(d, rs_lo=N))
+    torch.cuda.synchronize()
+    _ext.check_device_errors(dev)
+    for r0 in (0, 127, 128 * 4055, 256 * 2027 + 3, M - 300):
+        ref = x[r0: r0 + 300].float() @ w.float().t()
+        assert _rel(d[r0: r0 + 300], ref) < 1e-2, r0
+
+
 def test_conv1x1_and_mlp2_fwd_bwd():
     from makani_b200.ops.conv import conv1x1, mlp2
     dev = _dev()

@@ -35,3 +35,9 @@ def test_peer_memory_instance_norm(sizes, world):
 def test_fused_channel_parallel_matmul(sizes, world):
     _need(world)
     _launch("fused_matmul", sizes, world, cuda=True)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_peer_allreduce_matches_nccl(world):
+    _need(world)
+    _launch("peer_allreduce", (1, 1, 1, 1), world, cuda=True)
