@@ -34,8 +34,11 @@ constexpr int NT = 512;
 
 // act: 0 none, 1 GELU (exact erf form), 2 GELU (tanh form); the launchers map the caller's on/off flag to 1 or 2
 // according to the process-wide setting
-__device__ __forceinline__ float gelu_f(float x, int act) { return gelu_fwd(x, act == 2); }
-__device__ __forceinline__ float dgelu_f(float x, int act) { return gelu_bwd(x, act == 2); }
+__device__ __forceinline__ GeluCoef coef_of(int act) {
+  return act == 2 ? GeluCoef{0.7978845608f, 0.0356774081f, 0.f} : GeluCoef{0.797717881f, 0.0367982429f, -3.15818913e-4f};
+}
+__device__ __forceinline__ float gelu_f(float x, int act) { return gelu_fwd(x, coef_of(act)); }
+__device__ __forceinline__ float dgelu_f(float x, int act) { return gelu_bwd(x, coef_of(act)); }
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

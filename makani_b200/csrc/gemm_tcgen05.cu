@@ -79,7 +79,8 @@ struct KParams {
   int ndiv; long long ns_hi;
   float alpha;
   const float* bias;
-  int bias_mode, act, gelu_tanh;
+  int bias_mode, act;
+  GeluCoef gelu;
   float act_param;
   const void* resid;
   void* preact;
@@ -678,7 +679,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
             if constexpr (EPI == 1) {
               if (p.act != 0) {      // ReLU / soft shrinkage (uniform over the launch)
 #pragma unroll
-                for (int j = 0; j < 8; ++j) f[j] = act_fwd(f[j], p.act, p.act_param, p.gelu_tanh);
+                for (int j = 0; j < 8; ++j) f[j] = act_fwd(f[j], p.act, p.act_param, p.gelu);
               }
             }
             if constexpr (EPI == 2) {
@@ -687,20 +688,31 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
               for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
               *reinterpret_cast<uint4*>(box_p + sw) = *reinterpret_cast<uint4*>(h);
 #pragma unroll
-              for (int j = 0; j < 8; ++j) f[j] = gelu_fwd(f[j], p.gelu_tanh);
+              for (int j = 0; j < 8; ++j) f[j] = gelu_fwd(f[j], p.gelu);
             }
             if constexpr (EPI == 3 || EPI == 4) {
               const uint4 ev = *reinterpret_cast<const uint4*>(esm + bx * (BM * 128) + rt * 128 + ((g ^ (rt & 7)) << 4));
               const __nv_bfloat162* eh = reinterpret_cast<const __nv_bfloat162*>(&ev);
+              if constexpr (EPI == 3) {
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const float2 x = __bfloat1622float2(eh[j]);
-                if constexpr (EPI == 3) {
+                for (int j = 0; j < 4; ++j) {
+                  const float2 x = __bfloat1622float2(eh[j]);
                   f[2 * j] += x.x;
                   f[2 * j + 1] += x.y;
-                } else {
-                  f[2 * j] *= act_bwd(x.x, p.act, p.gelu_tanh);
-                  f[2 * j + 1] *= act_bwd(x.y, p.act, p.gelu_tanh);
+                }
+              } else if (p.act == 2) {      // uniform over the launch: the GELU case carries no per-element selects
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 x = __bfloat1622float2(eh[j]);
+                  f[2 * j] *= gelu_bwd(x.x, p.gelu);
+                  f[2 * j + 1] *= gelu_bwd(x.y, p.gelu);
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 x = __bfloat1622float2(eh[j]);
+                  f[2 * j] *= act_bwd(x.x, p.act, p.gelu);
+                  f[2 * j + 1] *= act_bwd(x.y, p.act, p.gelu);
                 }
               }
             }
@@ -786,7 +798,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
             }
             if (p.act & 1) {
 #pragma unroll
-              for (int j = 0; j < 8; ++j) f[j] = act_fwd(f[j], p.act, p.act_param, p.gelu_tanh);
+              for (int j = 0; j < 8; ++j) f[j] = act_fwd(f[j], p.act, p.act_param, p.gelu);
             }
             if (p.resid) {
               if (!p.e_tma) {
@@ -807,7 +819,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
                 }
               }
 #pragma unroll
-              for (int j = 0; j < 8; ++j) f[j] = (p.act != 0 && !(p.act & 1)) ? f[j] * act_bwd(e8[j], p.act, p.gelu_tanh) : f[j] + e8[j];
+              for (int j = 0; j < 8; ++j) f[j] = (p.act != 0 && !(p.act & 1)) ? f[j] * act_bwd(e8[j], p.act, p.gelu) : f[j] + e8[j];
             }
             if (p.out_f32) {
               float4* o = reinterpret_cast<float4*>(static_cast<float*>(p.D) + off);
@@ -838,7 +850,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
                 if (p.out_f32) static_cast<float*>(p.preact)[o] = x;
                 else static_cast<__nv_bfloat16*>(p.preact)[o] = __float2bfloat16(x);
               }
-              if (p.act & 1) x = act_fwd(x, p.act, p.act_param, p.gelu_tanh);
+              if (p.act & 1) x = act_fwd(x, p.act, p.act_param, p.gelu);
               if (p.accumulate) {
                 atomicAdd(static_cast<float*>(p.D) + o, x);
               } else {
@@ -847,7 +859,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
                   if (p.e_tma) rr = e8[j];
                   else rr = p.out_f32 ? static_cast<const float*>(p.resid)[o]
                                       : __bfloat162float(static_cast<const __nv_bfloat16*>(p.resid)[o]);
-                  x = (p.act != 0 && !(p.act & 1)) ? x * act_bwd(rr, p.act, p.gelu_tanh) : x + rr;
+                  x = (p.act != 0 && !(p.act & 1)) ? x * act_bwd(rr, p.act, p.gelu) : x + rr;
                 }
                 if (p.out_f32) static_cast<float*>(p.D)[o] = x;
                 else {
@@ -1332,7 +1344,7 @@ cudaError_t gemm_launch(const GemmProblem& p, const GemmOperand& A, const GemmOp
   kp.d_zlo = e.d_zlo; kp.d_zhi = e.d_zhi;
   kp.rdiv = e.rdiv > 0 ? e.rdiv : 1 << 30; kp.rs_hi = e.rs_hi; kp.rs_lo = e.rs_lo;
   kp.ndiv = e.ndiv > 0 ? e.ndiv : 1 << 30; kp.ns_hi = e.ns_hi;
-  kp.alpha = e.alpha; kp.bias = e.bias; kp.bias_mode = e.bias ? e.bias_mode : 0; kp.act = e.act; kp.gelu_tanh = gelu_tanh(); kp.act_param = e.act_param;
+  kp.alpha = e.alpha; kp.bias = e.bias; kp.bias_mode = e.bias ? e.bias_mode : 0; kp.act = e.act; kp.gelu = gelu_coef(gelu_tanh()); kp.act_param = e.act_param;
   kp.resid = e.resid; kp.preact = e.preact; kp.D = e.D;
   kp.out_f32 = e.out_f32; kp.accumulate = e.accumulate;
   // 16-byte vector accesses need every stride (and the bases) aligned
@@ -1385,13 +1397,18 @@ cudaError_t gemm_launch(const GemmProblem& p, const GemmOperand& A, const GemmOp
   }
   // CTA pairs (256-row tiles, each CTA loads half of the B tile): single-device bf16 launches without row-triangular
   // structure and with at least two row blocks.  MAKANI_B200_CTA_PAIRS=0 keeps every launch on single CTAs.
-  static const int pairs_enabled = [] {
+  // Measured at 721x1440 (1 GPU, CUDA events): pairs win where the k loop is long (K = 768 convolutions, weight
+  // gradients, the longitude DFT: 3-11 %) and lose where it is short (K = 384: the epilogue, not the operand fill, is
+  // the bound there, and a pair has half as many independent tiles in flight), so the default is K >= 512.
+  // MAKANI_B200_CTA_PAIRS=0 / 1 forces none / all eligible launches.
+  static const int pairs_mode = [] {
     const char* e = getenv("MAKANI_B200_CTA_PAIRS");
-    return (e && e[0] == '0') ? 0 : 1;
+    return (e && e[0] == '0') ? 0 : ((e && e[0] == '1') ? 1 : 2);
   }();
   const bool no_peer = (peer == nullptr) || (peer->nseg <= 1 && peer->ndx == 0 && peer->nwait == 0 && peer->nsig == 0 &&
                                               peer->done_ctr == nullptr);
-  const int cg = (pairs_enabled && eb == 2 && no_peer && p.M > BM && p.rmin_a == 0 && p.rmax_a == 0) ? 2 : 1;
+  const bool eligible = eb == 2 && no_peer && p.M > BM && p.rmin_a == 0 && p.rmax_a == 0;
+  const int cg = (eligible && (pairs_mode == 1 || (pairs_mode == 2 && p.K >= 512))) ? 2 : 1;
   kp.m_tiles = (p.M + BM * cg - 1) / (BM * cg);
   kp.n_tiles = (p.N + bn - 1) / bn;
   kp.total_tiles = static_cast<long long>(kp.m_tiles) * kp.n_tiles * kp.splits * p.zlo_n * p.zhi_n;
