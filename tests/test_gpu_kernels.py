@@ -171,7 +171,7 @@ def test_gemm_cta_pairs_epilogues_ragged():
     TMA-store epilogue (plain, bias+GELU+saved pre-activation, +residual, *GELU'), batch of two, MN-major weight."""
     dev = _dev()
     torch.manual_seed(21)
-    Z, M, K = 2, 1000, 136
+    Z, M, K = 2, 1000, 520       # K >= 512: the launcher's default puts these shapes on CTA pairs
     for N in (384, 200):
         x = torch.randn(Z, M, K, device=dev).to(torch.bfloat16)
         w = torch.randn(N, K, device=dev).to(torch.bfloat16)
@@ -196,7 +196,7 @@ def test_gemm_headline_token_count():
     torch.matmul on a sample of row blocks, first, middle and last rows included."""
     dev = _dev()
     torch.manual_seed(22)
-    M, N, K = 721 * 1440, 384, 384
+    M, N, K = 721 * 1440, 384, 768     # the block MLP's second layer: runs on CTA pairs
     x = torch.randn(M, K, device=dev).to(torch.bfloat16)
     w = (torch.randn(N, K, device=dev) / math.sqrt(K)).to(torch.bfloat16)
     d = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
