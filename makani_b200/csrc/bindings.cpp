@@ -198,6 +198,7 @@ void gemm_impl(const Tensor& a, const Tensor& b, Tensor& d, const c10::optional<
     float f;
     memcpy(&f, &bits, sizeof(f));
     e.act_param = f;
+    e.bias_zs = ip[k++];
   }
   e.bias = nullptr;
   if (bias.has_value() && bias->defined()) {

@@ -79,6 +79,7 @@ struct KParams {
   int ndiv; long long ns_hi;
   float alpha;
   const float* bias;
+  long long bias_zs;              // elements between the bias vectors of consecutive z_lo batches (0: one shared vector)
   int bias_mode, act;
   GeluCoef gelu;
   float act_param;
@@ -615,8 +616,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
       const bool row_ok = r < p.M;
       const long long row_off = static_cast<long long>(c.zhi) * p.d_zhi + static_cast<long long>(c.zlo) * p.d_zlo +
                                 static_cast<long long>(r / p.rdiv) * p.rs_hi + static_cast<long long>(r % p.rdiv) * p.rs_lo;
+      const float* const bias_z = p.bias + static_cast<long long>(c.zlo) * p.bias_zs;
       float rbias = 0.f;
-      if (p.bias_mode == 1 && row_ok) rbias = __ldg(p.bias + r);
+      if (p.bias_mode == 1 && row_ok) rbias = __ldg(bias_z + r);
       int buf = 0, ebuf = 0;
       if (!c.skip) {
         buf = acc_it & 1;
@@ -667,12 +669,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
             for (int j = 0; j < 8; ++j) f[j] = fmaf(__uint_as_float(v[g * 8 + j]), p.alpha, rbias);
             if (p.bias_mode == 2) {
               if (n + 8 <= p.N) {
-                const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.bias + n));
-                const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.bias + n) + 1);
+                const float4 b0 = __ldg(reinterpret_cast<const float4*>(bias_z + n));
+                const float4 b1 = __ldg(reinterpret_cast<const float4*>(bias_z + n) + 1);
                 f[0] += b0.x; f[1] += b0.y; f[2] += b0.z; f[3] += b0.w;
                 f[4] += b1.x; f[5] += b1.y; f[6] += b1.z; f[7] += b1.w;
               } else {
-                for (int j = 0; j < 8 && n + j < p.N; ++j) f[j] += __ldg(p.bias + n + j);
+                for (int j = 0; j < 8 && n + j < p.N; ++j) f[j] += __ldg(bias_z + n + j);
               }
             }
             const uint32_t sw = static_cast<uint32_t>((g ^ (lane & 7)) << 4) + lane * 128;
@@ -763,7 +765,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
           } else if (p.bias_mode == 2) {
 #pragma unroll
             for (int j = 0; j < 8; ++j)
-              if (n + j < p.N) f[j] += __ldg(p.bias + n + j);
+              if (n + j < p.N) f[j] += __ldg(bias_z + n + j);
           }
           const bool full = (n + 8 <= p.N);
           const long long off = row_off + static_cast<long long>(n / p.ndiv) * p.ns_hi + (n % p.ndiv);
@@ -1344,7 +1346,7 @@ cudaError_t gemm_launch(const GemmProblem& p, const GemmOperand& A, const GemmOp
   kp.d_zlo = e.d_zlo; kp.d_zhi = e.d_zhi;
   kp.rdiv = e.rdiv > 0 ? e.rdiv : 1 << 30; kp.rs_hi = e.rs_hi; kp.rs_lo = e.rs_lo;
   kp.ndiv = e.ndiv > 0 ? e.ndiv : 1 << 30; kp.ns_hi = e.ns_hi;
-  kp.alpha = e.alpha; kp.bias = e.bias; kp.bias_mode = e.bias ? e.bias_mode : 0; kp.act = e.act; kp.gelu = gelu_coef(gelu_tanh()); kp.act_param = e.act_param;
+  kp.alpha = e.alpha; kp.bias = e.bias; kp.bias_zs = e.bias ? e.bias_zs : 0; kp.bias_mode = e.bias ? e.bias_mode : 0; kp.act = e.act; kp.gelu = gelu_coef(gelu_tanh()); kp.act_param = e.act_param;
   kp.resid = e.resid; kp.preact = e.preact; kp.D = e.D;
   kp.out_f32 = e.out_f32; kp.accumulate = e.accumulate;
   // 16-byte vector accesses need every stride (and the bases) aligned
@@ -1438,7 +1440,7 @@ cudaError_t gemm_launch(const GemmProblem& p, const GemmOperand& A, const GemmOp
   DMaps mdx;
   for (int q = 0; q < MAX_SEG - 1; ++q) mdx.m[q] = ma;   // placeholders: always valid descriptors
   if (eb == 2 && !e.out_f32 && kp.vec_ok && !e.accumulate && plain && e.d_zlo >= 0 && e.d_zhi >= 0 &&
-      (kp.bias_mode != 2 || (reinterpret_cast<uintptr_t>(e.bias) & 15) == 0)) {
+      (kp.bias_mode != 2 || ((reinterpret_cast<uintptr_t>(e.bias) & 15) == 0 && (kp.bias_zs % 4) == 0))) {
     if (!e.resid && !e.preact && (e.act == 0 || e.act == 3 || e.act == 5)) epi = 1;
     else if (!e.resid && e.preact && e.act == 1) epi = 2;
     else if (e.resid && kp.e_tma && !e.preact && e.act == 0) epi = 3;

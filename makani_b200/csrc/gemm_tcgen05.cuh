@@ -40,6 +40,7 @@ struct GemmEpilogue {
   float alpha;
   const float* bias;    // fp32, may be null
   int bias_mode;        // 1: per row r, 2: per column n
+  long long bias_zs;    // elements between the bias vectors of consecutive z_lo batches (0: one vector for all)
   int act;              // 0 none; 1 GELU, 3 ReLU, 5 soft shrinkage (threshold act_param); 2 / 4 / 6: multiply by the
                         // derivative of GELU / ReLU / soft shrinkage evaluated at `resid` (see gelu.cuh)
   float act_param;

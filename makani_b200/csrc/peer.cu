@@ -68,6 +68,9 @@ struct Vec16<float> {
   static __device__ __forceinline__ void store(float* p, const float (&f)[4]) {
     *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
   }
+  static __device__ __forceinline__ void store_cs(float* p, const float (&f)[4]) {
+    __stcs(reinterpret_cast<float4*>(p), make_float4(f[0], f[1], f[2], f[3]));
+  }
 };
 template <>
 struct Vec16<__nv_bfloat16> {
@@ -97,6 +100,13 @@ struct Vec16<__nv_bfloat16> {
 #pragma unroll
     for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
     *reinterpret_cast<uint4*>(p) = v;
+  }
+  static __device__ __forceinline__ void store_cs(__nv_bfloat16* p, const float (&f)[8]) {
+    uint4 v;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+    __stcs(reinterpret_cast<uint4*>(p), v);
   }
 };
 
@@ -136,7 +146,7 @@ __global__ void __maxnreg__(64) allreduce_kernel(const PeerPtrs p, int rank, lon
         const long long i = i0 + u * stride;
         if (i < end) {
 #pragma unroll
-          for (int r = 0; r < WORLD; ++r) raw[u][r] = *reinterpret_cast<const uint4*>(peer[r] + i * V);
+          for (int r = 0; r < WORLD; ++r) raw[u][r] = __ldcs(reinterpret_cast<const uint4*>(peer[r] + i * V));   // streaming: keep L2 for the GEMMs
         }
       }
 #pragma unroll
@@ -151,7 +161,7 @@ __global__ void __maxnreg__(64) allreduce_kernel(const PeerPtrs p, int rank, lon
 #pragma unroll
           for (int j = 0; j < V; ++j) acc[j] *= scale;
 #pragma unroll
-          for (int r = 0; r < WORLD; ++r) Vec16<T>::store(peer[r] + i * V, acc);
+          for (int r = 0; r < WORLD; ++r) Vec16<T>::store_cs(peer[r] + i * V, acc);
         }
       }
     }
@@ -174,7 +184,21 @@ template <typename T>
 cudaError_t launch_allreduce(int world, unsigned blocks, cudaStream_t s, const PeerPtrs& p, int rank, long long n, float scale,
                              uint64_t wait_ns, int* err) {
   switch (world) {
-#define MK_AR(W) case W: allreduce_kernel<T, W><<<blocks, AR_THREADS, 0, s>>>(p, rank, n, scale, wait_ns, err); break;
+  // The reduction has to run on SMs that a persistent GEMM CTA already occupies.  Kernels share an SM only under one
+  // shared-memory / L1 split, and the GEMMs run with the largest shared-memory carve-out, so this kernel asks for the
+  // same split although it uses no shared memory itself; otherwise it waits for SMs to drain and the GEMM CTA that
+  // lost its SM to this kernel runs as a straggler after the others.
+#define MK_AR(W)                                                                                                      \
+  case W: {                                                                                                           \
+    static bool carve = false;                                                                                        \
+    if (!carve) {                                                                                                     \
+      cudaFuncSetAttribute(allreduce_kernel<T, W>, cudaFuncAttributePreferredSharedMemoryCarveout,                    \
+                           cudaSharedmemCarveoutMaxShared);                                                           \
+      carve = true;                                                                                                   \
+    }                                                                                                                 \
+    allreduce_kernel<T, W><<<blocks, AR_THREADS, 0, s>>>(p, rank, n, scale, wait_ns, err);                            \
+    break;                                                                                                            \
+  }
     MK_AR(1) MK_AR(2) MK_AR(3) MK_AR(4) MK_AR(5) MK_AR(6) MK_AR(7) MK_AR(8)
 #undef MK_AR
     default: return cudaErrorInvalidValue;

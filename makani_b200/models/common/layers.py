@@ -16,6 +16,7 @@ import torch.nn.functional as F
 from torch.utils.checkpoint import checkpoint
 
 from ...ops import conv as conv_ops
+from ...ops import linear as linear_ops
 
 
 def drop_path(x: torch.Tensor, drop_prob: float = 0.0, training: bool = False) -> torch.Tensor:
@@ -120,10 +121,13 @@ class MLP(nn.Module):
             drop = nn.Identity()
         self.fwd = nn.Sequential(fc1, act_layer(), drop, fc2, drop)
         self._fusable = (input_format == "nchw" and _is_gelu(act_layer) and drop_rate == 0.0)
+        self._fusable_tokens = (input_format == "traditional" and _is_gelu(act_layer) and drop_rate == 0.0)
 
     def _run(self, x):
         if self._fusable and x.is_cuda and conv_ops.fast_path_ok(x):
             return conv_ops.mlp2(x, self.fwd[0].weight, self.fwd[0].bias, self.fwd[3].weight, self.fwd[3].bias)
+        if self._fusable_tokens and linear_ops.fast_path_ok(x):
+            return linear_ops.mlp2_lastdim(x, self.fwd[0].weight, self.fwd[0].bias, self.fwd[3].weight, self.fwd[3].bias)
         return self.fwd(x)
 
     def forward(self, x):

@@ -16,6 +16,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from ...ops import afno as afno_ops
 from ...ops import linear as linear_ops
 from ...parallel.helpers import compute_split_shapes
 from ...parallel.layers import DistributedMLP
@@ -43,7 +44,8 @@ class Mlp(nn.Module):
 
 
 class AFNO2D(nn.Module):
-    """rfft2 -> per-block complex (linear, ReLU, linear) -> softshrink -> irfft2, plus the input as skip."""
+    """rfft2 -> per-block complex (linear, ReLU, linear) -> softshrink -> irfft2, plus the input as skip
+    (makani/models/networks/afnonet.py:45-112), evaluated as one chain of tensor-core GEMMs."""
 
     def __init__(self, hidden_size, num_blocks=8, sparsity_threshold=0.01, hard_thresholding_fraction=1, hidden_size_factor=1):
         super().__init__()
@@ -68,29 +70,18 @@ class AFNO2D(nn.Module):
             p.sharded_dims_mp = [None, "matmul"] + [None] * (p.dim() - 2)
 
     def forward(self, x):
+        """x [B, H, W, C_local-or-full] NHWC tokens.  The whole filter (both FFTs, the block MLP, the skip) is the GEMM
+        chain of `ops/afno.py`; tensors it does not take (odd block sizes, fp32 on CUDA) go through its torch.fft twin."""
         msize = comm.get_size("matmul")
         if msize > 1:
             x = scatter_to_parallel_region(x, 3, "matmul")
-        bias = x
-        dtype = x.dtype
-        x = x.float()
         B, H, W, C = x.shape
-        xf = torch.fft.rfft2(x, dim=(1, 2), norm="ortho")
-        xf = xf.reshape(B, H, W // 2 + 1, self.num_blocks_local, self.block_size)
-        total = H // 2 + 1
-        kept = int(total * self.hard_thresholding_fraction)
-        xs = xf[:, total - kept: total + kept, :kept]
-        w1r, w1i, w2r, w2i = self.w1[0], self.w1[1], self.w2[0], self.w2[1]
-        mul = lambda a, w: torch.einsum("...bi,bio->...bo", a, w)
-        o1r = F.relu(mul(xs.real, w1r) - mul(xs.imag, w1i) + self.b1[0])
-        o1i = F.relu(mul(xs.imag, w1r) + mul(xs.real, w1i) + self.b1[1])
-        o2r = mul(o1r, w2r) - mul(o1i, w2i) + self.b2[0]
-        o2i = mul(o1i, w2r) + mul(o1r, w2i) + self.b2[1]
-        out = torch.zeros(B, H, W // 2 + 1, self.num_blocks_local, self.block_size, 2, device=x.device, dtype=torch.float32)
-        out[:, total - kept: total + kept, :kept] = torch.stack([o2r, o2i], dim=-1)
-        out = F.softshrink(out, lambd=self.sparsity_threshold)
-        out = torch.view_as_complex(out).reshape(B, H, W // 2 + 1, C)
-        y = torch.fft.irfft2(out, s=(H, W), dim=(1, 2), norm="ortho").to(dtype) + bias
+        kx, ncols = afno_ops.mode_window_v1(H, W, self.hard_thresholding_fraction)
+        hid = self.block_size * self.hidden_size_factor
+        xc = x.contiguous()
+        fn = afno_ops.afno_filter if afno_ops.fast_path_ok(xc, self.num_blocks_local, hid) else afno_ops.afno_filter_reference
+        y = fn(xc, self.w1[0], self.w1[1], self.b1[0], self.b1[1], self.w2[0], self.w2[1], self.b2[0], self.b2[1],
+               kx, ncols, self.sparsity_threshold, skip=xc)
         if msize > 1:
             y = gather_from_parallel_region(y, 3, self.chan_shapes, "matmul")
         return y

@@ -1,6 +1,23 @@
-"""Adaptive Fourier Neural Operator, NCHW variant with complex block-diagonal kernels, instance/layer norm and
-an optional (linear / identity) skip around the spectral filter.  Architecture and parameter names follow
-makani/models/networks/afnonet_v2.py:34-314."""
+"""AFNO, second generation ("AFNO" in the registry): patch tokens on an [embed, h, w] grid, per block
+
+    x -> norm1 -> spectral filter (+ its input, + a per-channel bias) -> + skip(x) -> norm2 -> MLP -> + x
+
+Checkpoint contract (parameter names and shapes of makani/models/networks/afnonet_v2.py:52-314):
+`patch_embed.proj`, `pos_embed [1, E, h*w]`, `blocks.{i}.{norm1, norm2, skip_layer, filter.{w1 [nb,bs,bs*f,2],
+b1 [1,E,1,1], w2 [nb,bs*f,bs,2]}, mlp}`, `head` (1x1 convolution without bias).
+
+Execution is laid out for B200: activations are NCHW tensors in channels-last memory (a token's channels are one
+contiguous line, which is what the TMA tiles of the GEMM engine want), and a block is five fused launches groups:
+
+  * instance norm: two streaming kernels (`ops/norm.py`);
+  * spectral filter: the GEMM chain of `ops/afno.py` (both FFTs restricted to the kept modes, block-diagonal complex MLP
+    with ReLU and soft shrinkage in the epilogues), which also adds its input in its last epilogue;
+  * skip: the 1x1 convolution of the block input is a GEMM whose epilogue adds the filter output; the filter's bias `b1` is
+    folded into that convolution's bias, so no elementwise pass is left;
+  * MLP: two GEMMs with bias + GELU and bias + residual epilogues (`ops/conv.py`).
+
+On CPU, or for dtypes / shapes the kernels do not take, each piece falls back to its plain torch formulation.
+"""
 
 from __future__ import annotations
 
@@ -8,93 +25,101 @@ from functools import partial
 
 import torch
 import torch.nn as nn
-import torch.nn.functional as F
 
-from ..common.activations import ComplexReLU
+from ...ops import afno as afno_ops
+from ...ops import conv as conv_ops
+from ...ops import norm as norm_ops
 from ..common.layers import MLP, DropPath, PatchEmbed
 
 
-def compl_mul_add_fwd(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
-    """Real-arithmetic complex product: a [b,k,i,x,y,2], b [k,i,o,2] -> [b,k,o,x,y,2]."""
-    tmp = torch.einsum("bkixys,kior->srbkoxy", a, b)
-    return torch.stack([tmp[0, 0] - tmp[1, 1], tmp[1, 0] + tmp[0, 1]], dim=-1)
-
-
-def compl_mul_add_fwd_c(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
-    return torch.view_as_real(torch.einsum("bkixy,kio->bkoxy", torch.view_as_complex(a), torch.view_as_complex(b)))
+def _cl(x: torch.Tensor) -> torch.Tensor:
+    """Channels-last memory for a 4-D NCHW-shaped activation (no copy when it already is)."""
+    return x.contiguous(memory_format=torch.channels_last)
 
 
 class AFNO2D(nn.Module):
+    """Spectral token mixer.  `forward` returns filter(x) + x + b1 unless `fold_bias` asks the caller to add `b1`."""
+
     def __init__(self, hidden_size, num_blocks=8, sparsity_threshold=0.0, hard_thresholding_fraction=1, hidden_size_factor=1,
                  use_complex_kernels=False):
         super().__init__()
-        assert hidden_size % num_blocks == 0, f"hidden_size {hidden_size} should be divisble by num_blocks {num_blocks}"
+        if hidden_size % num_blocks != 0:
+            raise ValueError(f"hidden_size {hidden_size} is not a multiple of num_blocks {num_blocks}")
         self.hidden_size, self.num_blocks = hidden_size, num_blocks
-        self.sparsity_threshold = sparsity_threshold
         self.block_size = hidden_size // num_blocks
-        self.hard_thresholding_fraction = hard_thresholding_fraction
         self.hidden_size_factor = hidden_size_factor
-        self.scale = 0.02
-        self.mult_handle = compl_mul_add_fwd_c if use_complex_kernels else compl_mul_add_fwd
-        bs, f = self.block_size, hidden_size_factor
-        self.w1 = nn.Parameter(self.scale * torch.randn(num_blocks, bs, bs * f, 2))
-        self.b1 = nn.Parameter(self.scale * torch.randn(1, num_blocks * bs, 1, 1))
-        self.w2 = nn.Parameter(self.scale * torch.randn(num_blocks, bs * f, bs, 2))
-        self.act = ComplexReLU(negative_slope=0.0, mode="cartesian")
+        self.sparsity_threshold = float(sparsity_threshold)
+        self.hard_thresholding_fraction = hard_thresholding_fraction
+        bs, hid, std = self.block_size, self.block_size * hidden_size_factor, 0.02
+        self.w1 = nn.Parameter(std * torch.randn(num_blocks, bs, hid, 2))
+        self.b1 = nn.Parameter(std * torch.randn(1, hidden_size, 1, 1))
+        self.w2 = nn.Parameter(std * torch.randn(num_blocks, hid, bs, 2))
+
+    def forward(self, x: torch.Tensor, fold_bias: bool = False) -> torch.Tensor:
+        B, C, H, W = x.shape
+        kx, ncols = afno_ops.mode_window_v2(H, W, self.hard_thresholding_fraction)
+        tok = _cl(x).permute(0, 2, 3, 1)                       # [B, H, W, C] view of the channels-last storage
+        hid = self.block_size * self.hidden_size_factor
+        fn = afno_ops.afno_filter if afno_ops.fast_path_ok(tok, self.num_blocks, hid) else afno_ops.afno_filter_reference
+        y = fn(tok, self.w1[..., 0], self.w1[..., 1], None, None, self.w2[..., 0], self.w2[..., 1], None, None,
+               kx, ncols, self.sparsity_threshold, skip=tok)
+        y = y.permute(0, 3, 1, 2)                               # back to an NCHW-shaped channels-last tensor
+        return y if fold_bias else y + self.b1.to(y.dtype)
+
+
+class _Norm(nn.Module):
+    """Instance norm with affine parameters (fused kernels on the channels-last path) or layer norm over (h, w); either
+    way the parameters are `weight` / `bias`, as in the checkpoints."""
+
+    def __init__(self, kind: str, channels: int, hw):
+        super().__init__()
+        self.kind, self.eps, self.hw = kind, 1e-6, tuple(hw)
+        if kind == "instance_norm":
+            shape = (channels,)
+        elif kind == "layer_norm":
+            shape = self.hw
+        else:
+            raise NotImplementedError(f"normalization {kind} not implemented")
+        self.weight = nn.Parameter(torch.ones(shape))
+        self.bias = nn.Parameter(torch.zeros(shape))
 
     def forward(self, x):
-        bias = x
-        dtype = x.dtype
-        x = x.float()
-        B, C, H, W = x.shape
-        tot_h, tot_w = H // 2 + 1, W // 2 + 1
-        kept_h = int(tot_h * self.hard_thresholding_fraction)
-        kept_w = int(tot_w * self.hard_thresholding_fraction)
-        xf = torch.fft.rfft2(x, dim=(-2, -1), norm="ortho").view(B, self.num_blocks, self.block_size, H, W // 2 + 1)
-        xr = torch.view_as_real(xf)
-        out = torch.zeros_like(xr)
-
-        def mlp(z):
-            o = torch.view_as_real(self.act(torch.view_as_complex(self.mult_handle(z.contiguous(), self.w1).contiguous())))
-            return self.mult_handle(o.contiguous(), self.w2)
-
-        if kept_h == tot_h:
-            out[:, :, :, :, :kept_w] = mlp(xr[:, :, :, :, :kept_w])
-        else:
-            out[:, :, :, :kept_h, :kept_w] = mlp(xr[:, :, :, :kept_h, :kept_w])
-            out[:, :, :, -kept_h:, :kept_w] = mlp(xr[:, :, :, -kept_h:, :kept_w])
-        out = F.softshrink(out, lambd=self.sparsity_threshold)
-        out = torch.view_as_complex(out).reshape(B, C, H, W // 2 + 1)
-        y = torch.fft.irfft2(out, s=(H, W), dim=(-2, -1), norm="ortho").to(dtype)
-        return y + self.b1.to(dtype) + bias
+        if self.kind == "instance_norm":
+            return norm_ops.instance_norm(x, self.weight, self.bias, self.eps, "none")
+        return torch.nn.functional.layer_norm(x, self.hw, self.weight.to(x.dtype), self.bias.to(x.dtype), self.eps)
 
 
 class Block(nn.Module):
-    def __init__(self, h, w, dim, mlp_ratio=4.0, drop=0.0, drop_path=0.0, act_layer=nn.GELU, norm_layer=nn.LayerNorm,
+    def __init__(self, h, w, dim, mlp_ratio=4.0, drop=0.0, drop_path=0.0, act_layer=nn.GELU, norm_kind="instance_norm",
                  num_blocks=8, sparsity_threshold=0.01, hard_thresholding_fraction=1.0, use_complex_kernels=True,
-                 skip_fno="linear", nested_skip_fno=True, checkpointing=False, verbose=True):
+                 skip_fno="linear", nested_skip_fno=True, checkpointing=False):
         super().__init__()
-        self.norm1 = norm_layer()
-        if skip_fno == "linear":
-            self.skip_layer = nn.Conv2d(dim, dim, 1, 1)
-        elif skip_fno == "identity":
-            self.skip_layer = nn.Identity()
-        else:
-            skip_fno = None
-        self.skip_fno, self.nested_skip_fno = skip_fno, nested_skip_fno
+        self.norm1 = _Norm(norm_kind, dim, (h, w))
+        self.norm2 = _Norm(norm_kind, dim, (h, w))
         self.filter = AFNO2D(dim, num_blocks, sparsity_threshold, hard_thresholding_fraction, use_complex_kernels=use_complex_kernels)
+        self.skip_fno = skip_fno if skip_fno in ("linear", "identity") else None
+        self.nested_skip_fno = nested_skip_fno
+        if self.skip_fno == "linear":
+            self.skip_layer = nn.Conv2d(dim, dim, 1, 1)
+        elif self.skip_fno == "identity":
+            self.skip_layer = nn.Identity()
         self.drop_path = DropPath(drop_path) if drop_path > 0.0 else nn.Identity()
-        self.norm2 = norm_layer()
         self.mlp = MLP(in_features=dim, hidden_features=int(dim * mlp_ratio), act_layer=act_layer, drop_rate=drop,
                        checkpointing=2 if checkpointing else 0)
 
     def forward(self, x):
         residual = x
-        x = self.filter(self.norm1(x))
-        if self.skip_fno is not None:
-            x = x + self.skip_layer(residual)
-            if not self.nested_skip_fno:
-                residual = x
+        if self.skip_fno == "linear":
+            # filter output enters the skip convolution as its epilogue residual; b1 rides on the convolution's bias
+            f = self.filter(self.norm1(x), fold_bias=True)
+            bias = self.skip_layer.bias + self.filter.b1.reshape(-1)
+            x = conv_ops.conv1x1(_cl(residual), self.skip_layer.weight, bias, resid=_cl(f))
+        else:
+            x = self.filter(self.norm1(x))
+            if self.skip_fno == "identity":
+                x = x + residual
+        if self.skip_fno is not None and not self.nested_skip_fno:
+            residual = x
         x = self.mlp(self.norm2(x))
         return self.drop_path(x) + residual
 
@@ -106,56 +131,46 @@ class AdaptiveFourierNeuralOperatorNet(nn.Module):
                  checkpointing=False, use_complex_kernels=True, verbose=False, **kwargs):
         super().__init__()
         self.img_size, self.patch_size = tuple(inp_shape), tuple(patch_size)
+        if len(self.patch_size) != 2:
+            raise ValueError(f"patch_size needs two entries, got {patch_size}")
+        if self.img_size[0] % self.patch_size[0] or self.img_size[1] % self.patch_size[1]:
+            raise ValueError(f"patch size {self.patch_size} does not divide the image {self.img_size}")
         self.inp_chans, self.out_chans, self.embed_dim = inp_chans, out_chans, embed_dim
-        assert len(patch_size) == 2, f"Expected patch_size to have two entries but got {patch_size} instead"
-        assert self.img_size[0] % self.patch_size[0] == 0 and self.img_size[1] % self.patch_size[1] == 0, \
-            f"the patch size {self.patch_size} does not divide the image dimensions {self.img_size} evenly"
+        self.h, self.w = self.img_size[0] // self.patch_size[0], self.img_size[1] // self.patch_size[1]
         self.patch_embed = PatchEmbed(img_size=self.img_size, patch_size=self.patch_size, in_chans=inp_chans, embed_dim=embed_dim)
-        self.pos_embed = nn.Parameter(torch.zeros(1, embed_dim, self.patch_embed.num_patches))
+        self.pos_embed = nn.Parameter(torch.zeros(1, embed_dim, self.h * self.w))
         self.pos_drop = nn.Dropout(p=drop_rate) if drop_rate > 0.0 else nn.Identity()
-        dpr = [x.item() for x in torch.linspace(0, drop_path_rate, num_layers)]
-        self.h = self.img_size[0] // self.patch_size[0]
-        self.w = self.img_size[1] // self.patch_size[1]
-        if normalization_layer == "layer_norm":
-            norm_layer = partial(nn.LayerNorm, normalized_shape=(self.h, self.w), eps=1e-6)
-        elif normalization_layer == "instance_norm":
-            norm_layer = partial(nn.InstanceNorm2d, num_features=embed_dim, eps=1e-6, affine=True, track_running_stats=False)
-        else:
-            raise NotImplementedError(f"normalization {normalization_layer} not implemented")
+        rates = torch.linspace(0, drop_path_rate, num_layers).tolist()
         self.blocks = nn.ModuleList([
-            Block(h=self.h, w=self.w, dim=embed_dim, mlp_ratio=mlp_ratio, drop=drop_rate, drop_path=dpr[i], norm_layer=norm_layer,
-                  num_blocks=num_blocks, sparsity_threshold=sparsity_threshold, hard_thresholding_fraction=hard_thresholding_fraction,
-                  use_complex_kernels=use_complex_kernels, skip_fno=skip_fno, nested_skip_fno=nested_skip_fno,
-                  checkpointing=checkpointing, verbose=verbose) for i in range(num_layers)])
+            Block(self.h, self.w, embed_dim, mlp_ratio=mlp_ratio, drop=drop_rate, drop_path=rates[i],
+                  norm_kind=normalization_layer, num_blocks=num_blocks, sparsity_threshold=sparsity_threshold,
+                  hard_thresholding_fraction=hard_thresholding_fraction, use_complex_kernels=use_complex_kernels,
+                  skip_fno=skip_fno, nested_skip_fno=nested_skip_fno, checkpointing=checkpointing)
+            for i in range(num_layers)])
         self.head = nn.Conv2d(embed_dim, out_chans * self.patch_size[0] * self.patch_size[1], 1, bias=False)
         nn.init.trunc_normal_(self.pos_embed, std=0.02)
-        self.apply(self._init_weights)
-
-    def _init_weights(self, m):
-        if isinstance(m, (nn.Linear, nn.Conv2d)):
-            nn.init.trunc_normal_(m.weight, std=0.02)
-            if m.bias is not None:
-                nn.init.constant_(m.bias, 0)
-        elif isinstance(m, nn.LayerNorm):
-            nn.init.constant_(m.bias, 0)
-            nn.init.constant_(m.weight, 1.0)
+        for m in self.modules():
+            if isinstance(m, (nn.Linear, nn.Conv2d)):
+                nn.init.trunc_normal_(m.weight, std=0.02)
+                if m.bias is not None:
+                    nn.init.zeros_(m.bias)
 
     @torch.jit.ignore
     def no_weight_decay(self):
         return {"pos_embed", "cls_token"}
 
     def forward_features(self, x):
-        B = x.shape[0]
-        x = self.patch_embed(x)
-        x = self.pos_drop(x + self.pos_embed.to(x.dtype))
-        x = x.reshape(B, self.embed_dim, self.h, self.w)
+        tokens = self.patch_embed(x)                                           # [B, E, h*w]
+        tokens = self.pos_drop(tokens + self.pos_embed.to(tokens.dtype))
+        x = _cl(tokens.reshape(tokens.shape[0], self.embed_dim, self.h, self.w))
         for blk in self.blocks:
             x = blk(x)
         return x
 
     def forward(self, x):
-        x = self.head(self.forward_features(x))
-        b = x.shape[0]
-        xv = x.view(b, self.patch_size[0], self.patch_size[1], -1, self.h, self.w)
-        xvt = torch.permute(xv, (0, 3, 4, 1, 5, 2)).contiguous()
-        return xvt.view(b, -1, self.h * self.patch_size[0], self.w * self.patch_size[1])
+        feat = self.forward_features(x)
+        y = conv_ops.conv1x1(feat, self.head.weight, None)                      # [B, out*p0*p1, h, w]
+        B, (p0, p1) = y.shape[0], self.patch_size
+        # un-patchify: channel index (p0, p1, c) of token (i, j) -> pixel (i*p0 + a, j*p1 + b) of channel c
+        y = y.reshape(B, p0, p1, self.out_chans, self.h, self.w).permute(0, 3, 4, 1, 5, 2)
+        return y.reshape(B, self.out_chans, self.h * p0, self.w * p1)

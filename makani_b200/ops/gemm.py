@@ -95,7 +95,7 @@ def _flat(t: torch.Tensor) -> torch.Tensor:
 
 
 def _emulate(M, N, K, A: Operand, B: Operand, D: Output, zlo_n, zhi_n, alpha, bias, bias_mode, act, resid, resid_offset,
-             preact, preact_offset, accumulate, tri: Tri, segments=None, act_param: float = 0.0):
+             preact, preact_offset, accumulate, tri: Tri, segments=None, act_param: float = 0.0, bias_zs: int = 0):
     fa, fb, fd = _flat(A.tensor), _flat(B.tensor), _flat(D.tensor)
     cdt = torch.float64 if fa.dtype == torch.float64 else torch.float32
 
@@ -124,7 +124,10 @@ def _emulate(M, N, K, A: Operand, B: Operand, D: Output, zlo_n, zhi_n, alpha, bi
     rmask = (r >= tri.rmin_a * zh + tri.rmin_b) & (r < tri.rmax_a * zh + tri.rmax_b)
     acc = acc * rmask.to(cdt)
     acc = acc * alpha
-    if bias is not None and bias_mode == BIAS_ROW:
+    if bias is not None and bias_zs:
+        bz = bias.to(cdt).reshape(-1).as_strided((zlo_n, M if bias_mode == BIAS_ROW else N), (bias_zs, 1))
+        acc = acc + (bz.view(1, zlo_n, -1, 1) if bias_mode == BIAS_ROW else bz.view(1, zlo_n, 1, -1))
+    elif bias is not None and bias_mode == BIAS_ROW:
         acc = acc + bias.to(cdt).view(1, 1, -1, 1)[:, :, :M]
     elif bias is not None and bias_mode == BIAS_COL:
         acc = acc + bias.to(cdt).view(1, 1, 1, -1)[..., :N]
@@ -170,7 +173,7 @@ def gemm(M: int, N: int, K: int, A: Operand, B: Operand, D: Output, *, zlo_n: in
          bias: Optional[torch.Tensor] = None, bias_mode: int = BIAS_NONE, act: int = ACT_NONE,
          resid: Optional[torch.Tensor] = None, resid_offset: int = 0, preact: Optional[torch.Tensor] = None,
          preact_offset: int = 0, accumulate: bool = False, splits: int = 1, tri: Optional[Tri] = None, bn: int = 0,
-         segments=None, sync=None, dests=None, act_param: float = 0.0) -> None:
+         segments=None, sync=None, dests=None, act_param: float = 0.0, bias_zs: int = 0) -> None:
     """Run the batched GEMM described above, writing into `D.tensor` in place.
 
     `segments` (list of `Segment`) spreads the k axis of B over several devices: `K` is then the padded k extent
@@ -182,7 +185,7 @@ def gemm(M: int, N: int, K: int, A: Operand, B: Operand, D: Output, *, zlo_n: in
         bias_mode = BIAS_NONE
     if not A.tensor.is_cuda:
         _emulate(M, N, K, A, B, D, zlo_n, zhi_n, alpha, bias, bias_mode, act, resid, resid_offset, preact, preact_offset,
-                 accumulate, tri, segments, act_param)
+                 accumulate, tri, segments, act_param, bias_zs)
         return
     ext = _ext.require()
     ip = [M, N, K, zlo_n, zhi_n, splits, bn,
@@ -190,7 +193,7 @@ def gemm(M: int, N: int, K: int, A: Operand, B: Operand, D: Output, *, zlo_n: in
           A.offset, int(A.mn_major), A.ld, A.zs_lo, A.zs_hi,
           B.offset, int(B.mn_major), B.ld, B.zs_lo, B.zs_hi,
           D.offset, int(accumulate), D.d_zlo, D.d_zhi, D.rdiv, D.rs_hi, D.rs_lo, D.ndiv, D.ns_hi,
-          bias_mode, act, resid_offset, preact_offset, _f32_bits(act_param), 0]
+          bias_mode, act, resid_offset, preact_offset, _f32_bits(act_param), int(bias_zs)]
     if segments or sync or dests:
         seg = []
         if segments and len(segments) > 1:

@@ -78,6 +78,38 @@ class _MLP2Last(torch.autograd.Function):
         return dx, dw1, db1, dw2, db2
 
 
+class _LinearLast(torch.autograd.Function):
+    """y = x W^T + b on the last dimension: one GEMM forward, data- and weight-gradient GEMMs backward."""
+
+    @staticmethod
+    def forward(ctx, x, w, b):
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1])
+        wq = _wq(w)
+        y, _ = _lin_fwd(x2, wq, b.detach().float().contiguous() if b is not None else None, ACT_NONE, False)
+        ctx.save_for_backward(x2, wq)
+        ctx.has_bias, ctx.shp = b is not None, shp
+        return y.reshape(*shp[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, wq = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
+        dx = _lin_dgrad(dy2, wq).reshape(ctx.shp) if ctx.needs_input_grad[0] else None
+        dw = _lin_wgrad(dy2, x2) if ctx.needs_input_grad[1] else None
+        db = dy2.float().sum(0) if ctx.has_bias else None
+        return dx, dw, db
+
+
+def linear_lastdim(x, w, b=None):
+    """`torch.nn.functional.linear` for bf16 CUDA tokens whose feature counts are multiples of 8; anything else falls
+    back to the torch op."""
+    if fast_path_ok(x) and w.shape[0] % 8 == 0:
+        _ext.require()
+        return _LinearLast.apply(x, w, b)
+    return torch.nn.functional.linear(x, w.to(x.dtype), None if b is None else b.to(x.dtype))
+
+
 def mlp2_lastdim(x, w1, b1, w2, b2):
     _ext.require()
     return _MLP2Last.apply(x, w1, b1, w2, b2)

@@ -48,6 +48,9 @@ class GradReducer:
         # join; `timeline_report()` returns when each bucket became ready, how long its reduction took and how long the
         # compute stream waited at the end of backward
         self.diag_timeline = os.environ.get("MAKANI_B200_DP_DIAG", "") == "timeline"
+        # MAKANI_B200_DP_DIAG=noar: everything as in a real run (symmetric buffer, buckets, side stream) except that the
+        # all-reduce kernels are not launched
+        self.diag_noar = os.environ.get("MAKANI_B200_DP_DIAG", "") == "noar"
         self._timeline = []
         self._t_zero = None
         self._t_join = None
@@ -133,7 +136,8 @@ class GradReducer:
         ev.record(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(self._side):
             self._side.wait_event(ev)
-            self.sym.all_reduce_(end - start, torch.float32, scale=1.0 / self.data_size, byte_offset=start * 4)
+            if not self.diag_noar:
+                self.sym.all_reduce_(end - start, torch.float32, scale=1.0 / self.data_size, byte_offset=start * 4)
             if timeline:
                 done = torch.cuda.Event(enable_timing=True)
                 done.record(self._side)

@@ -268,64 +268,47 @@ class DistributedAttention(nn.Module):
         return self.proj_drop(self.proj(y))
 
 
-def compl_mul_add_fwd(a, b, c):
-    return torch.einsum("bkixys,kiot->stbkoxy", a, b)
-
-
 class DistributedAFNO2Dv2(nn.Module):
-    """Block-diagonal complex two-layer MLP in Fourier space with the blocks sharded over the `matmul` group."""
+    """AFNO spectral filter (NCHW) with its channel blocks sharded over the `matmul` group: every rank runs the GEMM-chain
+    filter of `ops/afno.py` on its own blocks; the input is scattered / the output gathered along the channels unless
+    the caller already works on channel shards.  Interface and sharding tags of makani/mpu/layers.py:532-645
+    (`w1 [nb_local, bs, bs*f, 2]`, `b1`, `w2`, `b2` complex pairs; shared over `spatial`, sharded over `matmul`)."""
 
     def __init__(self, hidden_size, num_blocks=8, sparsity_threshold=0.01, hard_thresholding_fraction=1,
                  hidden_size_factor=1, input_is_matmul_parallel=False, output_is_matmul_parallel=False, use_complex_kernels=False):
         super().__init__()
-        assert hidden_size % num_blocks == 0
         msize = comm.get_size("matmul")
-        assert num_blocks % msize == 0
-        self.fft_handle = torch.fft.rfft2
-        self.ifft_handle = torch.fft.irfft2
+        if hidden_size % num_blocks or num_blocks % msize:
+            raise ValueError(f"hidden_size {hidden_size} / num_blocks {num_blocks} / matmul group {msize} do not divide")
         self.hidden_size, self.num_blocks = hidden_size, num_blocks
-        self.sparsity_threshold = sparsity_threshold
         self.num_blocks_local = num_blocks // msize
         self.block_size = hidden_size // num_blocks
+        self.sparsity_threshold = float(sparsity_threshold)
         self.hard_thresholding_fraction = hard_thresholding_fraction
         self.hidden_size_factor = hidden_size_factor
-        self.scale = 0.02
         self.input_parallel, self.output_parallel = input_is_matmul_parallel, output_is_matmul_parallel
         self.chan_shapes = compute_split_shapes(hidden_size, msize)
-        bs, f, nb = self.block_size, hidden_size_factor, self.num_blocks_local
-        self.w1 = nn.Parameter(self.scale * torch.randn(nb, bs, bs * f, 2))
-        self.b1 = nn.Parameter(self.scale * torch.randn(nb, bs * f, 1, 1, 2))
-        self.w2 = nn.Parameter(self.scale * torch.randn(nb, bs * f, bs, 2))
-        self.b2 = nn.Parameter(self.scale * torch.randn(nb, bs, 1, 1, 2))
+        bs, hid, nb, std = self.block_size, self.block_size * hidden_size_factor, self.num_blocks_local, 0.02
+        self.w1 = nn.Parameter(std * torch.randn(nb, bs, hid, 2))
+        self.b1 = nn.Parameter(std * torch.randn(nb, hid, 1, 1, 2))
+        self.w2 = nn.Parameter(std * torch.randn(nb, hid, bs, 2))
+        self.b2 = nn.Parameter(std * torch.randn(nb, bs, 1, 1, 2))
         for p in (self.w1, self.b1, self.w2, self.b2):
             p.is_shared_mp = ["spatial"]
-        self.w1.sharded_dims_mp = ["matmul", None, None, None]
-        self.b1.sharded_dims_mp = ["matmul", None, None, None, None]
-        self.w2.sharded_dims_mp = ["matmul", None, None, None]
-        self.b2.sharded_dims_mp = ["matmul", None, None, None, None]
+            p.sharded_dims_mp = ["matmul"] + [None] * (p.dim() - 1)
 
     def forward(self, x):
+        from ..ops import afno as afno_ops
         if not self.input_parallel:
             x = scatter_to_parallel_region(x, 1, "matmul")
-        bias = x
-        dtype = x.dtype
-        x = x.float()
         B, C, H, W = x.shape
-        total_modes = H // 2 + 1
-        kept = int(total_modes * self.hard_thresholding_fraction)
-        xf = self.fft_handle(x, dim=(-2, -1), norm="ortho")
-        xf = xf.view(B, self.num_blocks_local, self.block_size, H, W // 2 + 1)
-        w1, w2 = torch.view_as_complex(self.w1), torch.view_as_complex(self.w2)
-        b1, b2 = torch.view_as_complex(self.b1), torch.view_as_complex(self.b2)
-        sl = (slice(None), slice(None), slice(None), slice(total_modes - kept, total_modes + kept), slice(0, kept))
-        o1 = torch.einsum("bkixy,kio->bkoxy", xf[sl], w1) + b1
-        o1 = torch.view_as_complex(F.relu(torch.view_as_real(o1)))
-        o2 = torch.einsum("bkixy,kio->bkoxy", o1, w2) + b2
-        o2 = torch.view_as_complex(F.softshrink(torch.view_as_real(o2), lambd=self.sparsity_threshold))
-        out = torch.zeros_like(xf)
-        out[sl] = o2
-        out = out.reshape(B, C, H, W // 2 + 1)
-        x = self.ifft_handle(out, s=(H, W), dim=(-2, -1), norm="ortho").to(dtype) + bias
+        kx, ncols = afno_ops.mode_window_v2(H, W, self.hard_thresholding_fraction)
+        tok = x.contiguous(memory_format=torch.channels_last).permute(0, 2, 3, 1)
+        hid = self.block_size * self.hidden_size_factor
+        fn = afno_ops.afno_filter if afno_ops.fast_path_ok(tok, self.num_blocks_local, hid) else afno_ops.afno_filter_reference
+        b1, b2 = self.b1[:, :, 0, 0], self.b2[:, :, 0, 0]
+        y = fn(tok, self.w1[..., 0], self.w1[..., 1], b1[..., 0], b1[..., 1], self.w2[..., 0], self.w2[..., 1], b2[..., 0], b2[..., 1],
+               kx, ncols, self.sparsity_threshold, skip=tok).permute(0, 3, 1, 2)
         if not self.output_parallel:
-            x = gather_from_parallel_region(x, 1, self.chan_shapes, "matmul")
-        return x
+            y = gather_from_parallel_region(y, 1, self.chan_shapes, "matmul")
+        return y
