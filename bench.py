@@ -56,6 +56,10 @@ def parse():
     ap.add_argument("--multistep", type=int, default=1, help="multistep_count: autoregressive steps per training sample (loss over all of them)")
     ap.add_argument("--ref-graph", default="fwdbwd", choices=["none", "fwdbwd"], help="reference arm: its --cuda_graph_mode")
     ap.add_argument("--tiny", action="store_true", help="32x64 plumbing configuration (CPU friendly; not a bench value)")
+    ap.add_argument("--via", default="harness", choices=["harness", "trainer"],
+                    help="harness: network + loss + optimiser assembled by utils/bench_harness.py; trainer: the step of the "
+                         "product's entry point (cli_common.bootstrap -> Trainer with the recipe of config/sfnonet.yaml, synthetic "
+                         "data, --amp_mode bf16 --cuda_graph_mode step), i.e. what `python -m makani_b200.train` runs")
     return ap.parse_args()
 
 
@@ -189,10 +193,108 @@ def _gpu_uuid(torch, index):
         return None
 
 
+def via_trainer(args):
+    """The headline step through the training entry point: the same flags a user passes to `python -m makani_b200.train`
+    go through `cli_common.bootstrap`, the `Trainer` builds model (registry + stepper + preprocessor), loss, reducer and
+    optimiser from the recipe, and its own `_prepare_batch` / `_train_step` are timed on synthetic batches."""
+    import tempfile
+
+    import torch
+    import torch.distributed as dist
+
+    from makani_b200 import cli_common
+    from makani_b200.ops import _ext
+    from makani_b200.utils import comm
+    from makani_b200.utils.trainer import Trainer
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    mp = args.h * args.w * args.fin * args.fout
+    dp = max(1, world // mp)
+    recipe = "sfno_tiny" if args.tiny else "sfno_linear_73chq_sc3_layers8_edim384_bench"
+    argv = ["--yaml_config", os.path.join(ROOT, "config", "sfnonet.yaml"), "--config", recipe, "--enable_synthetic_data",
+            "--amp_mode", "bf16", "--cuda_graph_mode", "none" if args.no_graph else "step", "--batch_size", str(dp),
+            "--skip_validation", "--save_checkpoint", "none", "--multistep_count", str(args.multistep),
+            "--h_parallel_size", str(args.h), "--w_parallel_size", str(args.w), "--fin_parallel_size", str(args.fin),
+            "--fout_parallel_size", str(args.fout), "--exp_dir", tempfile.mkdtemp(prefix="makani_b200_bench_")]
+    cargs = cli_common.base_parser("bench").parse_args(argv)
+    params, world_rank = cli_common.bootstrap(cargs)
+    params["log_to_screen"] = False
+    if not args.tiny:
+        params["in_channels"] = list(range(len(params["channel_names"]) + 1))   # + the static cos(latitude) channel, delivered with the data
+    params["n_train_samples_per_epoch"] = params["batch_size"] * dp * 2
+    _ext.require()
+    trainer = Trainer(params, world_rank)
+    trainer._set_train()
+    data = next(iter(trainer.train_dataloader))
+    inp, tar = trainer._prepare_batch(data)
+
+    def barrier():
+        if world > 1:
+            dist.barrier(device_ids=[local_rank])
+        torch.cuda.synchronize()
+
+    for _ in range(5 + args.warmup):
+        loss = trainer._train_step(inp, tar)
+    barrier()
+    sampler = ClockSampler(local_rank, _gpu_uuid(torch, local_rank))
+    sampler.start()
+    l0 = _ext.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        loss = trainer._train_step(inp, tar)
+    ev1.record()
+    barrier()
+    launches = _ext.launch_count() - l0
+    clocks = sampler.stop()
+    t = torch.tensor([ev0.elapsed_time(ev1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = t.item() / args.steps
+    _ext.check_device_errors(dev)
+    if world_rank == 0:
+        print(json.dumps({
+            "metric": "SFNO-73ch 721x1440 bf16 train samples/s", "value": params["batch_size"] * dp / (ms / 1e3), "unit": "samples/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic N(0,1), random-init weights", "impl": "native",
+            "config": {"model": recipe.replace("_bench", ""), "global_batch": params["batch_size"] * dp,
+                       "seq_len": f"{params.img_shape_x}x{params.img_shape_y}",
+                       "parallelism": f"dp{dp}" + (f"xh{args.h}w{args.w}" if args.h * args.w > 1 else ""),
+                       "l2_policy": "inputs+activations per step (>2 GB) exceed the 126 MB L2", "loss": params.loss,
+                       "optimizer": type(trainer.optimizer).__name__, "cuda_graph": trainer.graph_mode,
+                       "multistep_count": args.multistep, "final_loss": float(loss),
+                       "entry": "cli_common.bootstrap -> Trainer._prepare_batch / _train_step (python -m makani_b200.train)"},
+            "clocks": clocks, "gpu_launches": launches}))
+    sys.stdout.flush()
+    if world > 1:
+        import threading
+
+        def _bail():
+            time.sleep(30.0)
+            os._exit(0)
+
+        threading.Thread(target=_bail, daemon=True).start()
+        trainer.graph = None
+        import gc
+        gc.collect()
+        torch.cuda.synchronize()
+        from makani_b200.parallel import peer
+        peer.release_slots()
+        dist.barrier(device_ids=[local_rank])
+        dist.destroy_process_group()
+    return 0
+
+
 def main():
     args = parse()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.via == "trainer":
+        return via_trainer(args)
 
     import torch
     import torch.distributed as dist
@@ -292,7 +394,7 @@ def main():
     if native:
         _ext.check_device_errors(dev)
     final_loss = float(loss)
-    if os.environ.get("MAKANI_B200_DP_DIAG") == "timeline" and getattr(runner, "reducer", None) is not None:
+    if "timeline" in os.environ.get("MAKANI_B200_DP_DIAG", "") and getattr(runner, "reducer", None) is not None:
         rep = runner.reducer.timeline_report()
         if rep is not None and rank == 0:
             print("timeline " + json.dumps(rep), file=sys.stderr)

@@ -26,6 +26,7 @@ def base_parser(description: str) -> argparse.ArgumentParser:
     p.add_argument("--parameters_reduction_buffer_count", default=1, type=int,
                    help="Number of buckets the gradient reduction is split into")
     p.add_argument("--run_num", default="00", type=str)
+    p.add_argument("--exp_dir", default=None, type=str, help="Override of the recipe's experiment root directory")
     p.add_argument("--yaml_config", default="./config/sfnonet.yaml", type=str)
     p.add_argument("--config", default="base_73chq", type=str)
     p.add_argument("--batch_size", default=-1, type=int, help="Override of the global batch size of the recipe")
@@ -53,6 +54,8 @@ def bootstrap(args, inference: bool = False):
     """Load the recipe, initialise the process topology and fill in every CLI-derived parameter."""
     params = YParams(os.path.abspath(args.yaml_config), args.config)
     params["epsilon_factor"] = args.epsilon_factor
+    if getattr(args, "exp_dir", None):
+        params["exp_dir"] = args.exp_dir
     for n in ("fin", "fout", "h", "w"):
         params[f"{n}_parallel_size"] = getattr(args, f"{n}_parallel_size")
     params["model_parallel_sizes"] = [args.h_parallel_size, args.w_parallel_size, args.fin_parallel_size, args.fout_parallel_size]

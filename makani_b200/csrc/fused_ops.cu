@@ -305,7 +305,7 @@ __global__ void __launch_bounds__(CL_THREADS) inorm_cl_sums_kernel(const __nv_bf
                                                                    const float* __restrict__ w, const float* __restrict__ b,
                                                                    const float* __restrict__ stats, float* __restrict__ sums,
                                                                    float* __restrict__ dw, float* __restrict__ db, int C, long long T,
-                                                                   int act, int slab, const StatExchange xc) {
+                                                                   int act, int slab, int shifted, const StatExchange xc) {
   extern __shared__ float sh_acc[];   // [C][2]
   const int V = C >> 3;
   const int R = CL_THREADS / V;
@@ -332,6 +332,13 @@ __global__ void __launch_bounds__(CL_THREADS) inorm_cl_sums_kernel(const __nv_bf
     if (t1 > T) t1 = T;
     const uint4* xv = reinterpret_cast<const uint4*>(x + static_cast<long long>(bidx) * T * C) + v;
     const uint4* gv = MODE == 1 ? reinterpret_cast<const uint4*>(dy + static_cast<long long>(bidx) * T * C) + v : nullptr;
+    // Shifted sums: sum (x - s) and sum (x - s)^2 with s = the sample's first token, so that the one-pass variance
+    // E[(x-s)^2] - E[x-s]^2 does not cancel when |mean| >> std.  (Only when the statistics are local to this device:
+    // sums that are merged across ranks need one common shift and stay unshifted.)
+    float sft[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sft[j] = 0.f;
+    if (MODE == 0 && shifted) unpack8(xv[0], sft);
     // four rows in flight per thread: independent 16-byte loads cover the HBM latency
     auto accum = [&](const uint4& xr, const uint4& gr) {
       float f[8];
@@ -339,8 +346,9 @@ __global__ void __launch_bounds__(CL_THREADS) inorm_cl_sums_kernel(const __nv_bf
       if (MODE == 0) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          a0[j] += f[j];
-          a1[j] += f[j] * f[j];
+          const float d = f[j] - sft[j];
+          a0[j] += d;
+          a1[j] += d * d;
         }
       } else {
         float g[8];
@@ -430,7 +438,7 @@ __global__ void __launch_bounds__(CL_THREADS) inorm_cl_apply_kernel(const __nv_b
                                                                     __nv_bfloat16* __restrict__ out, const float* __restrict__ w,
                                                                     const float* __restrict__ b, const float* __restrict__ sums,
                                                                     float* __restrict__ stats, int C, long long T, float inv_count,
-                                                                    float eps, int act, int slab, const StatExchange xc) {
+                                                                    float eps, int act, int slab, int shifted, const StatExchange xc) {
   const int V = C >> 3;
   const int R = CL_THREADS / V;
   const int v = threadIdx.x % V, r = threadIdx.x / V;
@@ -456,6 +464,10 @@ __global__ void __launch_bounds__(CL_THREADS) inorm_cl_apply_kernel(const __nv_b
     return;
   }
   float k0[8], k1[8], k2[8], k3[8], kw[8], kb[8];   // per-channel constants
+  float sft[8];                                      // shift of the statistics pass (the sample's first token) or 0
+#pragma unroll
+  for (int j = 0; j < 8; ++j) sft[j] = 0.f;
+  if (MODE == 0 && shifted) unpack8((reinterpret_cast<const uint4*>(x + static_cast<long long>(bidx) * T * C) + v)[0], sft);
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const int c = v * 8 + j;
@@ -472,8 +484,9 @@ __global__ void __launch_bounds__(CL_THREADS) inorm_cl_apply_kernel(const __nv_b
       s1 = sums[sc + 1];
     }
     if (MODE == 0) {
-      const float mean = s0 * inv_count;
-      const float var = fmaxf(s1 * inv_count - mean * mean, 0.f);
+      const float dm = s0 * inv_count;                 // mean of (x - shift)
+      const float mean = sft[j] + dm;
+      const float var = fmaxf(s1 * inv_count - dm * dm, 0.f);
       const float rstd = rsqrtf(var + eps);
       k0[j] = wc * rstd;
       k1[j] = bc - mean * k0[j];
@@ -886,6 +899,9 @@ cudaError_t inorm_cl_sums(const __nv_bfloat16* x, const __nv_bfloat16* dy, const
                           float* sums, float* dw, float* db, int B, int C, long long T, int act, int mode, cudaStream_t s,
                           const StatExchange* xch) {
   if (act) act = gelu_tanh() ? 2 : 1;
+  // mode: bit 0 = backward pass, bit 1 = forward statistics shifted by the first token (local statistics only)
+  const int shifted = ((mode >> 1) & 1) && (!xch || xch->npeers == 0);
+  mode &= 1;
   if (!cl_ok(C)) return cudaErrorInvalidValue;
   StatExchange xc;
   memset(&xc, 0, sizeof(xc));
@@ -894,8 +910,8 @@ cudaError_t inorm_cl_sums(const __nv_bfloat16* x, const __nv_bfloat16* dy, const
   const int slab = cl_slab(C, T, B, 2);
   dim3 grid(static_cast<unsigned>((T + slab - 1) / slab), B);
   const size_t sh = 2 * C * sizeof(float);
-  if (mode == 0) inorm_cl_sums_kernel<0><<<grid, CL_THREADS, sh, s>>>(x, dy, w, b, stats, sums, dw, db, C, T, act, slab, xc);
-  else inorm_cl_sums_kernel<1><<<grid, CL_THREADS, sh, s>>>(x, dy, w, b, stats, sums, dw, db, C, T, act, slab, xc);
+  if (mode == 0) inorm_cl_sums_kernel<0><<<grid, CL_THREADS, sh, s>>>(x, dy, w, b, stats, sums, dw, db, C, T, act, slab, shifted, xc);
+  else inorm_cl_sums_kernel<1><<<grid, CL_THREADS, sh, s>>>(x, dy, w, b, stats, sums, dw, db, C, T, act, slab, 0, xc);
   return cudaGetLastError();
 }
 
@@ -903,6 +919,9 @@ cudaError_t inorm_cl_apply(const __nv_bfloat16* x, const __nv_bfloat16* dy, __nv
                            const float* sums, float* stats, int B, int C, long long T, double count, float eps, int act, int mode,
                            cudaStream_t s, const StatExchange* xch) {
   if (act) act = gelu_tanh() ? 2 : 1;
+  // mode: bit 0 = backward pass, bit 1 = forward statistics shifted by the first token (local statistics only)
+  const int shifted = ((mode >> 1) & 1) && (!xch || xch->npeers == 0);
+  mode &= 1;
   if (!cl_ok(C)) return cudaErrorInvalidValue;
   StatExchange xc;
   memset(&xc, 0, sizeof(xc));
@@ -911,8 +930,8 @@ cudaError_t inorm_cl_apply(const __nv_bfloat16* x, const __nv_bfloat16* dy, __nv
   dim3 grid(static_cast<unsigned>((T + slab - 1) / slab), B);
   const float inv = static_cast<float>(1.0 / count);
   const size_t shx = xc.npeers > 0 ? 2 * C * sizeof(float) : 0;
-  if (mode == 0) inorm_cl_apply_kernel<0><<<grid, CL_THREADS, shx, s>>>(x, dy, out, w, b, sums, stats, C, T, inv, eps, act, slab, xc);
-  else inorm_cl_apply_kernel<1><<<grid, CL_THREADS, shx, s>>>(x, dy, out, w, b, sums, stats, C, T, inv, eps, act, slab, xc);
+  if (mode == 0) inorm_cl_apply_kernel<0><<<grid, CL_THREADS, shx, s>>>(x, dy, out, w, b, sums, stats, C, T, inv, eps, act, slab, shifted, xc);
+  else inorm_cl_apply_kernel<1><<<grid, CL_THREADS, shx, s>>>(x, dy, out, w, b, sums, stats, C, T, inv, eps, act, slab, 0, xc);
   return cudaGetLastError();
 }
 

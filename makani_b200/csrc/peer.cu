@@ -110,9 +110,13 @@ struct Vec16<__nv_bfloat16> {
   }
 };
 
-// 256 threads x at most 64 registers: a CTA of this kernel fits on an SM beside a persistent GEMM CTA (320 threads x up
-// to 144 registers), so that the reduction of a bucket really runs while backward continues.
-constexpr int AR_THREADS = 256;
+// 128 threads (one warp per SM sub-partition) x at most 64 registers: the register file is four banks of 16384
+// registers, one per sub-partition, and a persistent GEMM CTA (10 warps x up to 144 registers) leaves only 2560 of them
+// in the two sub-partitions that hold three of its warps.  A CTA of this kernel must fit into that remainder, or it
+// cannot share an SM with a GEMM CTA: it then takes the SM from the next GEMM launch, whose displaced CTA runs as a
+// straggler, and the reduction serialises with backward instead of overlapping it (measured: step time = compute +
+// reduction time for every grid size, with 256- and 512-thread versions of this kernel).
+constexpr int AR_THREADS = 128;
 
 // WORLD is a template parameter so that the loops over the peers unroll completely: all WORLD loads of a vector (and U
 // vectors per thread) are in flight together, which is what it takes to fill an NVLink round trip (about 2 us) with
@@ -237,9 +241,9 @@ cudaError_t peer_allreduce(const PeerPtrs& p, int world, int rank, long long n, 
   const uint64_t wait_ns = static_cast<uint64_t>(wait_seconds * 1e9);
   const int V = is_bf16 ? 8 : 4;
   long long per = (n / V + world - 1) / world;
-  long long blocks = (per + 255) / 256;
+  long long blocks = (per + AR_THREADS - 1) / AR_THREADS;
   if (blocks < 1) blocks = 1;
-  // 128 CTAs x 256 threads x 16 vectors of 16 B in flight saturate NVLink without starving compute (MAKANI_B200_AR_BLOCKS overrides,
+  // 128 CTAs x 128 threads x 8 vectors of 16 B in flight keep NVLink busy without starving compute (MAKANI_B200_AR_BLOCKS overrides,
   // read once; every rank of a group must use the same value because CTA i pairs with CTA i of its peers)
   static const int max_blocks = [] {
     const char* e = getenv("MAKANI_B200_AR_BLOCKS");

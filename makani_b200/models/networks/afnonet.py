@@ -79,6 +79,8 @@ class AFNO2D(nn.Module):
         kx, ncols = afno_ops.mode_window_v1(H, W, self.hard_thresholding_fraction)
         hid = self.block_size * self.hidden_size_factor
         xc = x.contiguous()
+        if xc.is_cuda and xc.dtype == torch.float32 and torch.is_autocast_enabled():
+            xc = xc.to(torch.get_autocast_gpu_dtype())     # layer norm hands fp32 on under autocast; the GEMM chain runs in bf16
         fn = afno_ops.afno_filter if afno_ops.fast_path_ok(xc, self.num_blocks_local, hid) else afno_ops.afno_filter_reference
         y = fn(xc, self.w1[0], self.w1[1], self.b1[0], self.b1[1], self.w2[0], self.w2[1], self.b2[0], self.b2[1],
                kx, ncols, self.sparsity_threshold, skip=xc)

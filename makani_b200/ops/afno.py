@@ -257,6 +257,18 @@ def afno_filter(x, w1r, w1i, b1r, b1i, w2r, w2i, b2r, b2i, kx: Sequence[int], nc
     return _AFNOFilter.apply(x, w1x, b1x, w2x, b2x, skip, plan, float(lam))
 
 
+_ROW_INDEX = {}
+
+
+def _row_index(kx, device):
+    """Kept-row indices as a device tensor, created once per (rows, device) so that no host-to-device copy happens inside
+    a CUDA-graph capture."""
+    key = (kx, str(device))
+    if key not in _ROW_INDEX:
+        _ROW_INDEX[key] = torch.as_tensor(list(kx), device=device)
+    return _ROW_INDEX[key]
+
+
 def afno_filter_reference(x, w1r, w1i, b1r, b1i, w2r, w2i, b2r, b2i, kx, ncols, lam, skip=None):
     """The same operator with torch.fft and einsum in fp32 (fallback for layouts the GEMM chain does not take, and the
     oracle of the tests)."""
@@ -264,7 +276,7 @@ def afno_filter_reference(x, w1r, w1i, b1r, b1i, w2r, w2i, b2r, b2i, kx, ncols, 
     nb = w1r.shape[0]
     bs = C // nb
     xf = torch.fft.rfft2(x.float(), dim=(1, 2), norm="ortho").reshape(B, H, W // 2 + 1, nb, bs)
-    idx = torch.as_tensor(list(kx), device=x.device)
+    idx = _row_index(tuple(kx), x.device)
     xs = xf[:, idx][:, :, :ncols]
     mul = lambda a, w: torch.einsum("...bi,bio->...bo", a, w.float())
     zero = 0.0

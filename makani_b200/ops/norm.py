@@ -76,10 +76,13 @@ class _InstanceNormCL(torch.autograd.Function):
             ext.inorm_cl_apply(x, None, y, wf, bf, sums, stats, B, C, cnt, float(eps), int(act), 0,
                                sync_descriptor(consume=slot), slot.sources())
         else:
-            ext.inorm_cl_sums(x, None, None, None, None, sums, None, None, B, C, 0, 0)
+            # statistics local to this device are accumulated around the first token (mode bit 1): no cancellation in
+            # E[x^2] - E[x]^2 for fields with |mean| >> std; sums merged across ranks stay unshifted
+            m0 = 2 if reduce_fn is None else 0
+            ext.inorm_cl_sums(x, None, None, None, None, sums, None, None, B, C, 0, m0)
             if reduce_fn is not None:
                 sums = reduce_fn(sums)
-            ext.inorm_cl_apply(x, None, y, wf, bf, sums, stats, B, C, cnt, float(eps), int(act), 0)
+            ext.inorm_cl_apply(x, None, y, wf, bf, sums, stats, B, C, cnt, float(eps), int(act), m0)
         ctx.save_for_backward(x, wf, bf, stats)
         ctx.act, ctx.cnt, ctx.reduce_fn, ctx.affine, ctx.slot = int(act), cnt, reduce_fn, weight is not None, slot
         return y

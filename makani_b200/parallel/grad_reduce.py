@@ -38,19 +38,26 @@ class GradReducer:
             total += (n + align - 1) // align * align
         self.total = total
         self.data_size = comm.get_size("data")
+        # groups (other than `data`) over which some parameter's gradient has to be summed
+        shared_names: List[str] = []
+        for p in self.params:
+            for g in getattr(p, "is_shared_mp", ["model"]):
+                if comm.get_size(g) > 1 and g not in shared_names:
+                    shared_names.append(g)
+        self._shared_names = shared_names
         if use_peer is None:
-            use_peer = (dev.type == "cuda" and dist.is_initialized() and self.data_size > 1 and self.data_size <= 8
-                        and dist.get_backend() == "nccl")
+            use_peer = (dev.type == "cuda" and dist.is_initialized() and dist.get_world_size() <= 8
+                        and (self.data_size > 1 or len(shared_names) > 0) and dist.get_backend() == "nccl")
         # diagnosis only: MAKANI_B200_DP_DIAG=noreduce leaves the data-parallel average out (replicas diverge), to tell
         # the cost of the reduction apart from what running N ranks side by side costs by itself
-        self.diag_noreduce = os.environ.get("MAKANI_B200_DP_DIAG", "") == "noreduce"
+        self.diag_noreduce = "noreduce" in os.environ.get("MAKANI_B200_DP_DIAG", "").split(",")
         # MAKANI_B200_DP_DIAG=timeline (eager steps only): CUDA events around every bucket's reduction and around the final
         # join; `timeline_report()` returns when each bucket became ready, how long its reduction took and how long the
         # compute stream waited at the end of backward
-        self.diag_timeline = os.environ.get("MAKANI_B200_DP_DIAG", "") == "timeline"
+        self.diag_timeline = "timeline" in os.environ.get("MAKANI_B200_DP_DIAG", "").split(",")
         # MAKANI_B200_DP_DIAG=noar: everything as in a real run (symmetric buffer, buckets, side stream) except that the
         # all-reduce kernels are not launched
-        self.diag_noar = os.environ.get("MAKANI_B200_DP_DIAG", "") == "noar"
+        self.diag_noar = "noar" in os.environ.get("MAKANI_B200_DP_DIAG", "").split(",")
         self._timeline = []
         self._t_zero = None
         self._t_join = None
@@ -59,7 +66,11 @@ class GradReducer:
         self.sym = None
         if use_peer:
             from .peer import SymmetricBuffer
-            self.sym = SymmetricBuffer(total * 4, group=comm.get_group("data"), device=dev)
+            # one buffer mapped by every rank of the node; the data-parallel average and each model-parallel sum run over
+            # their own sub-group of it with their own set of barrier flags
+            self.sym = SymmetricBuffer(total * 4, group=None, device=dev, flag_sets=1 + len(shared_names))
+            self._data_members = comm.get_group_ranks("data")
+            self._shared_members = {g: comm.get_group_ranks(g) for g in shared_names}
             self.flat = self.sym.view(torch.float32, total)
             self.flat.zero_()
         else:
@@ -137,7 +148,8 @@ class GradReducer:
         with torch.cuda.stream(self._side):
             self._side.wait_event(ev)
             if not self.diag_noar:
-                self.sym.all_reduce_(end - start, torch.float32, scale=1.0 / self.data_size, byte_offset=start * 4)
+                self.sym.all_reduce_(end - start, torch.float32, scale=1.0 / self.data_size, byte_offset=start * 4,
+                                     members=self._data_members, flag_set=0)
             if timeline:
                 done = torch.cuda.Event(enable_timing=True)
                 done.record(self._side)
@@ -173,14 +185,21 @@ class GradReducer:
                     e1.record(torch.cuda.current_stream(self.device))
                     self._t_join = (e0, e1)
             elif self.sym is not None:
-                self.sym.all_reduce_(self.total, torch.float32, scale=1.0 / self.data_size)
+                self.sym.all_reduce_(self.total, torch.float32, scale=1.0 / self.data_size, members=self._data_members, flag_set=0)
             else:
                 dist.all_reduce(self.flat, group=comm.get_group("data"))
                 self.flat.mul_(1.0 / self.data_size)
         for gname, ranges in self.shared.items():
-            grp = comm.get_group(gname)
-            for start, end in ranges:
-                dist.all_reduce(self.flat[start:end], group=grp)
+            if self.sym is not None:
+                # in-kernel peer sum over the ranks that share these parameters (no NCCL call on the step)
+                fs = 1 + self._shared_names.index(gname)
+                for start, end in ranges:
+                    self.sym.all_reduce_(end - start, torch.float32, scale=1.0, byte_offset=start * 4,
+                                         members=self._shared_members[gname], flag_set=fs)
+            else:
+                grp = comm.get_group(gname)
+                for start, end in ranges:
+                    dist.all_reduce(self.flat[start:end], group=grp)
 
     def timeline_report(self):
         """Of the last eager step (MAKANI_B200_DP_DIAG=timeline): per bucket (index, MB, ms after the start of the step at

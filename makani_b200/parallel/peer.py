@@ -27,7 +27,9 @@ PEER_SKEW_SECONDS = float(os.environ.get("MAKANI_B200_PEER_SKEW_SECONDS", "120")
 class SymmetricBuffer:
     """`nbytes` of device memory on every rank of `group`, mapped into every other rank."""
 
-    def __init__(self, nbytes: int, group=None, device: Optional[torch.device] = None):
+    def __init__(self, nbytes: int, group=None, device: Optional[torch.device] = None, flag_sets: int = 1):
+        """`flag_sets` > 1 reserves that many independent barrier-flag areas, so that collectives over different
+        sub-groups of `group` (see `all_reduce_`'s `members`) never share epoch counters."""
         assert dist.is_initialized(), "SymmetricBuffer needs an initialised process group"
         self.ext = _ext.require()
         self.group = group
@@ -36,9 +38,10 @@ class SymmetricBuffer:
         assert self.world <= 8, "peer collectives support up to 8 ranks (one NVSwitch node)"
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.nbytes = (int(nbytes) + 255) // 256 * 256
+        self.flag_sets = max(1, int(flag_sets))
         with torch.cuda.device(self.device):
             out: list = []
-            handle = self.ext.peer_alloc(self.nbytes + FLAG_BYTES, out)
+            handle = self.ext.peer_alloc(self.nbytes + self.flag_sets * FLAG_BYTES, out)
             self.local_ptr = out[0]
             handles: List[Optional[bytes]] = [None] * self.world
             dist.all_gather_object(handles, handle, group=group)
@@ -55,15 +58,30 @@ class SymmetricBuffer:
         return self.local[byte_offset: byte_offset + numel * esz].view(dtype)
 
     def all_reduce_(self, numel: int, dtype=torch.float32, scale: float = 1.0, byte_offset: int = 0,
-                    wait_seconds: Optional[float] = None) -> None:
+                    wait_seconds: Optional[float] = None, members: Optional[List[int]] = None, flag_set: int = 0) -> None:
         """In-place sum (times `scale`) over the group of `numel` elements starting at `byte_offset`.
+
+        `members` (ranks of this buffer's group, in the order of the sub-group, this rank among them) restricts the
+        reduction to a sub-group, e.g. the ranks that share a parameter under model parallelism; every sub-group
+        family must use its own `flag_set`, and all its members must issue the same sequence of calls on it.
 
         `wait_seconds` bounds how long a rank waits for its peers inside the kernel (default: `PEER_SKEW_SECONDS`).
         It is the tolerated skew between ranks, not a liveness check: when it runs out the kernel leaves with
         error code 16 and the fused optimiser skips its update."""
         assert dtype in (torch.float32, torch.bfloat16)
-        ptrs = [p + byte_offset for p in self.ptrs]
-        self.ext.peer_allreduce(ptrs, self.flag_ptrs, self.rank, int(numel), 1 if dtype == torch.bfloat16 else 0,
+        assert 0 <= flag_set < self.flag_sets
+        if members is None:
+            members, my = list(range(self.world)), self.rank
+        else:
+            members = [int(m) for m in members]
+            my = members.index(self.rank)
+        if len(members) == 1:
+            if scale != 1.0:
+                self.view(dtype, numel, byte_offset).mul_(scale)
+            return
+        ptrs = [self.ptrs[m] + byte_offset for m in members]
+        flags = [self.flag_ptrs[m] + flag_set * FLAG_BYTES for m in members]
+        self.ext.peer_allreduce(ptrs, flags, my, int(numel), 1 if dtype == torch.bfloat16 else 0,
                                 float(scale), float(PEER_SKEW_SECONDS if wait_seconds is None else wait_seconds),
                                 self.device.index)
 

@@ -101,6 +101,77 @@ def cases(H, W, dev, B=1, layout="cl"):
         return (lambda: instance_norm(x, w, b, 1e-6, "gelu")), 3 * C * hw * 2, 0.0
 
     out["inorm_gelu"] = inorm
+
+    # ---- the spectral stages of one SFNO block on the internal grid (H/3 x W/3 Gauss grid, lmax = H/3, mmax = lmax + 1)
+    def _plan():
+        from ..ops.spectral import SHTPlan
+        hi, wi = H // 3, W // 3
+        return SHTPlan.get(hi, wi, hi, hi + 1, "legendre-gauss", dev), hi, wi
+
+    def leg_analysis():
+        from ..ops.spectral import legendre_analysis
+        plan, hi, wi = _plan()
+        t1 = torch.randn(1, hi, plan.k2, C, device=dev).to(bf)
+        pairs = sum(max(0, plan.lmax - m) for m in range(plan.mmax))
+        nbytes = t1.numel() * 2 + plan.lmax * plan.mmax * 2 * C * 2 + plan.pw.numel() * 2
+        return (lambda: legendre_analysis(t1, plan.pw)), nbytes, 2.0 * pairs * hi * 2 * C
+
+    out["legendre_analysis"] = leg_analysis
+
+    def leg_synthesis():
+        from ..ops.spectral import legendre_synthesis
+        plan, hi, wi = _plan()
+        t3 = torch.randn(1, plan.mmax, plan.lmax, 2 * C, device=dev).to(bf)
+        pairs = sum(max(0, plan.lmax - m) for m in range(plan.mmax))
+        nbytes = t3.numel() * 2 + hi * plan.k2 * C * 2 + plan.p.numel() * 2
+        return (lambda: legendre_synthesis(t3, False, plan.p, hi)), nbytes, 2.0 * pairs * hi * 2 * C
+
+    out["legendre_synthesis"] = leg_synthesis
+
+    def contraction():
+        from ..ops.spectral import contract
+        plan, hi, wi = _plan()
+        t2 = torch.randn(1, plan.lmax, plan.mmax, 2 * C, device=dev).to(bf)
+        wx = (torch.randn(plan.lmax, 2 * C, 2 * C, device=dev) * 0.05).to(bf)
+        pairs = sum(min(l + 1, plan.mmax) for l in range(plan.lmax))
+        nbytes = 2 * t2.numel() * 2 + wx.numel() * 2
+        return (lambda: contract(t2, wx, False)), nbytes, 2.0 * pairs * (2 * C) * (2 * C)
+
+    out["contract"] = contraction
+
+    def adamw():
+        from ..ops.optim import FusedAdamW
+        n = 64 * 1024 * 1024                        # 64 Mi parameters: 28 bytes of traffic each (p, g, m, v read; p, m, v written)
+        prm = torch.nn.Parameter(torch.randn(n, device=dev))
+        prm.grad = torch.randn(n, device=dev)
+        opt = FusedAdamW([prm], lr=1e-3)
+        return (lambda: opt.step()), 28.0 * n, 0.0
+
+    out["adamw"] = adamw
+
+    def lp():
+        from ..ops.loss import weighted_lp_norms
+        pr = torch.randn(1, 73, H, W, device=dev).to(bf)
+        tg = torch.randn(1, 73, H, W, device=dev).to(bf)
+        q = torch.full((H,), 1.0 / (H * W), device=dev)
+        return (lambda: weighted_lp_norms(pr, tg, q, 2)), 2.0 * 73 * H * W * 2, 0.0
+
+    out["lp_norms"] = lp
+
+    def afno():
+        from ..ops import afno as afno_ops
+        hh, ww, cc, nb = H // 8, W // 8, 768, 8           # FourCastNet token grid for a 720 x 1440 field: 90 x 180
+        bs = cc // nb
+        x = torch.randn(1, hh, ww, cc, device=dev).to(bf)
+        ps = [torch.randn(nb, bs, bs, device=dev) * 0.05 for _ in range(2)] + [torch.zeros(nb, bs, device=dev) for _ in range(2)]
+        ps = ps + [torch.randn(nb, bs, bs, device=dev) * 0.05 for _ in range(2)] + [torch.zeros(nb, bs, device=dev) for _ in range(2)]
+        kx, ncols = afno_ops.mode_window_v1(hh, ww, 1.0)
+        nkx = len(kx)
+        flops = 2.0 * cc * (2 * ncols * ww * hh + 2 * nkx * 2 * hh * ncols) * 2 + 2.0 * 2 * ncols * nkx * nb * (2 * bs) * (2 * bs)
+        nbytes = 3.0 * x.numel() * 2                       # read x (twice: input and skip), write y; intermediates stay in L2
+        return (lambda: afno_ops.afno_filter(x, *ps, kx, ncols, 0.01, skip=x)), nbytes, flops
+
+    out["afno_filter"] = afno
     return out
 
 

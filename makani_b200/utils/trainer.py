@@ -295,6 +295,7 @@ class Trainer:
                 self.optimizer.prepare_tables()      # pointer tables are uploaded before the capture starts
             side.synchronize()
             self.graph = torch.cuda.CUDAGraph()
+            n0 = _ext.launch_count()
             with torch.cuda.graph(self.graph, stream=side):
                 self.static_loss = self._forward_backward(self.static_inp, self.static_tar)
                 if self.graph_mode == "step":
@@ -303,6 +304,9 @@ class Trainer:
                         self.optimizer.launch_step()
                     else:
                         self.optimizer.step()
+            # kernels of the extension inside the graph: counted per replay, not at capture time
+            self._launches_per_replay = _ext.launch_count() - n0
+            _ext.add_launches(-self._launches_per_replay)
         torch.cuda.current_stream(self.device).wait_stream(side)
 
     def _train_step(self, inp, tar):
@@ -314,6 +318,7 @@ class Trainer:
             if self.graph_mode == "step" and hasattr(self.optimizer, "prepare_step"):
                 self.optimizer.prepare_step()
             self.graph.replay()
+            _ext.add_launches(getattr(self, "_launches_per_replay", 0))
             loss = self.static_loss
             if self.graph_mode != "step":
                 self.gscaler.step(self.optimizer)

@@ -374,6 +374,56 @@ def case_peer_allreduce():
     ra.close()
 
 
+def case_peer_shared_sums():
+    """Gradient sums over model-parallel groups through the in-kernel peer all-reduce (`GradReducer` on a spatially
+    parallel layout) against NCCL all-reduces of the same gradients: parameters shared over `h`, `w`, `spatial`, `model`
+    and unshared ones, a complex parameter among them, three steps in a row."""
+    from makani_b200.ops import _ext
+    from makani_b200.parallel.grad_reduce import GradReducer
+    assert os.environ.get("MK_DEVICE") == "cuda"
+    dev = torch.device("cuda", comm.get_local_rank())
+    rank = dist.get_rank()
+    torch.manual_seed(5)
+    tags = [["h"], ["w"], ["spatial"], ["model"], [], ["h", "w"]]
+    m = torch.nn.Module()
+    for i, t in enumerate(tags):
+        shape = (257, 33) if i % 2 == 0 else (1000,)
+        prm = torch.nn.Parameter(torch.randn(*shape, device=dev))
+        prm.is_shared_mp = list(t)
+        m.register_parameter(f"p{i}", prm)
+    cw = torch.nn.Parameter(torch.randn(31, 7, dtype=torch.complex64, device=dev))
+    cw.is_shared_mp = ["spatial"]
+    m.register_parameter("cw", cw)
+    red = GradReducer(m)
+    assert red.sym is not None, "peer path not taken"
+    for it in range(3):
+        red.zero_grad()
+        g = torch.Generator(device=dev)
+        g.manual_seed(100 * it + rank)
+        expect = []
+        for prm in m.parameters():
+            gr = torch.randn(prm.shape, device=dev, generator=g, dtype=torch.float32) if not prm.is_complex() else \
+                torch.view_as_complex(torch.randn(*prm.shape, 2, device=dev, generator=g))
+            prm.grad.copy_(gr)
+            e = torch.view_as_real(gr).clone() if gr.is_complex() else gr.clone()
+            if comm.get_size("data") > 1:
+                dist.all_reduce(e, group=comm.get_group("data"))
+                e /= comm.get_size("data")
+            for name in prm.is_shared_mp:
+                if comm.get_size(name) > 1:
+                    dist.all_reduce(e, group=comm.get_group(name))
+            expect.append(e)
+        torch.cuda.synchronize()
+        dist.barrier()
+        red.reduce()
+        torch.cuda.synchronize()
+        _ext.check_device_errors(dev)
+        for prm, e in zip(m.parameters(), expect):
+            got = torch.view_as_real(prm.grad) if prm.grad.is_complex() else prm.grad
+            assert _rel(got, e) < 1e-5, (_rel(got, e), prm.shape)
+    red.close()
+
+
 def case_fused_matmul():
     """Channel-parallel 1x1 convolution whose partial products are exchanged by the GEMM epilogue (peer memory) ==
     the full convolution: forward, input gradient (reduced over the other group), local weight and bias gradients."""

@@ -107,11 +107,7 @@ def test_afno_v2_network_matches_direct_formulation(frac, norm, skip):
         assert k in sd or k.startswith("blocks.1.mlp"), k
 
 
-@pytest.mark.gpu
-@pytest.mark.parametrize("ver", [1, 2])
-def test_afno_chain_gpu_bf16(ver):
-    """The tensor-core chain at the FourCastNet token grid (90 x 180 tokens, 768 channels, 8 blocks) against the fp32
-    torch.fft formulation of the same operator: output and every gradient."""
+def _gpu_case(ver, regime):
     from makani_b200.ops import _ext
     _ext.require()
     dev = torch.device("cuda", 0)
@@ -121,26 +117,55 @@ def test_afno_chain_gpu_bf16(ver):
     kx, ncols = (afno.mode_window_v1 if ver == 1 else afno.mode_window_v2)(H, W, 1.0)
     x32 = torch.randn(B, H, W, C, device=dev)
     ps32 = _params(nb, bs, hid, torch.float32, dev)
+    lam = 0.01
     with torch.no_grad():
         for p in ps32:
             p.mul_(0.3)
+        if regime == "linear":
+            # every ReLU input far above zero and no shrinkage: the operator is affine, its gradient has no masks
+            ps32[2].fill_(40.0)
+            ps32[3].fill_(40.0)
+            lam = 0.0
     g = torch.randn(B, H, W, C, device=dev)
     xb = x32.to(torch.bfloat16).requires_grad_()
     assert afno.fast_path_ok(xb, nb, hid)
-    y = afno.afno_filter(xb, *ps32, kx, ncols, 0.01, skip=xb)
+    y = afno.afno_filter(xb, *ps32, kx, ncols, lam, skip=xb)
     y.backward(g.to(torch.bfloat16))
     got = [y.detach().float(), xb.grad.float()] + [p.grad.clone() for p in ps32]
     for p in ps32:
         p.grad = None
     xr = x32.to(torch.bfloat16).float().requires_grad_()
-    yr = afno.afno_filter_reference(xr, *ps32, kx, ncols, 0.01, skip=xr)
+    yr = afno.afno_filter_reference(xr, *ps32, kx, ncols, lam, skip=xr)
     yr.backward(g.to(torch.bfloat16).float())
     ref = [yr.detach(), xr.grad] + [p.grad for p in ps32]
     torch.cuda.synchronize()
     _ext.check_device_errors(dev)
     names = ["y", "dx", "dw1r", "dw1i", "db1r", "db1i", "dw2r", "dw2i", "db2r", "db2i"]
-    for n, a, b in zip(names, got, ref):
-        assert _rel(a, b) < 4e-2, (n, _rel(a, b))
+    errs = {n: round(_rel(a, b), 4) for n, a, b in zip(names, got, ref)}
+    print(f"afno chain bf16 errors ({regime}, window v{ver})", errs)
+    return errs
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("ver", [1, 2])
+def test_afno_chain_gpu_bf16_affine_regime(ver):
+    """The tensor-core chain at the FourCastNet token grid (90 x 180 tokens, 768 channels, 8 blocks) against the fp32
+    torch.fft formulation, with biases that keep every ReLU open and no shrinkage: output and all gradients of the
+    (then affine) operator agree to bf16 accuracy."""
+    errs = _gpu_case(ver, "linear")
+    assert max(errs.values()) < 2e-2, errs
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("ver", [1, 2])
+def test_afno_chain_gpu_bf16(ver):
+    """Same, in the generic regime.  The output agrees to bf16 accuracy; the gradients are compared with a wider margin
+    because they are discontinuous in the ReLU / shrinkage masks: a 0.3 % perturbation of the pre-activations (bf16
+    DFT matrices and intermediates) flips about 0.25 % of the mask entries, and every flipped entry changes the
+    gradient by its full size, i.e. by sqrt(0.0025) = 5 % in the L2 norm (the CPU emulation of the chain shows the
+    same figure)."""
+    errs = _gpu_case(ver, "generic")
+    assert errs["y"] < 2e-2 and max(errs.values()) < 0.1, errs
 
 
 def test_distributed_afno2d_v2_single_rank_matches_filter():

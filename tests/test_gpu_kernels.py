@@ -275,6 +275,25 @@ def test_instance_norm_fwd_bwd():
                 assert _rel(a.float(), r_) < 2e-2
 
 
+def test_instance_norm_large_mean_small_spread():
+    """Channels-last instance norm of a field whose mean is 300 times its spread (one-pass variance must not cancel):
+    a 361x720 grid, statistics against torch in fp64 on the same bf16 data."""
+    from makani_b200.ops.norm import instance_norm
+    dev = _dev()
+    torch.manual_seed(31)
+    B, C, H, W = 1, 64, 361, 720
+    x = (300.0 + torch.randn(B, C, H, W, device=dev)).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    w = torch.rand(C, device=dev) + 0.5
+    b = torch.randn(C, device=dev) * 0.1
+    y = instance_norm(x, w, b, 1e-6, "none")
+    xd = x.double()
+    mean = xd.mean(dim=(2, 3), keepdim=True)
+    var = xd.var(dim=(2, 3), unbiased=False, keepdim=True)
+    ref = (xd - mean) / torch.sqrt(var + 1e-6) * w.double().view(1, -1, 1, 1) + b.double().view(1, -1, 1, 1)
+    torch.cuda.synchronize()
+    assert _rel(y.float(), ref) < 1e-2, _rel(y.float(), ref)
+
+
 def test_instance_norm_channels_last_fwd_bwd():
     from makani_b200.ops.norm import instance_norm
     dev = _dev()

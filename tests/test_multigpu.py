@@ -41,3 +41,9 @@ def test_fused_channel_parallel_matmul(sizes, world):
 def test_peer_allreduce_matches_nccl(world):
     _need(world)
     _launch("peer_allreduce", (1, 1, 1, 1), world, cuda=True)
+
+
+@pytest.mark.parametrize("sizes,world", [((2, 1, 1, 1), 2), ((2, 2, 1, 1), 4), ((2, 1, 1, 1), 4), ((4, 2, 1, 1), 8)])
+def test_peer_shared_parameter_sums(sizes, world):
+    _need(world)
+    _launch("peer_shared_sums", sizes, world, cuda=True)
