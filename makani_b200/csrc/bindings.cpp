@@ -13,6 +13,7 @@
 #include "gelu.cuh"
 #include "gemm_tcgen05.cuh"
 #include "peer.cuh"
+#include "spectral_modes.cuh"
 
 namespace {
 
@@ -371,6 +372,48 @@ void adamw_step(const Tensor& table, const Tensor& chunk_tensor, const Tensor& c
 
 int64_t adam_entry_bytes() { return sizeof(mk::AdamEntry); }
 
+// ---- mode-wise complex contractions (complex64 tensors, contiguous, mode index last)
+static const float* cfp(const Tensor& t) { return reinterpret_cast<const float*>(t.data_ptr()); }
+static float* cfpm(Tensor& t) { return reinterpret_cast<float*>(t.data_ptr()); }
+static void check_c64(const Tensor& t, const char* what) {
+  MK_CHECK(t.is_cuda() && t.is_contiguous() && t.scalar_type() == torch::kComplexFloat, what, ": contiguous complex64 CUDA tensor expected");
+}
+
+// mode: 0 out = a . w (a [B,I,S], w [I,O,S], out [B,O,S]); 1 da = dy . conj(w) (first arg dy, out da [B,I,S]);
+//       2 dw = conj(a) . dy (args a, dy; out [I,O,S])
+void modes_diag(const Tensor& x, const Tensor& y, Tensor& out, int64_t B, int64_t I, int64_t O, int64_t S, int64_t mode) {
+  check_c64(x, "modes_diag"); check_c64(y, "modes_diag"); check_c64(out, "modes_diag");
+  c10::cuda::CUDAGuard guard(x.device());
+  cudaError_t e;
+  if (mode == 0) {
+    MK_CHECK(x.numel() == B * I * S && y.numel() == I * O * S && out.numel() == B * O * S, "modes_diag fwd: shape mismatch");
+    e = mk::modes_diag_fwd(cfp(x), cfp(y), cfpm(out), (int)B, (int)I, (int)O, S, cur_stream());
+  } else if (mode == 1) {
+    MK_CHECK(x.numel() == B * O * S && y.numel() == I * O * S && out.numel() == B * I * S, "modes_diag dgrad: shape mismatch");
+    e = mk::modes_diag_dgrad(cfp(x), cfp(y), cfpm(out), (int)B, (int)I, (int)O, S, cur_stream());
+  } else {
+    MK_CHECK(x.numel() == B * I * S && y.numel() == B * O * S && out.numel() == I * O * S, "modes_diag wgrad: shape mismatch");
+    e = mk::modes_diag_wgrad(cfp(x), cfp(y), cfpm(out), (int)B, (int)I, (int)O, S, cur_stream());
+  }
+  check_cuda(e, "modes_diag");
+}
+
+// mode: 0 out = a * w; 1 out = a * conj(w) (a, out [B,I,S]; w [I,S/wdiv]); 2 dw = sum conj(a) dy (args a, dy; out [I,S/wdiv])
+void modes_sep(const Tensor& x, const Tensor& y, Tensor& out, int64_t B, int64_t I, int64_t S, int64_t wdiv, int64_t mode) {
+  check_c64(x, "modes_sep"); check_c64(y, "modes_sep"); check_c64(out, "modes_sep");
+  MK_CHECK(wdiv >= 1 && S % wdiv == 0, "modes_sep: the mode count must be a multiple of wdiv");
+  c10::cuda::CUDAGuard guard(x.device());
+  cudaError_t e;
+  if (mode == 2) {
+    MK_CHECK(x.numel() == B * I * S && y.numel() == B * I * S && out.numel() == I * (S / wdiv), "modes_sep wgrad: shape mismatch");
+    e = mk::modes_sep_wgrad(cfp(x), cfp(y), cfpm(out), (int)B, (int)I, S, (int)wdiv, cur_stream());
+  } else {
+    MK_CHECK(x.numel() == B * I * S && y.numel() == I * (S / wdiv) && out.numel() == B * I * S, "modes_sep: shape mismatch");
+    e = mk::modes_sep_mul(cfp(x), cfp(y), cfpm(out), (int)B, (int)I, S, (int)wdiv, (int)mode, cur_stream());
+  }
+  check_cuda(e, "modes_sep");
+}
+
 void spectral_expand(const Tensor& w, Tensor& wx) {
   MK_CHECK(w.is_cuda() && w.is_contiguous() && w.scalar_type() == torch::kComplexFloat && w.dim() == 3, "spectral_expand: complex64 [Cin,Cout,L]");
   const int64_t Cin = w.size(0), Cout = w.size(1), L = w.size(2);
@@ -483,6 +526,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("lp_norms", &lp_norms);
   m.def("lp_norms_bwd", &lp_norms_bwd);
   m.def("adamw_step", &adamw_step);
+  m.def("modes_diag", &modes_diag);
+  m.def("modes_sep", &modes_sep);
   m.def("adam_entry_bytes", &adam_entry_bytes);
   m.def("spectral_expand", &spectral_expand);
   m.def("spectral_fold", &spectral_fold, py::arg("dwx"), py::arg("dw"), py::arg("two_block") = false, py::arg("assign") = false);

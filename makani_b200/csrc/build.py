@@ -19,7 +19,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 BUILD = os.path.join(HERE, "build")
 TARGET = os.path.join(HERE, "_C.so")
 
-CU_SOURCES = ["gemm_tcgen05.cu", "fused_ops.cu", "peer.cu", "no_alloc.cu"]
+CU_SOURCES = ["gemm_tcgen05.cu", "fused_ops.cu", "peer.cu", "spectral_modes.cu", "no_alloc.cu"]
 CPP_SOURCES = ["bindings.cpp"]
 
 NVCC_FLAGS = [

@@ -1,8 +1,9 @@
 """Complex tensor contractions used by the spectral filters (torch formulations).
 
 Index convention: b batch, i input channel, o output channel, x degree l (or first mode index), y order m.
-Hot variant on GPUs: "dhconv" (`bixy,iox->boxy`), which `makani_b200.ops.spectral` runs on the tensor cores;
-these einsum forms serve CPU, fp32 and the less common operator types
+Hot variant on GPUs: "dhconv" (`bixy,iox->boxy`), which `makani_b200.ops.spectral` runs on the tensor cores; the
+"diagonal" and the separable operators run as streaming kernels (`makani_b200.ops.spectral_modes`) on CUDA complex64
+tensors; the einsum forms below serve CPU, other dtypes and the spectral-MLP products
 (behaviour of makani/models/common/contractions.py:19-178).
 """
 
@@ -10,9 +11,11 @@ from __future__ import annotations
 
 import torch
 
+from ...ops import spectral_modes as _modes
+
 
 def contract_diagonal(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
-    return torch.einsum("bixy,ioxy->boxy", a, b)
+    return _modes.contract_diagonal(a, b)
 
 
 def contract_dhconv(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
@@ -20,11 +23,11 @@ def contract_dhconv(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
 
 
 def contract_sep_diagonal(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
-    return torch.einsum("bixy,ixy->bixy", a, b)
+    return _modes.contract_sep_diagonal(a, b)
 
 
 def contract_sep_dhconv(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
-    return torch.einsum("bixy,ix->bixy", a, b)
+    return _modes.contract_sep_dhconv(a, b)
 
 
 # spectral MLP products: weights are shared over all modes ("io") or depend on the degree ("xio")

@@ -47,3 +47,9 @@ def test_peer_allreduce_matches_nccl(world):
 def test_peer_shared_parameter_sums(sizes, world):
     _need(world)
     _launch("peer_shared_sums", sizes, world, cuda=True)
+
+
+@pytest.mark.parametrize("sizes,world", [((2, 1, 1, 1), 2), ((1, 2, 1, 1), 2), ((2, 2, 1, 1), 4)])
+def test_fused_chains_repeat_bitwise(sizes, world):
+    _need(world)
+    _launch("fused_repeat", sizes, world, cuda=True)
