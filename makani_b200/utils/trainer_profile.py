@@ -4,7 +4,8 @@ toggle bracketed by a barrier so the windows of all ranks line up.
 
 Flag semantics: makani/train_profile.py (`--capture_mode`, `--capture_range_start/stop`, `--capture_ranks`) and
 makani/utils/trainer_profile.py:54-72,301-305,659-710.  Unlike the reference, which keeps a second copy of the
-whole trainer, this class only overrides the step wrappers.
+whole trainer, this class wraps the step, the two data loaders (NVTX range per fetch; the validation window counts
+validation steps) and the visualiser.
 """
 
 from __future__ import annotations
@@ -53,6 +54,60 @@ def _nvtx_pop(device):
         torch.cuda.nvtx.range_pop()
 
 
+class _InstrumentedLoader:
+    """Iterates a data loader with an NVTX range around every fetch ("data loading") and, when a capture window is
+    given, opens / closes the window around the loop body of the chosen steps: `before(i)` runs right before batch i is
+    handed out, `after(i)` when the body of step i has finished (i.e. when the next batch is asked for)."""
+
+    def __init__(self, loader, device, window=None, label="data loading"):
+        self.loader, self.device, self.window, self.label = loader, device, window, label
+
+    def __len__(self):
+        return len(self.loader)
+
+    def __getattr__(self, name):
+        return getattr(self.loader, name)
+
+    def __iter__(self):
+        it = iter(self.loader)
+        step = 0
+        while True:
+            if self.window is not None and step > 0:
+                self.window.after(step - 1)
+            _nvtx_push(self.label, self.device)
+            try:
+                batch = next(it)
+            except StopIteration:
+                _nvtx_pop(self.device)
+                return
+            _nvtx_pop(self.device)
+            if self.window is not None:
+                self.window.before(step)
+            yield batch
+            step += 1
+
+
+class _InstrumentedVisualizer:
+    """NVTX ranges around the visualiser calls (they run on the host between validation steps)."""
+
+    def __init__(self, viz, device):
+        self._viz, self._device = viz, device
+
+    def __getattr__(self, name):
+        attr = getattr(self._viz, name)
+        if not callable(attr):
+            return attr
+
+        def wrapped(*args, **kwargs):
+            _nvtx_push(f"visualization {name}", self._device)
+            try:
+                return attr(*args, **kwargs)
+            finally:
+                _nvtx_pop(self._device)
+
+        return wrapped
+
+
 class ProfilingTrainer(Trainer):
     def __init__(self, params, world_rank, job_type="train"):
         super().__init__(params, world_rank, job_type)
@@ -65,6 +120,8 @@ class ProfilingTrainer(Trainer):
         self._valid_window = _Window("validation" in mode, g("capture_range_start", 0), g("capture_range_stop", 50), ranks,
                                      world_rank, self.device)
         self._train_steps = 0
+        if self.visualizer is not None:
+            self.visualizer = _InstrumentedVisualizer(self.visualizer, self.device)
 
     def _train_step(self, inp, tar):
         step = self._train_steps
@@ -78,16 +135,27 @@ class ProfilingTrainer(Trainer):
 
     def train_one_epoch(self):
         _nvtx_push("training", self.device)
-        out = super().train_one_epoch()
-        _nvtx_pop(self.device)
+        loader = self.train_dataloader
+        self.train_dataloader = _InstrumentedLoader(loader, self.device)
+        try:
+            out = super().train_one_epoch()
+        finally:
+            self.train_dataloader = loader
+            _nvtx_pop(self.device)
         return out
 
     def validate_one_epoch(self, epoch):
-        self._valid_window.before(self._valid_window.start)
+        # the capture window counts validation steps (batches of the validation loader), as for training
         _nvtx_push("validation", self.device)
-        out = super().validate_one_epoch(epoch)
-        _nvtx_pop(self.device)
-        self._valid_window.after(self._valid_window.stop)
+        loader = self.valid_dataloader
+        self.valid_dataloader = _InstrumentedLoader(loader, self.device, window=self._valid_window)
+        try:
+            out = super().validate_one_epoch(epoch)
+        finally:
+            self.valid_dataloader = loader
+            if self._valid_window.active:       # the loader ended inside the window
+                self._valid_window.after(self._valid_window.stop)
+            _nvtx_pop(self.device)
         return out
 
 
