@@ -4,6 +4,7 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 
+#include <algorithm>
 #include <cstdint>
 #include <cstring>
 #include <map>
@@ -96,6 +97,22 @@ static bool parse_peer(mk::GemmPeer& g, const std::vector<int64_t>& seg, const s
   return !seg.empty() || !sync.empty();
 }
 
+// Host-side guard for the strided addressing of the GEMM engine: the lowest and highest element a launch can touch
+// must lie inside the tensor's storage.  `terms` are (count, stride) pairs; every index runs 0..count-1.
+static void check_extent(const Tensor& t, int64_t off, std::initializer_list<std::pair<int64_t, int64_t>> terms, const char* what) {
+  int64_t lo = off, hi = off;
+  for (const auto& ts : terms) {
+    if (ts.first <= 1) continue;
+    const int64_t span = (ts.first - 1) * ts.second;
+    if (span >= 0) hi += span; else lo += span;
+  }
+  const int64_t esz = static_cast<int64_t>(t.element_size());
+  const int64_t before = t.storage_offset();
+  const int64_t total = static_cast<int64_t>(t.storage().nbytes()) / esz;
+  MK_CHECK(lo + before >= 0 && hi + before < total, "gemm: ", what, " addressing leaves the tensor's storage (elements ", lo + before,
+           "..", hi + before, " of ", total, ")");
+}
+
 void gemm_impl(const Tensor& a, const Tensor& b, Tensor& d, const c10::optional<Tensor>& bias,
                const c10::optional<Tensor>& resid, const c10::optional<Tensor>& preact, const std::vector<int64_t>& ip,
                double alpha, const mk::GemmPeer* peer);
@@ -179,6 +196,10 @@ void gemm_impl(const Tensor& a, const Tensor& b, Tensor& d, const c10::optional<
   B.rows = p.N; B.mn_major = ip[k++]; B.ld = ip[k++]; B.zs_lo = ip[k++]; B.zs_hi = ip[k++];
   A.ptr = base_ptr(a) + a_off * eb;
   B.ptr = base_ptr(b) + b_off * eb;
+  // operand extents: the TMA descriptors clip rows and K to the problem, so the corner elements bound every load
+  check_extent(a, a_off, {{A.mn_major ? p.K : p.M, A.ld}, {A.mn_major ? p.M : p.K, 1}, {p.zlo_n, A.zs_lo}, {p.zhi_n, A.zs_hi}}, "A");
+  if (peer == nullptr || peer->nseg == 0)   // with segments B is gathered from the segment pointers instead
+    check_extent(b, b_off, {{B.mn_major ? p.K : p.N, B.ld}, {B.mn_major ? p.N : p.K, 1}, {p.zlo_n, B.zs_lo}, {p.zhi_n, B.zs_hi}}, "B");
   mk::GemmEpilogue e;
   const int64_t d_off = ip[k++];
   const int osz = static_cast<int>(d.element_size());
@@ -188,6 +209,12 @@ void gemm_impl(const Tensor& a, const Tensor& b, Tensor& d, const c10::optional<
   e.d_zlo = ip[k++]; e.d_zhi = ip[k++];
   e.rdiv = ip[k++]; e.rs_hi = ip[k++]; e.rs_lo = ip[k++];
   e.ndiv = ip[k++]; e.ns_hi = ip[k++];
+  {
+    const int64_t rdiv = e.rdiv > 0 ? e.rdiv : (1 << 30), ndiv = e.ndiv > 0 ? e.ndiv : (1 << 30);   // <= 0: no split
+    check_extent(d, d_off, {{p.zhi_n, e.d_zhi}, {p.zlo_n, e.d_zlo}, {(p.M + rdiv - 1) / rdiv, e.rs_hi},
+                            {std::min<int64_t>(p.M, rdiv), e.rs_lo}, {(p.N + ndiv - 1) / ndiv, e.ns_hi},
+                            {std::min<int64_t>(p.N, ndiv), 1}}, "output");
+  }
   e.alpha = static_cast<float>(alpha);
   e.bias_mode = ip[k++];
   e.act = ip[k++];

@@ -569,7 +569,44 @@ __device__ __forceinline__ float ldf<float>(const float* p, long long i) { retur
 template <>
 __device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p, long long i) { return __bfloat162float(p[i]); }
 
-template <typename T, int P>
+
+// 16-byte vector access for the loss kernels: VW elements of one latitude row per load (W is a multiple of VW there)
+template <typename T>
+struct LpVec;
+template <>
+struct LpVec<float> {
+  static constexpr int VW = 4;
+  static __device__ __forceinline__ void load(const float* p, long long i, float (&v)[4]) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(p + i));
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+  }
+  static __device__ __forceinline__ void store(float* p, long long i, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p + i) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+};
+template <>
+struct LpVec<__nv_bfloat16> {
+  static constexpr int VW = 8;
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, long long i, float (&v)[8]) {
+    const uint4 a = __ldg(reinterpret_cast<const uint4*>(p + i));
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&a);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(h[j]);
+      v[2 * j] = f.x;
+      v[2 * j + 1] = f.y;
+    }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, long long i, const float (&v)[8]) {
+    uint4 a;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&a);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+    *reinterpret_cast<uint4*>(p + i) = a;
+  }
+};
+
+template <typename T, int P, bool VEC>
 __global__ void __launch_bounds__(NT) lp_norms_kernel(const T* __restrict__ pred, const T* __restrict__ tgt,
                                                       const float* __restrict__ qlat, float* __restrict__ out,
                                                       float* __restrict__ partial, int* __restrict__ counters, int W,
@@ -581,16 +618,41 @@ __global__ void __launch_bounds__(NT) lp_norms_kernel(const T* __restrict__ pred
   long long end = beg + LP_CHUNK;
   if (end > hw) end = hw;
   float sd = 0.f, st = 0.f;
-  for (long long i = beg + threadIdx.x; i < end; i += NT) {
-    const float q = qlat[i / W];
-    const float p = ldf<T>(pp, i), t = ldf<T>(tp, i);
-    const float d = p - t;
-    if (P == 2) {
-      sd += q * d * d;
-      st += q * t * t;
-    } else {
-      sd += q * fabsf(d);
-      st += q * fabsf(t);
+  if (VEC) {
+    constexpr int VW = LpVec<T>::VW;
+#pragma unroll 4
+    for (long long i = beg + static_cast<long long>(threadIdx.x) * VW; i < end; i += static_cast<long long>(NT) * VW) {
+      const float q = qlat[static_cast<unsigned>(i) / static_cast<unsigned>(W)];
+      float p[VW], t[VW];
+      LpVec<T>::load(pp, i, p);
+      LpVec<T>::load(tp, i, t);
+      float ad = 0.f, at = 0.f;
+#pragma unroll
+      for (int j = 0; j < VW; ++j) {
+        const float d = p[j] - t[j];
+        if (P == 2) {
+          ad = fmaf(d, d, ad);
+          at = fmaf(t[j], t[j], at);
+        } else {
+          ad += fabsf(d);
+          at += fabsf(t[j]);
+        }
+      }
+      sd = fmaf(q, ad, sd);
+      st = fmaf(q, at, st);
+    }
+  } else {
+    for (long long i = beg + threadIdx.x; i < end; i += NT) {
+      const float q = qlat[i / W];
+      const float p = ldf<T>(pp, i), t = ldf<T>(tp, i);
+      const float d = p - t;
+      if (P == 2) {
+        sd += q * d * d;
+        st += q * t * t;
+      } else {
+        sd += q * fabsf(d);
+        st += q * fabsf(t);
+      }
     }
   }
   block_sum2(sd, st);
@@ -629,7 +691,7 @@ __device__ __forceinline__ void stf<float>(float* p, long long i, float v) { p[i
 template <>
 __device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16* p, long long i, float v) { p[i] = __float2bfloat16(v); }
 
-template <typename T, int P>
+template <typename T, int P, bool VEC>
 __global__ void __launch_bounds__(NT) lp_bwd_kernel(const T* __restrict__ pred, const T* __restrict__ tgt,
                                                     const float* __restrict__ qlat, const float* __restrict__ coef,
                                                     T* __restrict__ grad, int W, long long hw) {
@@ -639,13 +701,31 @@ __global__ void __launch_bounds__(NT) lp_bwd_kernel(const T* __restrict__ pred, 
   const long long beg = static_cast<long long>(blockIdx.x) * LP_CHUNK;
   long long end = beg + LP_CHUNK;
   if (end > hw) end = hw;
-  for (long long i = beg + threadIdx.x; i < end; i += NT) {
-    const float q = qlat[i / W];
-    const float d = ldf<T>(pred, base + i) - ldf<T>(tgt, base + i);
-    float g;
-    if (P == 2) g = 2.f * d;
-    else g = (d > 0.f) ? 1.f : ((d < 0.f) ? -1.f : 0.f);
-    stf<T>(grad, base + i, cf * q * g);
+  if (VEC) {
+    constexpr int VW = LpVec<T>::VW;
+#pragma unroll 4
+    for (long long i = beg + static_cast<long long>(threadIdx.x) * VW; i < end; i += static_cast<long long>(NT) * VW) {
+      const float cq = cf * qlat[static_cast<unsigned>(i) / static_cast<unsigned>(W)];
+      float p[VW], t[VW];
+      LpVec<T>::load(pred, base + i, p);
+      LpVec<T>::load(tgt, base + i, t);
+#pragma unroll
+      for (int j = 0; j < VW; ++j) {
+        const float d = p[j] - t[j];
+        const float g = (P == 2) ? 2.f * d : ((d > 0.f) ? 1.f : ((d < 0.f) ? -1.f : 0.f));
+        p[j] = cq * g;
+      }
+      LpVec<T>::store(grad, base + i, p);
+    }
+  } else {
+    for (long long i = beg + threadIdx.x; i < end; i += NT) {
+      const float q = qlat[i / W];
+      const float d = ldf<T>(pred, base + i) - ldf<T>(tgt, base + i);
+      float g;
+      if (P == 2) g = 2.f * d;
+      else g = (d > 0.f) ? 1.f : ((d < 0.f) ? -1.f : 0.f);
+      stf<T>(grad, base + i, cf * q * g);
+    }
   }
 }
 
@@ -935,6 +1015,14 @@ cudaError_t inorm_cl_apply(const __nv_bfloat16* x, const __nv_bfloat16* dy, __nv
   return cudaGetLastError();
 }
 
+// The 16-byte path of the loss kernels needs every row to hold a whole number of vectors, 16-byte aligned planes and
+// element indices that fit 32 bits (the row index is a 32-bit division there).
+static bool lp_vec_ok(const void* a, const void* b, const void* c, int is_f32, int W, long long hw) {
+  const int vw = is_f32 ? 4 : 8;
+  const uintptr_t bits = reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c);
+  return (W % vw) == 0 && (bits & 15) == 0 && hw < (1ll << 31);
+}
+
 int lp_norms_chunks(long long hw) { return static_cast<int>((hw + LP_CHUNK - 1) / LP_CHUNK); }
 
 cudaError_t lp_norms(const void* pred, const void* tgt, int is_f32, const float* qlat, float* out, float* scratch,
@@ -949,13 +1037,23 @@ cudaError_t lp_norms(const void* pred, const void* tgt, int is_f32, const float*
   cudaError_t me = cudaMemsetAsync(counters, 0, sizeof(int) * static_cast<size_t>(planes), s);
   if (me != cudaSuccess) return me;
   dim3 grid(chunks, planes);
-  if (is_f32) {
-    if (P == 2) lp_norms_kernel<float, 2><<<grid, NT, 0, s>>>((const float*)pred, (const float*)tgt, qlat, out, partial, counters, W, hw, chunks);
-    else lp_norms_kernel<float, 1><<<grid, NT, 0, s>>>((const float*)pred, (const float*)tgt, qlat, out, partial, counters, W, hw, chunks);
-  } else {
-    if (P == 2) lp_norms_kernel<__nv_bfloat16, 2><<<grid, NT, 0, s>>>((const __nv_bfloat16*)pred, (const __nv_bfloat16*)tgt, qlat, out, partial, counters, W, hw, chunks);
-    else lp_norms_kernel<__nv_bfloat16, 1><<<grid, NT, 0, s>>>((const __nv_bfloat16*)pred, (const __nv_bfloat16*)tgt, qlat, out, partial, counters, W, hw, chunks);
-  }
+  const bool vec = lp_vec_ok(pred, tgt, nullptr, is_f32, W, hw);
+#define MK_LP_NORMS(T, PP, V) \
+  lp_norms_kernel<T, PP, V><<<grid, NT, 0, s>>>((const T*)pred, (const T*)tgt, qlat, out, partial, counters, W, hw, chunks)
+#define MK_LP_NORMS_T(T)                        \
+  do {                                          \
+    if (P == 2) {                               \
+      if (vec) MK_LP_NORMS(T, 2, true);         \
+      else MK_LP_NORMS(T, 2, false);            \
+    } else {                                    \
+      if (vec) MK_LP_NORMS(T, 1, true);         \
+      else MK_LP_NORMS(T, 1, false);            \
+    }                                           \
+  } while (0)
+  if (is_f32) MK_LP_NORMS_T(float);
+  else MK_LP_NORMS_T(__nv_bfloat16);
+#undef MK_LP_NORMS_T
+#undef MK_LP_NORMS
   return cudaGetLastError();
 }
 
@@ -964,13 +1062,23 @@ cudaError_t lp_norms_bwd(const void* pred, const void* tgt, int is_f32, const fl
   if (planes <= 0) return cudaSuccess;
   const long long hw = static_cast<long long>(H) * W;
   dim3 grid(lp_norms_chunks(hw), planes);
-  if (is_f32) {
-    if (P == 2) lp_bwd_kernel<float, 2><<<grid, NT, 0, s>>>((const float*)pred, (const float*)tgt, qlat, coef, (float*)grad, W, hw);
-    else lp_bwd_kernel<float, 1><<<grid, NT, 0, s>>>((const float*)pred, (const float*)tgt, qlat, coef, (float*)grad, W, hw);
-  } else {
-    if (P == 2) lp_bwd_kernel<__nv_bfloat16, 2><<<grid, NT, 0, s>>>((const __nv_bfloat16*)pred, (const __nv_bfloat16*)tgt, qlat, coef, (__nv_bfloat16*)grad, W, hw);
-    else lp_bwd_kernel<__nv_bfloat16, 1><<<grid, NT, 0, s>>>((const __nv_bfloat16*)pred, (const __nv_bfloat16*)tgt, qlat, coef, (__nv_bfloat16*)grad, W, hw);
-  }
+  const bool vec = lp_vec_ok(pred, tgt, grad, is_f32, W, hw);
+#define MK_LP_BWD(T, PP, V) \
+  lp_bwd_kernel<T, PP, V><<<grid, NT, 0, s>>>((const T*)pred, (const T*)tgt, qlat, coef, (T*)grad, W, hw)
+#define MK_LP_BWD_T(T)                        \
+  do {                                        \
+    if (P == 2) {                             \
+      if (vec) MK_LP_BWD(T, 2, true);         \
+      else MK_LP_BWD(T, 2, false);            \
+    } else {                                  \
+      if (vec) MK_LP_BWD(T, 1, true);         \
+      else MK_LP_BWD(T, 1, false);            \
+    }                                         \
+  } while (0)
+  if (is_f32) MK_LP_BWD_T(float);
+  else MK_LP_BWD_T(__nv_bfloat16);
+#undef MK_LP_BWD_T
+#undef MK_LP_BWD
   return cudaGetLastError();
 }
 

@@ -318,8 +318,11 @@ __device__ __forceinline__ TileCoord decode_tile(const KParams& p, long long t, 
   return c;
 }
 
-constexpr int STG_WARP_BYTES = 2 * 32 * 128;          // two 32-row x 128-byte staging boxes per epilogue warp
-constexpr int STG_BYTES = 8 * STG_WARP_BYTES;          // specialised epilogues stage tiles here for TMA stores
+// Specialised epilogues stage their output for TMA stores in 32-row x 128-byte boxes, two per epilogue warp.  The
+// epilogues with a TMA-fed operand (3, 4) run 128-column tiles, where a warp writes one box per tile: its previous
+// store left the box a whole tile ago, so one box is enough and the other 32 KB go to a further operand stage.
+__host__ __device__ constexpr int stg_warp_bytes(int epi) { return (epi == 3 || epi == 4) ? 32 * 128 : 2 * 32 * 128; }
+__host__ __device__ constexpr int stg_bytes(int epi) { return epi == 0 ? 0 : 8 * stg_warp_bytes(epi); }
 
 // EPI selects a compile-time specialised epilogue (bf16 output, 16-byte vector stores, row bias only):
 //   0 generic (all options decided at run time)      1 plain store
@@ -364,7 +367,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
   // layout: [stages][E tile x2 (optional)][staging][barriers]
   const uint32_t e_off = STAGES * STAGE_BYTES;
   const uint32_t stg_off = e_off + (p.e_tma ? 2 * E_BYTES : 0);
-  const uint32_t bar_off = stg_off + (EPI != 0 ? STG_BYTES : 0);
+  const uint32_t bar_off = stg_off + stg_bytes(EPI);
   uint8_t* bar_ptr = smem + bar_off;
   const uint32_t bar_base = smem_base + bar_off;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -445,7 +448,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       int s = 0;
-      uint32_t ph = 0, epi_it = 0;
+      uint32_t ph = 0;
       bool ok = peers_ready;
       if (p.sync.nwait > 0) asm volatile("fence.proxy.async;" ::: "memory");   // flags acquired in the prologue order the TMA loads below
       // pair: every load of both CTAs is counted on the leader's "full" barrier
@@ -453,20 +456,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
       for (long long t = tile0; t < p.total_tiles && ok; t += tile_step) {
         const TileCoord c = decode_tile<BK, CG>(p, t, crank);
         const int m0 = c.mt * BM, n0 = c.nt * BN;
-        if (p.e_tma && !(c.skip && p.accumulate)) {
-          // epilogue operand (residual / saved pre-activation) for this tile
-          const int eb = epi_it & 1;
-          if (!mbar_wait(eempty_bar(eb), ((epi_it >> 1) & 1u) ^ 1u)) {
-            atomicExch(p.err, 5);
-            break;
-          }
-          mbar_expect_tx(efull_bar(eb), E_BYTES);
-#pragma unroll
-          for (int j = 0; j < BN / 64; ++j)
-            tma_load_4d(smem_base + e_off + eb * E_BYTES + j * (BM * 128), &map_e, efull_bar(eb), n0 + j * 64, m0, c.zlo,
-                        c.zhi);
-          ++epi_it;
-        }
         if (c.skip) continue;
         const int azl = p.a_zlo ? c.zlo : 0, azh = p.a_zhi ? c.zhi : 0;
         const int bzl = p.b_zlo ? c.zlo : 0, bzh = p.b_zhi ? c.zhi : 0;
@@ -530,6 +519,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
             }
           }
         }
+      }
+    } else if (lane == 1 && p.e_tma && peers_ready) {
+      // ---------------------------------------------------------------- producer of the epilogue operand
+      // A thread of its own: the tile of the residual / saved pre-activation for tile t+2 can only be requested when
+      // the epilogue of tile t has released its buffer.  Issued from the operand producer's loop, that wait held
+      // back the A and B loads of the tiles in between, and the tensor cores waited for a memory round trip per tile.
+      if (p.sync.nwait > 0) asm volatile("fence.proxy.async;" ::: "memory");
+      uint32_t epi_it = 0;
+      for (long long t = tile0; t < p.total_tiles; t += tile_step) {
+        const TileCoord c = decode_tile<BK, CG>(p, t, crank);
+        if (c.skip && p.accumulate) continue;
+        const int eb = epi_it & 1;
+        if (!mbar_wait(eempty_bar(eb), ((epi_it >> 1) & 1u) ^ 1u)) {
+          atomicExch(p.err, 5);
+          break;
+        }
+        mbar_expect_tx(efull_bar(eb), E_BYTES);
+#pragma unroll
+        for (int j = 0; j < BN / 64; ++j)
+          tma_load_4d(smem_base + e_off + eb * E_BYTES + j * (BM * 128), &map_e, efull_bar(eb), c.nt * BN + j * 64, c.mt * BM,
+                      c.zlo, c.zhi);
+        ++epi_it;
       }
     }
   } else if (warp == 1) {
@@ -640,8 +651,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
       if constexpr (EPI != 0) {
         // ---------------- specialised bf16 epilogues: registers -> swizzled smem box -> TMA store (full lines, clipped
         // at the matrix edge by the tensor map)
-        const uint32_t stg_base = smem_base + stg_off + (warp - 2) * STG_WARP_BYTES;
-        uint8_t* const stg_ptr = smem + stg_off + (warp - 2) * STG_WARP_BYTES;
+        constexpr bool ONE_BOX = (EPI == 3 || EPI == 4);
+        const uint32_t stg_base = smem_base + stg_off + (warp - 2) * stg_warp_bytes(EPI);
+        uint8_t* const stg_ptr = smem + stg_off + (warp - 2) * stg_warp_bytes(EPI);
         int sb = 0;
         for (int bx = half; bx < BN / 64; bx += 2) {
           const int nb = n0 + bx * 64;
@@ -656,10 +668,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
             for (int j = 0; j < 64; ++j) v[j] = 0u;
           }
           // the staging box written two stores ago (one for the two-output epilogue) must have been read out
-          if constexpr (EPI == 2) tma_store_wait_read<0>();
+          if constexpr (EPI == 2 || ONE_BOX) tma_store_wait_read<0>();
           else tma_store_wait_read<1>();
           __syncwarp();
-          uint8_t* const box_d = stg_ptr + (EPI == 2 ? 32 * 128 : sb * 32 * 128);
+          uint8_t* const box_d = stg_ptr + (EPI == 2 ? 32 * 128 : (ONE_BOX ? 0 : sb * 32 * 128));
           uint8_t* const box_p = stg_ptr;
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
@@ -729,7 +741,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
             const int r0 = c.mt * BM + q * 32;
             if (r0 < p.M) {
               if constexpr (EPI == 2) tma_store_4d(&map_p, stg_base, nb, r0, c.zlo, c.zhi);
-              tma_store_4d(&map_d, stg_base + (EPI == 2 ? 32 * 128 : sb * 32 * 128), nb, r0, c.zlo, c.zhi);
+              tma_store_4d(&map_d, stg_base + (EPI == 2 ? 32 * 128 : (ONE_BOX ? 0 : sb * 32 * 128)), nb, r0, c.zlo, c.zhi);
               if constexpr (EPI == 1) {
                 for (int dq = 0; dq < p.ndx; ++dq)   // the same box goes to every peer's copy (plain stores over NVLink)
                   tma_store_4d(&maps_dx.m[dq], stg_base + sb * 32 * 128, nb, r0, c.zlo, c.zhi);
@@ -1002,7 +1014,7 @@ template <int BN, int EB, int EPI, int CG>
 cudaError_t launch_t(const CUtensorMap& ma, const BMaps& mb, const CUtensorMap& me, const CUtensorMap& md,
                      const CUtensorMap& mp, const DMaps& mdx, KParams& kp, cudaStream_t stream) {
   constexpr int STAGE = A_STAGE_BYTES + (BN / CG) * 128;
-  constexpr int FIXED = (EPI != 0 ? STG_BYTES : 0) + 8 * (2 * MAX_STAGES + 8) + 16 + 1024;
+  constexpr int FIXED = stg_bytes(EPI) + 8 * (2 * MAX_STAGES + 8) + 16 + 1024;
   const int e_bytes = kp.e_tma ? 2 * BM * BN * 2 : 0;
   int stages = (SMEM_LIMIT - FIXED - e_bytes) / STAGE;
   if (stages > MAX_STAGES) stages = MAX_STAGES;

@@ -352,10 +352,11 @@ def test_lp_norms_fwd_bwd():
     from makani_b200.ops.loss import weighted_lp_norms
     dev = _dev()
     torch.manual_seed(8)
-    B, C, H, W = 2, 5, 33, 64
-    q = torch.rand(H, device=dev) / (H * W)
-    for dtype in [torch.float32, torch.bfloat16]:
-        for p in [1, 2]:
+    # W = 64 takes the 16-byte loads, W = 50 the scalar path; 1100 x 64 spans two chunks of a plane
+    for (B, C, H, W), dtype, p in [(s_, d_, p_) for s_ in [(2, 5, 33, 64), (2, 5, 33, 50), (1, 3, 1100, 64)]
+                                   for d_ in [torch.float32, torch.bfloat16] for p_ in [1, 2]]:
+        q = torch.rand(H, device=dev) / (H * W)
+        if True:
             pr = torch.randn(B, C, H, W, device=dev).to(dtype).requires_grad_()
             tg = torch.randn(B, C, H, W, device=dev).to(dtype)
             out = weighted_lp_norms(pr, tg, q, p)
@@ -508,7 +509,7 @@ def test_sfno_bf16_vs_fp32_reference():
             assert g.norm().item() < 1e-2, n
             continue
         worst = max(worst, _rel(g, r))
-        assert _rel(g, r) < 0.15, n
+        assert _rel(g, r) < 0.05, n
     print("sfno bf16 vs fp32: output", round(_rel(y.float(), yr), 4), "worst parameter gradient", round(worst, 4))
     _ext.check_device_errors(dev)
 
@@ -533,6 +534,47 @@ def test_mode_wise_contractions():
         for got, ref in ((y1, y2), (a1.grad, a2.grad), (w1.grad, w2.grad)):
             assert _rel(torch.view_as_real(got.detach()), torch.view_as_real(ref.detach())) < 1e-5, eq
     _ext.check_device_errors(dev)
+
+
+def test_loss_curve_native_bf16_tracks_fp32_formulation():
+    """Fifty optimisation steps of a small SFNO: the native bf16 kernels (fused AdamW included) against the plain torch
+    fp32 formulation of the same model from the same initial weights and data; the two loss curves stay together."""
+    from makani_b200.models.networks.sfnonet import SphericalFourierNeuralOperatorNet as SFNO
+    from makani_b200.ops.optim import FusedAdamW
+    dev = _dev()
+
+    def run(native):
+        torch.manual_seed(77)
+        m = SFNO(inp_shape=(64, 128), out_shape=(64, 128), scale_factor=2, inp_chans=8, out_chans=8, embed_dim=32, num_layers=2).to(dev)
+        g = torch.Generator(device=dev)
+        g.manual_seed(5)
+        xs = [torch.randn(2, 8, 64, 128, device=dev, generator=g) for _ in range(4)]
+        ts = [0.5 * x.roll(3, dims=-1) + 0.1 * x ** 2 for x in xs]      # a learnable map
+        losses = []
+        if native:
+            m.set_compute_dtype(torch.bfloat16)
+            opt = FusedAdamW(m.parameters(), lr=2e-3, weight_decay=0.0)
+        else:
+            opt = torch.optim.AdamW(m.parameters(), lr=2e-3, weight_decay=0.0)
+        _ext.set_native(native)
+        try:
+            for it in range(50):
+                opt.zero_grad()
+                y = m(xs[it % 4])
+                loss = (y.float() - ts[it % 4]).square().mean()
+                loss.backward()
+                opt.step()
+                losses.append(float(loss))
+        finally:
+            _ext.set_native(True)
+        return torch.tensor(losses)
+
+    ref, nat = run(False), run(True)
+    _ext.check_device_errors(dev)
+    assert nat[-1] < 0.8 * nat[0], "the native run does not learn"
+    rel = ((nat - ref).abs() / ref).max().item()
+    print("loss curve: first", float(ref[0]), float(nat[0]), "last", float(ref[-1]), float(nat[-1]), "max rel diff", round(rel, 4))
+    assert rel < 5e-2, rel
 
 
 def test_swap_ri_and_two_block_weight_gradient():
