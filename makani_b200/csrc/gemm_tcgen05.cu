@@ -6,6 +6,8 @@
 //   warp 1      : TMEM allocator + MMA issuer (one elected lane)
 //   warps 2..9  : epilogue; warp w reads TMEM lanes [32*(w%4), 32*(w%4)+32), the two warps that share a lane
 //                 quarter take alternating column chunks
+//   warp 10     : only in launches whose epilogue operand (residual, saved pre-activation) is prefetched by TMA
+//                 (352 threads): its producer, so that waiting for a free operand buffer never delays A and B
 // Two accumulator buffers in TMEM let the epilogue of tile i overlap the main loop of tile i+1.
 // Every mbarrier wait is bounded; on expiry the kernel records a code in *err and drains.
 //
@@ -40,6 +42,7 @@ namespace {
 constexpr int BM = 128;
 constexpr int A_STAGE_BYTES = BM * 128;
 constexpr int NUM_THREADS = 320;   // TMA warp + MMA warp + 8 epilogue warps
+constexpr int E_WARP = 10;         // launches with a TMA-fed epilogue operand run an eleventh warp: its producer
 constexpr int MAX_STAGES = 6;
 constexpr int MAX_SEG = 8;
 
@@ -127,6 +130,10 @@ __device__ __forceinline__ uint64_t global_ns() {
   return t;
 }
 
+// The suspend-time hint lets the hardware park a waiting thread until the phase completes (it wakes at once when it
+// does) instead of returning to the polling loop every few dozen cycles: the three single-thread roles of a CTA spend
+// most of their time waiting, and their polling instructions competed with the epilogue warps for issue slots.
+constexpr uint32_t MBAR_SUSPEND_HINT_NS = 4000;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   uint64_t t0 = 0;
   for (uint32_t it = 0;; ++it) {
@@ -134,14 +141,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     asm volatile(
         "{\n\t"
         ".reg .pred P1;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2, %3;\n\t"
         "selp.b32 %0, 1, 0, P1;\n\t"
         "}\n"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(MBAR_SUSPEND_HINT_NS)
         : "memory");
     if (ok) return true;
-    if ((it & 1023u) == 1023u) {
+    if ((it & 63u) == 63u) {
       const uint64_t now = global_ns();
       if (t0 == 0) t0 = now;
       else if (now - t0 > WAIT_LIMIT_NS) return false;
@@ -258,6 +265,17 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
 // Shared-memory matrix descriptor, 128-byte swizzle, sm_100 version field = 1.
 __device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
   uint64_t d = 0;
@@ -343,7 +361,7 @@ __device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int* p
 }
 
 template <int BN, int EB, int EPI, int CG>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(NUM_THREADS + 32, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ BMaps maps_b,
             const __grid_constant__ CUtensorMap map_e, const __grid_constant__ CUtensorMap map_d,
             const __grid_constant__ CUtensorMap map_p, const __grid_constant__ DMaps maps_dx, const KParams p) {
@@ -520,11 +538,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
           }
         }
       }
-    } else if (lane == 1 && p.e_tma && peers_ready) {
-      // ---------------------------------------------------------------- producer of the epilogue operand
-      // A thread of its own: the tile of the residual / saved pre-activation for tile t+2 can only be requested when
-      // the epilogue of tile t has released its buffer.  Issued from the operand producer's loop, that wait held
-      // back the A and B loads of the tiles in between, and the tensor cores waited for a memory round trip per tile.
+    }
+  } else if (warp == E_WARP) {
+    // ------------------------------------------------------------------ producer of the epilogue operand
+    // A warp of its own: the tile of the residual / saved pre-activation for tile t+2 can only be requested when the
+    // epilogue of tile t has released its buffer.  Issued from the operand producer's loop, that wait held back the
+    // A and B loads of the tiles in between; issued from another lane of the producer warp, its polling held up that
+    // warp's TMA issue.
+    if (lane == 0 && p.e_tma && peers_ready) {
       if (p.sync.nwait > 0) asm volatile("fence.proxy.async;" ::: "memory");
       uint32_t epi_it = 0;
       for (long long t = tile0; t < p.total_tiles; t += tile_step) {
@@ -658,27 +679,32 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
         for (int bx = half; bx < BN / 64; bx += 2) {
           const int nb = n0 + bx * 64;
           if (nb >= p.N) break;
-          uint32_t v[64];
-          if (!c.skip) {
-            const uint32_t taddr = tmem_base + buf * BN + bx * 64 + (static_cast<uint32_t>(q * 32) << 16);
-            tmem_ld32(taddr, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
-            tmem_ld32(taddr + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
-          } else {
-#pragma unroll
-            for (int j = 0; j < 64; ++j) v[j] = 0u;
-          }
+          const uint32_t taddr = tmem_base + buf * BN + bx * 64 + (static_cast<uint32_t>(q * 32) << 16);
           // the staging box written two stores ago (one for the two-output epilogue) must have been read out
           if constexpr (EPI == 2 || ONE_BOX) tma_store_wait_read<0>();
           else tma_store_wait_read<1>();
           __syncwarp();
           uint8_t* const box_d = stg_ptr + (EPI == 2 ? 32 * 128 : (ONE_BOX ? 0 : sb * 32 * 128));
           uint8_t* const box_p = stg_ptr;
+          // The 64 columns of a box go through a ROLLED loop of four 16-column steps.  Unrolled, the body of one box ran
+          // to tens of KB of straight-line code per epilogue flavour, the eight epilogue warps (each at another place
+          // in it) missed the instruction caches on most fetches, and "no instruction" was their top stall reason.
+#pragma unroll 1
+          for (int it = 0; it < 4; ++it) {
+          uint32_t v[16];
+          if (!c.skip) {
+            tmem_ld16(taddr + it * 16, v);
+          } else {
 #pragma unroll
-          for (int g = 0; g < 8; ++g) {
+            for (int j = 0; j < 16; ++j) v[j] = 0u;
+          }
+#pragma unroll
+          for (int gg = 0; gg < 2; ++gg) {
+            const int g = it * 2 + gg;
             const int n = nb + g * 8;
             float f[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) f[j] = fmaf(__uint_as_float(v[g * 8 + j]), p.alpha, rbias);
+            for (int j = 0; j < 8; ++j) f[j] = fmaf(__uint_as_float(v[gg * 8 + j]), p.alpha, rbias);
             if (p.bias_mode == 2) {
               if (n + 8 <= p.N) {
                 const float4 b0 = __ldg(reinterpret_cast<const float4*>(bias_z + n));
@@ -734,6 +760,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
 #pragma unroll
             for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
             *reinterpret_cast<uint4*>(box_d + sw) = *reinterpret_cast<uint4*>(h);
+          }
           }
           fence_async_smem();
           __syncwarp();
@@ -904,7 +931,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
 
   // ------------------------------------------------------------------ teardown
   if constexpr (EPI != 0) {
-    if (warp >= 2 && lane == 0) {
+    if (warp >= 2 && warp < E_WARP && lane == 0) {
       tma_store_wait_all();
       asm volatile("fence.proxy.async;" ::: "memory");   // order the bulk stores before the generic-proxy signalling below
     }
@@ -1024,6 +1051,7 @@ cudaError_t launch_t(const CUtensorMap& ma, const BMaps& mb, const CUtensorMap& 
   }
   kp.stages = stages;
   const int smem = stages * STAGE + e_bytes + FIXED;
+  const int threads = kp.e_tma ? NUM_THREADS + 32 : NUM_THREADS;
   static bool configured = false;
   static int pair_clusters = 0;     // CTA pairs that can be resident at once (CG = 2)
   if (!configured) {
@@ -1038,7 +1066,7 @@ cudaError_t launch_t(const CUtensorMap& ma, const BMaps& mb, const CUtensorMap& 
       qa[0].val.clusterDim.y = 1;
       qa[0].val.clusterDim.z = 1;
       qc.gridDim = dim3(2 * (sm_count() / 2), 1, 1);
-      qc.blockDim = dim3(NUM_THREADS, 1, 1);
+      qc.blockDim = dim3(NUM_THREADS + 32, 1, 1);
       qc.dynamicSmemBytes = SMEM_LIMIT;
       qc.attrs = qa;
       qc.numAttrs = 1;
@@ -1070,7 +1098,7 @@ cudaError_t launch_t(const CUtensorMap& ma, const BMaps& mb, const CUtensorMap& 
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters), 1, 1);
-    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.blockDim = dim3(threads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cfg.attrs = attr;
@@ -1079,7 +1107,7 @@ cudaError_t launch_t(const CUtensorMap& ma, const BMaps& mb, const CUtensorMap& 
   }
   long long grid = kp.total_tiles < num_sms ? kp.total_tiles : num_sms;
   if (grid < 1) grid = 1;
-  gemm_kernel<BN, EB, EPI, CG><<<static_cast<unsigned>(grid), NUM_THREADS, smem, stream>>>(ma, mb, me, md, mp, mdx, kp);
+  gemm_kernel<BN, EB, EPI, CG><<<static_cast<unsigned>(grid), threads, smem, stream>>>(ma, mb, me, md, mp, mdx, kp);
   return cudaGetLastError();
 }
 
