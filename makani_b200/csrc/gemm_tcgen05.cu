@@ -251,15 +251,10 @@ __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t da, uint64_t db
   }
 }
 
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&v)[8]) {
   asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
       : "r"(taddr)
       : "memory");
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -676,6 +671,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
         const uint32_t stg_base = smem_base + stg_off + (warp - 2) * stg_warp_bytes(EPI);
         uint8_t* const stg_ptr = smem + stg_off + (warp - 2) * stg_warp_bytes(EPI);
         int sb = 0;
+#pragma unroll 1
         for (int bx = half; bx < BN / 64; bx += 2) {
           const int nb = n0 + bx * 64;
           if (nb >= p.N) break;
@@ -704,17 +700,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
             const int n = nb + g * 8;
             float f[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) f[j] = fmaf(__uint_as_float(v[gg * 8 + j]), p.alpha, rbias);
-            if (p.bias_mode == 2) {
+            for (int j = 0; j < 8; ++j) f[j] = rbias;
+            if (p.bias_mode == 2) {      // the column bias rides on the scaling fma below
               if (n + 8 <= p.N) {
                 const float4 b0 = __ldg(reinterpret_cast<const float4*>(bias_z + n));
                 const float4 b1 = __ldg(reinterpret_cast<const float4*>(bias_z + n) + 1);
-                f[0] += b0.x; f[1] += b0.y; f[2] += b0.z; f[3] += b0.w;
-                f[4] += b1.x; f[5] += b1.y; f[6] += b1.z; f[7] += b1.w;
+                f[0] = b0.x; f[1] = b0.y; f[2] = b0.z; f[3] = b0.w;
+                f[4] = b1.x; f[5] = b1.y; f[6] = b1.z; f[7] = b1.w;
               } else {
-                for (int j = 0; j < 8 && n + j < p.N; ++j) f[j] += __ldg(bias_z + n + j);
+                for (int j = 0; j < 8 && n + j < p.N; ++j) f[j] = __ldg(bias_z + n + j);
               }
             }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] = fmaf(__uint_as_float(v[gg * 8 + j]), p.alpha, f[j]);
             const uint32_t sw = static_cast<uint32_t>((g ^ (lane & 7)) << 4) + lane * 128;
             if constexpr (EPI == 1) {
               if (p.act != 0) {      // ReLU / soft shrinkage (uniform over the launch)
@@ -779,25 +777,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
           sb ^= 1;
         }
       } else
+#pragma unroll 1
       for (int cc = half; cc < BN / 32; cc += 2) {
         const int nc = n0 + cc * 32;
         if (nc >= p.N) break;       // uniform across the warp
-        uint32_t v[32];
-        if (!c.skip) {
-          const uint32_t taddr = tmem_base + buf * BN + cc * 32 + (static_cast<uint32_t>(q * 32) << 16);
-          tmem_ld32(taddr, v);
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = 0u;
-        }
-        if (!row_ok) continue;
-#pragma unroll
+        const uint32_t taddr = tmem_base + buf * BN + cc * 32 + (static_cast<uint32_t>(q * 32) << 16);
+        // rolled: one copy of the (large, many-layout) body serves the four 8-column groups, which keeps the
+        // epilogue within the instruction cache
+#pragma unroll 1
         for (int g = 0; g < 4; ++g) {
           const int n = nc + g * 8;
-          if (n >= p.N) break;
+          if (n >= p.N) break;      // uniform across the warp
+          uint32_t v[8];
+          if (!c.skip) {
+            tmem_ld8(taddr + g * 8, v);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = 0u;
+          }
+          if (!row_ok) continue;
           float f[8];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[g * 8 + j]) * p.alpha;
+          for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[j]) * p.alpha;
           if (p.bias_mode == 1) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) f[j] += rbias;

@@ -24,6 +24,9 @@ FLAG_BYTES = 128 * 9 * 4  # PEER_MAX_BLOCKS * (PEER_MAX + 1) * sizeof(uint32), s
 PEER_SKEW_SECONDS = float(os.environ.get("MAKANI_B200_PEER_SKEW_SECONDS", "120"))
 
 
+_DIAG_SELF = "selfar" in os.environ.get("MAKANI_B200_DP_DIAG", "").split(",")
+
+
 class SymmetricBuffer:
     """`nbytes` of device memory on every rank of `group`, mapped into every other rank."""
 
@@ -80,6 +83,10 @@ class SymmetricBuffer:
                 self.view(dtype, numel, byte_offset).mul_(scale)
             return
         ptrs = [self.ptrs[m] + byte_offset for m in members]
+        if _DIAG_SELF:
+            # diagnosis only (results are wrong): every "peer" is this rank's own buffer, so the kernel does the same
+            # work and handshakes without any NVLink traffic; tells link contention from SM / L2 / HBM contention
+            ptrs = [self.ptrs[self.rank] + byte_offset] * len(members)
         flags = [self.flag_ptrs[m] + flag_set * FLAG_BYTES for m in members]
         self.ext.peer_allreduce(ptrs, flags, my, int(numel), 1 if dtype == torch.bfloat16 else 0,
                                 float(scale), float(PEER_SKEW_SECONDS if wait_seconds is None else wait_seconds),
