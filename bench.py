@@ -209,8 +209,10 @@ def via_trainer(args):
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
+    on_gpu = torch.cuda.is_available()      # without a GPU only the plumbing runs (--tiny): not a bench value
+    if on_gpu:
+        torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank) if on_gpu else torch.device("cpu")
     mp = args.h * args.w * args.fin * args.fout
     dp = max(1, world // mp)
     recipe = "sfno_tiny" if args.tiny else "sfno_linear_73chq_sc3_layers8_edim384_bench"
@@ -225,7 +227,8 @@ def via_trainer(args):
     if not args.tiny:
         params["in_channels"] = list(range(len(params["channel_names"]) + 1))   # + the static cos(latitude) channel, delivered with the data
     params["n_train_samples_per_epoch"] = params["batch_size"] * dp * 2
-    _ext.require()
+    if on_gpu:
+        _ext.require()
     trainer = Trainer(params, world_rank)
     trainer._set_train()
     data = next(iter(trainer.train_dataloader))
@@ -233,29 +236,36 @@ def via_trainer(args):
 
     def barrier():
         if world > 1:
-            dist.barrier(device_ids=[local_rank])
-        torch.cuda.synchronize()
+            dist.barrier(device_ids=[local_rank] if on_gpu else None)
+        if on_gpu:
+            torch.cuda.synchronize()
 
     for _ in range(5 + args.warmup):
         loss = trainer._train_step(inp, tar)
     barrier()
-    sampler = ClockSampler(local_rank, _gpu_uuid(torch, local_rank))
-    sampler.start()
-    l0 = _ext.launch_count()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local_rank, _gpu_uuid(torch, local_rank)) if on_gpu else None
+    if sampler is not None:
+        sampler.start()
+    l0 = _ext.launch_count() if on_gpu else 0
+    if on_gpu:
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
-    ev0.record()
+    t0 = time.perf_counter()
+    if on_gpu:
+        ev0.record()
     for _ in range(args.steps):
         loss = trainer._train_step(inp, tar)
-    ev1.record()
+    if on_gpu:
+        ev1.record()
     barrier()
-    launches = _ext.launch_count() - l0
-    clocks = sampler.stop()
-    t = torch.tensor([ev0.elapsed_time(ev1)], dtype=torch.float64, device=dev)
+    launches = (_ext.launch_count() - l0) if on_gpu else 0
+    clocks = sampler.stop() if sampler is not None else None
+    t = torch.tensor([ev0.elapsed_time(ev1) if on_gpu else (time.perf_counter() - t0) * 1e3], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = t.item() / args.steps
-    _ext.check_device_errors(dev)
+    if on_gpu:
+        _ext.check_device_errors(dev)
     if world_rank == 0:
         print(json.dumps({
             "metric": "SFNO-73ch 721x1440 bf16 train samples/s", "value": params["batch_size"] * dp / (ms / 1e3), "unit": "samples/s",
@@ -281,10 +291,11 @@ def via_trainer(args):
         trainer.graph = None
         import gc
         gc.collect()
-        torch.cuda.synchronize()
-        from makani_b200.parallel import peer
-        peer.release_slots()
-        dist.barrier(device_ids=[local_rank])
+        if on_gpu:
+            torch.cuda.synchronize()
+            from makani_b200.parallel import peer
+            peer.release_slots()
+        dist.barrier(device_ids=[local_rank] if on_gpu else None)
         dist.destroy_process_group()
     return 0
 

@@ -5,9 +5,11 @@
 
 Per size and dtype: CUDA events around each call (after warm-up; the ranks are aligned by a barrier before every
 call), median over iterations, maximum over ranks.  Reported: algorithm bandwidth (bytes of the buffer / time), bus
-bandwidth (x 2(N-1)/N, the figure NCCL's tests quote) and the fraction of the two-shot kernel's own NVLink roofline:
-each rank pulls (N-1)/N of the buffer and pushes (N-1)/N of it, in opposite link directions, so the floor is
-(N-1)/N x bytes / 770 GB/s (measured peer-copy rate per direction).  These kernels handshake across GPUs, so they are
+bandwidth (x 2(N-1)/N, the figure NCCL's tests quote) and the fraction of the kernel's NVLink roofline.  Every rank
+reduces one slice: it pulls that slice from its N-1 peers and pushes the result to them.  Both the data a rank pulls and
+the results its peers push to it arrive on its ingress links, (N-1)/N of the buffer each, so the floor is
+2(N-1)/N x bytes / 770 GB/s (measured peer-copy rate per direction): the fraction is bus bandwidth / 770 GB/s.  These
+kernels handshake across GPUs, so they are
 timed with events and never put under a profiler's kernel replay.
 """
 
@@ -73,7 +75,7 @@ def main():
             t_nccl = _time(lambda: dist.all_reduce(w), args.iters, dev)
             _ext.check_device_errors(dev)
             b = mb * 1024 * 1024
-            floor = (world - 1) / world * b / NVLINK_BPS * 1e3
+            floor = 2 * (world - 1) / world * b / NVLINK_BPS * 1e3
             rows.append(dict(mb=mb, dtype=str(dtype).replace("torch.", ""), peer_ms=t_peer, nccl_ms=t_nccl,
                              peer_algbw_gbs=b / t_peer / 1e6, peer_busbw_gbs=b / t_peer / 1e6 * 2 * (world - 1) / world,
                              nccl_busbw_gbs=b / t_nccl / 1e6 * 2 * (world - 1) / world, roofline_ms=floor,
@@ -82,7 +84,7 @@ def main():
         print(json.dumps(dict(world=world, results=rows)))
         for r in rows:
             print(f"{r['mb']:5d} MB {r['dtype']:9s} peer {r['peer_ms']:7.3f} ms (bus {r['peer_busbw_gbs']:6.1f} GB/s, "
-                  f"{100 * r['fraction']:.0f}% of the 770 GB/s two-shot floor)   NCCL {r['nccl_ms']:7.3f} ms (bus {r['nccl_busbw_gbs']:6.1f} GB/s)")
+                  f"{100 * r['fraction']:.0f}% of the 770 GB/s ingress floor)   NCCL {r['nccl_ms']:7.3f} ms (bus {r['nccl_busbw_gbs']:6.1f} GB/s)")
     buf.close()
     dist.barrier()
     dist.destroy_process_group()
