@@ -61,6 +61,21 @@ def test_gemm_majors_bf16(a_mn, b_mn, shape, bn):
         assert _rel(got, ref) < 1e-2
 
 
+def test_gemm_rejects_addressing_outside_the_storage():
+    """The host checks the corner elements of A, B and the output before anything is launched."""
+    from makani_b200.ops.gemm import gemm
+    dev = _dev()
+    M, N, K = 256, 128, 64
+    a = torch.randn(M, K, device=dev).to(torch.bfloat16)
+    b = torch.randn(N, K, device=dev).to(torch.bfloat16)
+    small = torch.zeros(M - 1, N, device=dev, dtype=torch.bfloat16)      # one output row short
+    with pytest.raises(RuntimeError, match="leaves the tensor's storage"):
+        gemm(M, N, K, Operand(a, ld=K), Operand(b, ld=K), Output(small, rs_lo=N))
+    with pytest.raises(RuntimeError, match="leaves the tensor's storage"):
+        gemm(M, N, K, Operand(a, ld=K + 8), Operand(b, ld=K), Output(torch.zeros(M, N, device=dev, dtype=torch.bfloat16), rs_lo=N))
+    _ext.check_device_errors(dev)
+
+
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False)])
 def test_gemm_tf32(a_mn, b_mn):
     dev = _dev()
