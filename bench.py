@@ -224,8 +224,9 @@ def via_trainer(args):
     cargs = cli_common.base_parser("bench").parse_args(argv)
     params, world_rank = cli_common.bootstrap(cargs)
     params["log_to_screen"] = False
-    if not args.tiny:
-        params["in_channels"] = list(range(len(params["channel_names"]) + 1))   # + the static cos(latitude) channel, delivered with the data
+    # the 74th input channel of the headline model is the cosine of the solar zenith angle: the loader delivers it per
+    # time step and the preprocessor appends it to every (autoregressive) input, as in the reference's recipe
+    params["add_zenith"] = True
     params["n_train_samples_per_epoch"] = params["batch_size"] * dp * 2
     if on_gpu:
         _ext.require()
