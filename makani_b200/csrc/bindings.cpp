@@ -217,7 +217,11 @@ void gemm_impl(const Tensor& a, const Tensor& b, Tensor& d, const c10::optional<
   }
   e.alpha = static_cast<float>(alpha);
   e.bias_mode = ip[k++];
-  e.act = ip[k++];
+  {
+    const int64_t actw = ip[k++];     // low byte: activation code; bit 8: the second output holds the derivative
+    e.act = static_cast<int>(actw & 0xff);
+    e.save_deriv = static_cast<int>((actw >> 8) & 1);
+  }
   const int64_t resid_off = ip[k++];
   const int64_t preact_off = ip[k++];
   {

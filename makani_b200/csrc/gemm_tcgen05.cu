@@ -83,7 +83,7 @@ struct KParams {
   float alpha;
   const float* bias;
   long long bias_zs;              // elements between the bias vectors of consecutive z_lo batches (0: one shared vector)
-  int bias_mode, act;
+  int bias_mode, act, save_deriv;
   GeluCoef gelu;
   float act_param;
   const void* resid;
@@ -722,11 +722,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
             }
             if constexpr (EPI == 2) {
               __nv_bfloat162 h[4];
+              if (p.save_deriv) {      // uniform over the launch: second output = GELU'(pre-activation)
+                float d[8];
 #pragma unroll
-              for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
-              *reinterpret_cast<uint4*>(box_p + sw) = *reinterpret_cast<uint4*>(h);
+                for (int j = 0; j < 8; ++j) gelu_fwd_bwd(f[j], p.gelu, f[j], d[j]);
 #pragma unroll
-              for (int j = 0; j < 8; ++j) f[j] = gelu_fwd(f[j], p.gelu);
+                for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(d[2 * j], d[2 * j + 1]);
+                *reinterpret_cast<uint4*>(box_p + sw) = *reinterpret_cast<uint4*>(h);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+                *reinterpret_cast<uint4*>(box_p + sw) = *reinterpret_cast<uint4*>(h);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = gelu_fwd(f[j], p.gelu);
+              }
             }
             if constexpr (EPI == 3 || EPI == 4) {
               const uint4 ev = *reinterpret_cast<const uint4*>(esm + bx * (BM * 128) + rt * 128 + ((g ^ (rt & 7)) << 4));
@@ -737,6 +746,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
                   const float2 x = __bfloat1622float2(eh[j]);
                   f[2 * j] += x.x;
                   f[2 * j + 1] += x.y;
+                }
+              } else if (p.act == 8) {      // uniform over the launch: the operand is the saved derivative
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 x = __bfloat1622float2(eh[j]);
+                  f[2 * j] *= x.x;
+                  f[2 * j + 1] *= x.y;
                 }
               } else if (p.act == 2) {      // uniform over the launch: the GELU case carries no per-element selects
 #pragma unroll
@@ -827,14 +843,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
           if (full && p.vec_ok && !p.accumulate) {
             // ---- vector path: 8 consecutive columns
             if (p.preact) {
+              float s8[8];     // second output: the pre-activation, or GELU' of it
+#pragma unroll
+              for (int j = 0; j < 8; ++j) s8[j] = p.save_deriv ? gelu_bwd(f[j], p.gelu) : f[j];
               if (p.out_f32) {
                 float4* o = reinterpret_cast<float4*>(static_cast<float*>(p.preact) + off);
-                o[0] = make_float4(f[0], f[1], f[2], f[3]);
-                o[1] = make_float4(f[4], f[5], f[6], f[7]);
+                o[0] = make_float4(s8[0], s8[1], s8[2], s8[3]);
+                o[1] = make_float4(s8[4], s8[5], s8[6], s8[7]);
               } else {
                 __nv_bfloat162 h[4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+                for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(s8[2 * j], s8[2 * j + 1]);
                 *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.preact) + off) = *reinterpret_cast<uint4*>(h);
               }
             }
@@ -889,8 +908,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ B
               const long long o = row_off + static_cast<long long>(nj / p.ndiv) * p.ns_hi + (nj % p.ndiv);
               float x = f[j];
               if (p.preact) {
-                if (p.out_f32) static_cast<float*>(p.preact)[o] = x;
-                else static_cast<__nv_bfloat16*>(p.preact)[o] = __float2bfloat16(x);
+                const float sx = p.save_deriv ? gelu_bwd(x, p.gelu) : x;
+                if (p.out_f32) static_cast<float*>(p.preact)[o] = sx;
+                else static_cast<__nv_bfloat16*>(p.preact)[o] = __float2bfloat16(sx);
               }
               if (p.act & 1) x = act_fwd(x, p.act, p.act_param, p.gelu);
               if (p.accumulate) {
@@ -1387,7 +1407,7 @@ cudaError_t gemm_launch(const GemmProblem& p, const GemmOperand& A, const GemmOp
   kp.d_zlo = e.d_zlo; kp.d_zhi = e.d_zhi;
   kp.rdiv = e.rdiv > 0 ? e.rdiv : 1 << 30; kp.rs_hi = e.rs_hi; kp.rs_lo = e.rs_lo;
   kp.ndiv = e.ndiv > 0 ? e.ndiv : 1 << 30; kp.ns_hi = e.ns_hi;
-  kp.alpha = e.alpha; kp.bias = e.bias; kp.bias_zs = e.bias ? e.bias_zs : 0; kp.bias_mode = e.bias ? e.bias_mode : 0; kp.act = e.act; kp.gelu = gelu_coef(gelu_tanh()); kp.act_param = e.act_param;
+  kp.alpha = e.alpha; kp.bias = e.bias; kp.bias_zs = e.bias ? e.bias_zs : 0; kp.bias_mode = e.bias ? e.bias_mode : 0; kp.act = e.act; kp.save_deriv = (e.save_deriv && e.act == 1 && e.preact) ? 1 : 0; kp.gelu = gelu_coef(gelu_tanh()); kp.act_param = e.act_param;
   kp.resid = e.resid; kp.preact = e.preact; kp.D = e.D;
   kp.out_f32 = e.out_f32; kp.accumulate = e.accumulate;
   // 16-byte vector accesses need every stride (and the bases) aligned
@@ -1485,7 +1505,7 @@ cudaError_t gemm_launch(const GemmProblem& p, const GemmOperand& A, const GemmOp
     if (!e.resid && !e.preact && (e.act == 0 || e.act == 3 || e.act == 5)) epi = 1;
     else if (!e.resid && e.preact && e.act == 1) epi = 2;
     else if (e.resid && kp.e_tma && !e.preact && e.act == 0) epi = 3;
-    else if (e.resid && kp.e_tma && !e.preact && (e.act == 2 || e.act == 4 || e.act == 6)) epi = 4;
+    else if (e.resid && kp.e_tma && !e.preact && (e.act == 2 || e.act == 4 || e.act == 6 || e.act == 8)) epi = 4;
     if (epi != 0) {
       bool ok = make_map_e(&md, e.D, p.M, p.N, e.rs_lo, e.d_zlo, e.d_zhi, p.zlo_n, p.zhi_n, bn, 32);
       if (ok && epi == 2) ok = make_map_e(&mp, e.preact, p.M, p.N, e.rs_lo, e.d_zlo, e.d_zhi, p.zlo_n, p.zhi_n, bn, 32);

@@ -42,7 +42,10 @@ struct GemmEpilogue {
   int bias_mode;        // 1: per row r, 2: per column n
   long long bias_zs;    // elements between the bias vectors of consecutive z_lo batches (0: one vector for all)
   int act;              // 0 none; 1 GELU, 3 ReLU, 5 soft shrinkage (threshold act_param); 2 / 4 / 6: multiply by the
-                        // derivative of GELU / ReLU / soft shrinkage evaluated at `resid` (see gelu.cuh)
+                        // derivative of GELU / ReLU / soft shrinkage evaluated at `resid`; 8: multiply by `resid`
+                        // itself (see gelu.cuh)
+  int save_deriv;       // act == 1 with a second output: that output receives GELU'(pre-activation) instead of the
+                        // pre-activation, so that the backward pass multiplies by it (act 8) without evaluating anything
   float act_param;
   const void* resid;    // optional tensor added after the activation (odd act or 0), or the operand of the derivative
                         // (even act: saved pre-activation for GELU, saved output for ReLU / shrinkage); same

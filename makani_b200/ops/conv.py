@@ -22,7 +22,7 @@ from typing import Optional
 import torch
 
 from . import _ext
-from .gemm import ACT_DGELU, ACT_GELU, ACT_NONE, BIAS_COL, BIAS_ROW, Operand, Output, gemm, pad_to
+from .gemm import ACT_GELU, ACT_MULAUX, ACT_NONE, BIAS_COL, BIAS_ROW, Operand, Output, gemm, pad_to
 
 NCHW, CL = "nchw", "cl"
 
@@ -95,9 +95,10 @@ def _out(y, lay):
     return Output(y, rs_lo=T, d_zlo=C * T)          # rows = channels
 
 
-def _conv_fwd(x, wq, ci, bias, act, resid, want_preact, out_layout=None, out=None, sync=None, dests=None):
+def _conv_fwd(x, wq, ci, bias, act, resid, want_preact, out_layout=None, out=None, sync=None, dests=None, deriv=False):
     """`out` (optional) receives the result instead of a fresh tensor; `sync` / `dests` are handed to the GEMM
-    (handshake descriptor and additional copies of the output buffer in peers' memory)."""
+    (handshake descriptor and additional copies of the output buffer in peers' memory).  With `deriv` the second
+    output holds GELU'(pre-activation) instead of the pre-activation."""
     B, C, H, W = x.shape
     assert C == ci
     T = H * W
@@ -111,10 +112,10 @@ def _conv_fwd(x, wq, ci, bias, act, resid, want_preact, out_layout=None, out=Non
     wop = Operand(wq, ld=wq.shape[1])
     if out_layout == CL:
         gemm(T, co, ci, _tok_rows(x, lay), wop, _out(y, CL), zlo_n=B, bias=bias, bias_mode=BIAS_COL, act=act,
-             resid=resid, preact=pre, sync=sync, dests=dests)
+             resid=resid, preact=pre, sync=sync, dests=dests, preact_deriv=deriv)
     else:
         gemm(co, T, ci, wop, _tok_rows(x, lay), _out(y, NCHW), zlo_n=B, bias=bias, bias_mode=BIAS_ROW, act=act,
-             resid=resid, preact=pre, sync=sync, dests=dests)
+             resid=resid, preact=pre, sync=sync, dests=dests, preact_deriv=deriv)
     return y, pre
 
 
@@ -203,9 +204,10 @@ class _MLP2(torch.autograd.Function):
         b1f = b1.detach().float().contiguous() if b1 is not None else None
         b2f = b2.detach().float().contiguous() if b2 is not None else None
         hid_layout = CL if ch % 8 == 0 else NCHW
-        h, pre = _conv_fwd(x, w1q, ci, b1f, ACT_GELU, None, want_preact=True, out_layout=hid_layout)
+        # the first GEMM's second output is GELU'(pre-activation): the backward epilogue then only multiplies
+        h, dact = _conv_fwd(x, w1q, ci, b1f, ACT_GELU, None, want_preact=True, out_layout=hid_layout, deriv=True)
         y, _ = _conv_fwd(h, w2q, ch, b2f, ACT_NONE, resid, want_preact=False, out_layout=out_layout)
-        ctx.save_for_backward(x, w1q, w2q, pre, h)
+        ctx.save_for_backward(x, w1q, w2q, dact, h)
         ctx.dims = (ci, ch)
         ctx.flags = (b1 is not None, b2 is not None, resid is not None)
         ctx.wshapes = (w1.shape, w2.shape)
@@ -213,11 +215,11 @@ class _MLP2(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        x, w1q, w2q, pre, h = ctx.saved_tensors
+        x, w1q, w2q, dact, h = ctx.saved_tensors
         ci, ch = ctx.dims
         has_b1, has_b2, has_res = ctx.flags
         dy = _canon(dy)
-        dpre = _conv_dgrad(dy, w2q, ch, act=ACT_DGELU, aux=pre, x_layout=layout_of(pre))
+        dpre = _conv_dgrad(dy, w2q, ch, act=ACT_MULAUX, aux=dact, x_layout=layout_of(dact))
         dw2 = _conv_wgrad(dy, h).reshape(ctx.wshapes[1])
         db2 = _chan_sum(dy) if has_b2 else None
         dx = _conv_dgrad(dpre, w1q, ci, x_layout=layout_of(x)) if ctx.needs_input_grad[0] else None

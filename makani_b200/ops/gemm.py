@@ -19,6 +19,7 @@ import torch
 from . import _ext
 
 ACT_NONE, ACT_GELU, ACT_DGELU, ACT_RELU, ACT_DRELU, ACT_SHRINK, ACT_DSHRINK = 0, 1, 2, 3, 4, 5, 6
+ACT_MULAUX = 8      # multiply by the epilogue operand itself (a derivative saved by the forward pass: `preact_deriv`)
 BIAS_NONE, BIAS_ROW, BIAS_COL = 0, 1, 2
 _BIG = 1 << 30
 
@@ -94,8 +95,19 @@ def _flat(t: torch.Tensor) -> torch.Tensor:
     return t.as_strided((n,), (1,))
 
 
+def _gelu_derivative(x: torch.Tensor) -> torch.Tensor:
+    if _ext.gelu_approximation() == "tanh":
+        u = 0.7978845608028654 * (x + 0.044715 * x ** 3)
+        t = torch.tanh(u)
+        return 0.5 * (1.0 + t) + 0.5 * x * (1.0 - t * t) * 0.7978845608028654 * (1.0 + 3 * 0.044715 * x * x)
+    cdf = 0.5 * (1.0 + torch.erf(x * 0.7071067811865476))
+    pdf = torch.exp(-0.5 * x * x) * 0.3989422804014327
+    return cdf + x * pdf
+
+
 def _emulate(M, N, K, A: Operand, B: Operand, D: Output, zlo_n, zhi_n, alpha, bias, bias_mode, act, resid, resid_offset,
-             preact, preact_offset, accumulate, tri: Tri, segments=None, act_param: float = 0.0, bias_zs: int = 0):
+             preact, preact_offset, accumulate, tri: Tri, segments=None, act_param: float = 0.0, bias_zs: int = 0,
+             preact_deriv: bool = False):
     fa, fb, fd = _flat(A.tensor), _flat(B.tensor), _flat(D.tensor)
     cdt = torch.float64 if fa.dtype == torch.float64 else torch.float32
 
@@ -137,7 +149,8 @@ def _emulate(M, N, K, A: Operand, B: Operand, D: Output, zlo_n, zhi_n, alpha, bi
            + (n // D.ndiv) * D.ns_hi + (n % D.ndiv))
     idx = idx.expand(zhi_n, zlo_n, M, N).reshape(-1)
     if preact is not None:
-        _flat(preact).index_put_((idx - D.offset + preact_offset,), acc.reshape(-1).to(preact.dtype))
+        second = _gelu_derivative(acc) if (preact_deriv and act == ACT_GELU) else acc
+        _flat(preact).index_put_((idx - D.offset + preact_offset,), second.reshape(-1).to(preact.dtype))
     if act == ACT_GELU:
         acc = torch.nn.functional.gelu(acc, approximate=_ext.gelu_approximation())
     elif act == ACT_RELU:
@@ -151,15 +164,9 @@ def _emulate(M, N, K, A: Operand, B: Operand, D: Output, zlo_n, zhi_n, alpha, bi
         elif act == ACT_DSHRINK:
             acc = acc * (rv != 0).to(cdt)
         elif act == ACT_DGELU:
-            x = rv
-            if _ext.gelu_approximation() == "tanh":
-                u = 0.7978845608028654 * (x + 0.044715 * x ** 3)
-                t = torch.tanh(u)
-                acc = acc * (0.5 * (1.0 + t) + 0.5 * x * (1.0 - t * t) * 0.7978845608028654 * (1.0 + 3 * 0.044715 * x * x))
-            else:
-                cdf = 0.5 * (1.0 + torch.erf(x * 0.7071067811865476))
-                pdf = torch.exp(-0.5 * x * x) * 0.3989422804014327
-                acc = acc * (cdf + x * pdf)
+            acc = acc * _gelu_derivative(rv)
+        elif act == ACT_MULAUX:
+            acc = acc * rv
         else:
             acc = acc + rv
     vals = acc.reshape(-1).to(fd.dtype)
@@ -173,19 +180,24 @@ def gemm(M: int, N: int, K: int, A: Operand, B: Operand, D: Output, *, zlo_n: in
          bias: Optional[torch.Tensor] = None, bias_mode: int = BIAS_NONE, act: int = ACT_NONE,
          resid: Optional[torch.Tensor] = None, resid_offset: int = 0, preact: Optional[torch.Tensor] = None,
          preact_offset: int = 0, accumulate: bool = False, splits: int = 1, tri: Optional[Tri] = None, bn: int = 0,
-         segments=None, sync=None, dests=None, act_param: float = 0.0, bias_zs: int = 0) -> None:
+         segments=None, sync=None, dests=None, act_param: float = 0.0, bias_zs: int = 0,
+         preact_deriv: bool = False) -> None:
     """Run the batched GEMM described above, writing into `D.tensor` in place.
 
     `segments` (list of `Segment`) spreads the k axis of B over several devices: `K` is then the padded k extent
     of A and `B.tensor` only supplies dtype and strides.  `sync` is the 31-entry handshake descriptor built by
     `makani_b200.parallel.peer.sync_descriptor` (CUDA only).  `dests` lists device addresses of additional copies of
-    the output buffer (peers' memory) that receive the same bf16 stores as `D.tensor`."""
+    the output buffer (peers' memory) that receive the same bf16 stores as `D.tensor`.
+
+    `preact` receives the value before the activation; with `preact_deriv` (act = ACT_GELU only) it receives GELU' of
+    that value instead, which the backward pass multiplies in with `act=ACT_MULAUX, resid=<that tensor>`."""
     tri = tri or Tri()
+    assert not preact_deriv or (act == ACT_GELU and preact is not None)
     if bias is None:
         bias_mode = BIAS_NONE
     if not A.tensor.is_cuda:
         _emulate(M, N, K, A, B, D, zlo_n, zhi_n, alpha, bias, bias_mode, act, resid, resid_offset, preact, preact_offset,
-                 accumulate, tri, segments, act_param, bias_zs)
+                 accumulate, tri, segments, act_param, bias_zs, preact_deriv)
         return
     ext = _ext.require()
     ip = [M, N, K, zlo_n, zhi_n, splits, bn,
@@ -193,7 +205,7 @@ def gemm(M: int, N: int, K: int, A: Operand, B: Operand, D: Output, *, zlo_n: in
           A.offset, int(A.mn_major), A.ld, A.zs_lo, A.zs_hi,
           B.offset, int(B.mn_major), B.ld, B.zs_lo, B.zs_hi,
           D.offset, int(accumulate), D.d_zlo, D.d_zhi, D.rdiv, D.rs_hi, D.rs_lo, D.ndiv, D.ns_hi,
-          bias_mode, act, resid_offset, preact_offset, _f32_bits(act_param), int(bias_zs)]
+          bias_mode, act | (256 if preact_deriv else 0), resid_offset, preact_offset, _f32_bits(act_param), int(bias_zs)]
     if segments or sync or dests:
         seg = []
         if segments and len(segments) > 1:

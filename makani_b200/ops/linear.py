@@ -9,7 +9,7 @@ from __future__ import annotations
 import torch
 
 from . import _ext
-from .gemm import ACT_DGELU, ACT_GELU, ACT_NONE, BIAS_COL, Operand, Output, gemm, pad_to
+from .gemm import ACT_GELU, ACT_MULAUX, ACT_NONE, BIAS_COL, Operand, Output, gemm, pad_to
 
 
 def fast_path_ok(x: torch.Tensor) -> bool:
@@ -20,12 +20,13 @@ def _wq(w):
     return w.detach().to(torch.bfloat16).contiguous()
 
 
-def _lin_fwd(x2, wq, bias, act, want_pre):
+def _lin_fwd(x2, wq, bias, act, want_pre, deriv=False):
     T, C = x2.shape
     O = wq.shape[0]
     y = torch.empty(T, O, dtype=torch.bfloat16, device=x2.device)
     pre = torch.empty_like(y) if want_pre else None
-    gemm(T, O, C, Operand(x2, ld=C), Operand(wq, ld=C), Output(y, rs_lo=O), bias=bias, bias_mode=BIAS_COL, act=act, preact=pre)
+    gemm(T, O, C, Operand(x2, ld=C), Operand(wq, ld=C), Output(y, rs_lo=O), bias=bias, bias_mode=BIAS_COL, act=act, preact=pre,
+         preact_deriv=deriv)
     return y, pre
 
 
@@ -58,18 +59,18 @@ class _MLP2Last(torch.autograd.Function):
         w1q, w2q = _wq(w1), _wq(w2)
         b1f = b1.detach().float().contiguous() if b1 is not None else None
         b2f = b2.detach().float().contiguous() if b2 is not None else None
-        h, pre = _lin_fwd(x2, w1q, b1f, ACT_GELU, True)
+        h, dact = _lin_fwd(x2, w1q, b1f, ACT_GELU, True, deriv=True)     # second output: GELU'(pre-activation)
         y, _ = _lin_fwd(h, w2q, b2f, ACT_NONE, False)
-        ctx.save_for_backward(x2, w1q, w2q, pre, h)
+        ctx.save_for_backward(x2, w1q, w2q, dact, h)
         ctx.flags = (b1 is not None, b2 is not None)
         ctx.shp = shp
         return y.reshape(*shp[:-1], w2.shape[0])
 
     @staticmethod
     def backward(ctx, dy):
-        x2, w1q, w2q, pre, h = ctx.saved_tensors
+        x2, w1q, w2q, dact, h = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
-        dpre = _lin_dgrad(dy2, w2q, act=ACT_DGELU, aux=pre)
+        dpre = _lin_dgrad(dy2, w2q, act=ACT_MULAUX, aux=dact)
         dw2 = _lin_wgrad(dy2, h)
         db2 = dy2.float().sum(0) if ctx.flags[1] else None
         dx = _lin_dgrad(dpre, w1q).reshape(ctx.shp) if ctx.needs_input_grad[0] else None

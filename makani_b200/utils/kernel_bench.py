@@ -19,7 +19,7 @@ import torch
 
 from ..ops import _ext
 from ..ops.conv import _conv_dgrad, _conv_fwd, _conv_wgrad, prep_weight
-from ..ops.gemm import ACT_DGELU, ACT_GELU, ACT_NONE, Operand, Output, gemm
+from ..ops.gemm import ACT_DGELU, ACT_GELU, ACT_MULAUX, ACT_NONE, Operand, Output, gemm
 
 
 def _peaks():
@@ -55,28 +55,30 @@ def cases(H, W, dev, B=1, layout="cl"):
     out = {}
     lay = (lambda t: t.contiguous(memory_format=torch.channels_last)) if layout == "cl" else (lambda t: t)
 
-    def conv_case(ci, co, act, preact, resid):
+    def conv_case(ci, co, act, preact, resid, deriv=False):
         x = lay(torch.randn(B, ci, H, W, device=dev).to(bf))
         w = prep_weight(torch.randn(co, ci, device=dev) * 0.05)
         b = torch.zeros(co, device=dev)
         r = lay(torch.randn(B, co, H, W, device=dev).to(bf)) if resid else None
         nbytes = (ci + co * (2 if preact else 1) + (co if resid else 0)) * hw * 2
         flops = 2.0 * ci * co * hw
-        return (lambda: _conv_fwd(x, w, ci, b, act, r, preact)), nbytes, flops
+        return (lambda: _conv_fwd(x, w, ci, b, act, r, preact, deriv=deriv)), nbytes, flops
 
-    out["conv_fc1"] = lambda: conv_case(C, C2, ACT_GELU, True, False)          # MLP fc1: bias + GELU + saved pre-activation
+    out["conv_fc1"] = lambda: conv_case(C, C2, ACT_GELU, True, False, deriv=True)   # MLP fc1: bias + GELU + saved GELU'
+    out["conv_fc1_pre"] = lambda: conv_case(C, C2, ACT_GELU, True, False)      # same with the pre-activation saved instead
     out["conv_fc2"] = lambda: conv_case(C2, C, ACT_NONE, False, False)         # MLP fc2
     out["conv_skip"] = lambda: conv_case(C, C, ACT_NONE, False, True)          # outer skip with fused residual add
     out["conv_plain"] = lambda: conv_case(C, C, ACT_NONE, False, False)
 
-    def dgrad_gelu():
+    def dgrad_gelu(act):
         dy = lay(torch.randn(1, C, H, W, device=dev).to(bf))
         w = prep_weight(torch.randn(C, C2, device=dev) * 0.05)
         pre = lay(torch.randn(1, C2, H, W, device=dev).to(bf))
         nbytes = (C + 2 * C2) * hw * 2
-        return (lambda: _conv_dgrad(dy, w, C2, act=ACT_DGELU, aux=pre)), nbytes, 2.0 * C * C2 * hw
+        return (lambda: _conv_dgrad(dy, w, C2, act=act, aux=pre)), nbytes, 2.0 * C * C2 * hw
 
-    out["conv_dgrad_gelu"] = dgrad_gelu
+    out["conv_dgrad_gelu"] = lambda: dgrad_gelu(ACT_MULAUX)      # what the MLP runs: times the saved GELU'
+    out["conv_dgrad_gelu_eval"] = lambda: dgrad_gelu(ACT_DGELU)  # GELU' evaluated from a saved pre-activation
 
     def wgrad():
         dy = lay(torch.randn(1, C, H, W, device=dev).to(bf))

@@ -6,7 +6,7 @@ import pytest
 import torch
 
 from makani_b200.ops import _ext
-from makani_b200.ops.gemm import (ACT_DGELU, ACT_GELU, ACT_NONE, BIAS_COL, BIAS_ROW, Operand, Output, Tri, _emulate,
+from makani_b200.ops.gemm import (ACT_DGELU, ACT_GELU, ACT_MULAUX, ACT_NONE, BIAS_COL, BIAS_ROW, Operand, Output, Tri, _emulate,
                                   gemm)
 
 pytestmark = pytest.mark.gpu
@@ -204,6 +204,45 @@ def test_gemm_cta_pairs_epilogues_ragged():
                                  resid=res if use_res else None, preact=pre, bn=bn)
                 for got, ref in outs:
                     assert _rel(got, ref) < 1e-2, (N, bn, act, use_res)
+
+
+def test_gemm_saved_gelu_derivative_and_multiply():
+    """The forward epilogue that saves GELU'(pre-activation) in its second output, and the backward epilogue that only
+    multiplies by it: token-major shapes (TMA-store epilogues, single CTAs and pairs, ragged edges) and a strided
+    channel-major layout (generic epilogue), each against the fp32 emulation."""
+    dev = _dev()
+    torch.manual_seed(23)
+    Z, M = 2, 1000
+    for K, N in ((384, 200), (520, 384)):
+        x = torch.randn(Z, M, K, device=dev).to(torch.bfloat16)
+        w = (torch.randn(N, K, device=dev) * 0.05).to(torch.bfloat16)
+        bias = torch.randn(N, device=dev)
+        d = torch.zeros(Z, M, N, device=dev, dtype=torch.bfloat16)
+        sec = torch.zeros_like(d)
+        outs = _run_both(M, N, K, Operand(x, ld=K, zs_lo=M * K), Operand(w, ld=K), Output(d, rs_lo=N, d_zlo=M * N), zlo_n=Z,
+                         bias=bias, bias_mode=BIAS_COL, act=ACT_GELU, preact=sec, preact_deriv=True)
+        for got, ref in outs:
+            assert _rel(got, ref) < 1e-2, (K, N)
+        # backward flavour: (dy W) * saved derivative
+        dy = torch.randn(Z, M, K, device=dev).to(torch.bfloat16)
+        dd = torch.zeros(Z, M, N, device=dev, dtype=torch.bfloat16)
+        outs = _run_both(M, N, K, Operand(dy, ld=K, zs_lo=M * K), Operand(w, ld=K), Output(dd, rs_lo=N, d_zlo=M * N), zlo_n=Z,
+                         act=ACT_MULAUX, resid=sec)
+        for got, ref in outs:
+            assert _rel(got, ref) < 1e-2, (K, N)
+    # channel-major output with a row bias: the generic epilogue
+    Mc, Nc, Kc = 96, 520, 80
+    wc = torch.randn(Mc, Kc, device=dev).to(torch.bfloat16)
+    xc = torch.randn(Z, Kc, Nc, device=dev).to(torch.bfloat16)
+    bc = torch.randn(Mc, device=dev)
+    dc = torch.zeros(Z, Mc, Nc, device=dev, dtype=torch.bfloat16)
+    sc = torch.zeros_like(dc)
+    outs = _run_both(Mc, Nc, Kc, Operand(wc, ld=Kc), Operand(xc, ld=Nc, mn_major=True, zs_lo=Kc * Nc),
+                     Output(dc, rs_lo=Nc, d_zlo=Mc * Nc), zlo_n=Z, bias=bc, bias_mode=BIAS_ROW, act=ACT_GELU, preact=sc,
+                     preact_deriv=True)
+    for got, ref in outs:
+        assert _rel(got, ref) < 1e-2
+    _ext.check_device_errors(dev)
 
 
 def test_gemm_headline_token_count():
