@@ -8,7 +8,7 @@ import pytest
 import torch
 
 from makani_b200.ops import conv as C
-from makani_b200.ops.gemm import ACT_DGELU, ACT_GELU, ACT_NONE, BIAS_ROW, Operand, Output, Tri, gemm
+from makani_b200.ops.gemm import ACT_DGELU, ACT_GELU, ACT_MULAUX, ACT_NONE, BIAS_ROW, Operand, Output, Tri, gemm
 from makani_b200.ops.optim import FusedAdamW
 from makani_b200.ops.spectral import expand_weight, fold_weight_grad
 
@@ -31,6 +31,30 @@ def test_emulated_gemm_majors_batches_and_scatter():
     acc = torch.ones(2 * M, N)
     gemm(2 * M, N, K, Operand(a2, ld=K), Operand(b2, ld=K), Output(acc, rs_lo=N), accumulate=True)
     assert torch.allclose(acc, 1.0 + a2 @ b2.t(), atol=1e-5)
+
+
+def test_emulated_gemm_saved_gelu_derivative_matches_autograd():
+    """`preact_deriv` stores d gelu / d pre in the second output; multiplying an upstream gradient by it (ACT_MULAUX)
+    gives what autograd gives through gelu, and what ACT_DGELU gives from a saved pre-activation."""
+    torch.manual_seed(3)
+    M, N, K = 6, 9, 5
+    a, b, bias = torch.randn(M, K), torch.randn(N, K), torch.randn(M)
+    y, dact, pre = torch.zeros(M, N), torch.zeros(M, N), torch.zeros(M, N)
+    gemm(M, N, K, Operand(a, ld=K), Operand(b, ld=K), Output(y, rs_lo=N), bias=bias, bias_mode=BIAS_ROW, act=ACT_GELU,
+         preact=dact, preact_deriv=True)
+    gemm(M, N, K, Operand(a, ld=K), Operand(b, ld=K), Output(torch.zeros(M, N), rs_lo=N), bias=bias, bias_mode=BIAS_ROW,
+         act=ACT_GELU, preact=pre)
+    z = (a @ b.t() + bias[:, None]).requires_grad_()
+    yr = torch.nn.functional.gelu(z)
+    assert torch.allclose(y, yr.detach(), atol=1e-5) and torch.allclose(pre, z.detach(), atol=1e-5)
+    # upstream gradient g = u v^T through both backward flavours
+    u, v = torch.randn(M, 1), torch.randn(N, 1)
+    g = u @ v.t()
+    (dz,) = torch.autograd.grad(yr, z, g)
+    out1, out2 = torch.zeros(M, N), torch.zeros(M, N)
+    gemm(M, N, 1, Operand(u, ld=1), Operand(v, ld=1), Output(out1, rs_lo=N), act=ACT_MULAUX, resid=dact)
+    gemm(M, N, 1, Operand(u, ld=1), Operand(v, ld=1), Output(out2, rs_lo=N), act=ACT_DGELU, resid=pre)
+    assert torch.allclose(out1, dz, atol=1e-5) and torch.allclose(out2, dz, atol=1e-5)
 
 
 @pytest.mark.parametrize("x_cl", [False, True])
