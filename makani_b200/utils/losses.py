@@ -7,8 +7,8 @@ differently on purpose:
 * The spatial integrals run as one fused reduction kernel over the *local* tile followed by an all-reduce of
   the per-channel partial integrals over the `spatial` group.  The reference all-gathers prediction and target
   over `h` then `w` on every rank first (losses.py:137-159), which materialises the full field everywhere.
-* Quadrature selection compares the grid type with "legendre-gauss" (the reference compares with the
-  misspelt "legendre_gauss", so its Gauss rule is never selected).
+* Quadrature selection accepts the grid type "legendre-gauss" as well as "legendre_gauss" (the reference compares
+  with the latter spelling only, so with the spelling its recipes use its Gauss rule is never selected).
 """
 
 from __future__ import annotations
@@ -165,7 +165,9 @@ class LossHandler(nn.Module):
             cw = cw * tw.float()
         self.register_buffer("channel_weights", cw.float(), persistent=False)
 
-        rule = "legendre-gauss" if params.get("model_grid_type", "equiangular") == "legendre-gauss" else "naive"
+        rule = "legendre-gauss" if params.get("model_grid_type", "equiangular") in ("legendre-gauss", "legendre_gauss") else "naive"
+        if "geometric" not in tokens:
+            rule = "naive"      # the plain l1 / l2 names never use the Gauss rule (losses.py:110-121 of the reference)
         geo = dict(local_shape=local_shape, local_offset=local_offset, pole_mask=pole_mask)
         if "l2" in tokens:
             self.loss_obj = GeometricLpLoss(self.img_shape, self.crop_shape, self.crop_offset, p=2, absolute=absolute,

@@ -1,0 +1,269 @@
+"""Worker of tests/test_reference_parity.py: builds a network of the unmodified upstream package (installed under
+`baseline/_ref`, third-party packages stood in for by `baseline/shims`) and the same network of this framework from the
+same keyword arguments, loads the upstream state dict into this framework's network (strictly) and compares forward
+output and every gradient on CPU in fp32.  Runs in a process of its own because the repository also ships an alias
+package named `makani`.  Prints one JSON line per case."""
+
+import json
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+sys.path.insert(0, os.path.join(ROOT, "baseline", "shims"))
+
+import importlib
+import warnings
+
+warnings.filterwarnings("ignore")
+
+import torch
+
+SFNO = dict(inp_shape=(32, 64), out_shape=(32, 64), scale_factor=1, inp_chans=4, out_chans=3, embed_dim=16, num_layers=2,
+            model_grid_type="equiangular", sht_grid_type="legendre-gauss", hard_thresholding_fraction=1.0, use_mlp=True,
+            activation_function="gelu", encoder_layers=1, pos_embed="none", big_skip=True)
+
+CASES = {
+    "sfno_dhconv_instance_norm": ("sfnonet", "SphericalFourierNeuralOperatorNet", dict(SFNO, operator_type="dhconv", normalization_layer="instance_norm"), (32, 64), 4),
+    "sfno_dhconv_scale2_layer_norm": ("sfnonet", "SphericalFourierNeuralOperatorNet",
+                                      dict(SFNO, operator_type="dhconv", normalization_layer="layer_norm", scale_factor=2, pos_embed="direct"), (32, 64), 4),
+    # 33 latitudes: the upstream diagonal operator can only be built when the two mode counts agree
+    "sfno_diagonal": ("sfnonet", "SphericalFourierNeuralOperatorNet",
+                      dict(SFNO, inp_shape=(33, 64), out_shape=(33, 64), operator_type="diagonal", normalization_layer="none"), (33, 64), 4),
+    "fno": ("sfnonet", "FourierNeuralOperatorNet", dict(SFNO, operator_type="dhconv", normalization_layer="instance_norm"), (32, 64), 4),
+    "afno_v1": ("afnonet", "AdaptiveFourierNeuralOperatorNet",
+                dict(inp_shape=(32, 64), patch_size=(4, 4), inp_chans=4, out_chans=3, embed_dim=32, num_layers=2, num_blocks=4), (32, 64), 4),
+    "afno_v2": ("afnonet_v2", "AdaptiveFourierNeuralOperatorNet",
+                dict(inp_shape=(32, 64), patch_size=(4, 4), inp_chans=4, out_chans=3, embed_dim=32, num_layers=2, num_blocks=4), (32, 64), 4),
+    "vit": ("vit", "VisionTransformer",
+            dict(inp_shape=(32, 64), patch_size=(4, 4), inp_chans=4, out_chans=3, embed_dim=32, depth=2, num_heads=4), (32, 64), 4),
+}
+
+
+def rel(a, b):
+    if a.is_complex():
+        a, b = torch.view_as_real(a), torch.view_as_real(b)
+    return ((a.double() - b.double()).norm() / (b.double().norm() + 1e-30)).item()
+
+
+def run(name):
+    mod, cls, kw, hw, cin = CASES[name]
+    out = {"case": name}
+    try:
+        ref_cls = getattr(importlib.import_module(f"makani.models.networks.{mod}"), cls)
+        torch.manual_seed(0)
+        ref = ref_cls(**kw)
+    except Exception as e:      # an upstream network that cannot be built with stock arguments is reported, not compared
+        out["upstream_error"] = f"{type(e).__name__}: {e}"[:200]
+        return out
+    if ROOT not in sys.path:
+        sys.path.append(ROOT)
+    my_cls = getattr(importlib.import_module(f"makani_b200.models.networks.{mod}"), cls)
+    mine = my_cls(**kw)
+    sr, sm = ref.state_dict(), mine.state_dict()
+    out["only_upstream"] = sorted(set(sr) - set(sm))
+    out["only_here"] = sorted(set(sm) - set(sr))
+    out["shape_mismatch"] = [k for k in sr if k in sm and tuple(sr[k].shape) != tuple(sm[k].shape)]
+    if out["only_upstream"] or out["only_here"] or out["shape_mismatch"]:
+        return out
+    mine.load_state_dict(sr, strict=True)
+    torch.manual_seed(1)
+    x = torch.randn(2, cin, *hw)
+    ref.eval()
+    mine.eval()
+    try:
+        with torch.no_grad():
+            yr = ref(x)
+    except Exception as e:
+        out["upstream_error"] = f"forward: {type(e).__name__}: {e}"[:200]
+        return out
+    with torch.no_grad():
+        ym = mine(x)
+    out["forward"] = rel(ym, yr)
+    ref.train()
+    mine.train()
+    xr, xm = x.clone().requires_grad_(), x.clone().requires_grad_()
+    ref(xr).square().mean().backward()
+    mine(xm).square().mean().backward()
+    out["input_grad"] = rel(xm.grad, xr.grad)
+    gm = dict(mine.named_parameters())
+    worst, missing = 0.0, []
+    for n, p in ref.named_parameters():
+        g, h = p.grad, gm[n].grad
+        if (g is None) != (h is None):
+            missing.append(n)
+            continue
+        if g is None or g.norm().item() < 1e-12:
+            continue
+        worst = max(worst, rel(h, g))
+    out["worst_param_grad"] = worst
+    out["grad_presence_differs"] = missing
+    return out
+
+
+LOSSES = ["l2", "geometric l2", "absolute squared geometric l2", "weighted geometric l2", "geometric l1",
+          "absolute squared weighted geometric l2"]
+
+_LOSS_YAML = """
+base: &B
+    img_shape_x: 33
+    img_shape_y: 64
+    img_crop_shape_x: 33
+    img_crop_shape_y: 64
+    img_crop_offset_x: 0
+    img_crop_offset_y: 0
+    img_local_shape_x: 33
+    img_local_shape_y: 64
+    img_local_offset_x: 0
+    img_local_offset_y: 0
+    N_out_channels: 5
+    N_in_channels: 5
+    n_future: 0
+    channel_names: ["u10m", "v10m", "t2m", "z500", "t850"]
+    channel_weights: "auto"
+    model_grid_type: "equiangular"
+    loss: "l2"
+    pole_mask: 0
+    batch_size: 2
+    out_channels: [0, 1, 2, 3, 4]
+    in_channels: [0, 1, 2, 3, 4]
+"""
+
+
+def run_losses():
+    """`LossHandler(params)` of both packages on the same prediction / target: value and gradient."""
+    import tempfile
+
+    from makani.utils.losses import LossHandler as RefLoss
+    from makani.utils.YParams import YParams as RefY
+
+    if ROOT not in sys.path:
+        sys.path.append(ROOT)
+    from makani_b200.utils.losses import LossHandler as MyLoss
+    from makani_b200.utils.YParams import YParams as MyY
+
+    path = os.path.join(tempfile.mkdtemp(prefix="parity_"), "c.yaml")
+    with open(path, "w") as f:
+        f.write(_LOSS_YAML)
+    out = {"case": "losses", "value": {}, "grad": {}}
+    for grid in ("equiangular", "legendre_gauss"):
+        for name in LOSSES:
+            pr, pm = RefY(path, "base"), MyY(path, "base")
+            for q in (pr, pm):
+                q["loss"], q["model_grid_type"] = name, grid
+            lr, lm = RefLoss(pr), MyLoss(pm)
+            torch.manual_seed(0)
+            a = torch.randn(2, 5, 33, 64, requires_grad=True)
+            b, i = torch.randn(2, 5, 33, 64), torch.randn(2, 5, 33, 64)
+            a2 = a.detach().clone().requires_grad_()
+            vr, vm = lr(a, b, i), lm(a2, b, i)
+            vr.backward()
+            vm.backward()
+            out["value"][f"{grid}:{name}"] = abs(float(vr) - float(vm)) / abs(float(vr))
+            out["grad"][f"{grid}:{name}"] = rel(a2.grad, a.grad)
+    return out
+
+
+def run_metrics():
+    """The geometric metric functions and the time quadratures of both packages on the same fields."""
+    from makani.utils.metrics import functions as RF
+
+    if ROOT not in sys.path:
+        sys.path.append(ROOT)
+    from makani_b200.utils.metrics import functions as MF
+
+    out = {"case": "metrics", "err": {}}
+    torch.manual_seed(0)
+    x, y = torch.randn(3, 5, 33, 64), torch.randn(3, 5, 33, 64)
+    for grid in ("naive", "legendre-gauss", "clenshaw-curtiss"):      # the first argument is the quadrature rule
+        for name in ("GeometricL1", "GeometricRMSE", "GeometricACC"):
+            for cr, br in (("mean", "mean"), ("none", "mean"), ("none", "none"), ("sum", "sum")):
+                for norm in (False, True):
+                    kw = dict(grid_type=grid, img_shape=(33, 64), crop_shape=(33, 64), crop_offset=(0, 0), normalize=norm,
+                              channel_reduction=cr, batch_reduction=br)
+                    a, b = getattr(RF, name)(**kw)(x, y), getattr(MF, name)(**kw)(x, y)
+                    key = f"{grid}:{name}:{cr}:{br}:{int(norm)}"
+                    out["err"][key] = rel(b, a) if tuple(a.shape) == tuple(b.shape) else f"shape {tuple(a.shape)} vs {tuple(b.shape)}"
+    t = torch.randn(4, 9, 3)
+    for name, n in (("SimpsonQuadrature", 8), ("TrapezoidQuadrature", 8), ("Quadrature", 8)):
+        a = getattr(RF, name)(n, 0.25, torch.device("cpu"))(t, dim=1)
+        b = getattr(MF, name)(n, 0.25, torch.device("cpu"))(t, dim=1)
+        out["err"][name] = rel(b, a) if tuple(a.shape) == tuple(b.shape) else f"shape {tuple(a.shape)} vs {tuple(b.shape)}"
+    return out
+
+
+def run_wrapped(multistep):
+    """`model_registry.get_model(params)` (network inside the single- / multi-step wrapper with its preprocessor) of
+    both packages from the same recipe: state dict, evaluation forward, training forward (all autoregressive steps)."""
+    import logging
+
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import reference_arm as RA
+    from makani.models import model_registry
+    from makani.utils import comm
+    from makani.utils.trainer import Trainer
+    from makani.utils.YParams import YParams
+
+    sizes = [1, 1, 1, 1]
+    comm.init(model_parallel_sizes=sizes, model_parallel_names=["h", "w", "fin", "fout"], verbose=False)
+    recipe = os.path.join(ROOT, "config", "sfnonet.yaml")
+    params = YParams(recipe, "sfno_tiny")
+    nlat, nlon, n_out = params.img_shape_x, params.img_shape_y, len(params.channel_names)
+    for k, v in dict(model_parallel_sizes=sizes, model_parallel_names=["h", "w", "fin", "fout"], world_size=1, global_batch_size=2,
+                     batch_size=2, experiment_dir="/tmp/parity", resuming=False, amp_mode="none", jit_mode="none",
+                     cuda_graph_mode="none", skip_validation=True, enable_odirect=False, checkpointing=0,
+                     enable_synthetic_data=True, split_data_channels=False, multistep_count=multistep, n_future=multistep - 1,
+                     add_grid=True, add_zenith=False, add_orography=False, add_landmask=False, gridtype="sinusoidal",
+                     grid_num_frequencies=2).items():
+        params[k] = v
+    tr = Trainer.__new__(Trainer)
+    tr.params, tr.world_rank, tr.data_parallel_rank = None, 0, 0
+    tr.device, tr.logger = torch.device("cpu"), logging.getLogger()
+    tr.valid_dataset = RA._SyntheticDataset(n_out, n_out, nlat, nlon, [nlat], [nlon], 0, 0)
+    params = tr._update_parameters(params)      # upstream derives the channel counts etc.
+    torch.manual_seed(0)
+    ref = model_registry.get_model(params)
+    if ROOT not in sys.path:
+        sys.path.append(ROOT)
+    from makani_b200.models import model_registry as my_registry
+    from makani_b200.utils.YParams import YParams as MyY
+
+    mp = MyY(recipe, "sfno_tiny")
+    for k, v in params.to_dict().items():
+        mp[k] = v
+    mine = my_registry.get_model(mp)
+    sr, sm = ref.state_dict(), mine.state_dict()
+    out = {"case": f"wrapped_multistep{multistep}", "wrapper": type(ref).__name__,
+           "only_upstream": sorted(set(sr) - set(sm)), "only_here": sorted(set(sm) - set(sr)),
+           "shape_mismatch": [k for k in sr if k in sm and tuple(sr[k].shape) != tuple(sm[k].shape)]}
+    if out["only_upstream"] or out["only_here"] or out["shape_mismatch"]:
+        return out
+    mine.load_state_dict(sr, strict=True)
+    x = torch.randn(2, n_out, nlat, nlon)
+    ref.eval()
+    mine.eval()
+    with torch.no_grad():
+        out["eval_forward"] = rel(mine(x), ref(x))
+    ref.train()
+    mine.train()
+    yr, ym = ref(x), mine(x)
+    out["train_shape"] = [list(yr.shape), list(ym.shape)]
+    out["train_forward"] = rel(ym, yr)
+    return out
+
+
+if __name__ == "__main__":
+    import makani
+
+    assert os.path.realpath(makani.__file__).startswith(os.path.realpath(os.path.join(ROOT, "baseline", "_ref"))), makani.__file__
+    for name in (sys.argv[1:] or list(CASES) + ["losses", "metrics", "wrapped1", "wrapped2"]):
+        if name == "losses":
+            res = run_losses()
+        elif name == "metrics":
+            res = run_metrics()
+        elif name.startswith("wrapped"):
+            res = run_wrapped(int(name[len("wrapped"):]))
+        else:
+            res = run(name)
+        print(json.dumps(res))
+        sys.stdout.flush()

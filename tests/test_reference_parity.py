@@ -1,0 +1,69 @@
+"""Drop-in parity with the unmodified upstream package: for every network family, the same constructor arguments give
+the same state-dict keys and shapes, an upstream state dict loads strictly, and forward output, input gradient and every
+parameter gradient agree on CPU in fp32.  Needs the upstream package under `baseline/_ref` (installed offline, not
+tracked); skipped when it is absent.  The comparison runs in a child process (`tests/reference_parity_worker.py`)."""
+
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+CASES = ["sfno_dhconv_instance_norm", "sfno_dhconv_scale2_layer_norm", "sfno_diagonal", "fno", "afno_v1", "afno_v2", "vit"]
+
+
+@pytest.fixture(scope="module")
+def results():
+    if not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "makani")):
+        pytest.skip("upstream package not installed under baseline/_ref")
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="4")
+    env.pop("PYTHONPATH", None)
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "reference_parity_worker.py")] + CASES + ["losses", "metrics", "wrapped1", "wrapped2"],
+                          cwd="/tmp", env=env,
+                          capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    out = {}
+    for line in proc.stdout.splitlines():
+        if line.startswith("{"):
+            r = json.loads(line)
+            out[r["case"]] = r
+    return out
+
+
+@pytest.mark.parametrize("case", CASES)
+def test_network_matches_upstream(results, case):
+    r = results[case]
+    assert "upstream_error" not in r, r
+    assert r["only_upstream"] == [] and r["only_here"] == [] and r["shape_mismatch"] == [], r
+    assert r["grad_presence_differs"] == [], r
+    assert r["forward"] < 1e-5 and r["input_grad"] < 1e-4 and r["worst_param_grad"] < 1e-4, r
+
+
+def test_loss_handler_matches_upstream(results):
+    r = results["losses"]
+    assert len(r["value"]) == 12
+    for k, v in r["value"].items():
+        assert v < 1e-6, (k, v)
+    for k, v in r["grad"].items():
+        assert v < 1e-5, (k, v)
+
+
+@pytest.mark.parametrize("multistep", [1, 2])
+def test_wrapped_model_matches_upstream(results, multistep):
+    """Registry + preprocessor (sinusoidal grid features) + single- / multi-step wrapper: same state-dict keys as upstream
+    (so its checkpoints load), same outputs in evaluation and training mode."""
+    r = results[f"wrapped_multistep{multistep}"]
+    assert r["wrapper"] == ("SingleStepWrapper" if multistep == 1 else "MultiStepWrapper")
+    assert r["only_upstream"] == [] and r["only_here"] == [] and r["shape_mismatch"] == [], r
+    assert r["train_shape"][0] == r["train_shape"][1]
+    assert r["eval_forward"] < 1e-5 and r["train_forward"] < 1e-5, r
+
+
+def test_metric_functions_match_upstream(results):
+    """GeometricL1 / RMSE / ACC under the three quadrature rules and every reduction mode, and the time quadratures."""
+    r = results["metrics"]
+    assert len(r["err"]) == 75
+    for k, v in r["err"].items():
+        assert isinstance(v, float) and v < 1e-5, (k, v)
