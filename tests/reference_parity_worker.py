@@ -30,13 +30,24 @@ CASES = {
     # 33 latitudes: the upstream diagonal operator can only be built when the two mode counts agree
     "sfno_diagonal": ("sfnonet", "SphericalFourierNeuralOperatorNet",
                       dict(SFNO, inp_shape=(33, 64), out_shape=(33, 64), operator_type="diagonal", normalization_layer="none"), (33, 64), 4),
+    "sfno_three_layers_frequency_embedding": ("sfnonet", "SphericalFourierNeuralOperatorNet",
+                                              dict(SFNO, operator_type="dhconv", normalization_layer="instance_norm", bias=True, mlp_ratio=3.0,
+                                                   num_layers=3, big_skip=False, pos_embed="frequency", encoder_layers=2), (32, 64), 4),
+    "sfno_coarser_output_grid": ("sfnonet", "SphericalFourierNeuralOperatorNet",
+                                 dict(SFNO, operator_type="dhconv", normalization_layer="instance_norm", out_shape=(16, 32)), (32, 64), 4),
     "fno": ("sfnonet", "FourierNeuralOperatorNet", dict(SFNO, operator_type="dhconv", normalization_layer="instance_norm"), (32, 64), 4),
     "afno_v1": ("afnonet", "AdaptiveFourierNeuralOperatorNet",
                 dict(inp_shape=(32, 64), patch_size=(4, 4), inp_chans=4, out_chans=3, embed_dim=32, num_layers=2, num_blocks=4), (32, 64), 4),
+    "afno_v1_thresholded": ("afnonet", "AdaptiveFourierNeuralOperatorNet",
+                            dict(inp_shape=(32, 64), patch_size=(8, 8), inp_chans=4, out_chans=3, embed_dim=32, num_layers=2, num_blocks=4,
+                                 hard_thresholding_fraction=0.5, sparsity_threshold=0.05, mlp_ratio=2.0), (32, 64), 4),
     "afno_v2": ("afnonet_v2", "AdaptiveFourierNeuralOperatorNet",
                 dict(inp_shape=(32, 64), patch_size=(4, 4), inp_chans=4, out_chans=3, embed_dim=32, num_layers=2, num_blocks=4), (32, 64), 4),
     "vit": ("vit", "VisionTransformer",
             dict(inp_shape=(32, 64), patch_size=(4, 4), inp_chans=4, out_chans=3, embed_dim=32, depth=2, num_heads=4), (32, 64), 4),
+    "vit_qkv_bias": ("vit", "VisionTransformer",
+                     dict(inp_shape=(32, 64), patch_size=(8, 8), inp_chans=4, out_chans=3, embed_dim=48, depth=3, num_heads=6, mlp_ratio=2.0,
+                          qkv_bias=True), (32, 64), 4),
 }
 
 
@@ -88,12 +99,16 @@ def run(name):
     out["input_grad"] = rel(xm.grad, xr.grad)
     gm = dict(mine.named_parameters())
     worst, missing = 0.0, []
+    largest = max((p.grad.abs().max().item() for p in ref.parameters() if p.grad is not None), default=0.0)
     for n, p in ref.named_parameters():
         g, h = p.grad, gm[n].grad
         if (g is None) != (h is None):
             missing.append(n)
             continue
-        if g is None or g.norm().item() < 1e-12:
+        if g is None or g.abs().max().item() < 1e-5 * largest:
+            # a gradient that is zero in exact arithmetic (a bias in front of an instance norm): rounding noise on both sides
+            if h is not None and h.abs().max().item() > 1e-4 * largest:
+                worst = max(worst, 1.0)
             continue
         worst = max(worst, rel(h, g))
     out["worst_param_grad"] = worst

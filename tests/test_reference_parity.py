@@ -11,7 +11,8 @@ import sys
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-CASES = ["sfno_dhconv_instance_norm", "sfno_dhconv_scale2_layer_norm", "sfno_diagonal", "fno", "afno_v1", "afno_v2", "vit"]
+CASES = ["sfno_dhconv_instance_norm", "sfno_dhconv_scale2_layer_norm", "sfno_diagonal", "sfno_three_layers_frequency_embedding",
+         "sfno_coarser_output_grid", "fno", "afno_v1", "afno_v1_thresholded", "afno_v2", "vit", "vit_qkv_bias"]
 
 
 @pytest.fixture(scope="module")
