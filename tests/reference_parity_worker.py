@@ -267,15 +267,122 @@ def run_wrapped(multistep):
     return out
 
 
+def _upstream_trainer(multistep=1):
+    """An upstream Trainer object assembled far enough to build the model and to save / restore checkpoints."""
+    import logging
+
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import reference_arm as RA
+    from makani.models import model_registry
+    from makani.utils import comm
+    from makani.utils.trainer import Trainer
+    from makani.utils.YParams import YParams
+
+    sizes = [1, 1, 1, 1]
+    comm.init(model_parallel_sizes=sizes, model_parallel_names=["h", "w", "fin", "fout"], verbose=False)
+    recipe = os.path.join(ROOT, "config", "sfnonet.yaml")
+    params = YParams(recipe, "sfno_tiny")
+    nlat, nlon, n_out = params.img_shape_x, params.img_shape_y, len(params.channel_names)
+    for k, v in dict(model_parallel_sizes=sizes, model_parallel_names=["h", "w", "fin", "fout"], world_size=1, global_batch_size=2,
+                     batch_size=2, experiment_dir="/tmp/parity", resuming=False, amp_mode="none", jit_mode="none",
+                     cuda_graph_mode="none", skip_validation=True, enable_odirect=False, checkpointing=0,
+                     enable_synthetic_data=True, split_data_channels=False, multistep_count=multistep, n_future=multistep - 1,
+                     add_grid=True, add_zenith=False, add_orography=False, add_landmask=False, gridtype="sinusoidal",
+                     grid_num_frequencies=2, log_to_screen=False).items():
+        params[k] = v
+    tr = Trainer.__new__(Trainer)
+    tr.params, tr.world_rank, tr.data_parallel_rank = None, 0, 0
+    tr.device, tr.logger = torch.device("cpu"), logging.getLogger()
+    tr.valid_dataset = RA._SyntheticDataset(n_out, n_out, nlat, nlon, [nlat], [nlon], 0, 0)
+    params = tr._update_parameters(params)
+    tr.params = params
+    torch.manual_seed(0)
+    tr.model = model_registry.get_model(params)
+    return tr, params, recipe
+
+
+def run_checkpoints():
+    """A checkpoint written by the upstream trainer (legacy and flexible format) restores into this framework's model
+    and optimiser, and a checkpoint written here restores into the upstream trainer."""
+    import tempfile
+
+    tr, params, recipe = _upstream_trainer()
+    nlat, nlon, n_out = params.img_shape_x, params.img_shape_y, len(params.channel_names)
+    tr.optimizer = torch.optim.AdamW(tr.model.parameters(), lr=1e-3)
+    tr.scheduler = torch.optim.lr_scheduler.StepLR(tr.optimizer, step_size=3)
+    x = torch.randn(2, n_out, nlat, nlon)
+    tr.model.train()
+    tr.model(x).square().mean().backward()
+    tr.optimizer.step()
+    tr.scheduler.step()
+    tr.iters, tr.epoch = 7, 2
+    d = tempfile.mkdtemp(prefix="parity_ckpt_")
+    legacy, flexible = os.path.join(d, "legacy_mp{mp_rank}.tar"), os.path.join(d, "flexible_mp{mp_rank}.tar")
+    tr.save_checkpoint(legacy, checkpoint_mode="legacy")
+    tr.save_checkpoint(flexible, checkpoint_mode="flexible")
+
+    if ROOT not in sys.path:
+        sys.path.append(ROOT)
+    from makani_b200.models import model_registry as my_registry
+    from makani_b200.utils import checkpoint as my_ckpt
+    from makani_b200.utils.YParams import YParams as MyY
+
+    mp = MyY(recipe, "sfno_tiny")
+    for k, v in params.to_dict().items():
+        mp[k] = v
+    out = {"case": "checkpoints"}
+    tr.model.eval()
+    with torch.no_grad():
+        y_ref = tr.model(x)
+    for mode, path in (("legacy", legacy), ("flexible", flexible)):
+        torch.manual_seed(123)
+        mine = my_registry.get_model(mp)
+        opt = torch.optim.AdamW(mine.parameters(), lr=5e-2)
+        sch = torch.optim.lr_scheduler.StepLR(opt, step_size=3)
+        iters, epoch = my_ckpt.restore_checkpoint(path, mine, optimizer=opt, scheduler=sch, mode=mode,
+                                                  load_optimizer=(mode == "legacy"), load_scheduler=True, load_counters=True)
+        mine.eval()
+        with torch.no_grad():
+            out[f"{mode}_forward"] = rel(mine(x), y_ref)
+        out[f"{mode}_counters"] = [iters, epoch]
+        out[f"{mode}_scheduler_epoch"] = sch.last_epoch
+        if mode == "legacy":
+            so, sm = tr.optimizer.state_dict(), opt.state_dict()
+            out["legacy_optimizer_lr"] = sm["param_groups"][0]["lr"] / so["param_groups"][0]["lr"]
+            out["legacy_optimizer_state"] = max(rel(sm["state"][k]["exp_avg"], so["state"][k]["exp_avg"]) for k in so["state"])
+    # the other direction: written here, restored by the upstream trainer (its plain `torch.load` of a file that holds
+    # the recipe object needs the opt-out of weights-only loading on this version of torch, also for its own files)
+    os.environ["TORCH_FORCE_NO_WEIGHTS_ONLY_LOAD"] = "1"
+    torch.manual_seed(5)
+    mine = my_registry.get_model(mp)
+    mine.eval()
+    with torch.no_grad():
+        y_mine = mine(x)
+    for mode in ("legacy", "flexible"):
+        path = os.path.join(d, "here_" + mode + "_mp{mp_rank}.tar")
+        my_ckpt.save_checkpoint(path, mine, optimizer=None, scheduler=None, params=mp, iters=11, epoch=3, mode=mode)
+        try:
+            tr.restore_checkpoint(path, checkpoint_mode=mode, load_counters=True)
+            tr.model.eval()
+            with torch.no_grad():
+                out[f"upstream_reads_{mode}"] = rel(tr.model(x), y_mine)
+            out[f"upstream_reads_{mode}_counters"] = [tr.iters, tr.startEpoch]
+        except Exception as e:
+            out[f"upstream_reads_{mode}"] = f"{type(e).__name__}: {e}"[:300]
+    return out
+
+
 if __name__ == "__main__":
     import makani
 
     assert os.path.realpath(makani.__file__).startswith(os.path.realpath(os.path.join(ROOT, "baseline", "_ref"))), makani.__file__
-    for name in (sys.argv[1:] or list(CASES) + ["losses", "metrics", "wrapped1", "wrapped2"]):
+    for name in (sys.argv[1:] or list(CASES) + ["losses", "metrics", "wrapped1", "wrapped2", "checkpoints"]):
         if name == "losses":
             res = run_losses()
         elif name == "metrics":
             res = run_metrics()
+        elif name == "checkpoints":
+            res = run_checkpoints()
         elif name.startswith("wrapped"):
             res = run_wrapped(int(name[len("wrapped"):]))
         else:
