@@ -267,7 +267,7 @@ def run_wrapped(multistep):
     return out
 
 
-def _upstream_trainer(multistep=1):
+def _upstream_trainer(multistep=1, extra=None):
     """An upstream Trainer object assembled far enough to build the model and to save / restore checkpoints."""
     import logging
 
@@ -290,6 +290,8 @@ def _upstream_trainer(multistep=1):
                      add_grid=True, add_zenith=False, add_orography=False, add_landmask=False, gridtype="sinusoidal",
                      grid_num_frequencies=2, log_to_screen=False).items():
         params[k] = v
+    for k, v in (extra or {}).items():
+        params[k] = v
     tr = Trainer.__new__(Trainer)
     tr.params, tr.world_rank, tr.data_parallel_rank = None, 0, 0
     tr.device, tr.logger = torch.device("cpu"), logging.getLogger()
@@ -299,6 +301,41 @@ def _upstream_trainer(multistep=1):
     torch.manual_seed(0)
     tr.model = model_registry.get_model(params)
     return tr, params, recipe
+
+
+def run_wrapped_features():
+    """Zenith-angle channels (cached per step), input history and multistep training through the wrappers of both
+    packages: training-mode and evaluation-mode forward for every combination."""
+    if ROOT not in sys.path:
+        sys.path.append(ROOT)
+    out = {"case": "wrapped_features", "err": {}}
+    for ms, zen, nh in [(1, True, 0), (2, True, 0), (2, False, 1), (1, True, 1), (2, True, 1), (3, True, 2)]:
+        tr, params, recipe = _upstream_trainer(ms, dict(add_zenith=zen, n_history=nh, add_grid=False))
+        from makani_b200.models import model_registry as my_registry
+        from makani_b200.utils.YParams import YParams as MyY
+
+        mp = MyY(recipe, "sfno_tiny")
+        for k, v in params.to_dict().items():
+            mp[k] = v
+        ref, mine = tr.model, my_registry.get_model(mp)
+        mine.load_state_dict(ref.state_dict(), strict=True)
+        nlat, nlon, C = params.img_shape_x, params.img_shape_y, len(params.channel_names)
+        torch.manual_seed(ms * 10 + nh)
+        inp, tar = torch.randn(2, (nh + 1) * C, nlat, nlon), torch.randn(2, ms * C, nlat, nlon)
+        izen = torch.rand(2, nh + 1, 1, nlat, nlon) if zen else None
+        tzen = torch.rand(2, ms, 1, nlat, nlon) if zen else None
+        for mode in ("train", "eval"):
+            outs = []
+            for m in (ref, mine):
+                m.train() if mode == "train" else m.eval()
+                with torch.no_grad():
+                    # every model gets its own copies: the upstream preprocessor keeps (and later overwrites) the caller's tensors
+                    ip, _ = m.preprocessor.cache_unpredicted_features(inp.clone(), tar.clone(), None if izen is None else izen.clone(),
+                                                                      None if tzen is None else tzen.clone())
+                    outs.append(m(m.preprocessor.flatten_history(ip)))
+            same = tuple(outs[0].shape) == tuple(outs[1].shape)
+            out["err"][f"multistep{ms}_zenith{int(zen)}_history{nh}_{mode}"] = rel(outs[1], outs[0]) if same else "shape"
+    return out
 
 
 def run_checkpoints():
@@ -376,13 +413,15 @@ if __name__ == "__main__":
     import makani
 
     assert os.path.realpath(makani.__file__).startswith(os.path.realpath(os.path.join(ROOT, "baseline", "_ref"))), makani.__file__
-    for name in (sys.argv[1:] or list(CASES) + ["losses", "metrics", "wrapped1", "wrapped2", "checkpoints"]):
+    for name in (sys.argv[1:] or list(CASES) + ["losses", "metrics", "wrapped1", "wrapped2", "wrapped_features", "checkpoints"]):
         if name == "losses":
             res = run_losses()
         elif name == "metrics":
             res = run_metrics()
         elif name == "checkpoints":
             res = run_checkpoints()
+        elif name == "wrapped_features":
+            res = run_wrapped_features()
         elif name.startswith("wrapped"):
             res = run_wrapped(int(name[len("wrapped"):]))
         else:

@@ -21,7 +21,7 @@ def results():
         pytest.skip("upstream package not installed under baseline/_ref")
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="4")
     env.pop("PYTHONPATH", None)
-    proc = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "reference_parity_worker.py")] + CASES + ["losses", "metrics", "wrapped1", "wrapped2", "checkpoints"],
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "reference_parity_worker.py")] + CASES + ["losses", "metrics", "wrapped1", "wrapped2", "wrapped_features", "checkpoints"],
                           cwd="/tmp", env=env,
                           capture_output=True, text=True, timeout=900)
     assert proc.returncode == 0, proc.stderr[-2000:]
@@ -79,3 +79,10 @@ def test_checkpoints_are_interchangeable_with_upstream(results):
         assert r[f"{mode}_counters"] == [7, 2] and r[f"{mode}_scheduler_epoch"] == 1, r
         assert r[f"upstream_reads_{mode}"] < 1e-6 and r[f"upstream_reads_{mode}_counters"] == [11, 3], r
     assert r["legacy_optimizer_lr"] == 1.0 and r["legacy_optimizer_state"] < 1e-7, r
+
+
+def test_zenith_history_and_multistep_match_upstream(results):
+    r = results["wrapped_features"]
+    assert len(r["err"]) == 12
+    for k, v in r["err"].items():
+        assert isinstance(v, float) and v < 1e-5, (k, v)
