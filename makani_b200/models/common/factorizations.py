@@ -2,8 +2,8 @@
 
 The reference delegates these to tensorly / tltorch `FactorizedTensor`
 (makani/models/common/factorizations.py:33-247, spectral_convolution.py:151-265).  Neither package is needed
-here: each factorisation stores its factors as complex parameters, can be reconstructed to the dense weight
-(`to_tensor`) and contracted directly with the input without reconstruction (`contract`).
+here: each factorisation stores its factors as complex parameters and is reconstructed to the dense weight
+(`to_tensor`) before the contraction.
 """
 
 from __future__ import annotations
@@ -74,3 +74,27 @@ class FactorizedWeight(nn.Module):
 
     def forward(self):
         return self.to_tensor()
+
+
+def get_contract_fun(weight, implementation: str = "reconstructed", separable: bool = False, operator_type: str = "diagonal",
+                     complex: bool = True):
+    """`(x, weight) -> x * weight` in spectral space for a dense or factorised weight, by the calling convention of
+    makani/models/common/factorizations.py:212-247.  Both implementations ("reconstructed", "factorized") form the
+    dense weight from the factors and apply the contraction of `operator_type`: reconstructing costs less than the
+    contraction itself at the ranks and mode counts of these models, so no factor-by-factor path is kept."""
+    from .contractions import get_contract_fun as dense_contraction
+
+    if implementation not in ("reconstructed", "factorized"):
+        raise ValueError(f"implementation must be 'reconstructed' or 'factorized', got {implementation!r}")
+    if not (torch.is_tensor(weight) or isinstance(weight, FactorizedWeight)):
+        raise ValueError(f"unexpected weight type {type(weight).__name__}")
+    dense = dense_contraction(operator_type, separable)
+
+    def as_complex(t):
+        return torch.view_as_complex(t) if (complex and not t.is_complex() and t.shape[-1] == 2) else t
+
+    def contract(x, w):
+        w = w.to_tensor() if isinstance(w, FactorizedWeight) else w
+        return dense(as_complex(x), as_complex(w))
+
+    return contract

@@ -22,3 +22,10 @@ def count_parameters(model: torch.nn.Module, device) -> int:
         if comm.get_size("model") > 1:
             dist.all_reduce(total, group=comm.get_group("model"))
     return int(round(total.item()))
+
+
+def check_parameters(model: torch.nn.Module) -> None:
+    """Debug print of every trainable parameter's shape, strides and contiguity (makani/models/helpers.py:41-44)."""
+    for name, p in model.named_parameters():
+        if p.requires_grad:
+            print(name, tuple(p.shape), p.stride(), p.is_contiguous())

@@ -109,3 +109,57 @@ def scatter_to_parallel_region(x, dim, name):
 
 def gather_from_parallel_region(x, dim, shapes, name):
     return x if comm.get_size(name) == 1 else _GatherFrom.apply(x, dim, shapes, name)
+
+
+# ------------------------------------------------------------------------------------------------ gradient reduction
+
+
+class ReducedModule(torch.nn.Module):
+    """What `init_gradient_reduction_hooks` returns: the model under `.module` (state-dict keys carry the `module.`
+    prefix, as with DistributedDataParallel) plus a `GradReducer` that runs by itself at the end of every backward
+    pass.  A plain training loop (`loss.backward(); optimizer.step(); optimizer.zero_grad()`) therefore needs no call
+    into this framework, whichever `set_to_none` it uses."""
+
+    def __init__(self, module: torch.nn.Module, bucket_mb: float = 25.0):
+        super().__init__()
+        from .grad_reduce import GradReducer
+
+        self.module = module
+        # no overlap: gradients that autograd allocated itself (after `zero_grad(set_to_none=True)`) are moved into the
+        # reducer's flat buffer when backward ends, so the reduction cannot start before that
+        self.reducer = GradReducer(module, bucket_mb=bucket_mb, overlap=False)
+        self._views = [p.grad for p in self.reducer.params]
+        self._queued = False
+        for p in self.reducer.params:
+            p.register_post_accumulate_grad_hook(self._on_grad)
+
+    def _on_grad(self, _param):
+        if not self._queued:
+            self._queued = True
+            torch.autograd.Variable._execution_engine.queue_callback(self._finish)
+
+    def _finish(self):
+        self._queued = False
+        with torch.no_grad():
+            for p, view in zip(self.reducer.params, self._views):
+                if p.grad is None:
+                    view.zero_()                 # unused in this pass: contributes nothing to the average
+                elif p.grad.data_ptr() != view.data_ptr():
+                    view.copy_(p.grad)
+                p.grad = view
+        self.reducer.reduce()
+
+    def forward(self, *args, **kwargs):
+        return self.module(*args, **kwargs)
+
+
+def init_gradient_reduction_hooks(model, device_ids=None, output_device=None, bucket_cap_mb=25, broadcast_buffers=True,
+                                  find_unused_parameters=False, gradient_as_bucket_view=True, static_graph=False):
+    """Calling convention of makani/mpu/mappings.py:30-174: returns the model wrapped such that, after every backward
+    pass, gradients are averaged over the `data` group and summed over the groups named in `param.is_shared_mp`.
+    Without an initialised process group the model is returned unchanged.  The DDP-specific arguments are accepted and
+    ignored: there are no buckets to tune and no buffers to broadcast (the trainer of this framework drives a
+    `GradReducer` directly, with overlap; this entry point serves user loops written against the upstream function)."""
+    if not dist.is_initialized():
+        return model
+    return ReducedModule(model, bucket_mb=float(bucket_cap_mb))

@@ -172,6 +172,17 @@ def plot_rollout_metrics(acc_curves, rmse_curves, params, epoch, model_name, com
             plt.close(fig)
 
 
+def visualize_field(tag, func_string, prediction, target, lat, lon, scale, bias, diverging):
+    """One comparison frame: un-normalise (`scale * x + bias`), apply the functor given as source text (e.g.
+    `"lambda x: np.sqrt(np.square(x[0]) + np.square(x[1]))"`, as in makani/utils/visualize.py:135-154) and plot
+    prediction beside target.  Returns `(tag, image)`."""
+    func = eval(func_string)      # the plot list of a recipe is trusted configuration, exactly as upstream
+    pred, targ = func(scale * prediction + bias), func(scale * target + bias)
+    image = plot_comparison(pred, targ, lat, lon, pred_title="Prediction", truth_title="Ground truth", projection="mollweide",
+                            diverging=diverging)
+    return tag, image
+
+
 def _render(args):
     pred, targ, lat, lon, title = args
     try:

@@ -531,6 +531,58 @@ def case_patch_embed():
     assert _rel(xl.grad, split_tensor_along_dim(xr.grad, 1, msize)[mrank]) < 1e-5
 
 
+def case_reduction_hooks():
+    """`init_gradient_reduction_hooks` in a plain user loop: after every backward pass the gradients equal the average
+    over the data-parallel ranks of what a serial model gets on each rank's batch, with either flavour of zero_grad,
+    with a complex parameter and with a parameter that takes no part in a pass."""
+    from makani_b200.parallel.mappings import init_gradient_reduction_hooks
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a = torch.nn.Linear(5, 7)
+            self.b = torch.nn.Linear(7, 3)
+            self.c = torch.nn.Parameter(torch.randn(7, dtype=torch.complex64))
+            self.unused = torch.nn.Parameter(torch.randn(4))
+
+        def forward(self, x, use_all=True):
+            h = torch.view_as_real(self.a(x).to(torch.complex64) * self.c).sum(-1)
+            y = self.b(torch.tanh(h))
+            return y + self.unused.sum() if use_all else y
+
+    torch.manual_seed(0)                      # same initial weights on every rank
+    net, ref = Net(), Net()
+    ref.load_state_dict(net.state_dict())
+    model = init_gradient_reduction_hooks(net, device_ids=None, output_device=None, bucket_cap_mb=1)
+    assert list(model.state_dict())[0].startswith("module.")
+    world, rank = comm.get_size("data"), comm.get_rank("data")
+    opt = torch.optim.SGD(model.parameters(), lr=0.1)
+    ropt = torch.optim.SGD(ref.parameters(), lr=0.1)
+    for step, (set_to_none, use_all) in enumerate([(True, True), (False, True), (True, False), (False, False), (True, True)]):
+        xs = [torch.randn(4, 5, generator=torch.Generator().manual_seed(100 * step + r)) for r in range(world)]
+        model(xs[rank], use_all).square().mean().backward()
+        # serial reference: average of the per-rank gradients
+        ropt.zero_grad(set_to_none=True)
+        acc = None
+        for r in range(world):
+            gs = torch.autograd.grad(ref(xs[r], use_all).square().mean(), [p for p in ref.parameters()], allow_unused=True)
+            gs = [torch.zeros_like(p) if g is None else g for g, p in zip(gs, ref.parameters())]
+            acc = gs if acc is None else [a + g for a, g in zip(acc, gs)]
+        for (n, p), g in zip(net.named_parameters(), acc):
+            want = g / world
+            got = p.grad
+            if want.is_complex():
+                want, got = torch.view_as_real(want), torch.view_as_real(got)
+            assert (got - want).abs().max().item() < 1e-5 * (1.0 + want.abs().max().item()), (step, n)
+        for p, g in zip(ref.parameters(), acc):
+            p.grad = g / world
+        opt.step()
+        ropt.step()
+        opt.zero_grad(set_to_none=set_to_none)
+    for p, q in zip(net.parameters(), ref.parameters()):
+        assert torch.allclose(torch.view_as_real(p) if p.is_complex() else p, torch.view_as_real(q) if q.is_complex() else q, atol=1e-5)
+
+
 if __name__ == "__main__":
     case = sys.argv[1]
     sizes = [int(a) for a in sys.argv[2:6]]

@@ -338,6 +338,54 @@ def run_wrapped_features():
     return out
 
 
+def run_reshape_fields():
+    """`utils.img_utils.reshape_fields` (sample preparation of the numpy data path) of both packages."""
+    import tempfile
+    import types
+
+    import numpy as np
+    from makani.utils.img_utils import reshape_fields as ref_fn
+
+    if ROOT not in sys.path:
+        sys.path.append(ROOT)
+    from makani_b200.utils.img_utils import reshape_fields as my_fn
+
+    d = tempfile.mkdtemp(prefix="parity_fields_")
+    rng = np.random.default_rng(0)
+    C = 6
+    stats = {}
+    for name, arr in (("min", rng.normal(size=(1, C, 1, 1)) - 3), ("max", rng.normal(size=(1, C, 1, 1)) + 3),
+                      ("mean", rng.normal(size=(1, C, 1, 1))), ("std", rng.uniform(0.5, 2.0, size=(1, C, 1, 1)))):
+        stats[name] = os.path.join(d, name + ".npy")
+        np.save(stats[name], arr.astype(np.float32))
+    out = {"case": "reshape_fields", "err": {}}
+    for norm in ("zscore", "minmax"):
+        for grid in (None, "linear", "sinusoidal"):
+            for which, nhist, train in (("inp", 1, True), ("inp", 0, False), ("tar", 0, True)):
+                chans = [0, 2, 3, 5]
+                p = types.SimpleNamespace(in_channels=chans, out_channels=chans, min_path=stats["min"], max_path=stats["max"],
+                                          global_means_path=stats["mean"], global_stds_path=stats["std"], normalization=norm,
+                                          add_grid=grid is not None, gridtype=grid, n_grid_channels={None: 0, "linear": 2, "sinusoidal": 4}[grid],
+                                          roll=True)
+                img = rng.normal(size=(nhist + 1, len(chans), 24, 48)).astype(np.float32)
+                # evaluation samples are not cropped: the window is the whole field there
+                args = (which, 16, 32, 3, 5, p, 7, train) if train else (which, 24, 48, 0, 0, p, 7, train)
+                key = f"{norm}:{grid}:{which}:{nhist}:{int(train)}"
+                b = my_fn(img.copy(), *args)
+                try:
+                    a = ref_fn(img.copy(), *args)
+                except ValueError:
+                    # upstream reshapes an input with grid channels by the channel count without them and fails;
+                    # checked here instead: data channels first, then the grid channels, per history step
+                    n_grid = p.n_grid_channels
+                    ok = which == "inp" and n_grid > 0 and b.shape[0] == (nhist + 1) * (len(chans) + n_grid)
+                    out["err"][key] = 0.0 if ok else "upstream failed and the shape here is unexpected"
+                    out.setdefault("upstream_failed", []).append(key)
+                    continue
+                out["err"][key] = rel(b.double(), a.double()) if tuple(a.shape) == tuple(b.shape) else f"shape {tuple(a.shape)} vs {tuple(b.shape)}"
+    return out
+
+
 def run_checkpoints():
     """A checkpoint written by the upstream trainer (legacy and flexible format) restores into this framework's model
     and optimiser, and a checkpoint written here restores into the upstream trainer."""
@@ -413,7 +461,7 @@ if __name__ == "__main__":
     import makani
 
     assert os.path.realpath(makani.__file__).startswith(os.path.realpath(os.path.join(ROOT, "baseline", "_ref"))), makani.__file__
-    for name in (sys.argv[1:] or list(CASES) + ["losses", "metrics", "wrapped1", "wrapped2", "wrapped_features", "checkpoints"]):
+    for name in (sys.argv[1:] or list(CASES) + ["losses", "metrics", "wrapped1", "wrapped2", "wrapped_features", "reshape_fields", "checkpoints"]):
         if name == "losses":
             res = run_losses()
         elif name == "metrics":
@@ -422,6 +470,8 @@ if __name__ == "__main__":
             res = run_checkpoints()
         elif name == "wrapped_features":
             res = run_wrapped_features()
+        elif name == "reshape_fields":
+            res = run_reshape_fields()
         elif name.startswith("wrapped"):
             res = run_wrapped(int(name[len("wrapped"):]))
         else:

@@ -105,3 +105,9 @@ def test_fused_channel_parallel_matmul_algebra(sizes):
 @pytest.mark.parametrize("sizes", [(1, 1, 2, 1), (1, 1, 2, 2)])
 def test_distributed_patch_embed(sizes):
     _launch("patch_embed", sizes, sizes[2] * sizes[3])
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_gradient_reduction_hooks_in_a_plain_loop(world):
+    """`init_gradient_reduction_hooks` (the upstream entry point for user loops) on 2 and 3 data-parallel ranks."""
+    _launch("reduction_hooks", (1, 1, 1, 1), world)

@@ -63,3 +63,27 @@ def test_state_dict_names_follow_the_checkpoint_contract():
               "model.residual_transform.weight"]:
         assert k in names, k
     assert not any("sht" in k or "weights" == k.split(".")[-1] and "trans" in k for k in names)
+
+
+def test_contraction_handle_and_parameter_report(capsys):
+    """`factorizations.get_contract_fun` (dense tensor, real-view tensor and factorised weight give the same product as
+    the dense contraction) and `helpers.check_parameters`."""
+    import torch
+
+    from makani_b200.models.common.contractions import get_contract_fun as dense_fun
+    from makani_b200.models.common.factorizations import FactorizedWeight, get_contract_fun
+    from makani_b200.models.helpers import check_parameters
+
+    torch.manual_seed(0)
+    x = torch.randn(2, 3, 5, 6, dtype=torch.complex64)
+    for op, shape in (("dhconv", [3, 4, 5]), ("diagonal", [3, 4, 5, 6])):
+        w = FactorizedWeight(shape, rank=0.5, factorization="cp")
+        want = dense_fun(op, False)(x, w.to_tensor())
+        for impl in ("reconstructed", "factorized"):
+            assert torch.allclose(get_contract_fun(w, impl, False, op)(x, w), want, atol=1e-6)
+        dense = w.to_tensor().detach()
+        assert torch.allclose(get_contract_fun(dense, "factorized", False, op)(x, dense), want, atol=1e-6)
+        assert torch.allclose(get_contract_fun(dense, "reconstructed", False, op)(torch.view_as_real(x), torch.view_as_real(dense)), want, atol=1e-6)
+    check_parameters(torch.nn.Linear(3, 2))
+    out = capsys.readouterr().out
+    assert "weight (2, 3)" in out and "bias (2,)" in out

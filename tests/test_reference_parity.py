@@ -21,7 +21,7 @@ def results():
         pytest.skip("upstream package not installed under baseline/_ref")
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="4")
     env.pop("PYTHONPATH", None)
-    proc = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "reference_parity_worker.py")] + CASES + ["losses", "metrics", "wrapped1", "wrapped2", "wrapped_features", "checkpoints"],
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "reference_parity_worker.py")] + CASES + ["losses", "metrics", "wrapped1", "wrapped2", "wrapped_features", "reshape_fields", "checkpoints"],
                           cwd="/tmp", env=env,
                           capture_output=True, text=True, timeout=900)
     assert proc.returncode == 0, proc.stderr[-2000:]
@@ -86,3 +86,12 @@ def test_zenith_history_and_multistep_match_upstream(results):
     assert len(r["err"]) == 12
     for k, v in r["err"].items():
         assert isinstance(v, float) and v < 1e-5, (k, v)
+
+
+def test_reshape_fields_matches_upstream(results):
+    """Sample preparation of the numpy data path; upstream itself fails on inputs with grid channels (it reshapes by the
+    channel count without them), those combinations are checked for their shape only."""
+    r = results["reshape_fields"]
+    assert len(r["err"]) == 18 and len(r.get("upstream_failed", [])) == 8
+    for k, v in r["err"].items():
+        assert isinstance(v, float) and v < 1e-6, (k, v)

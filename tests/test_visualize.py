@@ -49,3 +49,14 @@ def test_comparison_frame_curves_and_gif(tmp_path):
         w.add(f"step{step}", rng.standard_normal((2, 17, 32)), rng.standard_normal((2, 17, 32)))
     out = w.finalize()
     assert os.path.isfile(out["ch0"])
+
+
+def test_visualize_field_applies_the_functor_to_unscaled_fields():
+    import numpy as np
+
+    from makani_b200.utils.visualize import visualize_field
+
+    rng = np.random.default_rng(0)
+    pred, targ = rng.normal(size=(2, 16, 32)), rng.normal(size=(2, 16, 32))
+    tag, image = visualize_field("wind", "lambda x: np.sqrt(np.square(x[0]) + np.square(x[1]))", pred, targ, None, None, 2.0, 1.0, False)
+    assert tag == "wind" and image is not None and image.size[0] > 0 and image.size[1] > 0
