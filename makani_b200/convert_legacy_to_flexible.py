@@ -58,6 +58,13 @@ def merge_states(states, sizes, sharded_dims):
     return out
 
 
+def get_params(path):
+    """The recipe a run wrote into its experiment directory (`<path>/config.json`), as a params object."""
+    from .utils.YParams import ParamsBase
+
+    return ParamsBase.from_json(os.path.join(path, "config.json"))
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--input_path", required=True, type=str)

@@ -17,6 +17,15 @@ from . import comm
 from .trainer import Trainer
 
 
+def cudaProfilerStart():
+    """Names the reference's profiling trainer exports (makani/utils/trainer_profile.py:54-72, there through ctypes)."""
+    torch.cuda.profiler.start()
+
+
+def cudaProfilerStop():
+    torch.cuda.profiler.stop()
+
+
 class _Window:
     def __init__(self, enabled, start, stop, ranks, world_rank, device):
         self.enabled = enabled and (not ranks or world_rank in ranks)
