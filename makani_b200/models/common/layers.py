@@ -130,9 +130,13 @@ class MLP(nn.Module):
             return linear_ops.mlp2_lastdim(x, self.fwd[0].weight, self.fwd[0].bias, self.fwd[3].weight, self.fwd[3].bias)
         return self.fwd(x)
 
+    def checkpoint_forward(self, x):
+        """The forward pass with its activations recomputed in backward (makani/models/common/layers.py `MLP`)."""
+        return checkpoint(self._run, x, use_reentrant=False)
+
     def forward(self, x):
         if self.checkpointing >= 2 and self.training:
-            return checkpoint(self._run, x, use_reentrant=False)
+            return self.checkpoint_forward(x)
         return self._run(x)
 
 

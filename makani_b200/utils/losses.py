@@ -109,6 +109,23 @@ class GeometricH1Loss(nn.Module):
             return self.alpha * l2 + (1 - self.alpha) * h1
         return self.alpha * torch.sqrt(l2) + (1 - self.alpha) * torch.sqrt(h1)
 
+    def _reduce(self, val, mask=None):
+        if mask is not None:
+            val = val * mask
+        if self.reduction:
+            if self.size_average:
+                return torch.mean(val) if mask is None else torch.sum(val) / torch.sum(mask)
+            return torch.sum(val)
+        return val
+
+    def abs(self, prd, tar):
+        """Absolute H1 error per sample (makani/utils/losses.py:298-318)."""
+        return self._reduce(self._combine(*self._norms2(prd - tar)))
+
+    def rel(self, prd, tar, mask=None):
+        """H1 error relative to the H1 norm of the target (makani/utils/losses.py:320-345)."""
+        return self._reduce(self._combine(*self._norms2(prd - tar)) / self._combine(*self._norms2(tar)), mask)
+
     def forward(self, prd, tar, chw=None, mask=None):
         val = self._combine(*self._norms2(prd - tar))
         if not self.absolute:

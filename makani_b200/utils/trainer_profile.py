@@ -17,13 +17,20 @@ from . import comm
 from .trainer import Trainer
 
 
-def cudaProfilerStart():
-    """Names the reference's profiling trainer exports (makani/utils/trainer_profile.py:54-72, there through ctypes)."""
-    torch.cuda.profiler.start()
+def cudaProfilerStart(device=None, enabled=True):
+    """Names and calling convention of makani/utils/trainer_profile.py:59-74 (there through ctypes): a barrier so that
+    the windows of all ranks line up, then the profiler toggle on the ranks where `enabled`."""
+    if dist.is_initialized():
+        dist.barrier(device_ids=[device.index] if device is not None and device.type == "cuda" else None)
+    if enabled and torch.cuda.is_available():
+        torch.cuda.profiler.start()
 
 
-def cudaProfilerStop():
-    torch.cuda.profiler.stop()
+def cudaProfilerStop(device=None, enabled=True):
+    if enabled and torch.cuda.is_available():
+        torch.cuda.profiler.stop()
+    if dist.is_initialized():
+        dist.barrier(device_ids=[device.index] if device is not None and device.type == "cuda" else None)
 
 
 class _Window:
@@ -131,6 +138,33 @@ class ProfilingTrainer(Trainer):
         self._train_steps = 0
         if self.visualizer is not None:
             self.visualizer = _InstrumentedVisualizer(self.visualizer, self.device)
+
+    def test_model_output(self, model):
+        """Checkpoint self-test (makani/utils/trainer_profile.py:842-866): the first call stores a random input and the
+        model's output for it in the experiment directory; later calls (e.g. after a restore) log how far the output
+        for the same input has moved."""
+        import os
+
+        import numpy as np
+
+        p = self.params
+        hl = p.get("img_local_shape_x", p.img_shape_x)
+        wl = p.get("img_local_shape_y", p.img_shape_y)
+        cin = p.N_in_channels
+        if p.get("split_data_channels", False):
+            cin = (cin + comm.get_size("matmul") - 1) // comm.get_size("matmul")
+        mrank = comm.get_rank("model")
+        f_in = os.path.join(p.experiment_dir, f"random_tensor{mrank}.npy")
+        f_out = os.path.join(p.experiment_dir, f"random_output{mrank}.npy")
+        if not os.path.exists(f_in):
+            np.save(f_in, torch.rand(p.batch_size, cin, hl, wl).numpy())
+        x = torch.from_numpy(np.load(f_in)).float().to(self.device)
+        with torch.no_grad():
+            out = model(x).detach().float().cpu().numpy()
+        if os.path.exists(f_out):
+            diff = (out - np.load(f_out)).ravel()
+            self.logger.info(f"Diff metrics: norm = {np.linalg.norm(diff)}, max = {diff.max()}, min = {diff.min()}")
+        np.save(f_out, out)
 
     def _train_step(self, inp, tar):
         step = self._train_steps

@@ -113,3 +113,19 @@ def test_loss_is_differentiable_and_zero_at_the_target(fields):
 def test_unknown_loss_is_rejected():
     with pytest.raises(ValueError):
         LossHandler(_params(loss="hinge"))
+
+
+def test_h1_loss_abs_and_rel_methods():
+    """`GeometricH1Loss.abs` / `.rel` (the two entry points of the reference's class) agree with `forward`."""
+    import torch
+
+    from makani_b200.utils.losses import GeometricH1Loss
+
+    torch.manual_seed(0)
+    prd, tar = torch.randn(2, 3, 16, 32), torch.randn(2, 3, 16, 32)
+    for squared in (False, True):
+        rel = GeometricH1Loss((16, 32), absolute=False, squared=squared)
+        ab = GeometricH1Loss((16, 32), absolute=True, squared=squared)
+        assert torch.allclose(rel.rel(prd, tar), rel(prd, tar))
+        assert torch.allclose(ab.abs(prd, tar), ab(prd, tar))
+        assert float(ab.abs(prd, prd)) == 0.0
