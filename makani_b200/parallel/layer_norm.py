@@ -93,13 +93,13 @@ class _DistInstanceNormFn(torch.autograd.Function):
 
 
 class DistributedInstanceNorm2d(nn.Module):
-    def __init__(self, num_features, eps=1e-05, affine=False):
+    def __init__(self, num_features, eps=1e-05, affine=False, device=None, dtype=None):
         super().__init__()
         self.eps, self.affine, self.num_features = eps, affine, num_features
         self._counts = {}
         if affine:
-            self.weight = nn.Parameter(torch.ones(num_features))
-            self.bias = nn.Parameter(torch.zeros(num_features))
+            self.weight = nn.Parameter(torch.ones(num_features, device=device, dtype=dtype))
+            self.bias = nn.Parameter(torch.zeros(num_features, device=device, dtype=dtype))
             self.weight.is_shared_mp = ["spatial"]
             self.bias.is_shared_mp = ["spatial"]
 

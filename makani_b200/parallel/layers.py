@@ -241,7 +241,7 @@ class DistributedAttention(nn.Module):
     """Multi-head self attention with heads split over `comm_hidden_name` (sequence stays whole)."""
 
     def __init__(self, dim, input_format="traditional", comm_inp_name="fin", comm_hidden_name="fout", num_heads=8,
-                 qkv_bias=False, attn_drop_rate=0.0, proj_drop_rate=0.0, norm_layer=nn.LayerNorm):
+                 qkv_bias=False, qk_norm=False, attn_drop_rate=0.0, proj_drop_rate=0.0, norm_layer=nn.LayerNorm):
         super().__init__()
         assert dim % num_heads == 0
         assert num_heads % comm.get_size(comm_hidden_name) == 0, "heads must divide over the hidden group"
@@ -255,8 +255,13 @@ class DistributedAttention(nn.Module):
         nn.init.trunc_normal_(self.proj.weight, std=0.02)
         self.attn_drop_rate = attn_drop_rate
         self.proj_drop = nn.Dropout(proj_drop_rate)
-        self.q_norm = norm_layer(self.head_dim) if norm_layer is not None and norm_layer is not nn.Identity else nn.Identity()
-        self.k_norm = norm_layer(self.head_dim) if norm_layer is not None and norm_layer is not nn.Identity else nn.Identity()
+        # per-head normalisation of queries and keys only on request (makani/mpu/layers.py:464,482-483); each rank holds
+        # whole heads, so these small parameters are private to it
+        self.q_norm = norm_layer(self.head_dim) if qk_norm else nn.Identity()
+        self.k_norm = norm_layer(self.head_dim) if qk_norm else nn.Identity()
+        for norm in (self.q_norm, self.k_norm):
+            for prm in norm.parameters():
+                prm.is_shared_mp = []
 
     def forward(self, x):
         B, N, C = x.shape

@@ -517,15 +517,20 @@ class Trainer:
         except Exception:
             pass
 
-    def log_weights_and_grads(self, weights_and_grads_path):
-        """Dump every parameter and its gradient of this model rank to `<path>/weights_and_grads_step{iters}.tar`."""
+    def log_weights_and_grads(self, weights_and_grads_path, model=None, iters=None, epoch=None):
+        """Dump every parameter and its gradient of this model rank to
+        `<path>/weights_and_grads_epoch{epoch}_step{iters}_mp{rank}.tar` (file name of makani/utils/trainer.py:1175-1181);
+        `model`, `iters`, `epoch` default to the trainer's own."""
         if self.data_parallel_rank != 0:
             return
+        model = self.model if model is None else model
+        iters = self.iters if iters is None else iters
+        epoch = self.epoch if epoch is None else epoch
         os.makedirs(weights_and_grads_path, exist_ok=True)
-        weights = {k: v.detach().cpu() for k, v in self.model.named_parameters()}
-        grads = {k: v.grad.detach().cpu() for k, v in self.model.named_parameters() if v.grad is not None}
-        fname = os.path.join(weights_and_grads_path, f"weights_and_grads_step{self.iters:05d}_mp{comm.get_rank('model')}.tar")
-        torch.save({"step": self.iters, "weights": weights, "grads": grads}, fname)
+        weights = {k: v.detach().cpu() for k, v in model.named_parameters()}
+        grads = {k: v.grad.detach().cpu() for k, v in model.named_parameters() if v.grad is not None}
+        fname = os.path.join(weights_and_grads_path, f"weights_and_grads_epoch{epoch}_step{iters}_mp{comm.get_rank('model')}.tar")
+        torch.save({"step": iters, "epoch": epoch, "weights": weights, "grads": grads}, fname)
 
     # ------------------------------------------------------------------------------------------ checkpoints
     def save_checkpoint(self, checkpoint_path, model=None, checkpoint_mode="flexible"):
