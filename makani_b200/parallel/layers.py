@@ -265,7 +265,9 @@ class DistributedAttention(nn.Module):
 
     def forward(self, x):
         B, N, C = x.shape
-        qkv = self.qkv(x).reshape(B, N, self.num_heads_local, 3, self.head_dim).permute(3, 0, 2, 1, 4)
+        # local rows of the qkv projection are ordered (q | k | v, local head, head_dim), as in makani/mpu/layers.py:507:
+        # at one rank that is the serial layout, and a rank's rows are the q, k and v rows of its own heads
+        qkv = self.qkv(x).reshape(B, N, 3, self.num_heads_local, self.head_dim).permute(2, 0, 3, 1, 4)
         q, k, v = qkv.unbind(0)
         q, k = self.q_norm(q), self.k_norm(k)
         y = F.scaled_dot_product_attention(q, k, v, dropout_p=self.attn_drop_rate if self.training else 0.0)

@@ -531,6 +531,45 @@ def case_patch_embed():
     assert _rel(xl.grad, split_tensor_along_dim(xr.grad, 1, msize)[mrank]) < 1e-5
 
 
+def case_attention():
+    """Channel-parallel attention == serial attention when every rank holds the q, k and v rows of its own heads (and
+    its slice of the input features), for fin x fout splits."""
+    from makani_b200.models.networks.vit import Attention
+    from makani_b200.parallel.layers import DistributedAttention
+    torch.manual_seed(4)
+    B, N, C, H = 2, 7, 16, 4
+    hd = C // H
+    nfi, nfo, fi, fo = comm.get_size("fin"), comm.get_size("fout"), comm.get_rank("fin"), comm.get_rank("fout")
+    ser = Attention(C, num_heads=H, qkv_bias=True)
+    with torch.no_grad():
+        for prm in ser.parameters():
+            prm.copy_(torch.randn_like(prm) * 0.3)
+    layer = DistributedAttention(C, input_format="traditional", comm_inp_name="fin", comm_hidden_name="fout", num_heads=H, qkv_bias=True)
+    hl = H // nfo
+    rows = torch.cat([torch.arange(part * C + (fo * hl) * hd, part * C + ((fo + 1) * hl) * hd) for part in range(3)])
+    cin = slice(fi * (C // nfi), (fi + 1) * (C // nfi))
+    hid = slice(fo * hl * hd, (fo + 1) * hl * hd)
+    with torch.no_grad():
+        layer.qkv.weight.copy_(ser.qkv.weight[rows][:, cin].reshape(layer.qkv.weight.shape))
+        # the bias is added after the reduction over the input-parallel ranks: every rank holds it for its output rows
+        layer.qkv.bias.copy_(ser.qkv.bias[rows].reshape(layer.qkv.bias.shape))
+        layer.proj.weight.copy_(ser.proj.weight[cin][:, hid].reshape(layer.proj.weight.shape))
+    x = torch.randn(B, N, C)
+    xr = x.clone().requires_grad_()
+    y_ref = ser(xr)
+    if getattr(ser.proj, "bias", None) is not None:
+        y_ref = y_ref - ser.proj.bias
+    xl = x[..., cin].contiguous().requires_grad_()
+    y = layer(xl)
+    assert y.shape == (B, N, C // nfi)
+    assert _rel(y, y_ref[..., cin]) < 1e-5
+    g = torch.randn_like(y_ref)
+    y_ref.backward(g)
+    y.backward(g[..., cin].contiguous())
+    assert _rel(xl.grad, xr.grad[..., cin]) < 1e-5
+    assert _rel(layer.qkv.weight.grad.reshape(len(rows), -1), ser.qkv.weight.grad[rows][:, cin]) < 1e-5
+
+
 def case_reduction_hooks():
     """`init_gradient_reduction_hooks` in a plain user loop: after every backward pass the gradients equal the average
     over the data-parallel ranks of what a serial model gets on each rank's batch, with either flavour of zero_grad,

@@ -386,6 +386,65 @@ def run_reshape_fields():
     return out
 
 
+def run_mpu_layers():
+    """The channel-parallel layer classes of `makani.mpu` against `makani_b200.parallel` on one rank: same state dict,
+    and with the same (random) weights the same output, input gradient and parameter gradients."""
+    from makani.mpu import layer_norm as RN
+    from makani.mpu import layers as RL
+    from makani.utils import comm
+
+    sizes, names = [1, 1, 1, 1], ["h", "w", "fin", "fout"]
+    comm.init(model_parallel_sizes=sizes, model_parallel_names=names, verbose=False)
+    if ROOT not in sys.path:
+        sys.path.append(ROOT)
+    from makani_b200.parallel import layer_norm as MN
+    from makani_b200.parallel import layers as ML
+    from makani_b200.utils import comm as my_comm
+
+    my_comm.init(model_parallel_sizes=sizes, model_parallel_names=names)
+    gelu = torch.nn.GELU
+    cases = [
+        ("matmul_nchw", "DistributedMatmul", RL, ML, dict(inp_dim=6, out_dim=5, input_format="nchw", bias=True), (2, 6, 8, 16)),
+        ("matmul_tokens", "DistributedMatmul", RL, ML, dict(inp_dim=6, out_dim=5, input_format="traditional", bias=True), (2, 7, 6)),
+        ("mlp_nchw", "DistributedMLP", RL, ML, dict(in_features=6, hidden_features=12, out_features=6, input_format="nchw", act_layer=gelu), (2, 6, 8, 16)),
+        ("mlp_tokens", "DistributedMLP", RL, ML, dict(in_features=6, hidden_features=12, out_features=6, input_format="traditional", act_layer=gelu), (2, 9, 6)),
+        ("patch_embed", "DistributedPatchEmbed", RL, ML, dict(img_size=(16, 32), patch_size=(4, 4), in_chans=3, embed_dim=8,
+                                                              input_is_matmul_parallel=False, output_is_matmul_parallel=True), (2, 3, 16, 32)),
+        ("attention_bias", "DistributedAttention", RL, ML, dict(dim=16, input_format="traditional", num_heads=4, qkv_bias=True), (2, 9, 16)),
+        ("attention_qk_norm", "DistributedAttention", RL, ML, dict(dim=16, input_format="traditional", num_heads=4, qk_norm=True), (2, 9, 16)),
+        ("layer_norm", "DistributedLayerNorm", RN, MN, dict(normalized_shape=5, elementwise_affine=True), (2, 5, 8, 16)),
+        ("real_fft2", "DistributedRealFFT2", RL, ML, dict(nlat=8, nlon=16), (2, 3, 8, 16)),
+    ]
+    out = {"case": "mpu_layers", "err": {}}
+    for tag, name, R, M, kw, shape in cases:
+        torch.manual_seed(0)
+        r, m = getattr(R, name)(**kw), getattr(M, name)(**kw)
+        sr, sm = r.state_dict(), m.state_dict()
+        if set(sr) != set(sm) or any(tuple(sr[k].shape) != tuple(sm[k].shape) for k in sr):
+            out["err"][tag] = f"state dict differs: {sorted(set(sr) ^ set(sm))}"
+            continue
+        with torch.no_grad():
+            for prm in r.parameters():       # the upstream classes start from all-ones weights: that hides any re-ordering
+                prm.copy_(torch.randn_like(prm) * 0.3)
+        m.load_state_dict(r.state_dict())
+        x = torch.randn(*shape)
+        xr, xm = x.clone().requires_grad_(), x.clone().requires_grad_()
+        yr, ym = r(xr), m(xm)
+        if tuple(yr.shape) != tuple(ym.shape):
+            out["err"][tag] = f"output shape {tuple(yr.shape)} vs {tuple(ym.shape)}"
+            continue
+        worst = rel(ym, yr)
+        yr.abs().square().sum().backward()
+        ym.abs().square().sum().backward()
+        worst = max(worst, rel(xm.grad, xr.grad))
+        gm = dict(m.named_parameters())
+        for n, prm in r.named_parameters():
+            if prm.grad is not None:
+                worst = max(worst, rel(gm[n].grad, prm.grad))
+        out["err"][tag] = worst
+    return out
+
+
 def run_checkpoints():
     """A checkpoint written by the upstream trainer (legacy and flexible format) restores into this framework's model
     and optimiser, and a checkpoint written here restores into the upstream trainer."""
@@ -461,7 +520,7 @@ if __name__ == "__main__":
     import makani
 
     assert os.path.realpath(makani.__file__).startswith(os.path.realpath(os.path.join(ROOT, "baseline", "_ref"))), makani.__file__
-    for name in (sys.argv[1:] or list(CASES) + ["losses", "metrics", "wrapped1", "wrapped2", "wrapped_features", "reshape_fields", "checkpoints"]):
+    for name in (sys.argv[1:] or list(CASES) + ["losses", "metrics", "wrapped1", "wrapped2", "wrapped_features", "reshape_fields", "mpu_layers", "checkpoints"]):
         if name == "losses":
             res = run_losses()
         elif name == "metrics":
@@ -472,6 +531,8 @@ if __name__ == "__main__":
             res = run_wrapped_features()
         elif name == "reshape_fields":
             res = run_reshape_fields()
+        elif name == "mpu_layers":
+            res = run_mpu_layers()
         elif name.startswith("wrapped"):
             res = run_wrapped(int(name[len("wrapped"):]))
         else:

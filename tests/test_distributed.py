@@ -111,3 +111,8 @@ def test_distributed_patch_embed(sizes):
 def test_gradient_reduction_hooks_in_a_plain_loop(world):
     """`init_gradient_reduction_hooks` (the upstream entry point for user loops) on 2 and 3 data-parallel ranks."""
     _launch("reduction_hooks", (1, 1, 1, 1), world)
+
+
+@pytest.mark.parametrize("sizes", [(1, 1, 1, 2), (1, 1, 2, 1), (1, 1, 2, 2)])
+def test_channel_parallel_attention_matches_serial(sizes):
+    _launch("attention", sizes, sizes[2] * sizes[3])
