@@ -77,6 +77,12 @@ def run(name):
     out["shape_mismatch"] = [k for k in sr if k in sm and tuple(sr[k].shape) != tuple(sm[k].shape)]
     if out["only_upstream"] or out["only_here"] or out["shape_mismatch"]:
         return out
+    # random values everywhere (biases, norm weights, position embeddings start from constants, which would hide a
+    # re-ordering), scaled so that activations stay of order one
+    with torch.no_grad():
+        for prm in ref.parameters():
+            prm.add_(torch.randn_like(prm) * 0.05)
+    sr = ref.state_dict()
     mine.load_state_dict(sr, strict=True)
     torch.manual_seed(1)
     x = torch.randn(2, cin, *hw)
