@@ -51,7 +51,8 @@ class ComplexActivation(nn.Module):
         if mode == "modulus":
             self.bias = nn.Parameter(torch.zeros(bias_shape if bias_shape is not None else 1, dtype=torch.float32))
         else:
-            self.bias = None
+            # an unused one-element buffer, part of the state dict exactly as in makani/models/common/activations.py:81-83
+            self.register_buffer("bias", torch.zeros(1, dtype=torch.float32))
 
     def forward(self, z):
         if self.mode == "cartesian":

@@ -451,6 +451,90 @@ def run_mpu_layers():
     return out
 
 
+def run_common_layers():
+    """Building blocks of `makani.models.common` against this framework's, one by one, with random weights: MLP,
+    EncoderDecoder, the FFT wrappers, the complex activations and the spectral convolution (SHT and FFT flavours)."""
+    import torch_harmonics as th
+    from makani.models.common import activations as RA
+    from makani.models.common import layers as RL
+    from makani.models.common import spectral_convolution as RS
+    from makani.utils import comm
+
+    sizes, names = [1, 1, 1, 1], ["h", "w", "fin", "fout"]
+    comm.init(model_parallel_sizes=sizes, model_parallel_names=names, verbose=False)
+    if ROOT not in sys.path:
+        sys.path.append(ROOT)
+    from makani_b200.models.common import activations as MA
+    from makani_b200.models.common import layers as ML
+    from makani_b200.models.common import spectral_convolution as MS
+    from makani_b200.sht import sht as my_sht
+    from makani_b200.utils import comm as my_comm
+
+    my_comm.init(model_parallel_sizes=sizes, model_parallel_names=names)
+    gelu, nlat, nlon = torch.nn.GELU, 16, 32
+    real, cplx, spec = (2, 6, 8, 16), "complex", "spectral"
+
+    def build(tag):
+        if tag == "spectral_conv_sht":
+            kw = dict(operator_type="dhconv", bias=True)
+            return (RS.SpectralConv(th.RealSHT(nlat, nlon, grid="legendre-gauss").float(), th.InverseRealSHT(nlat, nlon, grid="legendre-gauss").float(), 6, 6, **kw),
+                    MS.SpectralConv(my_sht.RealSHT(nlat, nlon, grid="legendre-gauss"), my_sht.InverseRealSHT(nlat, nlon, grid="legendre-gauss"), 6, 6, **kw))
+        if tag == "spectral_conv_fft":
+            kw = dict(operator_type="dhconv", bias=False)
+            return (RS.SpectralConv(RL.RealFFT2(nlat, nlon), RL.InverseRealFFT2(nlat, nlon), 6, 6, **kw),
+                    MS.SpectralConv(ML.RealFFT2(nlat, nlon), ML.InverseRealFFT2(nlat, nlon), 6, 6, **kw))
+        raise KeyError(tag)
+
+    cases = [
+        ("mlp_nchw", "MLP", RL, ML, dict(in_features=6, hidden_features=12, out_features=5, act_layer=gelu, output_bias=True, input_format="nchw"), real),
+        ("mlp_tokens", "MLP", RL, ML, dict(in_features=6, hidden_features=12, out_features=5, act_layer=gelu, output_bias=False, input_format="traditional"), (2, 9, 6)),
+        ("encoder_nchw", "EncoderDecoder", RL, ML, dict(num_layers=2, input_dim=6, output_dim=5, hidden_dim=8, act_layer=gelu, input_format="nchw"), real),
+        ("encoder_tokens", "EncoderDecoder", RL, ML, dict(num_layers=1, input_dim=6, output_dim=5, hidden_dim=8, act_layer=gelu, input_format="traditional"), (2, 9, 6)),
+        ("rfft2", "RealFFT2", RL, ML, dict(nlat=8, nlon=16, lmax=6, mmax=5), real),
+        ("irfft2", "InverseRealFFT2", RL, ML, dict(nlat=8, nlon=16, lmax=6, mmax=5), spec),
+        ("crelu_cartesian", "ComplexReLU", RA, MA, dict(negative_slope=0.1, mode="cartesian", bias_shape=(3, 1, 1)), cplx),
+        ("crelu_modulus", "ComplexReLU", RA, MA, dict(negative_slope=0.0, mode="modulus", bias_shape=(3, 1, 1), scale=2.0), cplx),
+        ("crelu_real", "ComplexReLU", RA, MA, dict(negative_slope=0.0, mode="real"), cplx),
+        ("cact_cartesian", "ComplexActivation", RA, MA, dict(activation=torch.nn.Tanh(), mode="cartesian", bias_shape=(3, 1, 1)), cplx),
+        ("cact_modulus", "ComplexActivation", RA, MA, dict(activation=torch.nn.Tanh(), mode="modulus", bias_shape=(3, 1, 1)), cplx),
+        ("spectral_conv_sht", None, None, None, None, (2, 6, nlat, nlon)),
+        ("spectral_conv_fft", None, None, None, None, (2, 6, nlat, nlon)),
+    ]
+    out = {"case": "common_layers", "err": {}}
+    for tag, name, R, M, kw, shape in cases:
+        torch.manual_seed(0)
+        r, m = build(tag) if name is None else (getattr(R, name)(**kw), getattr(M, name)(**kw))
+        sr, sm = r.state_dict(), m.state_dict()
+        if set(sr) != set(sm) or any(tuple(sr[k].shape) != tuple(sm[k].shape) for k in sr):
+            out["err"][tag] = f"state dict differs: {sorted(set(sr) ^ set(sm))}"
+            continue
+        with torch.no_grad():
+            for prm in r.parameters():
+                prm.copy_(torch.randn_like(prm) * 0.3)
+        m.load_state_dict(r.state_dict())
+        x = (torch.randn(2, 3, 8, 9, dtype=torch.complex64) if shape == cplx
+             else torch.randn(2, 3, 6, 5, dtype=torch.complex64) if shape == spec else torch.randn(*shape))
+        xr, xm = x.clone().requires_grad_(), x.clone().requires_grad_()
+        yr, ym = r(xr), m(xm)
+        worst = 0.0
+        if isinstance(yr, tuple):                      # spectral convolutions also return the (regridded) residual
+            worst = rel(ym[1], yr[1])
+            yr, ym = yr[0], ym[0]
+        if tuple(yr.shape) != tuple(ym.shape):
+            out["err"][tag] = f"output shape {tuple(yr.shape)} vs {tuple(ym.shape)}"
+            continue
+        worst = max(worst, rel(ym, yr))
+        yr.abs().square().sum().backward()
+        ym.abs().square().sum().backward()
+        worst = max(worst, rel(xm.grad, xr.grad))
+        gm = dict(m.named_parameters())
+        for n, prm in r.named_parameters():
+            if prm.grad is not None:
+                worst = max(worst, rel(gm[n].grad, prm.grad))
+        out["err"][tag] = worst
+    return out
+
+
 def run_checkpoints():
     """A checkpoint written by the upstream trainer (legacy and flexible format) restores into this framework's model
     and optimiser, and a checkpoint written here restores into the upstream trainer."""
@@ -526,7 +610,7 @@ if __name__ == "__main__":
     import makani
 
     assert os.path.realpath(makani.__file__).startswith(os.path.realpath(os.path.join(ROOT, "baseline", "_ref"))), makani.__file__
-    for name in (sys.argv[1:] or list(CASES) + ["losses", "metrics", "wrapped1", "wrapped2", "wrapped_features", "reshape_fields", "mpu_layers", "checkpoints"]):
+    for name in (sys.argv[1:] or list(CASES) + ["losses", "metrics", "wrapped1", "wrapped2", "wrapped_features", "reshape_fields", "mpu_layers", "common_layers", "checkpoints"]):
         if name == "losses":
             res = run_losses()
         elif name == "metrics":
@@ -539,6 +623,8 @@ if __name__ == "__main__":
             res = run_reshape_fields()
         elif name == "mpu_layers":
             res = run_mpu_layers()
+        elif name == "common_layers":
+            res = run_common_layers()
         elif name.startswith("wrapped"):
             res = run_wrapped(int(name[len("wrapped"):]))
         else:
