@@ -535,6 +535,36 @@ def run_common_layers():
     return out
 
 
+def run_grids():
+    """Grid conversion, quadrature weights (three rules, cropped and normalised) and the auxiliary channel names."""
+    import numpy as np
+    from makani.utils import features as RF
+    from makani.utils import grids as RG
+
+    if ROOT not in sys.path:
+        sys.path.append(ROOT)
+    from makani_b200.utils import features as MF
+    from makani_b200.utils import grids as MG
+
+    out = {"case": "grids", "err": {}}
+    lat = torch.linspace(np.pi / 2, -np.pi / 2, 17).double()
+    lon = torch.linspace(0, 2 * np.pi, 33)[:-1].double()
+    torch.manual_seed(0)
+    x = torch.randn(2, 3, 17, 32)
+    for src, dst in (("equiangular", "legendre-gauss"), ("equiangular", "equiangular")):
+        r, m = RG.GridConverter(src, dst, lat, lon), MG.GridConverter(src, dst, lat, lon)
+        out["err"][f"converter:{src}:{dst}"] = max(rel(m(x), r(x)), rel(torch.as_tensor(m.get_dst_coords()[0]), torch.as_tensor(r.get_dst_coords()[0])))
+    for rule in ("naive", "clenshaw-curtiss", "legendre-gauss"):
+        for tag, kw in (("full", {}), ("crop", dict(crop_shape=(8, 16), crop_offset=(4, 8))), ("normalized", dict(normalize=True))):
+            r, m = RG.GridQuadrature(rule, (17, 32), **kw), MG.GridQuadrature(rule, (17, 32), **kw)
+            xx = x[..., :8, :16] if tag == "crop" else x
+            out["err"][f"quadrature:{rule}:{tag}"] = rel(m(xx), r(xx))
+    for i, kw in enumerate((dict(add_zenith=True, add_grid=True, grid_type="sinusoidal", grid_num_frequencies=2, add_orography=True, add_landmask=True),
+                            dict(add_grid=True, grid_type="linear", add_landmask=True), dict(add_zenith=True))):
+        out["err"][f"aux_channels:{i}"] = 0.0 if RF.get_auxiliary_channels(**kw) == MF.get_auxiliary_channels(**kw) else 1.0
+    return out
+
+
 def run_checkpoints():
     """A checkpoint written by the upstream trainer (legacy and flexible format) restores into this framework's model
     and optimiser, and a checkpoint written here restores into the upstream trainer."""
@@ -610,7 +640,7 @@ if __name__ == "__main__":
     import makani
 
     assert os.path.realpath(makani.__file__).startswith(os.path.realpath(os.path.join(ROOT, "baseline", "_ref"))), makani.__file__
-    for name in (sys.argv[1:] or list(CASES) + ["losses", "metrics", "wrapped1", "wrapped2", "wrapped_features", "reshape_fields", "mpu_layers", "common_layers", "checkpoints"]):
+    for name in (sys.argv[1:] or list(CASES) + ["losses", "metrics", "wrapped1", "wrapped2", "wrapped_features", "reshape_fields", "mpu_layers", "common_layers", "grids", "checkpoints"]):
         if name == "losses":
             res = run_losses()
         elif name == "metrics":
@@ -625,6 +655,8 @@ if __name__ == "__main__":
             res = run_mpu_layers()
         elif name == "common_layers":
             res = run_common_layers()
+        elif name == "grids":
+            res = run_grids()
         elif name.startswith("wrapped"):
             res = run_wrapped(int(name[len("wrapped"):]))
         else:

@@ -21,7 +21,7 @@ def results():
         pytest.skip("upstream package not installed under baseline/_ref")
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="4")
     env.pop("PYTHONPATH", None)
-    proc = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "reference_parity_worker.py")] + CASES + ["losses", "metrics", "wrapped1", "wrapped2", "wrapped_features", "reshape_fields", "mpu_layers", "common_layers", "checkpoints"],
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "reference_parity_worker.py")] + CASES + ["losses", "metrics", "wrapped1", "wrapped2", "wrapped_features", "reshape_fields", "mpu_layers", "common_layers", "grids", "checkpoints"],
                           cwd="/tmp", env=env,
                           capture_output=True, text=True, timeout=900)
     assert proc.returncode == 0, proc.stderr[-2000:]
@@ -107,5 +107,12 @@ def test_channel_parallel_layers_match_upstream_on_one_rank(results):
 def test_common_building_blocks_match_upstream(results):
     r = results["common_layers"]
     assert len(r["err"]) == 13
+    for k, v in r["err"].items():
+        assert isinstance(v, float) and v < 1e-5, (k, v)
+
+
+def test_grids_quadrature_and_feature_names_match_upstream(results):
+    r = results["grids"]
+    assert len(r["err"]) == 14
     for k, v in r["err"].items():
         assert isinstance(v, float) and v < 1e-5, (k, v)
