@@ -2,10 +2,11 @@
 (optionally) a bf16 shadow copy, reading the hyper-parameters from device memory so that the launch can be
 replayed from a CUDA graph while the learning rate and step count change.
 
-Complex parameters are stored as complex64 and updated through their interleaved real view.  Two second-moment
-conventions exist in the reference's patched optimisers (makani/third_party/torch/optim/adam.py:391 uses
-g * conj(g), adamw.py:409 squares the complex number); `complex_mode="modulus"` (default) shares |g|^2 between
-the real and imaginary parts, `complex_mode="split"` treats them as independent reals (stock PyTorch).
+Complex parameters are stored as complex64 and updated through their interleaved real view.
+`complex_mode="split"` (default) treats real and imaginary parts as independent reals: that is stock
+`torch.optim.AdamW`, which the reference's trainer instantiates (makani/utils/trainer.py:426-433).
+`complex_mode="modulus"` shares |g|^2 between the two parts, the convention of the patched optimisers the reference
+ships but does not use (makani/third_party/torch/optim/adam.py:391).
 """
 
 from __future__ import annotations
@@ -23,7 +24,7 @@ _CHUNK = 1 << 16
 
 class FusedAdamW(torch.optim.Optimizer):
     def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, adamw: bool = True,
-                 complex_mode: str = "modulus", grad_scale: float = 1.0):
+                 complex_mode: str = "split", grad_scale: float = 1.0):
         defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
         super().__init__(params, defaults)
         self.adamw = adamw

@@ -216,7 +216,8 @@ class Trainer:
         ot = p.optimizer_type
         if ot in ("Adam", "AdamW", "FusedAdam"):
             if self.device.type == "cuda":
-                return FusedAdamW(params, lr=p.lr, betas=betas, weight_decay=p.weight_decay, adamw=(ot != "Adam"))
+                return FusedAdamW(params, lr=p.lr, betas=betas, weight_decay=p.weight_decay, adamw=(ot != "Adam"),
+                                  complex_mode=p.get("optimizer_complex_mode", "split"))
             cls = torch.optim.Adam if ot == "Adam" else torch.optim.AdamW
             return cls(params, betas=betas, lr=p.lr, weight_decay=p.weight_decay)
         if ot == "SGD":

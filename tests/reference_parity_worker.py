@@ -565,6 +565,66 @@ def run_grids():
     return out
 
 
+def run_training_steps():
+    """Five optimisation steps of the two stacks side by side (wrapped SFNO with two-step training, LossHandler, AdamW
+    with weight decay; the upstream side uses what its trainer instantiates, this side the fused optimiser's CPU path):
+    the loss curves and the final weights, complex spectral weights included, stay together."""
+    from makani.utils.losses import LossHandler as RefLoss
+
+    tr, params, recipe = _upstream_trainer(2, dict(add_grid=False))
+    if ROOT not in sys.path:
+        sys.path.append(ROOT)
+    from makani_b200.models import model_registry as my_registry
+    from makani_b200.ops.optim import FusedAdamW
+    from makani_b200.utils.losses import LossHandler as MyLoss
+    from makani_b200.utils.YParams import YParams as MyY
+
+    mp = MyY(recipe, "sfno_tiny")
+    for k, v in params.to_dict().items():
+        mp[k] = v
+    ref, mine = tr.model, my_registry.get_model(mp)
+    mine.load_state_dict(ref.state_dict(), strict=True)
+    lr_, lm_ = RefLoss(params), MyLoss(mp)
+    betas = (params.optimizer_beta1, params.optimizer_beta2)
+    opt_r = torch.optim.AdamW(ref.parameters(), betas=betas, lr=1e-2, weight_decay=0.05, foreach=True)
+    opt_m = FusedAdamW(mine.parameters(), betas=betas, lr=1e-2, weight_decay=0.05)
+    nlat, nlon, C = params.img_shape_x, params.img_shape_y, len(params.channel_names)
+    out = {"case": "training_steps", "loss": [], "has_complex": any(p.is_complex() for p in ref.parameters())}
+    ref.train()
+    mine.train()
+    lr_.train()
+    lm_.train()
+    for step in range(5):
+        g = torch.Generator().manual_seed(step)
+        inp, tar = torch.randn(2, C, nlat, nlon, generator=g), torch.randn(2, 2 * C, nlat, nlon, generator=g)
+        losses = []
+        for model, loss_fn, opt in ((ref, lr_, opt_r), (mine, lm_, opt_m)):
+            opt.zero_grad(set_to_none=True)
+            loss = loss_fn(model(inp.clone()), tar.clone(), inp.clone())
+            loss.backward()
+            opt.step()
+            losses.append(float(loss))
+        out["loss"].append(abs(losses[1] - losses[0]) / abs(losses[0]))
+    # Adam turns a gradient that is zero in exact arithmetic (a bias in front of an instance norm) into steps of +-lr
+    # whose sign is rounding noise: such parameters are left out of the comparison
+    pm = dict(mine.named_parameters())
+    largest = max(p.grad.abs().max().item() for p in ref.parameters() if p.grad is not None)
+    live = [n for n, p in ref.named_parameters() if p.grad is not None and p.grad.abs().max().item() > 1e-4 * largest]
+    out["compared"], out["left_out"] = len(live), len(pm) - len(live)
+    pr = dict(ref.named_parameters())
+
+    def masked_rel(n):
+        # the same holds element by element inside a tensor (e.g. spectral weights of modes that carry no signal)
+        a, b, g = pm[n].detach(), pr[n].detach(), pr[n].grad
+        if a.is_complex():
+            a, b, g = torch.view_as_real(a), torch.view_as_real(b), torch.view_as_real(g)
+        keep = g.abs() > 1e-3 * g.abs().max()
+        return ((a - b)[keep].double().norm() / (b[keep].double().norm() + 1e-30)).item()
+
+    out["weights"] = max(masked_rel(n) for n in live)
+    return out
+
+
 def run_checkpoints():
     """A checkpoint written by the upstream trainer (legacy and flexible format) restores into this framework's model
     and optimiser, and a checkpoint written here restores into the upstream trainer."""
@@ -640,7 +700,7 @@ if __name__ == "__main__":
     import makani
 
     assert os.path.realpath(makani.__file__).startswith(os.path.realpath(os.path.join(ROOT, "baseline", "_ref"))), makani.__file__
-    for name in (sys.argv[1:] or list(CASES) + ["losses", "metrics", "wrapped1", "wrapped2", "wrapped_features", "reshape_fields", "mpu_layers", "common_layers", "grids", "checkpoints"]):
+    for name in (sys.argv[1:] or list(CASES) + ["losses", "metrics", "wrapped1", "wrapped2", "wrapped_features", "reshape_fields", "mpu_layers", "common_layers", "grids", "training_steps", "checkpoints"]):
         if name == "losses":
             res = run_losses()
         elif name == "metrics":
@@ -657,6 +717,8 @@ if __name__ == "__main__":
             res = run_common_layers()
         elif name == "grids":
             res = run_grids()
+        elif name == "training_steps":
+            res = run_training_steps()
         elif name.startswith("wrapped"):
             res = run_wrapped(int(name[len("wrapped"):]))
         else:

@@ -21,7 +21,7 @@ def results():
         pytest.skip("upstream package not installed under baseline/_ref")
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="4")
     env.pop("PYTHONPATH", None)
-    proc = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "reference_parity_worker.py")] + CASES + ["losses", "metrics", "wrapped1", "wrapped2", "wrapped_features", "reshape_fields", "mpu_layers", "common_layers", "grids", "checkpoints"],
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "reference_parity_worker.py")] + CASES + ["losses", "metrics", "wrapped1", "wrapped2", "wrapped_features", "reshape_fields", "mpu_layers", "common_layers", "grids", "training_steps", "checkpoints"],
                           cwd="/tmp", env=env,
                           capture_output=True, text=True, timeout=900)
     assert proc.returncode == 0, proc.stderr[-2000:]
@@ -116,3 +116,13 @@ def test_grids_quadrature_and_feature_names_match_upstream(results):
     assert len(r["err"]) == 14
     for k, v in r["err"].items():
         assert isinstance(v, float) and v < 1e-5, (k, v)
+
+
+def test_five_training_steps_track_upstream(results):
+    """Same model, data, loss and AdamW hyper-parameters on both stacks: loss curve and weights (where the gradient is not
+    rounding noise) stay together; the model has complex spectral weights, so this pins the optimiser's complex
+    convention to the one of the upstream trainer (stock `torch.optim.AdamW`)."""
+    r = results["training_steps"]
+    assert r["has_complex"] and r["compared"] >= 20
+    assert max(r["loss"]) < 1e-5, r
+    assert r["weights"] < 1e-4, r
