@@ -10,3 +10,6 @@ def timezone(name):
     if name.upper() != "UTC":
         raise ValueError("only UTC is available in this stand-in")
     return utc
+
+
+__version__ = "2024.1"      # pandas asks for the version of every optional dependency it finds

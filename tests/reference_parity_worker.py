@@ -625,6 +625,54 @@ def run_training_steps():
     return out
 
 
+def run_metrics_handler():
+    """`MetricsHandler` of both packages fed with the same rollout: scalar logs, ACC / RMSE curves and the rollout table."""
+    os.environ["TORCHDYNAMO_DISABLE"] = "1"       # upstream wraps its metric handles in torch.compile
+    import numpy as np
+
+    tr, params, recipe = _upstream_trainer(1, dict(add_grid=False, dhours=6, dt=1))
+    from makani.utils.metric import MetricsHandler as RefHandler
+
+    if ROOT not in sys.path:
+        sys.path.append(ROOT)
+    from makani_b200.utils.metric import MetricsHandler as MyHandler
+    from makani_b200.utils.YParams import YParams as MyY
+
+    mp = MyY(recipe, "sfno_tiny")
+    for k, v in params.to_dict().items():
+        mp[k] = v
+    names = list(params.channel_names)
+    C, H, W = len(names), params.img_shape_x, params.img_shape_y
+    torch.manual_seed(0)
+    mult, clim, dev = torch.rand(C) + 0.5, torch.randn(C, H, W) * 0.1, torch.device("cpu")
+    kw = dict(rmse_var_names=names, acc_vars_names=names, acc_auc_var_names=names)
+    r, m = RefHandler(params, mult, clim, dev, **kw), MyHandler(mp, mult.clone(), clim.clone(), dev, **kw)
+    for h in (r, m):
+        h.initialize_buffers()
+        h.zero_buffers()
+    for it in range(3):
+        for idt in range(params.valid_autoreg_steps + 1):
+            p, t = torch.randn(2, C, H, W), torch.randn(2, C, H, W)
+            loss = torch.tensor(1.0 + 0.1 * (it + idt))
+            r.update(p.clone(), t.clone(), loss.clone(), idt)
+            m.update(p.clone(), t.clone(), loss.clone(), idt)
+    (lr, acc_r, rmse_r), (lm, acc_m, rmse_m) = r.finalize(final_inference=True), m.finalize(final_inference=True)
+    out = {"case": "metrics_handler", "err": {"acc_curve": rel(acc_m, acc_r), "rmse_curve": rel(rmse_m, rmse_r)}}
+    for sec in ("base", "metrics"):
+        for k, v in lr[sec].items():
+            if k == "rollouts":
+                continue
+            out["err"][f"{sec}/{k}"] = (abs(float(lm[sec][k]) - float(v)) / (abs(float(v)) + 1e-30)) if k in lm[sec] else "missing here"
+    rows_r = [list(row) for row in lr["metrics"]["rollouts"].data]
+    tab = lm["metrics"]["rollouts"]
+    rows_m = [list(row) for row in (tab["data"] if isinstance(tab, dict) else tab.data)]
+    same_labels = [x[:3] for x in rows_r] == [x[:3] for x in rows_m]
+    vals = max(abs(float(a[3]) - float(b[3])) / (abs(float(a[3])) + 1e-30) for a, b in zip(rows_r, rows_m)) if same_labels else 1.0
+    out["err"]["rollout_table"] = vals if same_labels and len(rows_r) == len(rows_m) else "labels differ"
+    out["table_rows"] = len(rows_r)
+    return out
+
+
 def run_checkpoints():
     """A checkpoint written by the upstream trainer (legacy and flexible format) restores into this framework's model
     and optimiser, and a checkpoint written here restores into the upstream trainer."""
@@ -700,7 +748,7 @@ if __name__ == "__main__":
     import makani
 
     assert os.path.realpath(makani.__file__).startswith(os.path.realpath(os.path.join(ROOT, "baseline", "_ref"))), makani.__file__
-    for name in (sys.argv[1:] or list(CASES) + ["losses", "metrics", "wrapped1", "wrapped2", "wrapped_features", "reshape_fields", "mpu_layers", "common_layers", "grids", "training_steps", "checkpoints"]):
+    for name in (sys.argv[1:] or list(CASES) + ["losses", "metrics", "wrapped1", "wrapped2", "wrapped_features", "reshape_fields", "mpu_layers", "common_layers", "grids", "training_steps", "metrics_handler", "checkpoints"]):
         if name == "losses":
             res = run_losses()
         elif name == "metrics":
@@ -719,6 +767,8 @@ if __name__ == "__main__":
             res = run_grids()
         elif name == "training_steps":
             res = run_training_steps()
+        elif name == "metrics_handler":
+            res = run_metrics_handler()
         elif name.startswith("wrapped"):
             res = run_wrapped(int(name[len("wrapped"):]))
         else:

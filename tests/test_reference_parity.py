@@ -21,7 +21,7 @@ def results():
         pytest.skip("upstream package not installed under baseline/_ref")
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="4")
     env.pop("PYTHONPATH", None)
-    proc = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "reference_parity_worker.py")] + CASES + ["losses", "metrics", "wrapped1", "wrapped2", "wrapped_features", "reshape_fields", "mpu_layers", "common_layers", "grids", "training_steps", "checkpoints"],
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "reference_parity_worker.py")] + CASES + ["losses", "metrics", "wrapped1", "wrapped2", "wrapped_features", "reshape_fields", "mpu_layers", "common_layers", "grids", "training_steps", "metrics_handler", "checkpoints"],
                           cwd="/tmp", env=env,
                           capture_output=True, text=True, timeout=900)
     assert proc.returncode == 0, proc.stderr[-2000:]
@@ -126,3 +126,10 @@ def test_five_training_steps_track_upstream(results):
     assert r["has_complex"] and r["compared"] >= 20
     assert max(r["loss"]) < 1e-5, r
     assert r["weights"] < 1e-4, r
+
+
+def test_metrics_handler_matches_upstream(results):
+    r = results["metrics_handler"]
+    assert r["table_rows"] == 24 and len(r["err"]) == 14
+    for k, v in r["err"].items():
+        assert isinstance(v, float) and v < 1e-5, (k, v)
