@@ -673,6 +673,36 @@ def run_metrics_handler():
     return out
 
 
+def run_initialisation():
+    """Constructed from the same seed, most parameter tensors of the two packages are bit-identical; the rest (drawn in
+    another order) must at least have the same spread and mean."""
+    if ROOT not in sys.path:
+        sys.path.append(ROOT)
+    out = {"case": "initialisation", "identical": 0, "same_statistics": 0, "off": []}
+    for name, (mod, cls, kw, hw, cin) in CASES.items():
+        ref_cls = getattr(importlib.import_module(f"makani.models.networks.{mod}"), cls)
+        my_cls = getattr(importlib.import_module(f"makani_b200.models.networks.{mod}"), cls)
+        torch.manual_seed(0)
+        sr = ref_cls(**kw).state_dict()
+        torch.manual_seed(0)
+        sm = my_cls(**kw).state_dict()
+        for k, a in sr.items():
+            b = sm[k]
+            if a.is_complex():
+                a, b = torch.view_as_real(a), torch.view_as_real(b)
+            a, b = a.float(), b.float()
+            if torch.equal(a, b):
+                out["identical"] += 1
+                continue
+            sa, sb = a.std().item(), b.std().item()
+            tol_mean = 4.0 * sa / (a.numel() ** 0.5) + 1e-6
+            if abs(sa - sb) <= 0.1 * sa + 1e-8 and abs(a.mean().item() - b.mean().item()) <= 2 * tol_mean:
+                out["same_statistics"] += 1
+            else:
+                out["off"].append(f"{name}:{k}: std {sa:.4g} vs {sb:.4g}, mean {a.mean().item():.3g} vs {b.mean().item():.3g}")
+    return out
+
+
 def run_checkpoints():
     """A checkpoint written by the upstream trainer (legacy and flexible format) restores into this framework's model
     and optimiser, and a checkpoint written here restores into the upstream trainer."""
@@ -748,7 +778,7 @@ if __name__ == "__main__":
     import makani
 
     assert os.path.realpath(makani.__file__).startswith(os.path.realpath(os.path.join(ROOT, "baseline", "_ref"))), makani.__file__
-    for name in (sys.argv[1:] or list(CASES) + ["losses", "metrics", "wrapped1", "wrapped2", "wrapped_features", "reshape_fields", "mpu_layers", "common_layers", "grids", "training_steps", "metrics_handler", "checkpoints"]):
+    for name in (sys.argv[1:] or list(CASES) + ["losses", "metrics", "wrapped1", "wrapped2", "wrapped_features", "reshape_fields", "mpu_layers", "common_layers", "grids", "training_steps", "metrics_handler", "initialisation", "checkpoints"]):
         if name == "losses":
             res = run_losses()
         elif name == "metrics":
@@ -769,6 +799,8 @@ if __name__ == "__main__":
             res = run_training_steps()
         elif name == "metrics_handler":
             res = run_metrics_handler()
+        elif name == "initialisation":
+            res = run_initialisation()
         elif name.startswith("wrapped"):
             res = run_wrapped(int(name[len("wrapped"):]))
         else:

@@ -21,7 +21,7 @@ def results():
         pytest.skip("upstream package not installed under baseline/_ref")
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="4")
     env.pop("PYTHONPATH", None)
-    proc = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "reference_parity_worker.py")] + CASES + ["losses", "metrics", "wrapped1", "wrapped2", "wrapped_features", "reshape_fields", "mpu_layers", "common_layers", "grids", "training_steps", "metrics_handler", "checkpoints"],
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "reference_parity_worker.py")] + CASES + ["losses", "metrics", "wrapped1", "wrapped2", "wrapped_features", "reshape_fields", "mpu_layers", "common_layers", "grids", "training_steps", "metrics_handler", "initialisation", "checkpoints"],
                           cwd="/tmp", env=env,
                           capture_output=True, text=True, timeout=900)
     assert proc.returncode == 0, proc.stderr[-2000:]
@@ -133,3 +133,9 @@ def test_metrics_handler_matches_upstream(results):
     assert r["table_rows"] == 24 and len(r["err"]) == 14
     for k, v in r["err"].items():
         assert isinstance(v, float) and v < 1e-5, (k, v)
+
+
+def test_parameter_initialisation_matches_upstream(results):
+    r = results["initialisation"]
+    assert r["off"] == [], r["off"]
+    assert r["identical"] > 250 and r["identical"] > 10 * r["same_statistics"], r
