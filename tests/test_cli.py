@@ -98,3 +98,18 @@ def test_makani_alias_package_resolves_to_this_framework():
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     out = subprocess.run([sys.executable, "-m", "makani.train", "--help"], cwd=root, capture_output=True, text=True, timeout=300)
     assert out.returncode == 0 and "--yaml_config" in out.stdout and "--cuda_graph_mode" in out.stdout
+
+
+def test_package_level_names_of_the_upstream_layout():
+    """What the upstream `__init__` files export is importable from the same places here (and through the alias)."""
+    import makani
+    from makani import Inferencer, Trainer  # noqa: F401
+    from makani.models import MultiStepWrapper, Preprocessor2D, SingleStepWrapper, model_registry  # noqa: F401
+    from makani.models.common import (MLP, ComplexActivation, ComplexReLU, DropPath, EncoderDecoder,  # noqa: F401
+                                      FactorizedSpectralConv, InverseRealFFT2, PatchEmbed, RealFFT2, SpectralAttention, SpectralConv)
+    from makani.utils.dataloaders.data_loader_dummy import DummyLoader  # noqa: F401
+    from makani.utils.parse_dataset_metada import parse_dataset_metadata  # noqa: F401
+    from makani.mpu.mappings import init_gradient_reduction_hooks  # noqa: F401
+
+    assert isinstance(makani.__version__, str)
+    assert Trainer.__module__ == "makani_b200.utils.trainer"
