@@ -110,6 +110,13 @@ def test_package_level_names_of_the_upstream_layout():
     from makani.utils.dataloaders.data_loader_dummy import DummyLoader  # noqa: F401
     from makani.utils.parse_dataset_metada import parse_dataset_metadata  # noqa: F401
     from makani.mpu.mappings import init_gradient_reduction_hooks  # noqa: F401
+    from makani.third_party.climt.zenith_angle import cos_zenith_angle
 
     assert isinstance(makani.__version__, str)
+    import datetime
+
+    import numpy as np
+    lon, lat = np.meshgrid(np.linspace(0, 360, 8, endpoint=False), np.linspace(90, -90, 5))
+    cz = cos_zenith_angle(datetime.datetime(2020, 6, 21, 12, tzinfo=datetime.timezone.utc), lon, lat)
+    assert cz.shape == (1, 5, 8) and cz.dtype == np.float32 and abs(float(cz[0, 2, 0]) - 1.0) < 0.1      # noon at 0E on the equator in June
     assert Trainer.__module__ == "makani_b200.utils.trainer"
