@@ -703,6 +703,51 @@ def run_initialisation():
     return out
 
 
+def run_history_and_residual():
+    """Exponential history normalisation through the wrappers, and residual targets: with `target: residual` the
+    upstream multistep wrapper adds the increment in place to its own input, so its first-step output is overwritten by
+    the second step; the check here is against its evaluation-mode steps chained by hand."""
+    if ROOT not in sys.path:
+        sys.path.append(ROOT)
+    from makani_b200.models import model_registry as my_registry
+    from makani_b200.utils.YParams import YParams as MyY
+
+    def pair(extra):
+        tr, params, recipe = _upstream_trainer(2, dict(add_grid=False, **extra))
+        mp = MyY(recipe, "sfno_tiny")
+        for k, v in params.to_dict().items():
+            mp[k] = v
+        mine = my_registry.get_model(mp)
+        mine.load_state_dict(tr.model.state_dict(), strict=True)
+        return tr.model, mine, params
+
+    out = {"case": "history_and_residual", "err": {}}
+    ref, mine, params = pair(dict(n_history=2, history_normalization_mode="exponential", history_normalization_decay=0.5))
+    C, H, W = len(params.channel_names), params.img_shape_x, params.img_shape_y
+    torch.manual_seed(0)
+    inp = torch.randn(2, 3 * C, H, W)
+    for mode in ("train", "eval"):
+        outs = []
+        for m in (ref, mine):
+            m.train() if mode == "train" else m.eval()
+            with torch.no_grad():
+                outs.append(m(inp.clone()))
+        out["err"][f"exponential_{mode}"] = rel(outs[1], outs[0])
+    ref, mine, params = pair(dict(n_history=0, target="residual"))
+    inp = torch.randn(2, C, H, W)
+    ref.eval()
+    mine.train()
+    with torch.no_grad():
+        s1 = ref(inp.clone())
+        s2 = ref(s1.clone())
+        ym = mine(inp.clone())
+    out["err"]["residual_step1"], out["err"]["residual_step2"] = rel(ym[:, :C], s1), rel(ym[:, C:], s2)
+    mine.eval()
+    with torch.no_grad():
+        out["err"]["residual_eval"] = rel(mine(inp.clone()), s1)
+    return out
+
+
 def run_checkpoints():
     """A checkpoint written by the upstream trainer (legacy and flexible format) restores into this framework's model
     and optimiser, and a checkpoint written here restores into the upstream trainer."""
@@ -778,7 +823,7 @@ if __name__ == "__main__":
     import makani
 
     assert os.path.realpath(makani.__file__).startswith(os.path.realpath(os.path.join(ROOT, "baseline", "_ref"))), makani.__file__
-    for name in (sys.argv[1:] or list(CASES) + ["losses", "metrics", "wrapped1", "wrapped2", "wrapped_features", "reshape_fields", "mpu_layers", "common_layers", "grids", "training_steps", "metrics_handler", "initialisation", "checkpoints"]):
+    for name in (sys.argv[1:] or list(CASES) + ["losses", "metrics", "wrapped1", "wrapped2", "wrapped_features", "reshape_fields", "mpu_layers", "common_layers", "grids", "training_steps", "metrics_handler", "initialisation", "history_and_residual", "checkpoints"]):
         if name == "losses":
             res = run_losses()
         elif name == "metrics":
@@ -801,6 +846,8 @@ if __name__ == "__main__":
             res = run_metrics_handler()
         elif name == "initialisation":
             res = run_initialisation()
+        elif name == "history_and_residual":
+            res = run_history_and_residual()
         elif name.startswith("wrapped"):
             res = run_wrapped(int(name[len("wrapped"):]))
         else:

@@ -21,7 +21,7 @@ def results():
         pytest.skip("upstream package not installed under baseline/_ref")
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="4")
     env.pop("PYTHONPATH", None)
-    proc = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "reference_parity_worker.py")] + CASES + ["losses", "metrics", "wrapped1", "wrapped2", "wrapped_features", "reshape_fields", "mpu_layers", "common_layers", "grids", "training_steps", "metrics_handler", "initialisation", "checkpoints"],
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "reference_parity_worker.py")] + CASES + ["losses", "metrics", "wrapped1", "wrapped2", "wrapped_features", "reshape_fields", "mpu_layers", "common_layers", "grids", "training_steps", "metrics_handler", "initialisation", "history_and_residual", "checkpoints"],
                           cwd="/tmp", env=env,
                           capture_output=True, text=True, timeout=900)
     assert proc.returncode == 0, proc.stderr[-2000:]
@@ -139,3 +139,10 @@ def test_parameter_initialisation_matches_upstream(results):
     r = results["initialisation"]
     assert r["off"] == [], r["off"]
     assert r["identical"] > 250 and r["identical"] > 10 * r["same_statistics"], r
+
+
+def test_history_normalisation_and_residual_targets(results):
+    r = results["history_and_residual"]
+    assert len(r["err"]) == 5
+    for k, v in r["err"].items():
+        assert isinstance(v, float) and v < 1e-5, (k, v)
