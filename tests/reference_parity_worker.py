@@ -182,6 +182,22 @@ def run_losses():
             vm.backward()
             out["value"][f"{grid}:{name}"] = abs(float(vr) - float(vm)) / abs(float(vr))
             out["grad"][f"{grid}:{name}"] = rel(a2.grad, a.grad)
+    # multistep training: predictions and targets of all steps stacked along the channels, per-step weights
+    for nf in (1, 2):
+        for name in ("absolute squared geometric l2", "weighted geometric l1"):
+            pr, pm = RefY(path, "base"), MyY(path, "base")
+            for q in (pr, pm):
+                q["loss"], q["n_future"] = name, nf
+            lr, lm = RefLoss(pr).train(), MyLoss(pm).train()
+            torch.manual_seed(nf)
+            a = torch.randn(2, 5 * (nf + 1), 33, 64, requires_grad=True)
+            b, i = torch.randn(2, 5 * (nf + 1), 33, 64), torch.randn(2, 5, 33, 64)
+            a2 = a.detach().clone().requires_grad_()
+            vr, vm = lr(a, b, i), lm(a2, b, i)
+            vr.backward()
+            vm.backward()
+            out["value"][f"multistep{nf + 1}:{name}"] = abs(float(vr) - float(vm)) / abs(float(vr))
+            out["grad"][f"multistep{nf + 1}:{name}"] = rel(a2.grad, a.grad)
     return out
 
 

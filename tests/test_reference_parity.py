@@ -44,7 +44,7 @@ def test_network_matches_upstream(results, case):
 
 def test_loss_handler_matches_upstream(results):
     r = results["losses"]
-    assert len(r["value"]) == 12
+    assert len(r["value"]) == 16
     for k, v in r["value"].items():
         assert v < 1e-6, (k, v)
     for k, v in r["grad"].items():
